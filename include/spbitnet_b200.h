@@ -1,0 +1,212 @@
+/*
+ * spbitnet_b200.h -- C-ABI of the B200 (sm_100a) sparse-ternary inference hot path.
+ *
+ * One plain-C entry point per host wrapper of the reference engine API
+ * (namespace spbitnet, include/spbitnet/sparse_ternary_kernels.h and
+ * include/spbitnet/inference_kernels.h in the reference project), with the
+ * same argument order and meaning.  Differences from the C++ originals, all
+ * forced by the C boundary:
+ *   - cudaStream_t is passed as void* (NULL = the legacy default stream);
+ *   - half* is passed as void* (IEEE binary16, 2 bytes per element);
+ *   - every call returns an int status instead of calling exit(): 0 on
+ *     success, a negative SPB_E_* otherwise; spb_last_error_string() describes
+ *     the last failure on the calling thread.
+ * All pointers are DEVICE pointers owned by the caller unless a parameter is
+ * documented as host memory.  Calls are asynchronous on the given stream and
+ * never synchronise, allocate or free (the engine and the *_host calls are the
+ * exception: they own buffers).  rows==0 or cols==0 returns 0 without a launch,
+ * like the reference (src/kernels/sparse_ternary.cu:244,261,280).
+ *
+ * The weight format is the reference's (include/spbitnet/sparse_ternary_tensor.h:12-39):
+ * per group of four consecutive columns a 4-bit position bitmap with two bits
+ * set (meta, 8 groups per uint32, LSB first) and a 2-bit sign pair (values, 16
+ * groups per uint32, LSB first; bit0 = lower-index non-zero, 0 => +1, 1 => -1).
+ * Row strides are in uint32 words.  cols must be a multiple of 4.
+ */
+#ifndef SPBITNET_B200_H
+#define SPBITNET_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SPB_OK 0
+#define SPB_E_INVALID (-1)     /* bad argument (null pointer, cols % 4, negative size ...) */
+#define SPB_E_CUDA (-2)        /* a CUDA runtime call or launch failed */
+#define SPB_E_TIMEOUT (-3)     /* a bounded device-side wait ran out */
+#define SPB_E_UNSUPPORTED (-4) /* shape outside what the kernel handles */
+#define SPB_E_FORMAT (-5)      /* packed data fails validation */
+
+const char* spb_last_error_string(void);
+/* Library version string, e.g. "spbitnet_b200 0.1 sm_100a". */
+const char* spb_version(void);
+/* 1 (default): kernels are launched with programmatic dependent launch so that the
+ * weight prefetch of one kernel overlaps the tail of the previous one on the same
+ * stream.  0: plain stream-ordered launches.  Returns the previous setting. */
+int spb_set_pdl(int enabled);
+
+/* ---- sparse-ternary kernels: include/spbitnet/sparse_ternary_kernels.h ---------- */
+
+/* sparse_ternary_unpack_gpu (sparse_ternary_kernels.h:16-19; src/kernels/sparse_ternary.cu:58-102,240-254).
+ * out: rows*cols int8, row-major. */
+int spb_sparse_ternary_unpack(const uint32_t* meta, const uint32_t* values, int8_t* out,
+                              int rows, int cols, int meta_row_stride, int values_row_stride,
+                              void* stream);
+
+/* sparse_ternary_gemv_gpu (sparse_ternary_kernels.h:29-33; src/kernels/sparse_ternary.cu:116-168,256-272).
+ * x: cols int8; y: rows int32 accumulators, bit-exact. */
+int spb_sparse_ternary_gemv(const uint32_t* meta, const uint32_t* values, const int8_t* x,
+                            int32_t* y, int rows, int cols, int meta_row_stride,
+                            int values_row_stride, void* stream);
+
+/* The same walk with the dequantisation of dequantize_gpu applied in fp32 and kept
+ * in fp32: y[r] = float(acc[r]) * ((gamma * absmax) / 127.0f), evaluated in that
+ * order (src/kernels/inference_kernels.cu:169-170).  d_absmax: 1 float on the device.
+ * y_acc may be NULL; when given it also receives the int32 accumulators. */
+int spb_sparse_ternary_gemv_scaled(const uint32_t* meta, const uint32_t* values, const int8_t* x,
+                                   float* y, int32_t* y_acc, const float* d_absmax, float gamma,
+                                   int rows, int cols, int meta_row_stride,
+                                   int values_row_stride, void* stream);
+
+/* fused_sparse_bitlinear_gpu (sparse_ternary_kernels.h:43-48; src/kernels/sparse_ternary.cu:181-234,274-291).
+ * x: cols half, quantised inline with *d_absmax; output: rows half. */
+int spb_fused_sparse_bitlinear(const uint32_t* meta, const uint32_t* values, const void* x,
+                               void* output, const float* d_absmax, float gamma, int rows,
+                               int cols, int meta_row_stride, int values_row_stride,
+                               void* stream);
+
+/* BitLinear on an activation that is already quantised (absmax_quantize_gpu output):
+ * the integer walk of sparse_ternary_gemv_gpu followed by dequantize_gpu in one
+ * launch.  Results equal spb_fused_sparse_bitlinear on the unquantised vector. */
+int spb_sparse_bitlinear_q8(const uint32_t* meta, const uint32_t* values, const int8_t* xq,
+                            void* output, const float* d_absmax, float gamma, int rows,
+                            int cols, int meta_row_stride, int values_row_stride,
+                            void* stream);
+
+/* Batched form.  The reference has no sparse_ternary_gemm; its batched path is
+ * CuSparseLtGemm::execute (include/spbitnet/cusparselt_backend.h:47-50), whose operand
+ * layout this follows: X is [cols, n] column-major with ld = cols (n activation rows
+ * of cols int8), Y is [rows, n] column-major with ld = rows (n output rows of rows
+ * int32).  Y[j*rows + r] = sum_c W[r][c] * X[j*cols + c].  Any n >= 1. */
+int spb_sparse_ternary_gemm(const uint32_t* meta, const uint32_t* values, const int8_t* X,
+                            int32_t* Y, int rows, int cols, int n, int meta_row_stride,
+                            int values_row_stride, void* stream);
+
+/* ---- transformer kernels: include/spbitnet/inference_kernels.h ------------------- */
+
+/* rms_norm_gpu (inference_kernels.h:14-15; src/kernels/inference_kernels.cu:15-56). input may alias output. */
+int spb_rms_norm(const void* input, const float* weight, void* output, int size, float eps,
+                 void* stream);
+/* absmax_quantize_gpu (inference_kernels.h:19-20; inference_kernels.cu:69-114). */
+int spb_absmax_quantize(const void* input, int8_t* output, float* d_absmax, int size,
+                        void* stream);
+/* absmax_reduce_gpu (inference_kernels.h:24-25; inference_kernels.cu:120-148). */
+int spb_absmax_reduce(const void* input, float* d_absmax, int size, void* stream);
+/* dequantize_gpu (inference_kernels.h:29-30; inference_kernels.cu:162-171). */
+int spb_dequantize(const int32_t* input, void* output, const float* d_absmax, float gamma,
+                   int size, void* stream);
+/* rope_gpu (inference_kernels.h:33-34; inference_kernels.cu:185-206). In place. */
+int spb_rope(void* vec, int num_heads, int head_dim, int pos, float theta, void* stream);
+/* scatter_kv_gpu (inference_kernels.h:38-39; inference_kernels.cu:215-227). */
+int spb_scatter_kv(const void* src, void* cache, int num_kv_heads, int head_dim,
+                   int max_seq_len, int pos, void* stream);
+/* attention_scores_gpu (inference_kernels.h:44-47; inference_kernels.cu:241-275). */
+int spb_attention_scores(const void* Q, const void* K_cache, float* scores, int num_heads,
+                         int num_kv_heads, int head_dim, int max_seq_len, int seq_len,
+                         float scale, void* stream);
+/* softmax_gpu (inference_kernels.h:51-52; inference_kernels.cu:283-339). In place. */
+int spb_softmax(float* scores, int num_heads, int max_seq_len, int seq_len, void* stream);
+/* attention_output_gpu (inference_kernels.h:56-59; inference_kernels.cu:350-371). */
+int spb_attention_output(const float* scores, const void* V_cache, void* output, int num_heads,
+                         int num_kv_heads, int head_dim, int max_seq_len, int seq_len,
+                         void* stream);
+/* relu2_mul_gpu (inference_kernels.h:62-63; inference_kernels.cu:379-390). */
+int spb_relu2_mul(const void* gate, const void* up, void* output, int size, void* stream);
+/* relu2_mul_f32_gpu (inference_kernels.h:67-68; inference_kernels.cu:399-410). */
+int spb_relu2_mul_f32(const void* gate, const void* up, float* output, int size, void* stream);
+/* rms_norm_f32in_gpu (inference_kernels.h:72-73; inference_kernels.cu:418-455). */
+int spb_rms_norm_f32in(const float* input, const float* weight, void* output, int size,
+                       float eps, void* stream);
+/* float_to_half_gpu (inference_kernels.h:76-77; inference_kernels.cu:460-466). */
+int spb_float_to_half(const float* input, void* output, int size, void* stream);
+/* residual_add_gpu (inference_kernels.h:80-81; inference_kernels.cu:471-479). */
+int spb_residual_add(const void* a, const void* b, void* output, int size, void* stream);
+/* half_gemv_gpu (inference_kernels.h:86-87; inference_kernels.cu:488-531). */
+int spb_half_gemv(const void* W, const void* x, float* y, int rows, int cols, void* stream);
+
+/* One-launch decode attention for a single new token: attention_scores_gpu, softmax_gpu
+ * and attention_output_gpu (src/inference.cu:188-202) without the scores round trip.
+ * Q: (num_heads, head_dim) half; caches (num_kv_heads, max_seq_len, head_dim) half;
+ * output (num_heads, head_dim) half. */
+int spb_decode_attention(const void* Q, const void* K_cache, const void* V_cache, void* output,
+                         int num_heads, int num_kv_heads, int head_dim, int max_seq_len,
+                         int seq_len, float scale, void* stream);
+
+/* ---- host-side format helpers: include/spbitnet/sparse_ternary_tensor.h ----------- */
+
+/* Row strides in uint32 words (sparse_ternary_tensor.h:254-264). */
+int spb_meta_words_per_row(int cols);
+int spb_values_words_per_row(int cols);
+/* SparseTernaryTensor::pack_from_dense (sparse_ternary_tensor.h:58-108). HOST pointers.
+ * meta/values are overwritten.  SPB_E_FORMAT if a group keeps other than two entries. */
+int spb_pack_from_dense(const int8_t* weights, const uint8_t* mask, int rows, int cols,
+                        uint32_t* meta, uint32_t* values);
+/* SparseTernaryTensor::pack_with_pruning (sparse_ternary_tensor.h:123-191). HOST pointers. */
+int spb_pack_with_pruning(const float* latent, int rows, int cols, uint32_t* meta,
+                          uint32_t* values);
+/* SparseTernaryTensor::unpack_to_int8 (sparse_ternary_tensor.h:197-232). HOST pointers. */
+int spb_unpack_to_int8_host(const uint32_t* meta, const uint32_t* values, int rows, int cols,
+                            int meta_row_stride, int values_row_stride, int8_t* out);
+/* SPB_OK when every visited bitmap has exactly two bits set, else SPB_E_FORMAT. HOST pointers.
+ * The kernels reproduce the reference GPU table on other bitmaps (both positions 0,
+ * src/kernels/sparse_ternary.cu:34-51), which its CPU unpack does not; loaders should reject them. */
+int spb_validate_packed(const uint32_t* meta, int rows, int cols, int meta_row_stride);
+
+/* ---- engine: include/spbitnet/inference.h:23-70, src/inference.cu ----------------- */
+
+typedef struct spb_engine spb_engine;
+
+typedef struct {
+    int hidden_size, num_hidden_layers, num_attention_heads, num_key_value_heads;
+    int head_dim, intermediate_size, vocab_size, max_position_embeddings;
+    float rms_norm_eps, rope_theta;
+} spb_model_config; /* the fields of ModelConfig the forward pass reads (include/spbitnet/model.h:22-38) */
+
+/* InferenceEngine::InferenceEngine (src/inference.cu:16-69): allocates KV caches and
+ * scratch on the current device.  Weights are attached afterwards; the engine borrows them. */
+spb_engine* spb_engine_create(const spb_model_config* cfg);
+void spb_engine_destroy(spb_engine* e);
+/* SparseLinear (include/spbitnet/model.h:46-60). which: 0 q, 1 k, 2 v, 3 o, 4 gate, 5 up, 6 down. */
+int spb_engine_set_linear(spb_engine* e, int layer, int which, const uint32_t* d_meta,
+                          const uint32_t* d_values, float gamma, int rows, int cols,
+                          int meta_stride, int values_stride);
+/* TransformerLayer norms (model.h:63-83). which: 0 input_layernorm, 1 post_attention_layernorm,
+ * 2 attn_sub_norm, 3 ffn_sub_norm (2 and 3 optional). */
+int spb_engine_set_norm(spb_engine* e, int layer, int which, const float* d_weight);
+/* embed_tokens / lm_head (NULL = tied) / final_norm (model.h:118-128). */
+int spb_engine_set_globals(spb_engine* e, const void* d_embed, const void* d_lm_head,
+                           const float* d_final_norm);
+/* InferenceEngine::forward (src/inference.cu:123-283): one token, returns the DEVICE
+ * logits pointer (vocab_size floats) through *d_logits. */
+int spb_engine_forward(spb_engine* e, int token_id, const float** d_logits);
+/* InferenceEngine::reset (src/inference.cu:91-100). */
+int spb_engine_reset(spb_engine* e);
+/* InferenceEngine::seq_len (include/spbitnet/inference.h:38). */
+int spb_engine_seq_len(const spb_engine* e);
+/* The greedy loop of src/main.cpp:266-300 with the arg-max on the device (first
+ * maximum wins, like std::max_element): feeds prompt[0..n_prompt-2], then generates
+ * max_tokens tokens starting from prompt[n_prompt-1]; stops early at eos_token_id
+ * (pass -1 for none).  prompt/out_tokens are HOST pointers; returns the number of
+ * tokens written to out_tokens, or a negative status. */
+int spb_engine_generate(spb_engine* e, const int* prompt, int n_prompt, int max_tokens,
+                        int eos_token_id, int* out_tokens);
+/* Copies the last forward's logits to HOST memory (vocab_size floats); synchronises. */
+int spb_engine_copy_logits(spb_engine* e, float* h_logits);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPBITNET_B200_H */

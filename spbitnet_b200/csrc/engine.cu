@@ -1,0 +1,366 @@
+// Host-side decode engine: the B200 counterpart of spbitnet::InferenceEngine
+// (include/spbitnet/inference.h:23-70, src/inference.cu).  Same state (KV caches,
+// scratch vectors, sequence position), same op order and rounding points as
+// InferenceEngine::forward (src/inference.cu:123-283), but
+//   * one pooled device allocation instead of ~75 cudaMallocs,
+//   * the activation is quantised once per normed vector and shared by q/k/v and by
+//     gate/up (the reference recomputes the same absmax 2-3 times, src/inference.cu:106-117),
+//   * the small vector ops between GEMVs are fused (fused_ops.cu),
+//   * the whole token is a CUDA graph of PDL-chained kernels whose position lives in
+//     device memory, replayed once per token on a private stream,
+//   * the arg-max of the greedy loop (src/main.cpp:285-287) runs on the device.
+#include <cmath>
+#include <new>
+#include <vector>
+
+#include "fused_ops.cuh"
+
+namespace spb {
+
+struct Linear {
+    const uint32_t* meta = nullptr;
+    const uint32_t* values = nullptr;
+    float gamma = 0.0f;
+    int rows = 0, cols = 0, ms = 0, vs = 0;
+};
+
+struct Layer {
+    Linear lin[7];             // q k v o gate up down
+    const float* norm[4] = {};  // input_ln, post_attn_ln, attn_sub_norm, ffn_sub_norm
+};
+
+}  // namespace spb
+
+using namespace spb;
+
+struct spb_engine {
+    spb_model_config cfg{};
+    std::vector<Layer> layers;
+    const __half* embed = nullptr;
+    const __half* lm_head = nullptr;
+    const float* final_norm = nullptr;
+
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    uint8_t* pool = nullptr;
+    size_t pool_bytes = 0;
+    size_t kv_bytes_per_layer = 0;
+    __half *kcache = nullptr, *vcache = nullptr;
+    __half *x = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr, *o = nullptr;
+    __half *gate = nullptr, *up = nullptr, *down = nullptr, *xfinal = nullptr;
+    int8_t* xq = nullptr;   // quantised activation, max(hidden, inter, heads*head_dim)
+    float* absmax = nullptr;
+    float* logits = nullptr;
+    float* bval = nullptr;
+    int* bidx = nullptr;
+    int *d_pos = nullptr, *d_next = nullptr, *d_prompt = nullptr, *d_out = nullptr;
+    int prompt_cap = 0;
+    int n_prompt_in_graph = 0;
+    int argmax_blocks = 0;
+
+    cudaGraphExec_t graph = nullptr;  // one token, position and token read from device memory
+    bool graph_generates = false;     // the captured graph records tokens into d_out
+    int seq_len = 0;
+};
+
+namespace {
+
+constexpr int kMaxTokensOut = 1 << 16;
+
+int cuda_fail(const char* what, cudaError_t err) {
+    cudaGetLastError();
+    return fail(SPB_E_CUDA, "%s: %s", what, cudaGetErrorString(err));
+}
+
+#define SPB_CUDA(call)                                           \
+    do {                                                         \
+        cudaError_t err__ = (call);                              \
+        if (err__ != cudaSuccess) return cuda_fail(#call, err__); \
+    } while (0)
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+int bitlinear(spb_engine* e, const Linear& L, const int8_t* xq, const float* absmax, __half* out) {
+    if (!L.meta) return fail(SPB_E_INVALID, "engine: a linear layer has no weights attached");
+    return spb_sparse_bitlinear_q8(L.meta, L.values, xq, out, absmax, L.gamma, L.rows, L.cols, L.ms, L.vs,
+                                   e->stream);
+}
+
+// Enqueues one token's worth of kernels on e->stream.  The first kernel reads the token
+// (prompt[pos] while pos < n_prompt, else the previous arg-max) and the last advances pos.
+int enqueue_token(spb_engine* e, bool record_tokens) {
+    const spb_model_config& c = e->cfg;
+    const int H = c.hidden_size, hd = c.head_dim, nh = c.num_attention_heads, nkv = c.num_key_value_heads;
+    const int inter = c.intermediate_size;
+    void* s = e->stream;
+    int rc;
+    if ((rc = embed_token(e->embed, e->x, H, e->d_prompt, e->n_prompt_in_graph, e->d_next, e->d_pos, s))) return rc;
+    const float attn_scale = 1.0f / sqrtf(static_cast<float>(hd));
+    for (int l = 0; l < c.num_hidden_layers; ++l) {
+        const Layer& L = e->layers[l];
+        __half* kc = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(e->kcache) + l * e->kv_bytes_per_layer);
+        __half* vc = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(e->vcache) + l * e->kv_bytes_per_layer);
+        // input norm (+ the previous layer's down-projection residual add)
+        if ((rc = residual_norm_quant(l == 0 ? nullptr : e->down, nullptr, e->x, L.norm[0], nullptr, e->xq,
+                                      e->absmax, H, c.rms_norm_eps, s))) return rc;
+        if ((rc = bitlinear(e, L.lin[0], e->xq, e->absmax, e->q))) return rc;
+        if ((rc = bitlinear(e, L.lin[1], e->xq, e->absmax, e->k))) return rc;
+        if ((rc = bitlinear(e, L.lin[2], e->xq, e->absmax, e->v))) return rc;
+        if ((rc = rope_scatter(e->q, e->k, e->v, kc, vc, nh, nkv, hd, c.max_position_embeddings, c.rope_theta,
+                               e->d_pos, s))) return rc;
+        if ((rc = decode_attention_pos(e->q, kc, vc, e->attn, nh, nkv, hd, c.max_position_embeddings,
+                                       attn_scale, e->d_pos, s))) return rc;
+        if ((rc = spb_absmax_quantize(e->attn, e->xq, e->absmax + 1, nh * hd, s))) return rc;
+        if ((rc = bitlinear(e, L.lin[3], e->xq, e->absmax + 1, e->o))) return rc;
+        // attn_sub_norm -> residual add -> post-attention norm -> quantise
+        if ((rc = residual_norm_quant(e->o, L.norm[2], e->x, L.norm[1], nullptr, e->xq, e->absmax, H,
+                                      c.rms_norm_eps, s))) return rc;
+        if ((rc = bitlinear(e, L.lin[4], e->xq, e->absmax, e->gate))) return rc;
+        if ((rc = bitlinear(e, L.lin[5], e->xq, e->absmax, e->up))) return rc;
+        if ((rc = relu2_norm_quant(e->gate, e->up, L.norm[3], nullptr, e->xq, e->absmax + 1, inter,
+                                   c.rms_norm_eps, s))) return rc;
+        if ((rc = bitlinear(e, L.lin[6], e->xq, e->absmax + 1, e->down))) return rc;
+    }
+    // last residual add + final norm
+    if ((rc = residual_norm_quant(c.num_hidden_layers ? e->down : nullptr, nullptr, e->x, e->final_norm,
+                                  e->xfinal, e->xq, e->absmax, H, c.rms_norm_eps, s))) return rc;
+    if ((rc = spb_half_gemv(e->lm_head ? e->lm_head : e->embed, e->xfinal, e->logits, c.vocab_size, H, s))) return rc;
+    return argmax_advance(e->logits, c.vocab_size, e->bval, e->bidx, e->argmax_blocks, e->d_next,
+                          record_tokens ? e->d_out : nullptr, e->d_pos, s);
+}
+
+int check_ready(const spb_engine* e) {
+    if (!e) return fail(SPB_E_INVALID, "engine: null handle");
+    if (!e->embed || !e->final_norm) return fail(SPB_E_INVALID, "engine: globals not set");
+    for (const Layer& L : e->layers) {
+        for (int i = 0; i < 7; ++i)
+            if (!L.lin[i].meta) return fail(SPB_E_INVALID, "engine: a linear layer has no weights attached");
+        if (!L.norm[0] || !L.norm[1]) return fail(SPB_E_INVALID, "engine: a layer norm is missing");
+    }
+    return SPB_OK;
+}
+
+void drop_graph(spb_engine* e) {
+    if (e->graph) {
+        cudaGraphExecDestroy(e->graph);
+        e->graph = nullptr;
+    }
+}
+
+int ensure_graph(spb_engine* e, bool record_tokens, int n_prompt) {
+    if (e->graph && e->graph_generates == record_tokens && e->n_prompt_in_graph == n_prompt) return SPB_OK;
+    drop_graph(e);
+    e->n_prompt_in_graph = n_prompt;
+    SPB_CUDA(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
+    int rc = enqueue_token(e, record_tokens);
+    cudaGraph_t g = nullptr;
+    cudaError_t err = cudaStreamEndCapture(e->stream, &g);
+    if (rc) {
+        if (g) cudaGraphDestroy(g);
+        return rc;
+    }
+    if (err != cudaSuccess) return cuda_fail("cudaStreamEndCapture", err);
+    err = cudaGraphInstantiate(&e->graph, g, 0);
+    cudaGraphDestroy(g);
+    if (err != cudaSuccess) return cuda_fail("cudaGraphInstantiate", err);
+    e->graph_generates = record_tokens;
+    return SPB_OK;
+}
+
+}  // namespace
+
+extern "C" spb_engine* spb_engine_create(const spb_model_config* cfg) {
+    if (!cfg || cfg->hidden_size <= 0 || cfg->num_hidden_layers < 0 || cfg->num_attention_heads <= 0 ||
+        cfg->num_key_value_heads <= 0 || cfg->head_dim <= 0 || cfg->head_dim % 2 || cfg->intermediate_size <= 0 ||
+        cfg->vocab_size <= 0 || cfg->max_position_embeddings <= 0) {
+        fail(SPB_E_INVALID, "spb_engine_create: bad config");
+        return nullptr;
+    }
+    spb_engine* e = new (std::nothrow) spb_engine();
+    if (!e) return nullptr;
+    e->cfg = *cfg;
+    e->layers.resize(cfg->num_hidden_layers);
+    cudaGetDevice(&e->device);
+    const int H = cfg->hidden_size, qdim = cfg->num_attention_heads * cfg->head_dim;
+    const int kvdim = cfg->num_key_value_heads * cfg->head_dim, inter = cfg->intermediate_size;
+    const int maxdim = std::max(std::max(H, qdim), inter);
+    e->kv_bytes_per_layer = align_up(sizeof(__half) * static_cast<size_t>(kvdim) * cfg->max_position_embeddings, 256);
+    e->argmax_blocks = std::max(1, std::min(128, (cfg->vocab_size + 1023) / 1024));
+
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return o; };
+    const size_t o_kc = take(e->kv_bytes_per_layer * cfg->num_hidden_layers);
+    const size_t o_vc = take(e->kv_bytes_per_layer * cfg->num_hidden_layers);
+    const size_t o_x = take(2 * H), o_q = take(2 * qdim), o_k = take(2 * kvdim), o_v = take(2 * kvdim);
+    const size_t o_attn = take(2 * qdim), o_o = take(2 * H), o_gate = take(2 * inter), o_up = take(2 * inter);
+    const size_t o_down = take(2 * H), o_xf = take(2 * H), o_xq = take(maxdim), o_abs = take(16);
+    const size_t o_logits = take(4 * static_cast<size_t>(cfg->vocab_size));
+    const size_t o_bval = take(4 * 128), o_bidx = take(4 * 128), o_ints = take(16);
+    const size_t o_out = take(4 * static_cast<size_t>(kMaxTokensOut));
+    e->pool_bytes = off;
+    if (cudaMalloc(&e->pool, e->pool_bytes) != cudaSuccess || cudaMemset(e->pool, 0, e->pool_bytes) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) != cudaSuccess) {
+        cuda_fail("spb_engine_create", cudaGetLastError());
+        if (e->pool) cudaFree(e->pool);
+        delete e;
+        return nullptr;
+    }
+    uint8_t* p = e->pool;
+    e->kcache = reinterpret_cast<__half*>(p + o_kc);
+    e->vcache = reinterpret_cast<__half*>(p + o_vc);
+    e->x = reinterpret_cast<__half*>(p + o_x);
+    e->q = reinterpret_cast<__half*>(p + o_q);
+    e->k = reinterpret_cast<__half*>(p + o_k);
+    e->v = reinterpret_cast<__half*>(p + o_v);
+    e->attn = reinterpret_cast<__half*>(p + o_attn);
+    e->o = reinterpret_cast<__half*>(p + o_o);
+    e->gate = reinterpret_cast<__half*>(p + o_gate);
+    e->up = reinterpret_cast<__half*>(p + o_up);
+    e->down = reinterpret_cast<__half*>(p + o_down);
+    e->xfinal = reinterpret_cast<__half*>(p + o_xf);
+    e->xq = reinterpret_cast<int8_t*>(p + o_xq);
+    e->absmax = reinterpret_cast<float*>(p + o_abs);
+    e->logits = reinterpret_cast<float*>(p + o_logits);
+    e->bval = reinterpret_cast<float*>(p + o_bval);
+    e->bidx = reinterpret_cast<int*>(p + o_bidx);
+    e->d_pos = reinterpret_cast<int*>(p + o_ints);
+    e->d_next = e->d_pos + 1;
+    e->d_out = reinterpret_cast<int*>(p + o_out);
+    return e;
+}
+
+extern "C" void spb_engine_destroy(spb_engine* e) {
+    if (!e) return;
+    cudaStreamSynchronize(e->stream);
+    drop_graph(e);
+    if (e->d_prompt) cudaFree(e->d_prompt);
+    cudaFree(e->pool);
+    cudaStreamDestroy(e->stream);
+    delete e;
+}
+
+extern "C" int spb_engine_set_linear(spb_engine* e, int layer, int which, const uint32_t* d_meta,
+                                     const uint32_t* d_values, float gamma, int rows, int cols,
+                                     int meta_stride, int values_stride) {
+    if (!e || layer < 0 || layer >= static_cast<int>(e->layers.size()) || which < 0 || which > 6)
+        return fail(SPB_E_INVALID, "spb_engine_set_linear: bad layer/which");
+    if (!d_meta || !d_values || rows <= 0 || cols <= 0 || cols % 4)
+        return fail(SPB_E_INVALID, "spb_engine_set_linear: bad tensor");
+    const spb_model_config& c = e->cfg;
+    const int qdim = c.num_attention_heads * c.head_dim, kvdim = c.num_key_value_heads * c.head_dim;
+    const int want_rows[7] = {qdim, kvdim, kvdim, c.hidden_size, c.intermediate_size, c.intermediate_size, c.hidden_size};
+    const int want_cols[7] = {c.hidden_size, c.hidden_size, c.hidden_size, qdim, c.hidden_size, c.hidden_size, c.intermediate_size};
+    if (rows != want_rows[which] || cols != want_cols[which])
+        return fail(SPB_E_INVALID, "spb_engine_set_linear: layer %d tensor %d is %dx%d, config wants %dx%d", layer,
+                    which, rows, cols, want_rows[which], want_cols[which]);
+    Linear& L = e->layers[layer].lin[which];
+    L.meta = d_meta; L.values = d_values; L.gamma = gamma; L.rows = rows; L.cols = cols;
+    L.ms = meta_stride; L.vs = values_stride;
+    drop_graph(e);
+    return SPB_OK;
+}
+
+extern "C" int spb_engine_set_norm(spb_engine* e, int layer, int which, const float* d_weight) {
+    if (!e || layer < 0 || layer >= static_cast<int>(e->layers.size()) || which < 0 || which > 3)
+        return fail(SPB_E_INVALID, "spb_engine_set_norm: bad layer/which");
+    e->layers[layer].norm[which] = d_weight;
+    drop_graph(e);
+    return SPB_OK;
+}
+
+extern "C" int spb_engine_set_globals(spb_engine* e, const void* d_embed, const void* d_lm_head,
+                                      const float* d_final_norm) {
+    if (!e || !d_embed || !d_final_norm) return fail(SPB_E_INVALID, "spb_engine_set_globals: null pointer");
+    e->embed = static_cast<const __half*>(d_embed);
+    e->lm_head = static_cast<const __half*>(d_lm_head);
+    e->final_norm = d_final_norm;
+    drop_graph(e);
+    return SPB_OK;
+}
+
+extern "C" int spb_engine_forward(spb_engine* e, int token_id, const float** d_logits) {
+    int rc = check_ready(e);
+    if (rc) return rc;
+    if (token_id < 0 || token_id >= e->cfg.vocab_size) return fail(SPB_E_INVALID, "spb_engine_forward: token %d outside the vocabulary", token_id);
+    if (e->seq_len >= e->cfg.max_position_embeddings) return fail(SPB_E_INVALID, "spb_engine_forward: KV cache full (%d)", e->seq_len);
+    if ((rc = ensure_graph(e, false, 0))) return rc;
+    if ((rc = set_int(e->d_next, token_id, e->stream))) return rc;
+    SPB_CUDA(cudaGraphLaunch(e->graph, e->stream));
+    e->seq_len++;
+    if (d_logits) {
+        // The reference returns after enqueueing on the null stream; this engine runs on a
+        // private stream, so make the result visible to whoever reads it next.
+        SPB_CUDA(cudaStreamSynchronize(e->stream));
+        *d_logits = e->logits;
+    }
+    return SPB_OK;
+}
+
+extern "C" int spb_engine_reset(spb_engine* e) {
+    if (!e) return fail(SPB_E_INVALID, "spb_engine_reset: null handle");
+    const size_t kv_total = e->kv_bytes_per_layer * e->cfg.num_hidden_layers;
+    SPB_CUDA(cudaMemsetAsync(e->kcache, 0, kv_total, e->stream));
+    SPB_CUDA(cudaMemsetAsync(e->vcache, 0, kv_total, e->stream));
+    SPB_CUDA(cudaMemsetAsync(e->d_pos, 0, 16, e->stream));
+    SPB_CUDA(cudaStreamSynchronize(e->stream));
+    e->seq_len = 0;
+    return SPB_OK;
+}
+
+extern "C" int spb_engine_seq_len(const spb_engine* e) { return e ? e->seq_len : 0; }
+
+extern "C" int spb_engine_copy_logits(spb_engine* e, float* h_logits) {
+    if (!e || !h_logits) return fail(SPB_E_INVALID, "spb_engine_copy_logits: null pointer");
+    SPB_CUDA(cudaMemcpyAsync(h_logits, e->logits, sizeof(float) * e->cfg.vocab_size, cudaMemcpyDeviceToHost, e->stream));
+    SPB_CUDA(cudaStreamSynchronize(e->stream));
+    return SPB_OK;
+}
+
+extern "C" int spb_engine_generate(spb_engine* e, const int* prompt, int n_prompt, int max_tokens,
+                                   int eos_token_id, int* out_tokens) {
+    int rc = check_ready(e);
+    if (rc) return rc;
+    if (!prompt || n_prompt < 1 || max_tokens < 0 || (max_tokens > 0 && !out_tokens))
+        return fail(SPB_E_INVALID, "spb_engine_generate: bad arguments");
+    const int start = e->seq_len;
+    const int steps = n_prompt - 1 + max_tokens;
+    if (start + steps > e->cfg.max_position_embeddings || start + steps > kMaxTokensOut)
+        return fail(SPB_E_INVALID, "spb_engine_generate: %d positions exceed the KV cache", start + steps);
+    for (int i = 0; i < n_prompt; ++i)
+        if (prompt[i] < 0 || prompt[i] >= e->cfg.vocab_size)
+            return fail(SPB_E_INVALID, "spb_engine_generate: prompt token %d outside the vocabulary", prompt[i]);
+    // The prompt table is indexed by absolute position.
+    const int need = start + n_prompt;
+    if (need > e->prompt_cap) {
+        if (e->d_prompt) cudaFree(e->d_prompt);
+        e->d_prompt = nullptr;
+        const int cap = std::max(need, 1024);
+        SPB_CUDA(cudaMalloc(&e->d_prompt, sizeof(int) * cap));
+        e->prompt_cap = cap;
+        drop_graph(e);
+    }
+    SPB_CUDA(cudaMemcpyAsync(e->d_prompt + start, prompt, sizeof(int) * n_prompt, cudaMemcpyHostToDevice, e->stream));
+    if ((rc = ensure_graph(e, true, need))) return rc;
+    int produced = 0;
+    if (eos_token_id < 0) {
+        for (int s = 0; s < steps; ++s) SPB_CUDA(cudaGraphLaunch(e->graph, e->stream));
+        e->seq_len += steps;
+        produced = max_tokens;
+        if (produced > 0)
+            SPB_CUDA(cudaMemcpyAsync(out_tokens, e->d_out + start + n_prompt - 1, sizeof(int) * produced,
+                                     cudaMemcpyDeviceToHost, e->stream));
+        SPB_CUDA(cudaStreamSynchronize(e->stream));
+    } else {
+        for (int s = 0; s < n_prompt - 1; ++s) SPB_CUDA(cudaGraphLaunch(e->graph, e->stream));
+        e->seq_len += n_prompt - 1;
+        for (int t = 0; t < max_tokens; ++t) {
+            SPB_CUDA(cudaGraphLaunch(e->graph, e->stream));
+            SPB_CUDA(cudaMemcpyAsync(out_tokens + t, e->d_out + e->seq_len, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
+            SPB_CUDA(cudaStreamSynchronize(e->stream));
+            e->seq_len++;
+            produced = t + 1;
+            if (out_tokens[t] == eos_token_id) break;
+        }
+    }
+    return produced;
+}

@@ -1,0 +1,102 @@
+"""Python mirror of spbitnet::InferenceEngine (reference include/spbitnet/inference.h:23-70)
+over the C-ABI engine: forward(token) -> device logits, reset(), seq_len, plus the greedy
+loop of src/main.cpp:266-300 as generate()."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import torch
+
+from ._lib import ModelConfig, check, load, SpbError
+
+_CFG_KEYS = ["hidden_size", "num_hidden_layers", "num_attention_heads", "num_key_value_heads", "head_dim",
+             "intermediate_size", "vocab_size", "max_position_embeddings", "rms_norm_eps", "rope_theta"]
+
+
+class DeviceModel:
+    """Uploads a host model (spbitnet_b200.synth.random_model layout) to the current CUDA device.
+    Plays the part of spbitnet::Model (include/spbitnet/model.h): it owns the weight tensors."""
+
+    def __init__(self, model: dict, device=None):
+        self.config = dict(model["config"])
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.device = dev
+        self.embed = torch.from_numpy(model["embed"].view(np.int16)).to(dev).view(torch.float16)
+        self.final_norm = torch.from_numpy(model["final_norm"]).to(dev)
+        self.layers = []
+        cache = {}
+        for layer in model["layers"]:
+            key = id(layer)
+            if key not in cache or True:
+                lin = []
+                for t in layer["linear"]:
+                    meta = torch.from_numpy(t["meta"].view(np.int32)).to(dev)
+                    values = torch.from_numpy(t["values"].view(np.int32)).to(dev)
+                    lin.append(dict(t, d_meta=meta, d_values=values))
+                norms = [torch.from_numpy(n).to(dev) for n in layer["norm"]]
+                cache[key] = {"linear": lin, "norm": norms}
+            self.layers.append(cache[key])
+
+    def sparse_bytes(self) -> int:
+        return sum(t["d_meta"].numel() * 4 + t["d_values"].numel() * 4 for L in self.layers for t in L["linear"])
+
+
+class InferenceEngine:
+    def __init__(self, model: DeviceModel, use_sub_norm: bool = True):
+        self._lib = load()
+        self.model = model
+        cfg = ModelConfig(**{k: model.config[k] for k in _CFG_KEYS})
+        with torch.cuda.device(model.device):
+            self._h = self._lib.spb_engine_create(C.byref(cfg))
+        if not self._h:
+            raise SpbError(-2, self._lib.spb_last_error_string().decode())
+        for l, layer in enumerate(model.layers):
+            for i, t in enumerate(layer["linear"]):
+                check(self._lib.spb_engine_set_linear(self._h, l, i, C.c_void_p(t["d_meta"].data_ptr()),
+                                                      C.c_void_p(t["d_values"].data_ptr()), float(t["gamma"]),
+                                                      t["rows"], t["cols"], t["meta_stride"], t["values_stride"]))
+            for i, n in enumerate(layer["norm"]):
+                if i >= 2 and not use_sub_norm:
+                    continue
+                check(self._lib.spb_engine_set_norm(self._h, l, i, C.c_void_p(n.data_ptr())))
+        check(self._lib.spb_engine_set_globals(self._h, C.c_void_p(model.embed.data_ptr()), C.c_void_p(0),
+                                               C.c_void_p(model.final_norm.data_ptr())))
+
+    def forward(self, token_id: int) -> int:
+        """One token; returns the device address of the logits (vocab_size float32)."""
+        out = C.c_void_p(0)
+        check(self._lib.spb_engine_forward(self._h, int(token_id), C.byref(out)))
+        return out.value
+
+    def logits(self) -> np.ndarray:
+        h = np.empty(self.model.config["vocab_size"], np.float32)
+        check(self._lib.spb_engine_copy_logits(self._h, C.c_void_p(h.ctypes.data)))
+        return h
+
+    def reset(self) -> None:
+        check(self._lib.spb_engine_reset(self._h))
+
+    @property
+    def seq_len(self) -> int:
+        return self._lib.spb_engine_seq_len(self._h)
+
+    def generate(self, prompt, max_tokens: int, eos_token_id: int = -1) -> np.ndarray:
+        p = np.ascontiguousarray(prompt, np.int32)
+        out = np.zeros(max(max_tokens, 1), np.int32)
+        n = self._lib.spb_engine_generate(self._h, C.c_void_p(p.ctypes.data), len(p), int(max_tokens),
+                                          int(eos_token_id), C.c_void_p(out.ctypes.data))
+        if n < 0:
+            check(n)
+        return out[:n]
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.spb_engine_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

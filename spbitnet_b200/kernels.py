@@ -1,0 +1,140 @@
+"""Python mirror of the reference's kernel host wrappers (namespace spbitnet,
+include/spbitnet/sparse_ternary_kernels.h and inference_kernels.h): same names, same
+argument order, torch CUDA tensors in place of device pointers.  Every function forwards
+to the C-ABI of libspbitnet_b200.so; errors raise SpbError instead of exiting.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from ._lib import check, load
+
+
+def _p(t):
+    if t is None:
+        return C.c_void_p(0)
+    if isinstance(t, int):
+        return C.c_void_p(t)
+    return C.c_void_p(t.data_ptr())
+
+
+def _stream(stream):
+    if stream is None:
+        return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    if isinstance(stream, int):
+        return C.c_void_p(stream)
+    return C.c_void_p(stream.cuda_stream)
+
+
+def set_pdl(enabled: bool) -> bool:
+    return bool(load().spb_set_pdl(int(enabled)))
+
+
+# ---- sparse_ternary_kernels.h ---------------------------------------------------------
+
+def sparse_ternary_unpack_gpu(meta, values, out, rows, cols, meta_row_stride, values_row_stride, stream=None):
+    check(load().spb_sparse_ternary_unpack(_p(meta), _p(values), _p(out), rows, cols, meta_row_stride,
+                                           values_row_stride, _stream(stream)))
+
+
+def sparse_ternary_gemv_gpu(meta, values, x, y, rows, cols, meta_row_stride, values_row_stride, stream=None):
+    check(load().spb_sparse_ternary_gemv(_p(meta), _p(values), _p(x), _p(y), rows, cols, meta_row_stride,
+                                         values_row_stride, _stream(stream)))
+
+
+def sparse_ternary_gemv_scaled_gpu(meta, values, x, y, y_acc, d_absmax, gamma, rows, cols, meta_row_stride,
+                                   values_row_stride, stream=None):
+    check(load().spb_sparse_ternary_gemv_scaled(_p(meta), _p(values), _p(x), _p(y), _p(y_acc), _p(d_absmax),
+                                                float(gamma), rows, cols, meta_row_stride, values_row_stride,
+                                                _stream(stream)))
+
+
+def fused_sparse_bitlinear_gpu(meta, values, x, output, d_absmax, gamma, rows, cols, meta_row_stride,
+                               values_row_stride, stream=None):
+    check(load().spb_fused_sparse_bitlinear(_p(meta), _p(values), _p(x), _p(output), _p(d_absmax), float(gamma),
+                                            rows, cols, meta_row_stride, values_row_stride, _stream(stream)))
+
+
+def sparse_bitlinear_q8_gpu(meta, values, xq, output, d_absmax, gamma, rows, cols, meta_row_stride,
+                            values_row_stride, stream=None):
+    check(load().spb_sparse_bitlinear_q8(_p(meta), _p(values), _p(xq), _p(output), _p(d_absmax), float(gamma),
+                                         rows, cols, meta_row_stride, values_row_stride, _stream(stream)))
+
+
+def sparse_ternary_gemm_gpu(meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream=None):
+    check(load().spb_sparse_ternary_gemm(_p(meta), _p(values), _p(X), _p(Y), rows, cols, n, meta_row_stride,
+                                         values_row_stride, _stream(stream)))
+
+
+# ---- inference_kernels.h ----------------------------------------------------------------
+
+def rms_norm_gpu(input, weight, output, size, eps, stream=None):
+    check(load().spb_rms_norm(_p(input), _p(weight), _p(output), size, float(eps), _stream(stream)))
+
+
+def absmax_quantize_gpu(input, output, d_absmax, size, stream=None):
+    check(load().spb_absmax_quantize(_p(input), _p(output), _p(d_absmax), size, _stream(stream)))
+
+
+def absmax_reduce_gpu(input, d_absmax, size, stream=None):
+    check(load().spb_absmax_reduce(_p(input), _p(d_absmax), size, _stream(stream)))
+
+
+def dequantize_gpu(input, output, d_absmax, gamma, size, stream=None):
+    check(load().spb_dequantize(_p(input), _p(output), _p(d_absmax), float(gamma), size, _stream(stream)))
+
+
+def rope_gpu(vec, num_heads, head_dim, pos, theta, stream=None):
+    check(load().spb_rope(_p(vec), num_heads, head_dim, pos, float(theta), _stream(stream)))
+
+
+def scatter_kv_gpu(src, cache, num_kv_heads, head_dim, max_seq_len, pos, stream=None):
+    check(load().spb_scatter_kv(_p(src), _p(cache), num_kv_heads, head_dim, max_seq_len, pos, _stream(stream)))
+
+
+def attention_scores_gpu(Q, K_cache, scores, num_heads, num_kv_heads, head_dim, max_seq_len, seq_len, scale,
+                         stream=None):
+    check(load().spb_attention_scores(_p(Q), _p(K_cache), _p(scores), num_heads, num_kv_heads, head_dim,
+                                      max_seq_len, seq_len, float(scale), _stream(stream)))
+
+
+def softmax_gpu(scores, num_heads, max_seq_len, seq_len, stream=None):
+    check(load().spb_softmax(_p(scores), num_heads, max_seq_len, seq_len, _stream(stream)))
+
+
+def attention_output_gpu(scores, V_cache, output, num_heads, num_kv_heads, head_dim, max_seq_len, seq_len,
+                         stream=None):
+    check(load().spb_attention_output(_p(scores), _p(V_cache), _p(output), num_heads, num_kv_heads, head_dim,
+                                      max_seq_len, seq_len, _stream(stream)))
+
+
+def decode_attention_gpu(Q, K_cache, V_cache, output, num_heads, num_kv_heads, head_dim, max_seq_len, seq_len,
+                         scale, stream=None):
+    check(load().spb_decode_attention(_p(Q), _p(K_cache), _p(V_cache), _p(output), num_heads, num_kv_heads,
+                                      head_dim, max_seq_len, seq_len, float(scale), _stream(stream)))
+
+
+def relu2_mul_gpu(gate, up, output, size, stream=None):
+    check(load().spb_relu2_mul(_p(gate), _p(up), _p(output), size, _stream(stream)))
+
+
+def relu2_mul_f32_gpu(gate, up, output, size, stream=None):
+    check(load().spb_relu2_mul_f32(_p(gate), _p(up), _p(output), size, _stream(stream)))
+
+
+def rms_norm_f32in_gpu(input, weight, output, size, eps, stream=None):
+    check(load().spb_rms_norm_f32in(_p(input), _p(weight), _p(output), size, float(eps), _stream(stream)))
+
+
+def float_to_half_gpu(input, output, size, stream=None):
+    check(load().spb_float_to_half(_p(input), _p(output), size, _stream(stream)))
+
+
+def residual_add_gpu(a, b, output, size, stream=None):
+    check(load().spb_residual_add(_p(a), _p(b), _p(output), size, _stream(stream)))
+
+
+def half_gemv_gpu(W, x, y, rows, cols, stream=None):
+    check(load().spb_half_gemv(_p(W), _p(x), _p(y), rows, cols, _stream(stream)))
