@@ -181,6 +181,7 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
+    K.set_gemv_variant(args.variant)
     peak, peak_kind = measured_peaks()
     l2_bytes = torch.cuda.get_device_properties(local).L2_cache_size
     rows, cols = synth.METRIC_SHAPE
@@ -244,14 +245,29 @@ def run_ours(args):
     if not (ys[0].cpu().numpy() == chk).all():
         raise SystemExit("bench: GEMV result differs from the oracle; refusing to time it")
 
-    graph = torch.cuda.CUDAGraph()
-    side = torch.cuda.Stream()
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        launch_pass(metas, vals, xs, ys, rows, cols, ms_, vs_, copies)  # warm the capture stream
-    torch.cuda.current_stream().wait_stream(side)
-    with torch.cuda.graph(graph):
-        launch_pass(metas, vals, xs, ys, rows, cols, ms_, vs_, copies)
+    branch_streams = [torch.cuda.Stream() for _ in range(max(args.chains, 1))]
+
+    def capture(metas, vals, xs, ys, r, c, ms, vs, copies, chains):
+        """One step as a CUDA graph: `copies` GEMV launches spread round-robin over `chains`
+        parallel branches.  Launches of a branch are stream-ordered (PDL-chained); branches are
+        independent, which the GEMVs of a step are (distinct weights and outputs)."""
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            main = torch.cuda.current_stream()
+            if chains <= 1:
+                launch_pass(metas, vals, xs, ys, r, c, ms, vs, copies)
+            else:
+                for s in branch_streams[:chains]:
+                    s.wait_stream(main)
+                for i in range(copies):
+                    with torch.cuda.stream(branch_streams[i % chains]):
+                        K.sparse_ternary_gemv_gpu(metas[i], vals[i], xs[i % xs.shape[0]], ys[i], r, c, ms, vs)
+                for s in branch_streams[:chains]:
+                    main.wait_stream(s)
+        return g
+
+    graph = capture(metas, vals, xs, ys, rows, cols, ms_, vs_, copies, args.chains)
+    graph_chain = capture(metas, vals, xs, ys, rows, cols, ms_, vs_, copies, 1) if args.chains > 1 else graph
 
     sampler = ClockSampler(local)
     if rank == 0:
@@ -260,6 +276,8 @@ def run_ours(args):
     clocks = sampler.stop() if rank == 0 else {}
     ms_stream = time_device(lambda: launch_pass(metas, vals, xs, ys, rows, cols, ms_, vs_, copies),
                             max(1, args.steps // 2), 1)
+    ms_chain = time_device(graph_chain.replay, args.steps, args.warmup)
+    chain_us = ms_chain * 1e3 / (args.steps * copies)
     step_bytes = per * copies
     value = world * step_bytes * args.steps / (ms_graph * 1e-3) / 1e9
     per_launch_us = ms_graph * 1e3 / (args.steps * copies)
@@ -281,11 +299,9 @@ def run_ours(args):
             cs, cp, mt, vl, pb = make_set(r, c, max(2 * l2_bytes, 256 << 20), seed=0)
             xx = torch.from_numpy(rng.integers(-127, 128, (8, c), dtype=np.int8)).cuda()
             yy = torch.zeros((cp, r), dtype=torch.int32, device="cuda")
-            g2 = torch.cuda.CUDAGraph()
             launch_pass(mt, vl, xx, yy, r, c, cs["meta_stride"], cs["values_stride"], cp)
             torch.cuda.synchronize()
-            with torch.cuda.graph(g2):
-                launch_pass(mt, vl, xx, yy, r, c, cs["meta_stride"], cs["values_stride"], cp)
+            g2 = capture(mt, vl, xx, yy, r, c, cs["meta_stride"], cs["values_stride"], cp, args.chains)
             for _ in range(3):
                 g2.replay()
             torch.cuda.synchronize()
@@ -349,7 +365,9 @@ def run_ours(args):
                        "copies_per_step": copies, "working_set_mb": round(step_bytes / 2**20, 1),
                        "l2_mb": round(l2_bytes / 2**20, 1),
                        "cold_l2": "inputs larger than L2: every launch reads a different weight copy",
-                       "launch": "one CUDA graph replay per step (copies PDL-chained kernel launches)",
+                       "launch": f"one CUDA graph replay per step: {copies} GEMV launches in {args.chains} independent "
+                                 "branches (stream-ordered, PDL-chained inside a branch)",
+                       "chains": args.chains, "gemv_variant": args.variant,
                        "seed": 0},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
@@ -358,6 +376,9 @@ def run_ours(args):
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(x_host.numel()),
                     "d2h_bytes_per_step": int(y_host.numel() * 4), "ms_per_step": ms_e2e / args.steps},
             "stream_launch_gbs": stream_gbs,
+            "dependent_chain": {"us_per_gemv": chain_us, "gbs": per / (chain_us * 1e-6) / 1e9,
+                                "what": "the same launches as ONE stream-ordered chain (each GEMV waits for the "
+                                        "previous one before it reads x): the latency a decode step sees"},
             "gpu_launches": args.steps * copies,
             "clocks": clocks,
             "cpu_baseline": cpu,
@@ -402,6 +423,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--chains", type=int, default=8, help="independent branches per step graph")
+    ap.add_argument("--variant", type=int, default=0, help="GEMV kernel: 0 auto, 1 unit, 2 column-owner")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-decode", action="store_true")

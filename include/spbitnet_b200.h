@@ -47,6 +47,11 @@ const char* spb_version(void);
  * weight prefetch of one kernel overlaps the tail of the previous one on the same
  * stream.  0: plain stream-ordered launches.  Returns the previous setting. */
 int spb_set_pdl(int enabled);
+/* Which GEMV kernel the sparse-ternary entry points use when the layout allows the fast
+ * paths: 0 = automatic (default), 1 = unit kernel (weights expanded before the dependency
+ * wait: shortest dependent-chain latency), 2 = column-owner kernel (highest throughput).
+ * Results are identical.  Returns the previous setting. */
+int spb_set_gemv_variant(int variant);
 
 /* ---- sparse-ternary kernels: include/spbitnet/sparse_ternary_kernels.h ---------- */
 
@@ -161,8 +166,10 @@ int spb_pack_with_pruning(const float* latent, int rows, int cols, uint32_t* met
 int spb_unpack_to_int8_host(const uint32_t* meta, const uint32_t* values, int rows, int cols,
                             int meta_row_stride, int values_row_stride, int8_t* out);
 /* SPB_OK when every visited bitmap has exactly two bits set, else SPB_E_FORMAT. HOST pointers.
- * The kernels reproduce the reference GPU table on other bitmaps (both positions 0,
- * src/kernels/sparse_ternary.cu:34-51), which its CPU unpack does not; loaders should reject them. */
+ * The reference leaves other bitmaps undefined: its GPU table maps them to positions (0,0)
+ * (src/kernels/sparse_ternary.cu:34-51) while its CPU unpack yields as many non-zeros as bits.
+ * Loaders should reject them with this call; the GPU entry points require valid bitmaps and
+ * give an unspecified (but memory-safe) result otherwise. */
 int spb_validate_packed(const uint32_t* meta, int rows, int cols, int meta_row_stride);
 
 /* ---- engine: include/spbitnet/inference.h:23-70, src/inference.cu ----------------- */

@@ -45,6 +45,7 @@ SIGNATURES = {
     "spb_last_error_string": (C.c_char_p, []),
     "spb_version": (C.c_char_p, []),
     "spb_set_pdl": (_i, [_i]),
+    "spb_set_gemv_variant": (_i, [_i]),
     "spb_sparse_ternary_unpack": (_i, [_p, _p, _p, _i, _i, _i, _i, _p]),
     "spb_sparse_ternary_gemv": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _p]),
     "spb_sparse_ternary_gemv_scaled": (_i, [_p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _p]),

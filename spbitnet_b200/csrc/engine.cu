@@ -86,6 +86,23 @@ int bitlinear(spb_engine* e, const Linear& L, const int8_t* xq, const float* abs
                                    e->stream);
 }
 
+// Several projections of the same quantised activation in one launch (q/k/v, gate/up).
+int bitlinear_group(spb_engine* e, const Linear* const* L, __half* const* out, int n, const int8_t* xq,
+                    const float* absmax) {
+    const uint32_t* meta[3];
+    const uint32_t* values[3];
+    void* o[3];
+    float gamma[3];
+    int rows[3], ms[3], vs[3];
+    for (int i = 0; i < n; ++i) {
+        if (!L[i]->meta) return fail(SPB_E_INVALID, "engine: a linear layer has no weights attached");
+        if (L[i]->cols != L[0]->cols) return fail(SPB_E_INVALID, "engine: grouped layers differ in width");
+        meta[i] = L[i]->meta; values[i] = L[i]->values; o[i] = out[i]; gamma[i] = L[i]->gamma;
+        rows[i] = L[i]->rows; ms[i] = L[i]->ms; vs[i] = L[i]->vs;
+    }
+    return bitlinear_q8_group(meta, values, o, gamma, rows, ms, vs, n, xq, absmax, L[0]->cols, e->stream);
+}
+
 // Enqueues one token's worth of kernels on e->stream.  The first kernel reads the token
 // (prompt[pos] while pos < n_prompt, else the previous arg-max) and the last advances pos.
 int enqueue_token(spb_engine* e, bool record_tokens) {
@@ -103,9 +120,11 @@ int enqueue_token(spb_engine* e, bool record_tokens) {
         // input norm (+ the previous layer's down-projection residual add)
         if ((rc = residual_norm_quant(l == 0 ? nullptr : e->down, nullptr, e->x, L.norm[0], nullptr, e->xq,
                                       e->absmax, H, c.rms_norm_eps, s))) return rc;
-        if ((rc = bitlinear(e, L.lin[0], e->xq, e->absmax, e->q))) return rc;
-        if ((rc = bitlinear(e, L.lin[1], e->xq, e->absmax, e->k))) return rc;
-        if ((rc = bitlinear(e, L.lin[2], e->xq, e->absmax, e->v))) return rc;
+        {
+            const Linear* g3[3] = {&L.lin[0], &L.lin[1], &L.lin[2]};
+            __half* o3[3] = {e->q, e->k, e->v};
+            if ((rc = bitlinear_group(e, g3, o3, 3, e->xq, e->absmax))) return rc;
+        }
         if ((rc = rope_scatter(e->q, e->k, e->v, kc, vc, nh, nkv, hd, c.max_position_embeddings, c.rope_theta,
                                e->d_pos, s))) return rc;
         if ((rc = decode_attention_pos(e->q, kc, vc, e->attn, nh, nkv, hd, c.max_position_embeddings,
@@ -115,8 +134,11 @@ int enqueue_token(spb_engine* e, bool record_tokens) {
         // attn_sub_norm -> residual add -> post-attention norm -> quantise
         if ((rc = residual_norm_quant(e->o, L.norm[2], e->x, L.norm[1], nullptr, e->xq, e->absmax, H,
                                       c.rms_norm_eps, s))) return rc;
-        if ((rc = bitlinear(e, L.lin[4], e->xq, e->absmax, e->gate))) return rc;
-        if ((rc = bitlinear(e, L.lin[5], e->xq, e->absmax, e->up))) return rc;
+        {
+            const Linear* g2[2] = {&L.lin[4], &L.lin[5]};
+            __half* o2[2] = {e->gate, e->up};
+            if ((rc = bitlinear_group(e, g2, o2, 2, e->xq, e->absmax))) return rc;
+        }
         if ((rc = relu2_norm_quant(e->gate, e->up, L.norm[3], nullptr, e->xq, e->absmax + 1, inter,
                                    c.rms_norm_eps, s))) return rc;
         if ((rc = bitlinear(e, L.lin[6], e->xq, e->absmax + 1, e->down))) return rc;

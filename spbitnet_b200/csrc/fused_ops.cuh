@@ -20,4 +20,9 @@ int argmax_advance(const float* logits, int n, float* bval, int* bidx, int nbloc
                    int* d_out, int* d_pos, void* stream);
 int set_int(int* dst, int value, void* stream);
 
+// gemv.cu: up to three BitLinear layers that consume the same quantised activation, one launch.
+int bitlinear_q8_group(const uint32_t* const* meta, const uint32_t* const* values, void* const* out,
+                       const float* gamma, const int* rows, const int* ms, const int* vs, int nmat,
+                       const int8_t* xq, const float* d_absmax, int cols, void* stream);
+
 }  // namespace spb

@@ -32,6 +32,11 @@ def set_pdl(enabled: bool) -> bool:
     return bool(load().spb_set_pdl(int(enabled)))
 
 
+def set_gemv_variant(variant: int) -> int:
+    """0 automatic, 1 unit kernel (latency form), 2 column-owner kernel (throughput form)."""
+    return load().spb_set_gemv_variant(int(variant))
+
+
 # ---- sparse_ternary_kernels.h ---------------------------------------------------------
 
 def sparse_ternary_unpack_gpu(meta, values, out, rows, cols, meta_row_stride, values_row_stride, stream=None):
