@@ -269,6 +269,17 @@ def run_ours(args):
     graph = capture(metas, vals, xs, ys, rows, cols, ms_, vs_, copies, args.chains)
     graph_chain = capture(metas, vals, xs, ys, rows, cols, ms_, vs_, copies, 1) if args.chains > 1 else graph
 
+    work = K.GemvWorkList([(metas[i], vals[i], xs[i], ys[i], rows, cols, ms_, vs_) for i in range(copies)])
+    ys.zero_()
+    K.sparse_ternary_gemv_batch_gpu(work)
+    torch.cuda.synchronize()
+    if not (ys[0].cpu().numpy() == chk).all() or not (ys[copies - 1].cpu().numpy() ==
+            oracle.sparse_gemv(np.roll(case["meta"], copies - 1, 0), np.roll(case["values"], copies - 1, 0),
+                               x_host[copies - 1].numpy(), rows, cols, threads=os.cpu_count() or 1)).all():
+        raise SystemExit("bench: work-list GEMV result differs from the oracle; refusing to time it")
+    ms_batch = time_device(lambda: K.sparse_ternary_gemv_batch_gpu(work), args.steps, args.warmup)
+    batch_us = ms_batch * 1e3 / (args.steps * copies)
+
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -376,6 +387,9 @@ def run_ours(args):
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(x_host.numel()),
                     "d2h_bytes_per_step": int(y_host.numel() * 4), "ms_per_step": ms_e2e / args.steps},
             "stream_launch_gbs": stream_gbs,
+            "work_list": {"us_per_gemv": batch_us, "gbs": per / (batch_us * 1e-6) / 1e9,
+                          "frac_measured": per / (batch_us * 1e-6) / 1e9 / peak,
+                          "what": f"the same {copies} GEMVs as ONE persistent launch (spb_sparse_ternary_gemv_batch)"},
             "dependent_chain": {"us_per_gemv": chain_us, "gbs": per / (chain_us * 1e-6) / 1e9,
                                 "what": "the same launches as ONE stream-ordered chain (each GEMV waits for the "
                                         "previous one before it reads x): the latency a decode step sees"},

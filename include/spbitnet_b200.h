@@ -48,9 +48,9 @@ const char* spb_version(void);
  * stream.  0: plain stream-ordered launches.  Returns the previous setting. */
 int spb_set_pdl(int enabled);
 /* Which GEMV kernel the sparse-ternary entry points use when the layout allows the fast
- * paths: 0 = automatic (default), 1 = unit kernel (weights expanded before the dependency
- * wait: shortest dependent-chain latency), 2 = column-owner kernel (highest throughput).
- * Results are identical.  Returns the previous setting. */
+ * paths: 0 or 1 = pair kernel (default: one dp4a per two groups), 2 = per-group table kernel
+ * (one dp4a per group; kept for comparison).  Results are identical on valid bitmaps.
+ * Returns the previous setting. */
 int spb_set_gemv_variant(int variant);
 
 /* ---- sparse-ternary kernels: include/spbitnet/sparse_ternary_kernels.h ---------- */
@@ -66,6 +66,23 @@ int spb_sparse_ternary_unpack(const uint32_t* meta, const uint32_t* values, int8
 int spb_sparse_ternary_gemv(const uint32_t* meta, const uint32_t* values, const int8_t* x,
                             int32_t* y, int rows, int cols, int meta_row_stride,
                             int values_row_stride, void* stream);
+
+/* Work-list form: one launch computes n independent GEMVs (the semantics of n calls of
+ * spb_sparse_ternary_gemv) with a persistent grid, so per-launch fixed costs are paid once.
+ * d_items is a DEVICE array of n items that the caller uploads once (a decode step's list is
+ * static); it must satisfy spb_gemv_batch_check, which validates the HOST copy: cols a
+ * multiple of 128 (at most 32768), strides multiples of 4 / 2 words, meta/values/x 16/8/16-byte
+ * aligned.  max_rows / max_cols bound the items (they size shared memory). */
+typedef struct {
+    const uint32_t* meta;
+    const uint32_t* values;
+    const int8_t* x;
+    int32_t* y;
+    int rows, cols, meta_row_stride, values_row_stride;
+} spb_gemv_item;
+int spb_gemv_batch_check(const spb_gemv_item* h_items, int n);
+int spb_sparse_ternary_gemv_batch(const spb_gemv_item* d_items, int n, int max_rows, int max_cols,
+                                  void* stream);
 
 /* The same walk with the dequantisation of dequantize_gpu applied in fp32 and kept
  * in fp32: y[r] = float(acc[r]) * ((gamma * absmax) / 127.0f), evaluated in that

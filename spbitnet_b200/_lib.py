@@ -40,6 +40,13 @@ _p = C.c_void_p
 _i = C.c_int
 _f = C.c_float
 
+
+class GemvItem(C.Structure):
+    """spb_gemv_item: one entry of a GEMV work list."""
+    _fields_ = [("meta", C.c_void_p), ("values", C.c_void_p), ("x", C.c_void_p), ("y", C.c_void_p),
+                ("rows", C.c_int), ("cols", C.c_int), ("meta_row_stride", C.c_int), ("values_row_stride", C.c_int)]
+
+
 # name -> (restype, argtypes); every symbol include/spbitnet_b200.h declares.
 SIGNATURES = {
     "spb_last_error_string": (C.c_char_p, []),
@@ -51,6 +58,8 @@ SIGNATURES = {
     "spb_sparse_ternary_gemv_scaled": (_i, [_p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _p]),
     "spb_fused_sparse_bitlinear": (_i, [_p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _p]),
     "spb_sparse_bitlinear_q8": (_i, [_p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _p]),
+    "spb_gemv_batch_check": (_i, [_p, _i]),
+    "spb_sparse_ternary_gemv_batch": (_i, [_p, _i, _i, _i, _p]),
     "spb_sparse_ternary_gemm": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "spb_rms_norm": (_i, [_p, _p, _p, _i, _f, _p]),
     "spb_absmax_quantize": (_i, [_p, _p, _p, _i, _p]),

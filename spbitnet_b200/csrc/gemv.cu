@@ -181,40 +181,39 @@ __global__ void __launch_bounds__(kThreads) gemv_units_kernel(const GemvArgs a) 
 }
 
 // ---------------------------------------------------------------------------
-// "Column-owner" kernel: the throughput form.
+// Pair kernel (the default).
 //
-// A thread owns one 128-column block of x for the whole launch (32 registers) and walks
-// down the rows of its block, so the activation bytes cost no shared-memory bandwidth in
-// the inner loop.  Two groups (one meta byte, one sign nibble) are consumed by
+// Same block/unit mapping and the same two phases as the kernel above, but two groups (one
+// meta byte, one sign nibble) are consumed at a time:
 //   sel = sel_lut[meta byte & 0x77] : PRMT selector that gathers the four non-zero columns
 //   sgn = sgn_lut[sign nibble]      : their four signs as int8 +-1
 //   acc = dp4a(prmt(x_lo, x_hi, sel), sgn, acc)
 // i.e. one dp4a per two groups.  Three bits of a bitmap with exactly two of four bits set
-// determine the fourth, so the table is indexed by 3+3 bits; both tables are replicated
-// once per lane (bank = lane, no conflicts) and arrive in shared memory by one bulk
-// asynchronous copy (TMA) from a constant image in global memory.  Bitmaps must be valid
-// (spb_validate_packed); others decode as some valid bitmap.
-// One block of 512 threads per SM takes a contiguous range of rows of one matrix; the
-// per-thread partial sums of a row meet in shared memory and a warp folds each row.
+// determine the fourth, so the selector table is indexed by 3+3 bits.  Both tables are
+// replicated once per lane (bank = lane, no conflicts) and copied from a constant image in
+// global memory (L2-resident) with 128-bit loads.  The dependency wait sits between the table
+// copy and the expansion: the x chunks are requested right after it and land while the
+// weights are expanded to 16 selectors and 16 sign words in registers; the arithmetic is then
+// 8 x LDS.128 + 16 x (PRMT, dp4a).  Per-thread partial sums meet in a transposed shared array
+// and one thread per row folds them.
+// Bitmaps must be valid (spb_validate_packed); others decode as some valid bitmap.
 // ---------------------------------------------------------------------------
-constexpr int kColsThreads = 512;
 constexpr int kSelEntries = 120;  // (meta byte & 0x77) <= 0x77
-constexpr int kSgnEntries = 16;
-constexpr int kLaneLutWords = (kSelEntries + kSgnEntries) * 32;
-constexpr int kLaneLutBytes = kLaneLutWords * 4;  // 17408
-constexpr int kSelLutBytes = kSelEntries * 32 * 4;
-constexpr int kDepth = 4;  // units whose weights are in flight per thread
+constexpr int kSelBytes = kSelEntries * 32 * 4;  // 15360
+constexpr int kSgnBytes = 16 * 32 * 4;           // 2048
+constexpr int kWindow = 16384;
 
-struct LaneLutImage {
-    uint32_t w[kLaneLutWords];
+struct PairLutImage {
+    uint32_t sel[kSelEntries * 32];
+    uint32_t sgn[16 * 32];
 };
 
 constexpr uint32_t pair_selector(int b) {
-    // b = (meta byte & 0x77): low three bits of each nibble; the fourth bit is implied
+    // b = (meta byte & 0x77): the low three bits of each nibble; the fourth bit is implied
     uint32_t sel = 0;
     for (int half = 0; half < 2; ++half) {
         int n = (b >> (4 * half)) & 7;
-        int cnt = (n & 1) + ((n >> 1) & 1) + ((n >> 2) & 1);
+        const int cnt = (n & 1) + ((n >> 1) & 1) + ((n >> 2) & 1);
         if (cnt == 1) n |= 8;
         int bits = 0, p0 = 0, p1 = 0;
         for (int i = 0; i < 4; ++i)
@@ -229,62 +228,39 @@ constexpr uint32_t pair_selector(int b) {
     return sel;
 }
 
-constexpr LaneLutImage make_lane_lut_image() {
-    LaneLutImage t{};
+constexpr PairLutImage make_pair_lut_image() {
+    PairLutImage t{};
     for (int e = 0; e < kSelEntries; ++e)
-        for (int l = 0; l < 32; ++l) t.w[e * 32 + l] = pair_selector(e);
-    for (int n = 0; n < kSgnEntries; ++n) {
+        for (int l = 0; l < 32; ++l) t.sel[e * 32 + l] = pair_selector(e);
+    for (int n = 0; n < 16; ++n) {
         uint32_t w = 0;
         for (int i = 0; i < 4; ++i) w |= ((n >> i) & 1 ? 0xFFu : 0x01u) << (8 * i);
-        for (int l = 0; l < 32; ++l) t.w[(kSelEntries + n) * 32 + l] = w;
+        for (int l = 0; l < 32; ++l) t.sgn[n * 32 + l] = w;
     }
     return t;
 }
 
-__device__ __align__(128) const LaneLutImage g_lane_lut = make_lane_lut_image();
-
-struct ColsArgs {
-    GemvMat mat[kMaxMats];  // blk_begin = first block of the matrix
-    int nmat;
-    const void* x;
-    const float* d_absmax;
-    int cols, upr;
-    int rs;   // row slots per block = kColsThreads / upr
-    int rpc;  // rows per block
-};
+__device__ __align__(128) const PairLutImage g_pair_lut = make_pair_lut_image();
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
-// One unit against the thread's 32 x words.  lut_lane = shared address of the table + lane*4.
-__device__ __forceinline__ int mac_unit(const uint4& m, const uint2& v, const uint32_t (&xr)[32],
-                                        uint32_t lut_lane) {
-    const uint32_t mw[4] = {m.x, m.y, m.z, m.w};
-    const uint32_t vw[2] = {v.x, v.y};
-    int acc = 0;
-#pragma unroll
-    for (int p = 0; p < 16; ++p) {  // groups 2p and 2p+1
-        const int ms = 8 * (p & 3) - 7;  // meta byte p of its word, scaled by 128 (entry stride)
-        const uint32_t mb = (ms >= 0 ? (mw[p >> 2] >> ms) : (mw[p >> 2] << -ms)) & (0x77u << 7);
-        const int ss = 4 * (p & 7) - 7;  // sign nibble p of its word, scaled by 128
-        const uint32_t sn = (ss >= 0 ? (vw[p >> 3] >> ss) : (vw[p >> 3] << -ss)) & (0xFu << 7);
-        uint32_t sel, sg;
-        asm("ld.shared.u32 %0, [%1];" : "=r"(sel) : "r"(lut_lane + mb));
-        asm("ld.shared.u32 %0, [%1+%2];" : "=r"(sg) : "r"(lut_lane + sn), "n"(kSelLutBytes));
-        acc = __dp4a(static_cast<int>(__byte_perm(xr[2 * p], xr[2 * p + 1], sel)), static_cast<int>(sg), acc);
-    }
-    return acc;
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
 }
 
 template <int IN, int OUT>
-__global__ void __launch_bounds__(kColsThreads, 1) gemv_cols_kernel(const ColsArgs a) {
-    extern __shared__ __align__(128) uint8_t csmem[];
-    uint8_t* const smem = csmem;
-    // layout: [lane tables 17408][mbarrier 16][partials rpc*upr*4 (16-aligned)][xs cols (IN_F16)]
-    uint64_t* mbar = reinterpret_cast<uint64_t*>(smem + kLaneLutBytes);
-    int* partial = reinterpret_cast<int*>(smem + kLaneLutBytes + 16);
-    uint4* xs = reinterpret_cast<uint4*>(smem + kLaneLutBytes + 16 + ((a.rpc * a.upr * 4 + 15) & ~15));
+__global__ void __launch_bounds__(kThreads, 4) gemv_pairs_kernel(const GemvArgs a) {
+    extern __shared__ __align__(128) uint8_t psmem[];
+    // [sel 15360][sgn 2048][partials upr*pitch ints (16-aligned)][x cols bytes]
+    const uint32_t win_s = smem_u32(psmem);
+    uint8_t* win = psmem;
+    const int pitch = a.rpc | 1;
+    int* partial = reinterpret_cast<int*>(win + kSelBytes + kSgnBytes);
+    uint4* xs = reinterpret_cast<uint4*>(win + kSelBytes + kSgnBytes + ((a.upr * pitch * 4 + 15) & ~15));
 
     const int tid = threadIdx.x, lane = tid & 31;
     int mi = 0;
@@ -293,139 +269,120 @@ __global__ void __launch_bounds__(kColsThreads, 1) gemv_cols_kernel(const ColsAr
     const GemvMat& M = a.mat[mi];
     const int r_lo = (blockIdx.x - M.blk_begin) * a.rpc;
     const int nrows = min(a.rpc, M.rows - r_lo);
-    const int rs = tid / a.upr, cb = tid - rs * a.upr;
-    const bool active = rs < a.rs;
-    const int niter = (nrows + a.rs - 1) / a.rs;
+    const int nunits = nrows * a.upr;
 
     grid_dep_launch();
 
-    // ---- tables: one bulk copy global -> shared, completion on an mbarrier -----------------
-    const uint32_t mbar_s = smem_u32(mbar);
-    if (tid == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(mbar_s));
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar_s), "n"(kLaneLutBytes) : "memory");
-        asm volatile(
-            "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(smem)),
-            "l"(&g_lane_lut), "n"(kLaneLutBytes), "r"(mbar_s)
-            : "memory");
+    // ---- phase A: weights, tables, expansion to selectors and signs ---------------------------
+    const bool valid = tid < nunits;
+    int rl = 0, cb = 0;
+    uint4 m = make_uint4(0, 0, 0, 0);
+    uint2 v = make_uint2(0, 0);
+    if (valid) {
+        rl = tid / a.upr;
+        cb = tid - rl * a.upr;
+        const size_t row = static_cast<size_t>(r_lo + rl);
+        m = ld_stream_v4(M.meta + row * M.meta_stride + cb * 4);
+        v = ld_stream_v2(M.values + row * M.values_stride + cb * 2);
+    }
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(&g_pair_lut);
+        uint4* dst = reinterpret_cast<uint4*>(win);
+        for (int q = tid; q < (kSelBytes + kSgnBytes) / 16; q += kThreads) dst[q] = __ldg(src + q);
     }
 
-    // ---- weights of the first kDepth units: independent of any predecessor -----------------
-    const uint32_t* mp = M.meta + static_cast<size_t>(r_lo + rs) * M.meta_stride + cb * 4;
-    const uint32_t* vp = M.values + static_cast<size_t>(r_lo + rs) * M.values_stride + cb * 2;
-    const size_t m_step = static_cast<size_t>(a.rs) * M.meta_stride;
-    const size_t v_step = static_cast<size_t>(a.rs) * M.values_stride;
-    uint4 m[kDepth];
-    uint2 v[kDepth];
-#pragma unroll
-    for (int d = 0; d < kDepth; ++d) {
-        if (active && d * a.rs + rs < nrows) {
-            m[d] = ld_stream_v4(mp + d * m_step);
-            v[d] = ld_stream_v2(vp + d * v_step);
-        } else {
-            m[d] = make_uint4(0, 0, 0, 0);
-            v[d] = make_uint2(0, 0);
-        }
-    }
-
-    // ---- activations: only now may a predecessor's output be read --------------------------
+    // ---- phase B starts: only now may a predecessor's output be read.  The first two x chunks
+    // of every thread are requested here, so that their latency overlaps the expansion below
+    // (and, when no predecessor is pending, the weight loads above).
     grid_dep_wait();
+    const int nchunks = a.cols >> 4;
     float absmax = 0.0f;
     if (IN == IN_F16 || OUT != OUT_I32) absmax = *a.d_absmax;
-    uint32_t xr[32];
-    if (IN == IN_I8) {
-        const uint4* xg = static_cast<const uint4*>(a.x) + (active ? (cb << 3) : 0);
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-            const uint4 t = __ldg(xg + ch);
-            xr[4 * ch + 0] = t.x; xr[4 * ch + 1] = t.y; xr[4 * ch + 2] = t.z; xr[4 * ch + 3] = t.w;
-        }
-    } else {
-        const float scale = quant_scale(absmax);
+    const float qscale = quant_scale(absmax);
+    auto load_chunk = [&](int q, uint4& lo, uint4& hi) {
         const uint4* xg = static_cast<const uint4*>(a.x);
-        const int nchunks = a.cols >> 4;
-        for (int q = tid; q < nchunks; q += kColsThreads) {
-            const uint4 lo = xg[2 * q], hi = xg[2 * q + 1];
+        if (IN == IN_I8) {
+            lo = xg[q];
+        } else {
+            lo = xg[2 * q];
+            hi = xg[2 * q + 1];
+        }
+    };
+    auto store_chunk = [&](int q, const uint4& lo, const uint4& hi) {
+        uint4 out = lo;
+        if (IN == IN_F16) {
             const uint32_t hw[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-            uint32_t out[4];
+            uint32_t o[4];
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 uint32_t packed = 0;
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const __half2 h2 = *reinterpret_cast<const __half2*>(&hw[2 * k + e]);
-                    const int q0 = quantize_one(__low2float(h2), scale);
-                    const int q1 = quantize_one(__high2float(h2), scale);
+                    const int q0 = quantize_one(__low2float(h2), qscale);
+                    const int q1 = quantize_one(__high2float(h2), qscale);
                     packed |= (static_cast<uint32_t>(q0) & 0xFFu) << (16 * e);
                     packed |= (static_cast<uint32_t>(q1) & 0xFFu) << (16 * e + 8);
                 }
-                out[k] = packed;
+                o[k] = packed;
             }
-            const int c = q >> 3, i = q & 7;
-            xs[(c << 3) + (i ^ (c & 7))] = make_uint4(out[0], out[1], out[2], out[3]);
+            out = make_uint4(o[0], o[1], o[2], o[3]);
         }
-        __syncthreads();
-        const uint4* xb = xs + (active ? (cb << 3) : 0);
-        const int sw = active ? (cb & 7) : 0;
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-            const uint4 t = xb[ch ^ sw];
-            xr[4 * ch + 0] = t.x; xr[4 * ch + 1] = t.y; xr[4 * ch + 2] = t.z; xr[4 * ch + 3] = t.w;
-        }
-    }
+        const int c = q >> 3, i = q & 7;
+        xs[(c << 3) + (i ^ (c & 7))] = out;
+    };
+    uint4 xa_lo = make_uint4(0, 0, 0, 0), xa_hi = xa_lo, xb_lo = xa_lo, xb_hi = xa_lo;
+    if (tid < nchunks) load_chunk(tid, xa_lo, xa_hi);
+    if (tid + kThreads < nchunks) load_chunk(tid + kThreads, xb_lo, xb_hi);
 
-    // ---- wait for the tables (bounded); on expiry fill them with plain loads instead ----------
+    __syncthreads();  // tables complete
+
+    uint32_t sel[16], sgn[16];
     {
-        uint32_t done = 0;
-        for (int spin = 0; spin < 4096 && !done; ++spin) {
-            asm volatile(
-                "{\n\t.reg .pred p;\n\t"
-                "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\t"
-                "selp.u32 %0, 1, 0, p;\n\t}"
-                : "=r"(done)
-                : "r"(mbar_s)
-                : "memory");
-        }
-        if (!__syncthreads_and(done != 0)) {
-            uint32_t* lut = reinterpret_cast<uint32_t*>(smem);
-            for (int e = tid; e < kLaneLutWords; e += kColsThreads) lut[e] = g_lane_lut.w[e];
-            __syncthreads();
+        // produced by a volatile statement after the barrier, so that no table load can be
+        // scheduled above it
+        uint32_t sel_lane;
+        asm volatile("add.u32 %0, %1, %2;" : "=r"(sel_lane) : "r"(win_s), "r"(lane * 4) : "memory");
+        const uint32_t sgn_lane = sel_lane + kSelBytes;
+        const uint32_t mw[4] = {m.x, m.y, m.z, m.w};
+        const uint32_t vw[2] = {v.x, v.y};
+#pragma unroll
+        for (int p = 0; p < 16; ++p) {  // groups 2p and 2p+1: meta byte p, sign nibble p
+            const int ms = 8 * (p & 3) - 7, ss = 4 * (p & 7) - 7;
+            sel[p] = lds32(((ms >= 0 ? (mw[p >> 2] >> ms) : (mw[p >> 2] << -ms)) & (0x77u << 7)) + sel_lane);
+            sgn[p] = lds32(((ss >= 0 ? (vw[p >> 3] >> ss) : (vw[p >> 3] << -ss)) & (0xFu << 7)) + sgn_lane);
         }
     }
 
-    // ---- main loop: consume unit `it`, refill its slot with unit `it + kDepth` -----------------
-    // The table address is produced after the wait by a volatile statement, so that no table
-    // load can be scheduled above the wait.
-    uint32_t lut_lane;
-    asm volatile("add.u32 %0, %1, %2;" : "=r"(lut_lane) : "r"(smem_u32(smem)), "r"(lane * 4) : "memory");
-    int* my_partial = partial + rs * a.upr + cb;
-    for (int it0 = 0; it0 < niter; it0 += kDepth) {
-#pragma unroll
-        for (int d = 0; d < kDepth; ++d) {
-            const int it = it0 + d;
-            if (it >= niter) break;  // uniform across the block
-            const int lr = it * a.rs + rs;
-            if (active && lr < nrows) {
-                my_partial[it * a.rs * a.upr] = mac_unit(m[d], v[d], xr, lut_lane);
-                const int nx = it + kDepth;
-                if (nx * a.rs + rs < nrows) {
-                    m[d] = ld_stream_v4(mp + nx * m_step);
-                    v[d] = ld_stream_v2(vp + nx * v_step);
-                }
-            }
-        }
+    if (tid < nchunks) store_chunk(tid, xa_lo, xa_hi);
+    if (tid + kThreads < nchunks) store_chunk(tid + kThreads, xb_lo, xb_hi);
+    for (int q = tid + 2 * kThreads; q < nchunks; q += kThreads) {  // wide matrices
+        uint4 lo, hi = make_uint4(0, 0, 0, 0);
+        load_chunk(q, lo, hi);
+        store_chunk(q, lo, hi);
     }
     __syncthreads();
 
-    // ---- a warp folds each row ------------------------------------------------------------------
-    const float dq = (OUT != OUT_I32) ? dequant_scale(M.gamma, absmax) : 0.0f;
-    for (int lr = tid >> 5; lr < nrows; lr += kColsThreads / 32) {
-        int s = 0;
-        for (int c = lane; c < a.upr; c += 32) s += partial[lr * a.upr + c];
+    if (valid) {
+        const uint4* xb = xs + (cb << 3);
+        const int sw = cb & 7;
+        int acc = 0;
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, off);
-        if (lane == 0) store_out(M, r_lo + lr, s, dq, OUT);
+        for (int ch = 0; ch < 8; ++ch) {  // 16 columns = 4 groups = 2 pairs per chunk
+            const uint4 xv = xb[ch ^ sw];
+            acc = __dp4a(static_cast<int>(__byte_perm(xv.x, xv.y, sel[2 * ch])), static_cast<int>(sgn[2 * ch]), acc);
+            acc = __dp4a(static_cast<int>(__byte_perm(xv.z, xv.w, sel[2 * ch + 1])), static_cast<int>(sgn[2 * ch + 1]), acc);
+        }
+        partial[cb * pitch + rl] = acc;
+    }
+    __syncthreads();
+
+    // one thread per row folds its partials (consecutive rows -> consecutive banks)
+    const float dq = (OUT != OUT_I32) ? dequant_scale(M.gamma, absmax) : 0.0f;
+    for (int lr = tid; lr < nrows; lr += kThreads) {
+        int s = 0;
+        for (int c = 0; c < a.upr; ++c) s += partial[c * pitch + lr];
+        store_out(M, r_lo + lr, s, dq, OUT);
     }
 }
 
@@ -498,7 +455,7 @@ struct MatDesc {
     int rows, meta_stride, values_stride;
 };
 
-static int g_gemv_variant = 0;  // 0 auto, 1 unit kernel (latency form), 2 column-owner kernel (throughput form)
+static int g_gemv_variant = 0;  // 0/1 pair kernel (default), 2 per-group table kernel
 
 // Launches up to kMaxMats matrices that share x (and d_absmax) as one grid.
 template <int IN, int OUT>
@@ -528,32 +485,6 @@ static int run_gemv(const char* name, const MatDesc* mats, int nmat, const void*
         max_rows = max(max_rows, m.rows);
     }
 
-    if (fast && g_gemv_variant != 1 && cols / 128 <= kColsThreads) {
-        ColsArgs c{};
-        c.nmat = nmat;
-        c.x = x;
-        c.d_absmax = d_absmax;
-        c.cols = cols;
-        c.upr = cols / 128;
-        c.rs = kColsThreads / c.upr;
-        const int sms_ = sm_count();
-        // rows per block: one block per SM, but never more partial sums than shared memory holds
-        int rpc = max(1, (total_rows + sms_ - 1) / sms_);
-        const int rpc_cap = max(1, (150 * 1024) / (c.upr * 4));
-        rpc = min(rpc, rpc_cap);
-        c.rpc = rpc;
-        int blocks = 0;
-        for (int i = 0; i < nmat; ++i) {
-            const MatDesc& m = mats[i];
-            c.mat[i] = GemvMat{m.meta, m.values, m.y, m.y_acc, m.gamma, m.rows, m.meta_stride, m.values_stride, blocks};
-            blocks += (m.rows + rpc - 1) / rpc;
-        }
-        const size_t smem = kLaneLutBytes + 16 + ((rpc * c.upr * 4 + 15) & ~15) + (IN == IN_F16 ? static_cast<size_t>(cols) : 0);
-        int rc;
-        if ((rc = ensure_smem(gemv_cols_kernel<IN, OUT>, smem))) return rc;
-        return launch(name, gemv_cols_kernel<IN, OUT>, dim3(blocks), dim3(kColsThreads), smem, stream, c);
-    }
-
     GemvArgs a{};
     a.nmat = nmat;
     a.x = x;
@@ -575,10 +506,15 @@ static int run_gemv(const char* name, const MatDesc* mats, int nmat, const void*
         blocks += (m.rows + rpc - 1) / rpc;
     }
     if (!fast) return launch(name, gemv_generic_kernel<IN, OUT>, dim3(blocks), dim3(kThreads), 0, stream, a);
-    const size_t smem = kLutBytes + ((rpc * 4 + 15) & ~15) + static_cast<size_t>(cols);
     int rc;
-    if ((rc = ensure_smem(gemv_units_kernel<IN, OUT>, smem))) return rc;
-    return launch(name, gemv_units_kernel<IN, OUT>, dim3(blocks), dim3(kThreads), smem, stream, a);
+    if (g_gemv_variant == 2) {  // the per-group table kernel, kept for comparison
+        const size_t smem = kLutBytes + ((rpc * 4 + 15) & ~15) + static_cast<size_t>(cols);
+        if ((rc = ensure_smem(gemv_units_kernel<IN, OUT>, smem))) return rc;
+        return launch(name, gemv_units_kernel<IN, OUT>, dim3(blocks), dim3(kThreads), smem, stream, a);
+    }
+    const size_t smem = kSelBytes + kSgnBytes + ((a.upr * (rpc | 1) * 4 + 15) & ~15) + static_cast<size_t>(cols);
+    if ((rc = ensure_smem(gemv_pairs_kernel<IN, OUT>, smem))) return rc;
+    return launch(name, gemv_pairs_kernel<IN, OUT>, dim3(blocks), dim3(kThreads), smem, stream, a);
 }
 
 // Engine-internal: several BitLinear layers on the same pre-quantised activation in one launch.

@@ -49,6 +49,32 @@ def sparse_ternary_gemv_gpu(meta, values, x, y, rows, cols, meta_row_stride, val
                                          values_row_stride, _stream(stream)))
 
 
+class GemvWorkList:
+    """A device-resident list of GEMVs for sparse_ternary_gemv_batch_gpu.  items: iterable of
+    (meta, values, x, y, rows, cols, meta_row_stride, values_row_stride) with CUDA tensors (or
+    device addresses) for the first four."""
+
+    def __init__(self, items):
+        import numpy as np
+        from ._lib import GemvItem
+        items = list(items)
+        arr = (GemvItem * len(items))()
+        for i, (meta, values, x, y, rows, cols, ms, vs) in enumerate(items):
+            arr[i] = GemvItem(_p(meta).value, _p(values).value, _p(x).value, _p(y).value, rows, cols, ms, vs)
+        check(load().spb_gemv_batch_check(arr, len(items)))
+        self.n = len(items)
+        self.max_rows = max((it[4] for it in items), default=0)
+        self.max_cols = max((it[5] for it in items), default=0)
+        raw = np.frombuffer(bytes(arr), dtype=np.uint8).copy() if items else np.zeros(1, np.uint8)
+        self.d_items = torch.from_numpy(raw).cuda()
+        self._keep = items  # keeps the tensors alive
+
+
+def sparse_ternary_gemv_batch_gpu(work: GemvWorkList, stream=None):
+    check(load().spb_sparse_ternary_gemv_batch(_p(work.d_items), work.n, work.max_rows, work.max_cols,
+                                               _stream(stream)))
+
+
 def sparse_ternary_gemv_scaled_gpu(meta, values, x, y, y_acc, d_absmax, gamma, rows, cols, meta_row_stride,
                                    values_row_stride, stream=None):
     check(load().spb_sparse_ternary_gemv_scaled(_p(meta), _p(values), _p(x), _p(y), _p(y_acc), _p(d_absmax),

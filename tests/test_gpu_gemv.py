@@ -14,7 +14,7 @@ from gpu_util import Guarded, dev, host
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=[1, 2], ids=["unit-kernel", "column-kernel"], autouse=True)
+@pytest.fixture(params=[1, 2], ids=["pair-kernel", "group-table-kernel"], autouse=True)
 def gemv_variant(request):
     """Every test in this file runs once per GEMV kernel variant."""
     old = K.set_gemv_variant(request.param)
@@ -106,7 +106,7 @@ def test_padded_strides_and_unaligned_pointers():
 
 def test_invalid_bitmaps_follow_the_reference_gpu_table(gemv_variant):
     # src/kernels/sparse_ternary.cu:34-51: any bitmap without exactly two bits decodes as (0,0).
-    # The column-owner kernel only promises memory safety on such input (it must not fault).
+    # The pair kernel only promises memory safety on such input (it must not fault).
     cols = 128
     meta = np.array([[0x0F731248, 0x0, 0xEDB7FFFF, 0x33333333]], np.uint32)
     values = np.array([[0x9C3A5F01, 0x6E21D4B7]], np.uint32)
@@ -120,7 +120,7 @@ def test_invalid_bitmaps_follow_the_reference_gpu_table(gemv_variant):
         acc += (-1 if s & 1 else 1) * int(x[4 * g + p0]) + (-1 if s & 2 else 1) * int(x[4 * g + p1])
     case = dict(meta=meta, values=values, x=x, rows=1, cols=cols, meta_stride=4, values_stride=2)
     got = run_gemv(case)[0]
-    if gemv_variant == 1:
+    if gemv_variant == 2:
         assert got == acc
 
 
@@ -229,3 +229,28 @@ def test_gemm_full_size_properties(rows, cols):
     y1 = torch.empty(rows, dtype=torch.int32, device="cuda")
     K.sparse_ternary_gemv_gpu(d_meta, d_values, dev(X[5]), y1, rows, cols, case["meta_stride"], case["values_stride"])
     assert (host(y1) == Yh[5]).all()
+
+
+def test_work_list_batch_matches_oracle():
+    # one persistent launch over a list of GEMVs of mixed shapes == the same GEMVs one by one
+    shapes = [(6912, 2560), (640, 2560), (2560, 6912), (33, 128), (2048, 2048), (1, 256), (700, 8192), (6912, 2560)]
+    rng = np.random.default_rng(0)
+    items, wants, keep = [], [], []
+    for i, (rows, cols) in enumerate(shapes):
+        case = synth.gemv_case(rows, cols, seed=100 + i)
+        x = rng.integers(-128, 128, cols, dtype=np.int8)
+        wants.append(oracle.sparse_gemv(case["meta"], case["values"], x, rows, cols, threads=8))
+        y = torch.full((rows + 64,), 0x5A5A5A5A, dtype=torch.int32, device="cuda")
+        t = (dev(case["meta"]), dev(case["values"]), dev(x), y)
+        keep.append(t)
+        items.append((t[0], t[1], t[2], y.data_ptr() + 128, rows, cols, case["meta_stride"], case["values_stride"]))
+    work = K.GemvWorkList(items)
+    for _ in range(2):
+        K.sparse_ternary_gemv_batch_gpu(work)
+    torch.cuda.synchronize()
+    for (rows, cols), want, t in zip(shapes, wants, keep):
+        got = t[3].cpu().numpy()
+        assert (got[32:32 + rows] == want).all(), (rows, cols)
+        assert (got[:32] == 0x5A5A5A5A).all() and (got[32 + rows:] == 0x5A5A5A5A).all()
+    with pytest.raises(_lib.SpbError):
+        K.GemvWorkList([(keep[0][0], keep[0][1], keep[0][2], keep[0][3], 16, 132, 5, 3)])
