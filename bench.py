@@ -182,6 +182,12 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     K.set_gemv_variant(args.variant)
+    if args.only_decode:
+        if rank == 0:
+            print(json.dumps({"metric": "decode_tok_s_2b4t_shape", "decode": bench_decode(args), "n_gpus": world}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
     peak, peak_kind = measured_peaks()
     l2_bytes = torch.cuda.get_device_properties(local).L2_cache_size
     rows, cols = synth.METRIC_SHAPE
@@ -411,11 +417,13 @@ def bench_decode(args):
     from spbitnet_b200 import synth
     from spbitnet_b200.engine import DeviceModel, InferenceEngine
     cfg = dict(synth.BITNET_2B)
+    if args.decode_layers > 0:
+        cfg["num_hidden_layers"] = args.decode_layers
     model = synth.random_model(cfg, seed=0, shared_layer=True)
     dm = DeviceModel(model)
     eng = InferenceEngine(dm)
     prompt = np.random.default_rng(0).integers(0, cfg["vocab_size"], 128).astype(np.int32)
-    n_gen = 256
+    n_gen = args.decode_tokens
     eng.generate(prompt, 8)  # warm-up: graph capture, page-in
     eng.reset()
     torch.cuda.synchronize()
@@ -442,6 +450,9 @@ def main():
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--only-decode", action="store_true", help="skip the GEMV sections (profiling aid)")
+    ap.add_argument("--decode-layers", type=int, default=0, help="override the layer count of the decode model")
+    ap.add_argument("--decode-tokens", type=int, default=256)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
     if args.impl == "reference":

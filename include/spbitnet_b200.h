@@ -167,6 +167,17 @@ int spb_decode_attention(const void* Q, const void* K_cache, const void* V_cache
                          int num_heads, int num_kv_heads, int head_dim, int max_seq_len,
                          int seq_len, float scale, void* stream);
 
+/* The same result as spb_decode_attention from a split-KV pass: the positions are cut into
+ * chunks served by separate blocks (all query heads of a GQA group share one read of their K/V
+ * rows) and merged by a second small kernel.  Needs a device scratch buffer of at least
+ * spb_decode_attention_scratch_bytes(num_heads, head_dim, max_seq_len) bytes, owned by the caller;
+ * its contents need no initialisation and are overwritten.  num_heads must be a multiple of
+ * num_kv_heads with at most 8 query heads per KV head; head_dim <= 256. */
+size_t spb_decode_attention_scratch_bytes(int num_heads, int head_dim, int max_seq_len);
+int spb_decode_attention_split(const void* Q, const void* K_cache, const void* V_cache, void* output,
+                               int num_heads, int num_kv_heads, int head_dim, int max_seq_len, int seq_len,
+                               float scale, void* scratch, size_t scratch_bytes, void* stream);
+
 /* ---- host-side format helpers: include/spbitnet/sparse_ternary_tensor.h ----------- */
 
 /* Row strides in uint32 words (sparse_ternary_tensor.h:254-264). */

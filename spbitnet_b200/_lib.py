@@ -77,6 +77,8 @@ SIGNATURES = {
     "spb_residual_add": (_i, [_p, _p, _p, _i, _p]),
     "spb_half_gemv": (_i, [_p, _p, _p, _i, _i, _p]),
     "spb_decode_attention": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _p]),
+    "spb_decode_attention_scratch_bytes": (C.c_size_t, [_i, _i, _i]),
+    "spb_decode_attention_split": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _p, C.c_size_t, _p]),
     "spb_meta_words_per_row": (_i, [_i]),
     "spb_values_words_per_row": (_i, [_i]),
     "spb_pack_from_dense": (_i, [_p, _p, _i, _i, _p, _p]),

@@ -9,7 +9,9 @@
 //   * the whole token is a CUDA graph of PDL-chained kernels whose position lives in
 //     device memory, replayed once per token on a private stream,
 //   * the arg-max of the greedy loop (src/main.cpp:285-287) runs on the device.
+#include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <new>
 #include <vector>
 
@@ -46,10 +48,12 @@ struct spb_engine {
     size_t pool_bytes = 0;
     size_t kv_bytes_per_layer = 0;
     __half *kcache = nullptr, *vcache = nullptr;
-    __half *x = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr, *o = nullptr;
+    __half *x = nullptr, *x2 = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr, *o = nullptr;
     __half *gate = nullptr, *up = nullptr, *down = nullptr, *xfinal = nullptr;
     int8_t* xq = nullptr;   // quantised activation, max(hidden, inter, heads*head_dim)
     float* absmax = nullptr;
+    float* attn_scratch = nullptr;  // split-KV partial results
+    bool split_attention = false;
     float* logits = nullptr;
     float* bval = nullptr;
     int* bidx = nullptr;
@@ -60,6 +64,8 @@ struct spb_engine {
 
     cudaGraphExec_t graph = nullptr;  // one token, position and token read from device memory
     bool graph_generates = false;     // the captured graph records tokens into d_out
+    bool fused = false;               // vector ops run inside the BitLinear launches
+    bool force_unfused = false;
     int seq_len = 0;
 };
 
@@ -80,72 +86,82 @@ int cuda_fail(const char* what, cudaError_t err) {
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-int bitlinear(spb_engine* e, const Linear& L, const int8_t* xq, const float* absmax, __half* out) {
-    if (!L.meta) return fail(SPB_E_INVALID, "engine: a linear layer has no weights attached");
-    return spb_sparse_bitlinear_q8(L.meta, L.values, xq, out, absmax, L.gamma, L.rows, L.cols, L.ms, L.vs,
-                                   e->stream);
-}
-
-// Several projections of the same quantised activation in one launch (q/k/v, gate/up).
-int bitlinear_group(spb_engine* e, const Linear* const* L, __half* const* out, int n, const int8_t* xq,
-                    const float* absmax) {
-    const uint32_t* meta[3];
-    const uint32_t* values[3];
-    void* o[3];
-    float gamma[3];
-    int rows[3], ms[3], vs[3];
+BitLinearGroup make_group(const Linear* const* L, __half* const* out, int n) {
+    BitLinearGroup g{};
+    g.nmat = n;
+    g.cols = L[0]->cols;
     for (int i = 0; i < n; ++i) {
-        if (!L[i]->meta) return fail(SPB_E_INVALID, "engine: a linear layer has no weights attached");
-        if (L[i]->cols != L[0]->cols) return fail(SPB_E_INVALID, "engine: grouped layers differ in width");
-        meta[i] = L[i]->meta; values[i] = L[i]->values; o[i] = out[i]; gamma[i] = L[i]->gamma;
-        rows[i] = L[i]->rows; ms[i] = L[i]->ms; vs[i] = L[i]->vs;
+        g.meta[i] = L[i]->meta; g.values[i] = L[i]->values; g.out[i] = out[i]; g.gamma[i] = L[i]->gamma;
+        g.rows[i] = L[i]->rows; g.ms[i] = L[i]->ms; g.vs[i] = L[i]->vs;
     }
-    return bitlinear_q8_group(meta, values, o, gamma, rows, ms, vs, n, xq, absmax, L[0]->cols, e->stream);
+    return g;
 }
 
 // Enqueues one token's worth of kernels on e->stream.  The first kernel reads the token
 // (prompt[pos] while pos < n_prompt, else the previous arg-max) and the last advances pos.
+// With layouts the fused-producer GEMV kernels take (every benchmark model), a layer is six
+// launches: the vector ops between the BitLinears run inside the consuming launch.
 int enqueue_token(spb_engine* e, bool record_tokens) {
     const spb_model_config& c = e->cfg;
     const int H = c.hidden_size, hd = c.head_dim, nh = c.num_attention_heads, nkv = c.num_key_value_heads;
     const int inter = c.intermediate_size;
     void* s = e->stream;
     int rc;
-    if ((rc = embed_token(e->embed, e->x, H, e->d_prompt, e->n_prompt_in_graph, e->d_next, e->d_pos, s))) return rc;
+    __half* cur = e->x;
+    __half* other = e->x2;
+    if ((rc = embed_token(e->embed, cur, H, e->d_prompt, e->n_prompt_in_graph, e->d_next, e->d_pos, s))) return rc;
     const float attn_scale = 1.0f / sqrtf(static_cast<float>(hd));
     for (int l = 0; l < c.num_hidden_layers; ++l) {
         const Layer& L = e->layers[l];
         __half* kc = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(e->kcache) + l * e->kv_bytes_per_layer);
         __half* vc = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(e->vcache) + l * e->kv_bytes_per_layer);
-        // input norm (+ the previous layer's down-projection residual add)
-        if ((rc = residual_norm_quant(l == 0 ? nullptr : e->down, nullptr, e->x, L.norm[0], nullptr, e->xq,
-                                      e->absmax, H, c.rms_norm_eps, s))) return rc;
-        {
-            const Linear* g3[3] = {&L.lin[0], &L.lin[1], &L.lin[2]};
-            __half* o3[3] = {e->q, e->k, e->v};
-            if ((rc = bitlinear_group(e, g3, o3, 3, e->xq, e->absmax))) return rc;
+        const Linear* g3[3] = {&L.lin[0], &L.lin[1], &L.lin[2]};
+        __half* o3[3] = {e->q, e->k, e->v};
+        const Linear* g1o[1] = {&L.lin[3]};
+        __half* o1o[1] = {e->o};
+        const Linear* g2[2] = {&L.lin[4], &L.lin[5]};
+        __half* o2[2] = {e->gate, e->up};
+        const Linear* g1d[1] = {&L.lin[6]};
+        __half* o1d[1] = {e->down};
+        if (e->fused) {
+            // previous layer's down-projection residual add + input norm + quantise, inside q/k/v
+            if ((rc = bitlinear_resnorm_group(make_group(g3, o3, 3), cur, l == 0 ? nullptr : e->down, nullptr, L.norm[0],
+                                              other, c.rms_norm_eps, s))) return rc;
+            std::swap(cur, other);
+        } else {
+            if ((rc = residual_norm_quant(l == 0 ? nullptr : e->down, nullptr, cur, L.norm[0], nullptr, e->xq, e->absmax,
+                                          H, c.rms_norm_eps, s))) return rc;
+            if ((rc = bitlinear_q8_group(make_group(g3, o3, 3), e->xq, e->absmax, s))) return rc;
         }
         if ((rc = rope_scatter(e->q, e->k, e->v, kc, vc, nh, nkv, hd, c.max_position_embeddings, c.rope_theta,
                                e->d_pos, s))) return rc;
-        if ((rc = decode_attention_pos(e->q, kc, vc, e->attn, nh, nkv, hd, c.max_position_embeddings,
-                                       attn_scale, e->d_pos, s))) return rc;
-        if ((rc = spb_absmax_quantize(e->attn, e->xq, e->absmax + 1, nh * hd, s))) return rc;
-        if ((rc = bitlinear(e, L.lin[3], e->xq, e->absmax + 1, e->o))) return rc;
-        // attn_sub_norm -> residual add -> post-attention norm -> quantise
-        if ((rc = residual_norm_quant(e->o, L.norm[2], e->x, L.norm[1], nullptr, e->xq, e->absmax, H,
-                                      c.rms_norm_eps, s))) return rc;
-        {
-            const Linear* g2[2] = {&L.lin[4], &L.lin[5]};
-            __half* o2[2] = {e->gate, e->up};
-            if ((rc = bitlinear_group(e, g2, o2, 2, e->xq, e->absmax))) return rc;
+        if (e->split_attention) {
+            if ((rc = decode_attention_split(e->q, kc, vc, e->attn, nh, nkv, hd, c.max_position_embeddings, 0, e->d_pos,
+                                             attn_scale, e->attn_scratch, s))) return rc;
+        } else if ((rc = decode_attention_pos(e->q, kc, vc, e->attn, nh, nkv, hd, c.max_position_embeddings,
+                                              attn_scale, e->d_pos, s))) {
+            return rc;
         }
-        if ((rc = relu2_norm_quant(e->gate, e->up, L.norm[3], nullptr, e->xq, e->absmax + 1, inter,
-                                   c.rms_norm_eps, s))) return rc;
-        if ((rc = bitlinear(e, L.lin[6], e->xq, e->absmax + 1, e->down))) return rc;
+        if (e->fused) {
+            if ((rc = bitlinear_amax_group(make_group(g1o, o1o, 1), e->attn, s))) return rc;
+            // attn_sub_norm -> residual add -> post-attention norm -> quantise, inside gate/up
+            if ((rc = bitlinear_resnorm_group(make_group(g2, o2, 2), cur, e->o, L.norm[2], L.norm[1], other,
+                                              c.rms_norm_eps, s))) return rc;
+            std::swap(cur, other);
+            // relu2 * up -> ffn_sub_norm -> quantise, inside down
+            if ((rc = bitlinear_relu2_group(make_group(g1d, o1d, 1), e->gate, e->up, L.norm[3], c.rms_norm_eps, s))) return rc;
+        } else {
+            if ((rc = spb_absmax_quantize(e->attn, e->xq, e->absmax + 1, nh * hd, s))) return rc;
+            if ((rc = bitlinear_q8_group(make_group(g1o, o1o, 1), e->xq, e->absmax + 1, s))) return rc;
+            if ((rc = residual_norm_quant(e->o, L.norm[2], cur, L.norm[1], nullptr, e->xq, e->absmax, H, c.rms_norm_eps, s))) return rc;
+            if ((rc = bitlinear_q8_group(make_group(g2, o2, 2), e->xq, e->absmax, s))) return rc;
+            if ((rc = relu2_norm_quant(e->gate, e->up, L.norm[3], nullptr, e->xq, e->absmax + 1, inter, c.rms_norm_eps, s))) return rc;
+            if ((rc = bitlinear_q8_group(make_group(g1d, o1d, 1), e->xq, e->absmax + 1, s))) return rc;
+        }
     }
     // last residual add + final norm
-    if ((rc = residual_norm_quant(c.num_hidden_layers ? e->down : nullptr, nullptr, e->x, e->final_norm,
-                                  e->xfinal, e->xq, e->absmax, H, c.rms_norm_eps, s))) return rc;
+    if ((rc = residual_norm_quant(c.num_hidden_layers ? e->down : nullptr, nullptr, cur, e->final_norm, e->xfinal,
+                                  e->xq, e->absmax, H, c.rms_norm_eps, s))) return rc;
     if ((rc = spb_half_gemv(e->lm_head ? e->lm_head : e->embed, e->xfinal, e->logits, c.vocab_size, H, s))) return rc;
     return argmax_advance(e->logits, c.vocab_size, e->bval, e->bidx, e->argmax_blocks, e->d_next,
                           record_tokens ? e->d_out : nullptr, e->d_pos, s);
@@ -173,6 +189,12 @@ int ensure_graph(spb_engine* e, bool record_tokens, int n_prompt) {
     if (e->graph && e->graph_generates == record_tokens && e->n_prompt_in_graph == n_prompt) return SPB_OK;
     drop_graph(e);
     e->n_prompt_in_graph = n_prompt;
+    e->fused = !e->force_unfused;
+    for (const Layer& L : e->layers) {
+        const Linear* all[7] = {&L.lin[0], &L.lin[1], &L.lin[2], &L.lin[3], &L.lin[4], &L.lin[5], &L.lin[6]};
+        __half* none[7] = {};
+        for (int i = 0; i < 7 && e->fused; ++i) e->fused = bitlinear_group_is_fast(make_group(all + i, none + i, 1));
+    }
     SPB_CUDA(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
     int rc = enqueue_token(e, record_tokens);
     cudaGraph_t g = nullptr;
@@ -202,6 +224,8 @@ extern "C" spb_engine* spb_engine_create(const spb_model_config* cfg) {
     if (!e) return nullptr;
     e->cfg = *cfg;
     e->layers.resize(cfg->num_hidden_layers);
+    const char* unf = std::getenv("SPB_ENGINE_UNFUSED");  // testing aid: one launch per vector op group
+    e->force_unfused = unf && unf[0] == '1';
     cudaGetDevice(&e->device);
     const int H = cfg->hidden_size, qdim = cfg->num_attention_heads * cfg->head_dim;
     const int kvdim = cfg->num_key_value_heads * cfg->head_dim, inter = cfg->intermediate_size;
@@ -213,10 +237,14 @@ extern "C" spb_engine* spb_engine_create(const spb_model_config* cfg) {
     auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return o; };
     const size_t o_kc = take(e->kv_bytes_per_layer * cfg->num_hidden_layers);
     const size_t o_vc = take(e->kv_bytes_per_layer * cfg->num_hidden_layers);
-    const size_t o_x = take(2 * H), o_q = take(2 * qdim), o_k = take(2 * kvdim), o_v = take(2 * kvdim);
+    const size_t o_x = take(2 * H), o_x2 = take(2 * H), o_q = take(2 * qdim), o_k = take(2 * kvdim), o_v = take(2 * kvdim);
     const size_t o_attn = take(2 * qdim), o_o = take(2 * H), o_gate = take(2 * inter), o_up = take(2 * inter);
     const size_t o_down = take(2 * H), o_xf = take(2 * H), o_xq = take(maxdim), o_abs = take(16);
     const size_t o_logits = take(4 * static_cast<size_t>(cfg->vocab_size));
+    e->split_attention = cfg->num_attention_heads % cfg->num_key_value_heads == 0 &&
+                         cfg->num_attention_heads / cfg->num_key_value_heads <= 8 && cfg->head_dim <= 256;
+    const size_t o_ascr = take(decode_attention_scratch_bytes(cfg->num_attention_heads, cfg->head_dim,
+                                                              cfg->max_position_embeddings));
     const size_t o_bval = take(4 * 128), o_bidx = take(4 * 128), o_ints = take(16);
     const size_t o_out = take(4 * static_cast<size_t>(kMaxTokensOut));
     e->pool_bytes = off;
@@ -231,6 +259,7 @@ extern "C" spb_engine* spb_engine_create(const spb_model_config* cfg) {
     e->kcache = reinterpret_cast<__half*>(p + o_kc);
     e->vcache = reinterpret_cast<__half*>(p + o_vc);
     e->x = reinterpret_cast<__half*>(p + o_x);
+    e->x2 = reinterpret_cast<__half*>(p + o_x2);
     e->q = reinterpret_cast<__half*>(p + o_q);
     e->k = reinterpret_cast<__half*>(p + o_k);
     e->v = reinterpret_cast<__half*>(p + o_v);
@@ -243,6 +272,7 @@ extern "C" spb_engine* spb_engine_create(const spb_model_config* cfg) {
     e->xq = reinterpret_cast<int8_t*>(p + o_xq);
     e->absmax = reinterpret_cast<float*>(p + o_abs);
     e->logits = reinterpret_cast<float*>(p + o_logits);
+    e->attn_scratch = reinterpret_cast<float*>(p + o_ascr);
     e->bval = reinterpret_cast<float*>(p + o_bval);
     e->bidx = reinterpret_cast<int*>(p + o_bidx);
     e->d_pos = reinterpret_cast<int*>(p + o_ints);

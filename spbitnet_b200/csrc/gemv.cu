@@ -17,11 +17,21 @@
 //     conflicts) and consumes a group with one dp4a;
 //   * reduces the per-thread partials of a row with a segmented shuffle scan.
 // A "unit" is 128 consecutive columns of one row: 16 B of meta + 8 B of values.
-#include "spb_common.cuh"
+#include "fused_ops.cuh"
 
 namespace spb {
 
-enum { IN_I8 = 0, IN_F16 = 1 };
+// How the int8 activation vector of a launch comes to be.
+//   IN_I8      : given (absmax_quantize_gpu output)
+//   IN_F16     : half vector quantised with the given *d_absmax (fused_sparse_bitlinear_gpu)
+//   IN_F16_AMAX: half vector; every block forms absmax itself (absmax_reduce_gpu + the above)
+//   IN_RESNORM : x_out = half(x_in + [rms_norm(sub_w)](delta)); xn = half(rms_norm(w)(x_out)); quantise xn
+//                (rms_norm_gpu [sub-norm], residual_add_gpu, rms_norm_gpu, absmax_quantize_gpu)
+//   IN_RELU2   : m = relu2_mul_f32(gate, up); h = sub_w ? rms_norm_f32in(m) : float_to_half(m); quantise h
+// The last three let a BitLinear launch absorb the single-block vector kernels that precede it
+// in a decode step: every block recomputes the (short) vector redundantly, block 0 publishes
+// x_out.  All rounding points of the separate kernels are kept.
+enum { IN_I8 = 0, IN_F16 = 1, IN_F16_AMAX = 2, IN_RESNORM = 3, IN_RELU2 = 4 };
 enum { OUT_I32 = 0, OUT_F32 = 1, OUT_F16 = 2 };
 
 constexpr int kMaxMats = 3;
@@ -43,8 +53,13 @@ struct GemvMat {
 struct GemvArgs {
     GemvMat mat[kMaxMats];
     int nmat;
-    const void* x;          // int8 (IN_I8) or half (IN_F16), cols elements
-    const float* d_absmax;  // device scalar; read after the dependency wait
+    const void* x;          // int8 (IN_I8), half (IN_F16*), residual x_in (IN_RESNORM), gate (IN_RELU2)
+    const void* x2;         // delta (IN_RESNORM, may be null), up (IN_RELU2)
+    const float* w_sub;     // sub-norm weights (IN_RESNORM on delta, IN_RELU2), may be null
+    const float* w_norm;    // norm weights (IN_RESNORM)
+    void* x_out;            // updated residual stream (IN_RESNORM)
+    float eps;
+    const float* d_absmax;  // device scalar (IN_I8 with scaled output, IN_F16); read after the dependency wait
     int cols;
     int upr;  // units per row = cols / 128
     int rpc;  // rows per block
@@ -201,7 +216,6 @@ __global__ void __launch_bounds__(kThreads) gemv_units_kernel(const GemvArgs a) 
 constexpr int kSelEntries = 120;  // (meta byte & 0x77) <= 0x77
 constexpr int kSelBytes = kSelEntries * 32 * 4;  // 15360
 constexpr int kSgnBytes = 16 * 32 * 4;           // 2048
-constexpr int kWindow = 16384;
 
 struct PairLutImage {
     uint32_t sel[kSelEntries * 32];
@@ -252,15 +266,397 @@ __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
     return v;
 }
 
+// ---- activation producers ----------------------------------------------------------------
+__device__ __forceinline__ float blk_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = (lane < kThreads / 32) ? red[lane] : 0.0f;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, off);
+    return t;
+}
+__device__ __forceinline__ float blk_max(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, off));
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = (lane < kThreads / 32) ? red[lane] : 0.0f;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) t = fmaxf(t, __shfl_xor_sync(0xFFFFFFFFu, t, off));
+    return t;
+}
+
+// int8 element i of the activation vector lives at byte i of the swizzled chunk array.
+__device__ __forceinline__ int8_t* xs_byte(uint4* xs, int i) {
+    const int q = i >> 4, c = q >> 3, k = q & 7;
+    return reinterpret_cast<int8_t*>(xs + ((c << 3) + (k ^ (c & 7)))) + (i & 15);
+}
+
+// Strided-loop form of the normalising producers, for vectors too long for the register form.
+template <int IN>
+__device__ __noinline__ float produce_x_loops(const GemvArgs& a, uint4* xs, __half* hbuf, float* red,
+                                              bool publisher) {
+    const int tid = threadIdx.x;
+    const int n = a.cols;
+    if (IN == IN_RESNORM) {
+        const __half* x_in = static_cast<const __half*>(a.x);
+        const __half* delta = static_cast<const __half*>(a.x2);
+        __half* x_out = static_cast<__half*>(a.x_out);
+        // 1. residual stream: x_new = half(float(d) + float(x)), d = delta or its sub-norm
+        float s = 0.0f;
+        if (delta) {
+            float sub_scale = 1.0f;
+            if (a.w_sub) {
+                float ss = 0.0f;
+                for (int i = tid; i < n; i += kThreads) {
+                    const float v = __half2float(delta[i]);
+                    ss += v * v;
+                }
+                sub_scale = rsqrtf(blk_sum(ss, red) / static_cast<float>(n) + a.eps);
+            }
+            for (int i = tid; i < n; i += kThreads) {
+                float d = __half2float(delta[i]);
+                if (a.w_sub) d = __half2float(__float2half_rn(__fmul_rn(__fmul_rn(d, sub_scale), a.w_sub[i])));
+                const __half r = __float2half_rn(d + __half2float(x_in[i]));
+                hbuf[i] = r;
+                if (publisher) x_out[i] = r;
+                const float v = __half2float(r);
+                s += v * v;
+            }
+        } else {
+            for (int i = tid; i < n; i += kThreads) {
+                const __half r = x_in[i];
+                hbuf[i] = r;
+                if (publisher && x_out != x_in) x_out[i] = r;
+                const float v = __half2float(r);
+                s += v * v;
+            }
+        }
+        // 2. xn = half(x_new * rsqrt(mean + eps) * w); absmax over the rounded values
+        const float scale = rsqrtf(blk_sum(s, red) / static_cast<float>(n) + a.eps);
+        float mx = 0.0f;
+        for (int i = tid; i < n; i += kThreads) {
+            const __half h = __float2half_rn(__fmul_rn(__fmul_rn(__half2float(hbuf[i]), scale), a.w_norm[i]));
+            hbuf[i] = h;
+            mx = fmaxf(mx, fabsf(__half2float(h)));
+        }
+        const float absmax = blk_max(mx, red);
+        const float qs = quant_scale(absmax);
+        for (int i = tid; i < n; i += kThreads)
+            *xs_byte(xs, i) = static_cast<int8_t>(quantize_one(__half2float(hbuf[i]), qs));
+        return absmax;
+    }
+    // IN_RELU2
+    {
+        const __half* gate = static_cast<const __half*>(a.x);
+        const __half* up = static_cast<const __half*>(a.x2);
+        float scale = 1.0f;
+        if (a.w_sub) {
+            float s = 0.0f;
+            for (int i = tid; i < n; i += kThreads) {
+                const float r = fmaxf(0.0f, __half2float(gate[i]));
+                const float v = __fmul_rn(__fmul_rn(r, r), __half2float(up[i]));
+                s += v * v;
+            }
+            scale = rsqrtf(blk_sum(s, red) / static_cast<float>(n) + a.eps);
+        }
+        float mx = 0.0f;
+        for (int i = tid; i < n; i += kThreads) {
+            const float r = fmaxf(0.0f, __half2float(gate[i]));
+            const float v = __fmul_rn(__fmul_rn(r, r), __half2float(up[i]));
+            const __half h = a.w_sub ? __float2half_rn(__fmul_rn(__fmul_rn(v, scale), a.w_sub[i])) : __float2half_rn(v);
+            hbuf[i] = h;
+            mx = fmaxf(mx, fabsf(__half2float(h)));
+        }
+        const float absmax = blk_max(mx, red);
+        const float qs = quant_scale(absmax);
+        for (int i = tid; i < n; i += kThreads)
+            *xs_byte(xs, i) = static_cast<int8_t>(quantize_one(__half2float(hbuf[i]), qs));
+        return absmax;
+    }
+}
+
+// Fills xs (swizzled int8) and returns the absmax that belongs to it.  hbuf: cols halfs of
+// scratch (only touched by the normalising producers).
 template <int IN, int OUT>
-__global__ void __launch_bounds__(kThreads, 4) gemv_pairs_kernel(const GemvArgs a) {
+__device__ __forceinline__ float produce_x(const GemvArgs& a, uint4* xs, __half* hbuf, float* red,
+                                           bool publisher) {
+    const int tid = threadIdx.x;
+    const int n = a.cols, nchunks = n >> 4;
+    if (IN == IN_I8) {
+        const uint4* xg = static_cast<const uint4*>(a.x);
+        for (int q = tid; q < nchunks; q += kThreads) {
+            const int c = q >> 3, i = q & 7;
+            xs[(c << 3) + (i ^ (c & 7))] = xg[q];
+        }
+        return (OUT != OUT_I32) ? *a.d_absmax : 0.0f;
+    }
+    if (IN == IN_F16 || IN == IN_F16_AMAX) {
+        const uint4* xg = static_cast<const uint4*>(a.x);
+        float absmax;
+        if (IN == IN_F16) {
+            absmax = *a.d_absmax;
+        } else {
+            float mx = 0.0f;
+            for (int q = tid; q < 2 * nchunks; q += kThreads) {
+                const uint4 t = xg[q];
+                const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const __half2 h2 = *reinterpret_cast<const __half2*>(&w[k]);
+                    mx = fmaxf(mx, fmaxf(fabsf(__low2float(h2)), fabsf(__high2float(h2))));
+                }
+            }
+            absmax = blk_max(mx, red);
+        }
+        const float scale = quant_scale(absmax);
+        for (int q = tid; q < nchunks; q += kThreads) {
+            const uint4 lo = xg[2 * q], hi = xg[2 * q + 1];
+            const uint32_t hw[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+            uint32_t out[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                uint32_t packed = 0;
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const __half2 h2 = *reinterpret_cast<const __half2*>(&hw[2 * k + e]);
+                    const int q0 = quantize_one(__low2float(h2), scale);
+                    const int q1 = quantize_one(__high2float(h2), scale);
+                    packed |= (static_cast<uint32_t>(q0) & 0xFFu) << (16 * e);
+                    packed |= (static_cast<uint32_t>(q1) & 0xFFu) << (16 * e + 8);
+                }
+                out[k] = packed;
+            }
+            const int c = q >> 3, i = q & 7;
+            xs[(c << 3) + (i ^ (c & 7))] = make_uint4(out[0], out[1], out[2], out[3]);
+        }
+        return absmax;
+    }
+    // The normalising producers.  A thread owns up to kOwn chunks of 8 consecutive elements
+    // (chunk q = tid + k*256); all global loads of a pass are issued before any is consumed, and
+    // the values a later pass needs stay in registers as packed halves.  Vectors longer than
+    // kOwn*8*256 elements take the strided-loop form below.
+    constexpr int kOwn = 4;
+    const int nq = n >> 3;  // n is a multiple of 128
+    if (nq <= kOwn * kThreads) {
+        auto h2f2 = [](uint32_t w, float& lo, float& hi) {
+            const __half2 h2 = *reinterpret_cast<const __half2*>(&w);
+            lo = __low2float(h2);
+            hi = __high2float(h2);
+        };
+        auto pack2 = [](__half lo, __half hi) {
+            const __half2 h2 = __halves2half2(lo, hi);
+            return *reinterpret_cast<const uint32_t*>(&h2);
+        };
+        uint32_t hv[kOwn][4];  // the thread's elements as packed halves (x_new, then xn / h)
+        float absmax;
+        if (IN == IN_RESNORM) {
+            const uint4* x_in = static_cast<const uint4*>(a.x);
+            const uint4* delta = static_cast<const uint4*>(a.x2);
+            uint4* x_out = static_cast<uint4*>(a.x_out);
+            uint4 xv[kOwn], dv[kOwn];
+#pragma unroll
+            for (int k = 0; k < kOwn; ++k) {
+                const int q = tid + k * kThreads;
+                xv[k] = make_uint4(0, 0, 0, 0);
+                dv[k] = make_uint4(0, 0, 0, 0);
+                if (q < nq) {
+                    xv[k] = x_in[q];
+                    if (delta) dv[k] = delta[q];
+                }
+            }
+            float sub_scale = 1.0f;
+            if (delta && a.w_sub) {
+                float ss = 0.0f;
+#pragma unroll
+                for (int k = 0; k < kOwn; ++k) {
+                    const uint32_t w[4] = {dv[k].x, dv[k].y, dv[k].z, dv[k].w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        float lo, hi;
+                        h2f2(w[e], lo, hi);
+                        ss += lo * lo;
+                        ss += hi * hi;
+                    }
+                }
+                sub_scale = rsqrtf(blk_sum(ss, red) / static_cast<float>(n) + a.eps);
+            }
+            float s = 0.0f;
+#pragma unroll
+            for (int k = 0; k < kOwn; ++k) {
+                const int q = tid + k * kThreads;
+                const uint32_t xw[4] = {xv[k].x, xv[k].y, xv[k].z, xv[k].w};
+                const uint32_t dw[4] = {dv[k].x, dv[k].y, dv[k].z, dv[k].w};
+                float ws[8];
+                if (delta && a.w_sub && q < nq) {
+                    const float4 w0 = __ldg(reinterpret_cast<const float4*>(a.w_sub) + 2 * q);
+                    const float4 w1 = __ldg(reinterpret_cast<const float4*>(a.w_sub) + 2 * q + 1);
+                    ws[0] = w0.x; ws[1] = w0.y; ws[2] = w0.z; ws[3] = w0.w;
+                    ws[4] = w1.x; ws[5] = w1.y; ws[6] = w1.z; ws[7] = w1.w;
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) ws[e] = 1.0f;
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float x0, x1, d0, d1;
+                    h2f2(xw[e], x0, x1);
+                    h2f2(dw[e], d0, d1);
+                    __half r0, r1;
+                    if (delta) {
+                        if (a.w_sub) {
+                            d0 = __half2float(__float2half_rn(__fmul_rn(__fmul_rn(d0, sub_scale), ws[2 * e])));
+                            d1 = __half2float(__float2half_rn(__fmul_rn(__fmul_rn(d1, sub_scale), ws[2 * e + 1])));
+                        }
+                        r0 = __float2half_rn(d0 + x0);
+                        r1 = __float2half_rn(d1 + x1);
+                    } else {
+                        r0 = __float2half_rn(x0);
+                        r1 = __float2half_rn(x1);
+                    }
+                    hv[k][e] = pack2(r0, r1);
+                    const float f0 = __half2float(r0), f1 = __half2float(r1);
+                    s += f0 * f0;
+                    s += f1 * f1;
+                }
+                if (publisher && q < nq && (delta || x_out != static_cast<void*>(const_cast<uint4*>(x_in))))
+                    x_out[q] = make_uint4(hv[k][0], hv[k][1], hv[k][2], hv[k][3]);
+            }
+            const float scale = rsqrtf(blk_sum(s, red) / static_cast<float>(n) + a.eps);
+            float mx = 0.0f;
+#pragma unroll
+            for (int k = 0; k < kOwn; ++k) {
+                const int q = tid + k * kThreads;
+                float wn[8];
+                if (q < nq) {
+                    const float4 w0 = __ldg(reinterpret_cast<const float4*>(a.w_norm) + 2 * q);
+                    const float4 w1 = __ldg(reinterpret_cast<const float4*>(a.w_norm) + 2 * q + 1);
+                    wn[0] = w0.x; wn[1] = w0.y; wn[2] = w0.z; wn[3] = w0.w;
+                    wn[4] = w1.x; wn[5] = w1.y; wn[6] = w1.z; wn[7] = w1.w;
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) wn[e] = 0.0f;
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float f0, f1;
+                    h2f2(hv[k][e], f0, f1);
+                    const __half h0 = __float2half_rn(__fmul_rn(__fmul_rn(f0, scale), wn[2 * e]));
+                    const __half h1 = __float2half_rn(__fmul_rn(__fmul_rn(f1, scale), wn[2 * e + 1]));
+                    hv[k][e] = pack2(h0, h1);
+                    mx = fmaxf(mx, fmaxf(fabsf(__half2float(h0)), fabsf(__half2float(h1))));
+                }
+            }
+            absmax = blk_max(mx, red);
+        } else {  // IN_RELU2
+            const uint4* gate = static_cast<const uint4*>(a.x);
+            const uint4* up = static_cast<const uint4*>(a.x2);
+            uint4 gv[kOwn], uv[kOwn];
+#pragma unroll
+            for (int k = 0; k < kOwn; ++k) {
+                const int q = tid + k * kThreads;
+                gv[k] = make_uint4(0, 0, 0, 0);
+                uv[k] = make_uint4(0, 0, 0, 0);
+                if (q < nq) {
+                    gv[k] = gate[q];
+                    uv[k] = up[q];
+                }
+            }
+            auto relu2 = [](float gq, float uq) {
+                const float r = fmaxf(0.0f, gq);
+                return __fmul_rn(__fmul_rn(r, r), uq);
+            };
+            float scale = 1.0f;
+            if (a.w_sub) {
+                float s = 0.0f;
+#pragma unroll
+                for (int k = 0; k < kOwn; ++k) {
+                    const uint32_t gw[4] = {gv[k].x, gv[k].y, gv[k].z, gv[k].w};
+                    const uint32_t uw[4] = {uv[k].x, uv[k].y, uv[k].z, uv[k].w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        float g0, g1, u0, u1;
+                        h2f2(gw[e], g0, g1);
+                        h2f2(uw[e], u0, u1);
+                        const float m0 = relu2(g0, u0), m1 = relu2(g1, u1);
+                        s += m0 * m0;
+                        s += m1 * m1;
+                    }
+                }
+                scale = rsqrtf(blk_sum(s, red) / static_cast<float>(n) + a.eps);
+            }
+            float mx = 0.0f;
+#pragma unroll
+            for (int k = 0; k < kOwn; ++k) {
+                const int q = tid + k * kThreads;
+                const uint32_t gw[4] = {gv[k].x, gv[k].y, gv[k].z, gv[k].w};
+                const uint32_t uw[4] = {uv[k].x, uv[k].y, uv[k].z, uv[k].w};
+                float ws[8];
+                if (a.w_sub && q < nq) {
+                    const float4 w0 = __ldg(reinterpret_cast<const float4*>(a.w_sub) + 2 * q);
+                    const float4 w1 = __ldg(reinterpret_cast<const float4*>(a.w_sub) + 2 * q + 1);
+                    ws[0] = w0.x; ws[1] = w0.y; ws[2] = w0.z; ws[3] = w0.w;
+                    ws[4] = w1.x; ws[5] = w1.y; ws[6] = w1.z; ws[7] = w1.w;
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) ws[e] = 0.0f;
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float g0, g1, u0, u1;
+                    h2f2(gw[e], g0, g1);
+                    h2f2(uw[e], u0, u1);
+                    const float m0 = relu2(g0, u0), m1 = relu2(g1, u1);
+                    const __half h0 = a.w_sub ? __float2half_rn(__fmul_rn(__fmul_rn(m0, scale), ws[2 * e])) : __float2half_rn(m0);
+                    const __half h1 = a.w_sub ? __float2half_rn(__fmul_rn(__fmul_rn(m1, scale), ws[2 * e + 1])) : __float2half_rn(m1);
+                    hv[k][e] = pack2(h0, h1);
+                    if (q < nq) mx = fmaxf(mx, fmaxf(fabsf(__half2float(h0)), fabsf(__half2float(h1))));
+                }
+            }
+            absmax = blk_max(mx, red);
+        }
+        const float qs = quant_scale(absmax);
+#pragma unroll
+        for (int k = 0; k < kOwn; ++k) {
+            const int q = tid + k * kThreads;
+            if (q < nq) {
+                uint32_t o[2] = {0, 0};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float f0, f1;
+                    h2f2(hv[k][e], f0, f1);
+                    const uint32_t b0 = static_cast<uint32_t>(quantize_one(f0, qs)) & 0xFFu;
+                    const uint32_t b1 = static_cast<uint32_t>(quantize_one(f1, qs)) & 0xFFu;
+                    o[e >> 1] |= (b0 | (b1 << 8)) << (16 * (e & 1));
+                }
+                // elements 8q..8q+7 are half of the 16-byte chunk q>>1 of the swizzled x array
+                const int q16 = q >> 1, c = q16 >> 3, i = q16 & 7;
+                uint2* dst = reinterpret_cast<uint2*>(xs + ((c << 3) + (i ^ (c & 7)))) + (q & 1);
+                *dst = make_uint2(o[0], o[1]);
+            }
+        }
+        return absmax;
+    }
+    return produce_x_loops<IN>(a, xs, hbuf, red, publisher);
+}
+
+template <int IN, int OUT>
+__global__ void __launch_bounds__(kThreads, (IN >= IN_RESNORM) ? 2 : 4) gemv_pairs_kernel(const GemvArgs a) {
     extern __shared__ __align__(128) uint8_t psmem[];
-    // [sel 15360][sgn 2048][partials upr*pitch ints (16-aligned)][x cols bytes]
+    // [sel 15360][sgn 2048][red 64 floats][partials upr*pitch ints (16-aligned)][x cols bytes]
+    // [half scratch 2*cols bytes, only for the producers that normalise]
     const uint32_t win_s = smem_u32(psmem);
     uint8_t* win = psmem;
     const int pitch = a.rpc | 1;
-    int* partial = reinterpret_cast<int*>(win + kSelBytes + kSgnBytes);
-    uint4* xs = reinterpret_cast<uint4*>(win + kSelBytes + kSgnBytes + ((a.upr * pitch * 4 + 15) & ~15));
+    float* red = reinterpret_cast<float*>(win + kSelBytes + kSgnBytes);
+    int* partial = reinterpret_cast<int*>(win + kSelBytes + kSgnBytes + 256);
+    uint4* xs = reinterpret_cast<uint4*>(win + kSelBytes + kSgnBytes + 256 + ((a.upr * pitch * 4 + 15) & ~15));
 
     const int tid = threadIdx.x, lane = tid & 31;
     int mi = 0;
@@ -273,107 +669,71 @@ __global__ void __launch_bounds__(kThreads, 4) gemv_pairs_kernel(const GemvArgs 
 
     grid_dep_launch();
 
-    // ---- phase A: weights, tables, expansion to selectors and signs ---------------------------
-    const bool valid = tid < nunits;
-    int rl = 0, cb = 0;
+    // ---- phase A: weights of the first pass, tables, expansion to selectors and signs ---------
+    const int npass = (nunits + kThreads - 1) / kThreads;
     uint4 m = make_uint4(0, 0, 0, 0);
     uint2 v = make_uint2(0, 0);
-    if (valid) {
-        rl = tid / a.upr;
-        cb = tid - rl * a.upr;
-        const size_t row = static_cast<size_t>(r_lo + rl);
-        m = ld_stream_v4(M.meta + row * M.meta_stride + cb * 4);
-        v = ld_stream_v2(M.values + row * M.values_stride + cb * 2);
-    }
+    auto load_unit = [&](int u, uint4& mm, uint2& vv) {
+        if (u < nunits) {
+            const int r = u / a.upr, c = u - r * a.upr;
+            const size_t row = static_cast<size_t>(r_lo + r);
+            mm = ld_stream_v4(M.meta + row * M.meta_stride + c * 4);
+            vv = ld_stream_v2(M.values + row * M.values_stride + c * 2);
+        }
+    };
+    load_unit(tid, m, v);
     {
         const uint4* src = reinterpret_cast<const uint4*>(&g_pair_lut);
         uint4* dst = reinterpret_cast<uint4*>(win);
         for (int q = tid; q < (kSelBytes + kSgnBytes) / 16; q += kThreads) dst[q] = __ldg(src + q);
     }
-
-    // ---- phase B starts: only now may a predecessor's output be read.  The first two x chunks
-    // of every thread are requested here, so that their latency overlaps the expansion below
-    // (and, when no predecessor is pending, the weight loads above).
-    grid_dep_wait();
-    const int nchunks = a.cols >> 4;
-    float absmax = 0.0f;
-    if (IN == IN_F16 || OUT != OUT_I32) absmax = *a.d_absmax;
-    const float qscale = quant_scale(absmax);
-    auto load_chunk = [&](int q, uint4& lo, uint4& hi) {
-        const uint4* xg = static_cast<const uint4*>(a.x);
-        if (IN == IN_I8) {
-            lo = xg[q];
-        } else {
-            lo = xg[2 * q];
-            hi = xg[2 * q + 1];
-        }
-    };
-    auto store_chunk = [&](int q, const uint4& lo, const uint4& hi) {
-        uint4 out = lo;
-        if (IN == IN_F16) {
-            const uint32_t hw[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-            uint32_t o[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                uint32_t packed = 0;
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const __half2 h2 = *reinterpret_cast<const __half2*>(&hw[2 * k + e]);
-                    const int q0 = quantize_one(__low2float(h2), qscale);
-                    const int q1 = quantize_one(__high2float(h2), qscale);
-                    packed |= (static_cast<uint32_t>(q0) & 0xFFu) << (16 * e);
-                    packed |= (static_cast<uint32_t>(q1) & 0xFFu) << (16 * e + 8);
-                }
-                o[k] = packed;
-            }
-            out = make_uint4(o[0], o[1], o[2], o[3]);
-        }
-        const int c = q >> 3, i = q & 7;
-        xs[(c << 3) + (i ^ (c & 7))] = out;
-    };
-    uint4 xa_lo = make_uint4(0, 0, 0, 0), xa_hi = xa_lo, xb_lo = xa_lo, xb_hi = xa_lo;
-    if (tid < nchunks) load_chunk(tid, xa_lo, xa_hi);
-    if (tid + kThreads < nchunks) load_chunk(tid + kThreads, xb_lo, xb_hi);
-
     __syncthreads();  // tables complete
 
+    // produced by a volatile statement after the barrier, so that no table load can be
+    // scheduled above it
+    uint32_t sel_lane;
+    asm volatile("add.u32 %0, %1, %2;" : "=r"(sel_lane) : "r"(win_s), "r"(lane * 4) : "memory");
+    const uint32_t sgn_lane = sel_lane + kSelBytes;
     uint32_t sel[16], sgn[16];
-    {
-        // produced by a volatile statement after the barrier, so that no table load can be
-        // scheduled above it
-        uint32_t sel_lane;
-        asm volatile("add.u32 %0, %1, %2;" : "=r"(sel_lane) : "r"(win_s), "r"(lane * 4) : "memory");
-        const uint32_t sgn_lane = sel_lane + kSelBytes;
-        const uint32_t mw[4] = {m.x, m.y, m.z, m.w};
-        const uint32_t vw[2] = {v.x, v.y};
+    auto expand = [&](const uint4& mm, const uint2& vv) {
+        const uint32_t mw[4] = {mm.x, mm.y, mm.z, mm.w};
+        const uint32_t vw[2] = {vv.x, vv.y};
 #pragma unroll
         for (int p = 0; p < 16; ++p) {  // groups 2p and 2p+1: meta byte p, sign nibble p
             const int ms = 8 * (p & 3) - 7, ss = 4 * (p & 7) - 7;
             sel[p] = lds32(((ms >= 0 ? (mw[p >> 2] >> ms) : (mw[p >> 2] << -ms)) & (0x77u << 7)) + sel_lane);
             sgn[p] = lds32(((ss >= 0 ? (vw[p >> 3] >> ss) : (vw[p >> 3] << -ss)) & (0xFu << 7)) + sgn_lane);
         }
-    }
+    };
+    expand(m, v);
 
-    if (tid < nchunks) store_chunk(tid, xa_lo, xa_hi);
-    if (tid + kThreads < nchunks) store_chunk(tid + kThreads, xb_lo, xb_hi);
-    for (int q = tid + 2 * kThreads; q < nchunks; q += kThreads) {  // wide matrices
-        uint4 lo, hi = make_uint4(0, 0, 0, 0);
-        load_chunk(q, lo, hi);
-        store_chunk(q, lo, hi);
-    }
+    // ---- phase B: activations (only now may a predecessor's output be read) ------------------
+    grid_dep_wait();
+    const float absmax = produce_x<IN, OUT>(a, xs, reinterpret_cast<__half*>(xs) + (a.cols >> 1), red,
+                                             blockIdx.x == 0);
     __syncthreads();
 
-    if (valid) {
-        const uint4* xb = xs + (cb << 3);
-        const int sw = cb & 7;
-        int acc = 0;
+    for (int pass = 0; pass < npass; ++pass) {
+        const int u = pass * kThreads + tid;
+        uint4 mn = make_uint4(0, 0, 0, 0);
+        uint2 vn = make_uint2(0, 0);
+        if (pass + 1 < npass) load_unit(u + kThreads, mn, vn);  // next pass's weights in flight
+        if (pass > 0) expand(m, v);
+        if (u < nunits) {
+            const int rl = u / a.upr, cb = u - rl * a.upr;
+            const uint4* xb = xs + (cb << 3);
+            const int sw = cb & 7;
+            int acc = 0;
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {  // 16 columns = 4 groups = 2 pairs per chunk
-            const uint4 xv = xb[ch ^ sw];
-            acc = __dp4a(static_cast<int>(__byte_perm(xv.x, xv.y, sel[2 * ch])), static_cast<int>(sgn[2 * ch]), acc);
-            acc = __dp4a(static_cast<int>(__byte_perm(xv.z, xv.w, sel[2 * ch + 1])), static_cast<int>(sgn[2 * ch + 1]), acc);
+            for (int ch = 0; ch < 8; ++ch) {  // 16 columns = 4 groups = 2 pairs per chunk
+                const uint4 xv = xb[ch ^ sw];
+                acc = __dp4a(static_cast<int>(__byte_perm(xv.x, xv.y, sel[2 * ch])), static_cast<int>(sgn[2 * ch]), acc);
+                acc = __dp4a(static_cast<int>(__byte_perm(xv.z, xv.w, sel[2 * ch + 1])), static_cast<int>(sgn[2 * ch + 1]), acc);
+            }
+            partial[cb * pitch + rl] = acc;
         }
-        partial[cb * pitch + rl] = acc;
+        m = mn;
+        v = vn;
     }
     __syncthreads();
 
@@ -457,10 +817,20 @@ struct MatDesc {
 
 static int g_gemv_variant = 0;  // 0/1 pair kernel (default), 2 per-group table kernel
 
-// Launches up to kMaxMats matrices that share x (and d_absmax) as one grid.
+// Where the activation vector of a launch comes from (see the IN_* producers).
+struct XDesc {
+    const void* x = nullptr;
+    const void* x2 = nullptr;
+    const float* w_sub = nullptr;
+    const float* w_norm = nullptr;
+    void* x_out = nullptr;
+    float eps = 0.0f;
+    const float* d_absmax = nullptr;
+};
+
+// Launches up to kMaxMats matrices that share the activation vector as one grid.
 template <int IN, int OUT>
-static int run_gemv(const char* name, const MatDesc* mats, int nmat, const void* x, const float* d_absmax,
-                    int cols, void* stream) {
+static int run_gemv(const char* name, const MatDesc* mats, int nmat, const XDesc& xd, int cols, void* stream) {
     if (nmat < 1 || nmat > kMaxMats) return fail(SPB_E_INVALID, "%s: %d matrices in one launch", name, nmat);
     if (cols < 0) return fail(SPB_E_INVALID, "%s: negative size", name);
     int total_rows = 0;
@@ -470,10 +840,12 @@ static int run_gemv(const char* name, const MatDesc* mats, int nmat, const void*
     }
     if (total_rows == 0 || cols == 0) return SPB_OK;
     if (cols % 4 != 0) return fail(SPB_E_INVALID, "%s: cols=%d is not a multiple of 4", name, cols);
-    if (!x) return fail(SPB_E_INVALID, "%s: null pointer", name);
-    if ((IN == IN_F16 || OUT != OUT_I32) && !d_absmax) return fail(SPB_E_INVALID, "%s: d_absmax is null", name);
-    bool fast = cols % 128 == 0 && cols / 128 <= kThreads && aligned(x, 16) && cols <= 196608;
-    int max_rows = 0;
+    if (!xd.x) return fail(SPB_E_INVALID, "%s: null pointer", name);
+    if ((IN == IN_F16 || (IN == IN_I8 && OUT != OUT_I32)) && !xd.d_absmax)
+        return fail(SPB_E_INVALID, "%s: d_absmax is null", name);
+    if (IN == IN_RESNORM && (!xd.w_norm || !xd.x_out)) return fail(SPB_E_INVALID, "%s: null pointer", name);
+    if (IN == IN_RELU2 && !xd.x2) return fail(SPB_E_INVALID, "%s: null pointer", name);
+    bool fast = cols % 128 == 0 && cols / 128 <= kThreads && aligned(xd.x, 16) && cols <= 65536;
     for (int i = 0; i < nmat; ++i) {
         const MatDesc& m = mats[i];
         if (m.rows == 0) continue;
@@ -482,13 +854,19 @@ static int run_gemv(const char* name, const MatDesc* mats, int nmat, const void*
             return fail(SPB_E_INVALID, "%s: row stride shorter than a row", name);
         fast = fast && m.meta_stride % 4 == 0 && m.values_stride % 2 == 0 && aligned(m.meta, 16) &&
                aligned(m.values, 8);
-        max_rows = max(max_rows, m.rows);
     }
+    if (!fast && IN >= IN_F16_AMAX)
+        return fail(SPB_E_UNSUPPORTED, "%s: this layout has no fused-producer kernel (cols %% 128, strides, alignment)", name);
 
     GemvArgs a{};
     a.nmat = nmat;
-    a.x = x;
-    a.d_absmax = d_absmax;
+    a.x = xd.x;
+    a.x2 = xd.x2;
+    a.w_sub = xd.w_sub;
+    a.w_norm = xd.w_norm;
+    a.x_out = xd.x_out;
+    a.eps = xd.eps;
+    a.d_absmax = xd.d_absmax;
     a.cols = cols;
     const int sms = sm_count();
     int rpc = 8;  // generic path: a warp per row, 8 rows per block
@@ -497,6 +875,13 @@ static int run_gemv(const char* name, const MatDesc* mats, int nmat, const void*
         const int fill = max(1, kThreads / a.upr);       // rows that fill the block
         const int spread = (total_rows + sms - 1) / sms;  // rows per block at one block per SM
         rpc = max(1, min(fill, spread));
+        if (IN >= IN_F16_AMAX) {
+            // every block recomputes the activation vector: use about two fat blocks per SM, each
+            // making several passes over its rows, instead of many thin ones
+            const int want = (total_rows + 2 * sms - 1) / (2 * sms);
+            const int cap = max(fill, (32 * 1024 / 4) / a.upr);
+            rpc = max(rpc, min(cap, (want + fill - 1) / fill * fill));
+        }
     }
     a.rpc = rpc;
     int blocks = 0;
@@ -505,26 +890,78 @@ static int run_gemv(const char* name, const MatDesc* mats, int nmat, const void*
         a.mat[i] = GemvMat{m.meta, m.values, m.y, m.y_acc, m.gamma, m.rows, m.meta_stride, m.values_stride, blocks};
         blocks += (m.rows + rpc - 1) / rpc;
     }
-    if (!fast) return launch(name, gemv_generic_kernel<IN, OUT>, dim3(blocks), dim3(kThreads), 0, stream, a);
     int rc;
-    if (g_gemv_variant == 2) {  // the per-group table kernel, kept for comparison
-        const size_t smem = kLutBytes + ((rpc * 4 + 15) & ~15) + static_cast<size_t>(cols);
-        if ((rc = ensure_smem(gemv_units_kernel<IN, OUT>, smem))) return rc;
-        return launch(name, gemv_units_kernel<IN, OUT>, dim3(blocks), dim3(kThreads), smem, stream, a);
+    if constexpr (IN <= IN_F16) {
+        if (!fast) return launch(name, gemv_generic_kernel<IN, OUT>, dim3(blocks), dim3(kThreads), 0, stream, a);
+        if (g_gemv_variant == 2) {  // the per-group table kernel, kept for comparison
+            const size_t smem = kLutBytes + ((rpc * 4 + 15) & ~15) + static_cast<size_t>(cols);
+            if ((rc = ensure_smem(gemv_units_kernel<IN, OUT>, smem))) return rc;
+            return launch(name, gemv_units_kernel<IN, OUT>, dim3(blocks), dim3(kThreads), smem, stream, a);
+        }
     }
-    const size_t smem = kSelBytes + kSgnBytes + ((a.upr * (rpc | 1) * 4 + 15) & ~15) + static_cast<size_t>(cols);
+    const size_t smem = kSelBytes + kSgnBytes + 256 + ((a.upr * (rpc | 1) * 4 + 15) & ~15) +
+                        static_cast<size_t>(cols) * (IN >= IN_RESNORM ? 3 : 1);
     if ((rc = ensure_smem(gemv_pairs_kernel<IN, OUT>, smem))) return rc;
     return launch(name, gemv_pairs_kernel<IN, OUT>, dim3(blocks), dim3(kThreads), smem, stream, a);
 }
 
-// Engine-internal: several BitLinear layers on the same pre-quantised activation in one launch.
-int bitlinear_q8_group(const uint32_t* const* meta, const uint32_t* const* values, void* const* out,
-                       const float* gamma, const int* rows, const int* ms, const int* vs, int nmat,
-                       const int8_t* xq, const float* d_absmax, int cols, void* stream) {
+static int fill_mats(MatDesc* d, const BitLinearGroup& g) {
+    if (g.nmat < 1 || g.nmat > kMaxMats) return fail(SPB_E_INVALID, "bitlinear group: %d matrices", g.nmat);
+    for (int i = 0; i < g.nmat; ++i)
+        d[i] = MatDesc{g.meta[i], g.values[i], g.out[i], nullptr, g.gamma[i], g.rows[i], g.ms[i], g.vs[i]};
+    return SPB_OK;
+}
+
+// Engine-internal launchers: several BitLinear layers on one activation vector in one launch.
+int bitlinear_q8_group(const BitLinearGroup& g, const int8_t* xq, const float* d_absmax, void* stream) {
     MatDesc d[kMaxMats];
-    if (nmat > kMaxMats) return fail(SPB_E_INVALID, "bitlinear_q8_group: too many matrices");
-    for (int i = 0; i < nmat; ++i) d[i] = MatDesc{meta[i], values[i], out[i], nullptr, gamma[i], rows[i], ms[i], vs[i]};
-    return run_gemv<IN_I8, OUT_F16>("bitlinear_q8_group", d, nmat, xq, d_absmax, cols, stream);
+    if (int rc = fill_mats(d, g)) return rc;
+    XDesc xd;
+    xd.x = xq;
+    xd.d_absmax = d_absmax;
+    return run_gemv<IN_I8, OUT_F16>("bitlinear_q8_group", d, g.nmat, xd, g.cols, stream);
+}
+
+int bitlinear_amax_group(const BitLinearGroup& g, const void* x_half, void* stream) {
+    MatDesc d[kMaxMats];
+    if (int rc = fill_mats(d, g)) return rc;
+    XDesc xd;
+    xd.x = x_half;
+    return run_gemv<IN_F16_AMAX, OUT_F16>("bitlinear_amax_group", d, g.nmat, xd, g.cols, stream);
+}
+
+int bitlinear_resnorm_group(const BitLinearGroup& g, const void* x_in, const void* delta, const float* w_sub,
+                            const float* w_norm, void* x_out, float eps, void* stream) {
+    MatDesc d[kMaxMats];
+    if (int rc = fill_mats(d, g)) return rc;
+    XDesc xd;
+    xd.x = x_in;
+    xd.x2 = delta;
+    xd.w_sub = w_sub;
+    xd.w_norm = w_norm;
+    xd.x_out = x_out;
+    xd.eps = eps;
+    return run_gemv<IN_RESNORM, OUT_F16>("bitlinear_resnorm_group", d, g.nmat, xd, g.cols, stream);
+}
+
+int bitlinear_relu2_group(const BitLinearGroup& g, const void* gate, const void* up, const float* w_sub, float eps,
+                          void* stream) {
+    MatDesc d[kMaxMats];
+    if (int rc = fill_mats(d, g)) return rc;
+    XDesc xd;
+    xd.x = gate;
+    xd.x2 = up;
+    xd.w_sub = w_sub;
+    xd.eps = eps;
+    return run_gemv<IN_RELU2, OUT_F16>("bitlinear_relu2_group", d, g.nmat, xd, g.cols, stream);
+}
+
+// True when a BitLinear group can take the fused-producer kernels.
+bool bitlinear_group_is_fast(const BitLinearGroup& g) {
+    if (g.cols % 128 != 0 || g.cols / 128 > kThreads || g.cols > 65536) return false;
+    for (int i = 0; i < g.nmat; ++i)
+        if (g.ms[i] % 4 || g.vs[i] % 2 || !aligned(g.meta[i], 16) || !aligned(g.values[i], 8)) return false;
+    return true;
 }
 
 }  // namespace spb
@@ -541,7 +978,9 @@ extern "C" int spb_sparse_ternary_gemv(const uint32_t* meta, const uint32_t* val
                                        int32_t* y, int rows, int cols, int meta_row_stride,
                                        int values_row_stride, void* stream) {
     MatDesc d{meta, values, y, nullptr, 0.0f, rows, meta_row_stride, values_row_stride};
-    return run_gemv<IN_I8, OUT_I32>("spb_sparse_ternary_gemv", &d, 1, x, nullptr, cols, stream);
+    XDesc xd;
+    xd.x = x;
+    return run_gemv<IN_I8, OUT_I32>("spb_sparse_ternary_gemv", &d, 1, xd, cols, stream);
 }
 
 extern "C" int spb_sparse_ternary_gemv_scaled(const uint32_t* meta, const uint32_t* values,
@@ -549,7 +988,10 @@ extern "C" int spb_sparse_ternary_gemv_scaled(const uint32_t* meta, const uint32
                                               const float* d_absmax, float gamma, int rows, int cols,
                                               int meta_row_stride, int values_row_stride, void* stream) {
     MatDesc d{meta, values, y, y_acc, gamma, rows, meta_row_stride, values_row_stride};
-    return run_gemv<IN_I8, OUT_F32>("spb_sparse_ternary_gemv_scaled", &d, 1, x, d_absmax, cols, stream);
+    XDesc xd;
+    xd.x = x;
+    xd.d_absmax = d_absmax;
+    return run_gemv<IN_I8, OUT_F32>("spb_sparse_ternary_gemv_scaled", &d, 1, xd, cols, stream);
 }
 
 extern "C" int spb_fused_sparse_bitlinear(const uint32_t* meta, const uint32_t* values, const void* x,
@@ -557,7 +999,10 @@ extern "C" int spb_fused_sparse_bitlinear(const uint32_t* meta, const uint32_t* 
                                           int cols, int meta_row_stride, int values_row_stride,
                                           void* stream) {
     MatDesc d{meta, values, output, nullptr, gamma, rows, meta_row_stride, values_row_stride};
-    return run_gemv<IN_F16, OUT_F16>("spb_fused_sparse_bitlinear", &d, 1, x, d_absmax, cols, stream);
+    XDesc xd;
+    xd.x = x;
+    xd.d_absmax = d_absmax;
+    return run_gemv<IN_F16, OUT_F16>("spb_fused_sparse_bitlinear", &d, 1, xd, cols, stream);
 }
 
 extern "C" int spb_sparse_bitlinear_q8(const uint32_t* meta, const uint32_t* values, const int8_t* xq,
@@ -565,5 +1010,8 @@ extern "C" int spb_sparse_bitlinear_q8(const uint32_t* meta, const uint32_t* val
                                        int cols, int meta_row_stride, int values_row_stride,
                                        void* stream) {
     MatDesc d{meta, values, output, nullptr, gamma, rows, meta_row_stride, values_row_stride};
-    return run_gemv<IN_I8, OUT_F16>("spb_sparse_bitlinear_q8", &d, 1, xq, d_absmax, cols, stream);
+    XDesc xd;
+    xd.x = xq;
+    xd.d_absmax = d_absmax;
+    return run_gemv<IN_I8, OUT_F16>("spb_sparse_bitlinear_q8", &d, 1, xd, cols, stream);
 }

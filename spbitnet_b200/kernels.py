@@ -147,6 +147,18 @@ def decode_attention_gpu(Q, K_cache, V_cache, output, num_heads, num_kv_heads, h
                                       head_dim, max_seq_len, seq_len, float(scale), _stream(stream)))
 
 
+def decode_attention_scratch_bytes(num_heads, head_dim, max_seq_len) -> int:
+    return int(load().spb_decode_attention_scratch_bytes(num_heads, head_dim, max_seq_len))
+
+
+def decode_attention_split_gpu(Q, K_cache, V_cache, output, num_heads, num_kv_heads, head_dim, max_seq_len, seq_len,
+                               scale, scratch, stream=None):
+    nbytes = scratch.numel() * scratch.element_size()
+    check(load().spb_decode_attention_split(_p(Q), _p(K_cache), _p(V_cache), _p(output), num_heads, num_kv_heads,
+                                            head_dim, max_seq_len, seq_len, float(scale), _p(scratch), nbytes,
+                                            _stream(stream)))
+
+
 def relu2_mul_gpu(gate, up, output, size, stream=None):
     check(load().spb_relu2_mul(_p(gate), _p(up), _p(output), size, _stream(stream)))
 

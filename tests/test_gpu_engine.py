@@ -68,3 +68,19 @@ def test_wide_model_few_layers():
         assert np.abs(lg - want_logits[step]).max() < 1e-2, step
         tok = int(np.argmax(lg))
         assert tok == int(want_tokens[step]), step
+
+
+def test_unfused_path_gives_the_same_tokens(monkeypatch):
+    # SPB_ENGINE_UNFUSED=1 runs the vector ops as their own launches; results must not change
+    model = synth.random_model(synth.TINY, seed=7)
+    prompt = np.array([1, 2, 3, 400], np.int32)
+    fused = InferenceEngine(DeviceModel(model))
+    a = fused.generate(prompt, 8)
+    la = fused.logits()
+    monkeypatch.setenv("SPB_ENGINE_UNFUSED", "1")
+    unfused = InferenceEngine(DeviceModel(model))
+    b = unfused.generate(prompt, 8)
+    lb = unfused.logits()
+    assert (a == b).all() and (la == lb).all()
+    want, _ = oracle.Engine(model).generate(prompt, 8)
+    assert (a == want).all()

@@ -117,7 +117,8 @@ def test_attention_known_answer():
 
 
 @pytest.mark.parametrize("nh,nkv,hd,mx,sl", [(4, 2, 64, 32, 19), (20, 5, 128, 4096, 384), (20, 5, 128, 640, 1),
-                                              (64, 8, 128, 1024, 577), (3, 3, 40, 16, 16)])
+                                              (64, 8, 128, 1024, 577), (3, 3, 40, 16, 16), (20, 5, 128, 4096, 4096),
+                                              (8, 2, 128, 300, 129), (6, 2, 256, 260, 257)])
 def test_attention_three_kernels_and_fused(nh, nkv, hd, mx, sl):
     Q, Kc, Vc = _attn_inputs(nh, nkv, hd, mx, sl, sl)
     scale = 1.0 / np.sqrt(hd)
@@ -135,6 +136,14 @@ def test_attention_three_kernels_and_fused(nh, nkv, hd, mx, sl):
     out2 = Guarded(nh * hd * 2)
     K.decode_attention_gpu(dev(Q), dev(Kc), dev(Vc), out2.ptr, nh, nkv, hd, mx, sl, scale)
     assert close(out2.read(np.float16), o_want)
+    # split-KV form with caller-provided scratch (poisoned: it must need no initialisation)
+    nbytes = K.decode_attention_scratch_bytes(nh, hd, mx)
+    scratch = torch.full((nbytes // 4 + 8,), float("nan"), dtype=torch.float32, device="cuda")
+    for _ in range(2):
+        out3 = Guarded(nh * hd * 2)
+        K.decode_attention_split_gpu(dev(Q), dev(Kc), dev(Vc), out3.ptr, nh, nkv, hd, mx, sl, scale, scratch[:nbytes // 4])
+        assert close(out3.read(np.float16), o_want)
+    assert torch.isnan(scratch[nbytes // 4:]).all()
 
 
 def test_elementwise_exact():

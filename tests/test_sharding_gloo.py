@@ -1,0 +1,74 @@
+"""Host logic of the row-sharded path on CPU: shard plan, slice contents, and the gather order
+over a world_size-2 (and 3) gloo group.  The per-rank arithmetic here is the oracle's; the GPU
+kernels are exercised by the -m gpu tests."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import oracle
+from spbitnet_b200 import sharding, synth
+
+
+def test_row_ranges_cover_and_keep_heads_whole():
+    for rows, world, mult in [(2560, 8, 128), (640, 2, 128), (640, 4, 128), (6912, 8, 1), (28672, 8, 1), (7, 3, 1)]:
+        spans = [sharding.row_range(rows, world, r, mult) for r in range(world)]
+        assert spans[0][0] == 0 and spans[-1][1] == rows
+        assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+        assert all((s1 - s0) % mult == 0 for s0, s1 in spans)
+        sizes = [s1 - s0 for s0, s1 in spans]
+        assert max(sizes) - min(sizes) <= mult
+        assert sizes == sharding.gather_sizes(rows, world, mult)
+    with pytest.raises(ValueError):
+        sharding.row_range(100, 2, 0, 128)
+
+
+def test_slices_reproduce_the_full_product():
+    case = synth.gemv_case(640, 256, seed=3)
+    t = dict(case)
+    full = oracle.sparse_gemv(case["meta"], case["values"], case["x"], 640, 256)
+    parts = []
+    for r in range(5):
+        s = sharding.shard_rows(t, 5, r, multiple=128)
+        parts.append(oracle.sparse_gemv(s["meta"], s["values"], case["x"], s["rows"], 256))
+    assert (np.concatenate(parts) == full).all()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, rows, cols, mult, out_q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        case = synth.gemv_case(rows, cols, seed=11)
+        s = sharding.shard_rows(dict(case), world, rank, mult)
+        local = oracle.sparse_gemv(s["meta"], s["values"], case["x"], s["rows"], cols) if s["rows"] else np.zeros(0, np.int32)
+        full = sharding.all_gather_rows(torch.from_numpy(local), rows, mult)
+        want = oracle.sparse_gemv(case["meta"], case["values"], case["x"], rows, cols)
+        out_q.put((rank, bool((full.numpy() == want).all()), int(full.numel())))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,rows,mult", [(2, 640, 128), (3, 640, 128), (2, 37, 1)])
+def test_all_gather_of_row_slices_gloo(world, rows, mult):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, rows, 256, mult, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert sorted(r[0] for r in results) == list(range(world))
+    assert all(ok and n == rows for _, ok, n in results)
