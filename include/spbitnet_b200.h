@@ -178,6 +178,22 @@ int spb_decode_attention_split(const void* Q, const void* K_cache, const void* V
                                int num_heads, int num_kv_heads, int head_dim, int max_seq_len, int seq_len,
                                float scale, void* scratch, size_t scratch_bytes, void* stream);
 
+/* No counterpart in the reference.  spb_decode_attention_split for callers that cannot supply the
+ * scratch buffer: an engine whose device buffers were all laid out up front (the reference's
+ * InferenceEngine is one), code inside a stream capture, or a serving loop that must not stall
+ * the GPU cannot call cudaMalloc between decode steps.  The partial results go to an array built
+ * into the library instead (spb_decode_attention_noalloc_capacity() bytes, 2 MiB, resident on every
+ * GPU that loads the library until the process exits); the call allocates and frees nothing.
+ * Shapes whose partial results (spb_decode_attention_scratch_bytes) exceed the capacity are refused
+ * with SPB_E_UNSUPPORTED.  The first call on a device looks up the array's device address (one
+ * cudaGetSymbolAddress, with that device current); make that first call outside any stream capture.
+ * All calls on a device share the one array: calls that may overlap on the GPU (different
+ * streams without ordering) race on it and must be serialised by the caller. */
+size_t spb_decode_attention_noalloc_capacity(void);
+int spb_decode_attention_noalloc(const void* Q, const void* K_cache, const void* V_cache, void* output,
+                                 int num_heads, int num_kv_heads, int head_dim, int max_seq_len, int seq_len,
+                                 float scale, void* stream);
+
 /* ---- host-side format helpers: include/spbitnet/sparse_ternary_tensor.h ----------- */
 
 /* Row strides in uint32 words (sparse_ternary_tensor.h:254-264). */

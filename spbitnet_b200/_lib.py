@@ -79,6 +79,8 @@ SIGNATURES = {
     "spb_decode_attention": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _p]),
     "spb_decode_attention_scratch_bytes": (C.c_size_t, [_i, _i, _i]),
     "spb_decode_attention_split": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _p, C.c_size_t, _p]),
+    "spb_decode_attention_noalloc_capacity": (C.c_size_t, []),
+    "spb_decode_attention_noalloc": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _p]),
     "spb_meta_words_per_row": (_i, [_i]),
     "spb_values_words_per_row": (_i, [_i]),
     "spb_pack_from_dense": (_i, [_p, _p, _i, _i, _p, _p]),
