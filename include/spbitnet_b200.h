@@ -70,9 +70,9 @@ int spb_sparse_ternary_gemv(const uint32_t* meta, const uint32_t* values, const 
 /* Work-list form: one launch computes n independent GEMVs (the semantics of n calls of
  * spb_sparse_ternary_gemv) with a persistent grid, so per-launch fixed costs are paid once.
  * d_items is a DEVICE array of n items that the caller uploads once (a decode step's list is
- * static); it must satisfy spb_gemv_batch_check, which validates the HOST copy: cols a
- * multiple of 128 (at most 32768), strides multiples of 4 / 2 words, meta/values/x 16/8/16-byte
- * aligned.  max_rows / max_cols bound the items (they size shared memory). */
+ * static); it must be 16-byte aligned and satisfy spb_gemv_batch_check, which validates the HOST
+ * copy: cols a multiple of 256 (at most 32768), row strides multiples of 4 words, meta/values/x
+ * 16-byte aligned.  max_rows / max_cols bound the items (they size shared memory). */
 typedef struct {
     const uint32_t* meta;
     const uint32_t* values;

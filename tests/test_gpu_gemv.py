@@ -233,7 +233,8 @@ def test_gemm_full_size_properties(rows, cols):
 
 def test_work_list_batch_matches_oracle():
     # one persistent launch over a list of GEMVs of mixed shapes == the same GEMVs one by one
-    shapes = [(6912, 2560), (640, 2560), (2560, 6912), (33, 128), (2048, 2048), (1, 256), (700, 8192), (6912, 2560)]
+    shapes = [(6912, 2560), (640, 2560), (2560, 6912), (33, 256), (2048, 2048), (1, 256), (700, 8192), (6912, 2560),
+              (5, 512), (301, 2560), (8192, 2560), (6912, 2560)]
     rng = np.random.default_rng(0)
     items, wants, keep = [], [], []
     for i, (rows, cols) in enumerate(shapes):
@@ -253,4 +254,4 @@ def test_work_list_batch_matches_oracle():
         assert (got[32:32 + rows] == want).all(), (rows, cols)
         assert (got[:32] == 0x5A5A5A5A).all() and (got[32 + rows:] == 0x5A5A5A5A).all()
     with pytest.raises(_lib.SpbError):
-        K.GemvWorkList([(keep[0][0], keep[0][1], keep[0][2], keep[0][3], 16, 132, 5, 3)])
+        K.GemvWorkList([(keep[0][0], keep[0][1], keep[0][2], keep[0][3], 16, 128, 4, 2)])  # cols not a multiple of 256
