@@ -84,3 +84,41 @@ def test_unfused_path_gives_the_same_tokens(monkeypatch):
     assert (a == b).all() and (la == lb).all()
     want, _ = oracle.Engine(model).generate(prompt, 8)
     assert (a == want).all()
+
+
+def test_full_2b4t_shape_against_the_reference_cuda_kernels():
+    """The 30-layer 2B-4T-shape model, 16-token prompt + 64 greedy steps, against the reference's
+    own kernels on the same GPU: logits within 1e-2 max-abs, identical tokens."""
+    import ref_cuda_engine
+    if not ref_cuda_engine.available():
+        pytest.skip("oracle/_ref/libspb_refcuda.so not built")
+    cfg = dict(synth.BITNET_2B, max_position_embeddings=128)
+    model = synth.random_model(cfg, seed=2, shared_layer=True)
+    dm = DeviceModel(model)
+    ours, ref = InferenceEngine(dm), ref_cuda_engine.RefCudaEngine(dm)
+    prompt = np.random.default_rng(4).integers(0, cfg["vocab_size"], 16).astype(np.int32)
+    for t in prompt[:-1]:
+        ours.forward(int(t))
+        ref.forward(int(t))
+    tok, worst, margins = int(prompt[-1]), 0.0, []
+    for step in range(64):
+        ours.forward(tok)
+        a = ours.logits()
+        b = ref.forward(tok).cpu().numpy()
+        worst = max(worst, float(np.abs(a - b).max()))
+        top2 = np.sort(b)[-2:]
+        margins.append(float(top2[1] - top2[0]))
+        assert int(np.argmax(a)) == int(np.argmax(b)), (step, margins[-1], worst)
+        tok = int(np.argmax(b))
+    assert worst < 1e-2, worst
+    # and the device-side greedy loop reproduces the same 64 tokens
+    ours.reset()
+    ref_tokens = []
+    ref.__init__(dm)
+    for t in prompt[:-1]:
+        ref.forward(int(t))
+    tok = int(prompt[-1])
+    for _ in range(64):
+        tok = int(torch.argmax(ref.forward(tok)).item())
+        ref_tokens.append(tok)
+    assert (ours.generate(prompt, 64) == np.array(ref_tokens, np.int32)).all()
