@@ -365,6 +365,13 @@ def run_ours(args):
                "sample": f"{repsN} GEMVs of 6912x2560 in {dtN:.2f} s on {threads} threads "
                          f"(1 thread: {g1:.3f} GB/s over {reps1} GEMVs)"}
 
+    gemm = None
+    if rank == 0 and not args.no_gemm:
+        try:
+            gemm = bench_gemm(args, l2_bytes)
+        except Exception as exc:
+            gemm = {"error": repr(exc)}
+
     # ---- decode throughput on the 2B-4T-shape model (secondary figure) ----------------------
     decode = None
     if rank == 0 and not args.no_decode:
@@ -404,11 +411,58 @@ def run_ours(args):
             "cpu_baseline": cpu,
             "ref_cuda_same_gpu": ref_cuda,
             "sweep": sweep,
+            "gemm": gemm,
             "decode": decode,
         }
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def bench_gemm(args, l2_bytes):
+    """Batched product (prefill) at the two FFN shapes, N in {1,4,16,64,256,1024}: us per call over a
+    rotating set of weight copies larger than L2, weight-stream GB/s and dense-equivalent int8 TOP/s."""
+    import torch
+    from spbitnet_b200 import kernels as K, synth
+    out = {}
+    for (r, c) in synth.GEMM_SHAPES:
+        case = synth.gemv_case(r, c, seed=0)
+        per = r * 4 * (case["meta_stride"] + case["values_stride"])
+        copies = max(4, int(np.ceil(1.5 * l2_bytes / per)))
+        meta = torch.from_numpy(case["meta"].view(np.int32)).cuda()
+        values = torch.from_numpy(case["values"].view(np.int32)).cuda()
+        metas = torch.stack([meta.roll(i, 0) for i in range(copies)]).contiguous()
+        vals = torch.stack([values.roll(i, 0) for i in range(copies)]).contiguous()
+        for n in synth.GEMM_BATCHES:
+            X = torch.randint(-127, 128, (n, c), dtype=torch.int8, device="cuda")
+            Y = torch.empty((n, r), dtype=torch.int32, device="cuda")
+            row = {}
+            for name, variant in (("auto", 0), ("simt", 1)):
+                if variant == 1 and n > 64:
+                    continue
+                K.set_gemm_variant(variant)
+                def run():
+                    for i in range(copies):
+                        K.sparse_ternary_gemm_gpu(metas[i], vals[i], X, Y, r, c, n, case["meta_stride"], case["values_stride"])
+                run()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                reps = 3
+                e0.record()
+                for _ in range(reps):
+                    run()
+                e1.record()
+                torch.cuda.synchronize()
+                us = e0.elapsed_time(e1) * 1e3 / (reps * copies)
+                row[name] = {"us": round(us, 2), "weight_gbs": round(per / us / 1e3, 1),
+                             "dense_equiv_tops": round(2.0 * r * c * n / us / 1e6, 2)}
+            K.set_gemm_variant(0)
+            out[f"{r}x{c}_n{n}"] = row
+        del metas, vals
+    out["tc_timeouts"] = K.gemm_tc_timeouts()
+    out["what"] = ("spb_sparse_ternary_gemm per call; auto = tcgen05 kind::i8 form from n >= 16, SIMT below; "
+                   "dense_equiv_tops counts 2*M*K*N")
+    return out
 
 
 def bench_decode(args):
@@ -450,6 +504,7 @@ def main():
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--no-gemm", action="store_true")
     ap.add_argument("--only-decode", action="store_true", help="skip the GEMV sections (profiling aid)")
     ap.add_argument("--decode-layers", type=int, default=0, help="override the layer count of the decode model")
     ap.add_argument("--decode-tokens", type=int, default=256)

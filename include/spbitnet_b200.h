@@ -117,6 +117,15 @@ int spb_sparse_ternary_gemm(const uint32_t* meta, const uint32_t* values, const 
                             int32_t* Y, int rows, int cols, int n, int meta_row_stride,
                             int values_row_stride, void* stream);
 
+/* Which form spb_sparse_ternary_gemm uses: 0 = automatic (tcgen05 tensor-core form from 16 batch rows
+ * up when the layout allows it, SIMT form otherwise), 1 = SIMT form, 2 = tensor-core form for any n.
+ * Results are identical.  Returns the previous setting. */
+int spb_set_gemm_variant(int variant);
+/* Number of blocks of the tensor-core form whose bounded device-side wait ran out since the library
+ * was loaded (their outputs are unspecified); 0 in a healthy run, -1 if the counter cannot be read.
+ * Synchronises the device. */
+int spb_gemm_tc_timeouts(void);
+
 /* ---- transformer kernels: include/spbitnet/inference_kernels.h ------------------- */
 
 /* rms_norm_gpu (inference_kernels.h:14-15; src/kernels/inference_kernels.cu:15-56). input may alias output. */

@@ -141,9 +141,20 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_generic_kernel(const GemmAr
     if (lane == 0) a.Y[static_cast<size_t>(j) * a.rows + row] = acc;
 }
 
+int gemm_tc_launch(const uint32_t* meta, const uint32_t* values, const int8_t* X, int32_t* Y, int rows, int cols,
+                   int n, int meta_stride, int values_stride, void* stream);
+
+static int g_gemm_variant = 0;  // 0 automatic, 1 SIMT form, 2 tensor-core form whenever the layout allows
+
 }  // namespace spb
 
 using namespace spb;
+
+extern "C" int spb_set_gemm_variant(int variant) {
+    const int old = g_gemm_variant;
+    g_gemm_variant = variant;
+    return old;
+}
 
 extern "C" int spb_sparse_ternary_gemm(const uint32_t* meta, const uint32_t* values, const int8_t* X,
                                        int32_t* Y, int rows, int cols, int n, int meta_row_stride,
@@ -159,8 +170,10 @@ extern "C" int spb_sparse_ternary_gemm(const uint32_t* meta, const uint32_t* val
     auto al = [](const void* p, size_t k) { return (reinterpret_cast<uintptr_t>(p) & (k - 1)) == 0; };
     const size_t x_bytes = static_cast<size_t>(kBatchTile) * cols;
     const bool fast = cols % 128 == 0 && cols / 128 <= 512 && meta_row_stride % 4 == 0 &&
-                      values_row_stride % 2 == 0 && al(meta, 16) && al(values, 8) && al(X, 16) &&
-                      x_bytes <= 160 * 1024;
+                      values_row_stride % 2 == 0 && al(meta, 16) && al(values, 8) && al(X, 16);
+    // tensor cores from 16 batch rows up (below that the batch does not fill an MMA's N)
+    if (fast && g_gemm_variant != 1 && (n >= 16 || g_gemm_variant == 2))
+        return gemm_tc_launch(meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream);
     if (!fast) {
         const long long warps = static_cast<long long>(rows) * n;
         const unsigned grid = static_cast<unsigned>((warps * 32 + kGemmThreads - 1) / kGemmThreads);
@@ -173,6 +186,11 @@ extern "C" int spb_sparse_ternary_gemm(const uint32_t* meta, const uint32_t* val
     int rpc = max((rows + 4 * sms - 1) / (4 * sms), min(fill, (rows + sms - 1) / sms));
     a.rpc = max(1, min(rpc, rpc_cap));
     const int passes = (a.rpc * a.upr + kGemmThreads - 1) / kGemmThreads;
+    if (x_bytes > 160 * 1024) {
+        const long long warps = static_cast<long long>(rows) * n;
+        const unsigned grid1 = static_cast<unsigned>((warps * 32 + kGemmThreads - 1) / kGemmThreads);
+        return launch(name, gemm_generic_kernel, dim3(grid1), dim3(kGemmThreads), 0, stream, a);
+    }
     const dim3 grid((rows + a.rpc - 1) / a.rpc, (n + kBatchTile - 1) / kBatchTile);
     const size_t smem = kLutBytes + ((a.rpc * kBatchTile * 4 + 15) & ~15) + x_bytes;
     auto kernel = passes <= 1 ? gemm_units_kernel<1> : gemm_units_kernel<2>;

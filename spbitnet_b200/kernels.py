@@ -37,6 +37,15 @@ def set_gemv_variant(variant: int) -> int:
     return load().spb_set_gemv_variant(int(variant))
 
 
+def set_gemm_variant(variant: int) -> int:
+    """0 automatic, 1 SIMT form, 2 tcgen05 tensor-core form."""
+    return load().spb_set_gemm_variant(int(variant))
+
+
+def gemm_tc_timeouts() -> int:
+    return load().spb_gemm_tc_timeouts()
+
+
 # ---- sparse_ternary_kernels.h ---------------------------------------------------------
 
 def sparse_ternary_unpack_gpu(meta, values, out, rows, cols, meta_row_stride, values_row_stride, stream=None):

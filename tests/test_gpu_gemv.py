@@ -197,9 +197,19 @@ def test_unpack_matches_oracle(rows, cols):
         assert (out.read(np.int8).reshape(rows, cols) == want).all()
 
 
+@pytest.fixture(params=[1, 2], ids=["simt", "tcgen05"])
+def gemm_variant(request):
+    """1 = SIMT form, 2 = tcgen05 tensor-core form (forced for every n the layout allows)."""
+    old = K.set_gemm_variant(request.param)
+    yield request.param
+    K.set_gemm_variant(old)
+    assert K.gemm_tc_timeouts() == 0
+
+
 @pytest.mark.parametrize("rows,cols,n", [(64, 256, 16), (64, 256, 1), (37, 132, 5), (300, 2560, 4), (96, 6912, 19),
-                                          (2048, 2048, 32), (128, 512, 64)])
-def test_gemm_matches_oracle(rows, cols, n):
+                                          (2048, 2048, 32), (128, 512, 64), (128, 128, 16), (129, 384, 257),
+                                          (1000, 1024, 300), (256, 2560, 256)])
+def test_gemm_matches_oracle(rows, cols, n, gemm_variant):
     # tests/test_cusparselt.cu:127-274: exact int32 vs the CPU int8 GEMM
     case = synth.gemm_case(rows, cols, n, seed=n)
     want = oracle.sparse_gemm(case["meta"], case["values"], case["X"], rows, cols)
@@ -212,7 +222,7 @@ def test_gemm_matches_oracle(rows, cols, n):
 
 
 @pytest.mark.parametrize("rows,cols", synth.GEMM_SHAPES)
-def test_gemm_full_size_properties(rows, cols):
+def test_gemm_full_size_properties(rows, cols, gemm_variant):
     # full benchmark shapes: column j of the batch must equal the GEMV of row j (checked against
     # the oracle for a few rows), and the product is linear: W(a+b) = Wa + Wb
     n = 64
