@@ -182,6 +182,13 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     K.set_gemv_variant(args.variant)
+    if args.only_gemm:
+        if rank == 0:
+            l2 = torch.cuda.get_device_properties(local).L2_cache_size
+            print(json.dumps({"metric": "sparse_ternary_gemm", "gemm": bench_gemm(args, l2), "n_gpus": world}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
     if args.only_decode:
         if rank == 0:
             print(json.dumps({"metric": "decode_tok_s_2b4t_shape", "decode": bench_decode(args), "n_gpus": world}))
@@ -505,6 +512,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-gemm", action="store_true")
+    ap.add_argument("--only-gemm", action="store_true", help="only the batched-product section (profiling aid)")
     ap.add_argument("--only-decode", action="store_true", help="skip the GEMV sections (profiling aid)")
     ap.add_argument("--decode-layers", type=int, default=0, help="override the layer count of the decode model")
     ap.add_argument("--decode-tokens", type=int, default=256)

@@ -117,8 +117,8 @@ int spb_sparse_ternary_gemm(const uint32_t* meta, const uint32_t* values, const 
                             int32_t* Y, int rows, int cols, int n, int meta_row_stride,
                             int values_row_stride, void* stream);
 
-/* Which form spb_sparse_ternary_gemm uses: 0 = automatic (tcgen05 tensor-core form from 16 batch rows
- * up when the layout allows it, SIMT form otherwise), 1 = SIMT form, 2 = tensor-core form for any n.
+/* Which form spb_sparse_ternary_gemm uses: 0 = automatic (tcgen05 tensor-core form above 32 batch
+ * rows when the layout allows it, SIMT form otherwise), 1 = SIMT form, 2 = tensor-core form for any n.
  * Results are identical.  Returns the previous setting. */
 int spb_set_gemm_variant(int variant);
 /* Number of blocks of the tensor-core form whose bounded device-side wait ran out since the library

@@ -171,8 +171,8 @@ extern "C" int spb_sparse_ternary_gemm(const uint32_t* meta, const uint32_t* val
     const size_t x_bytes = static_cast<size_t>(kBatchTile) * cols;
     const bool fast = cols % 128 == 0 && cols / 128 <= 512 && meta_row_stride % 4 == 0 &&
                       values_row_stride % 2 == 0 && al(meta, 16) && al(values, 8) && al(X, 16);
-    // tensor cores from 16 batch rows up (below that the batch does not fill an MMA's N)
-    if (fast && g_gemm_variant != 1 && (n >= 16 || g_gemm_variant == 2))
+    // tensor cores above 32 batch rows (measured cross-over with the SIMT form on B200)
+    if (fast && g_gemm_variant != 1 && (n > 32 || g_gemm_variant == 2))
         return gemm_tc_launch(meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream);
     if (!fast) {
         const long long warps = static_cast<long long>(rows) * n;

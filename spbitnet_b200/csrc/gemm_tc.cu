@@ -3,11 +3,11 @@
 //   Y[j, r] = sum_c W[r, c] * X[j, c]      W: rows x cols compressed 2:4 ternary, X: n x cols int8
 //
 // A block owns 128 weight rows and up to 256 batch rows.  Per 128-column step of K it
-//   * expands its 128 units (one per thread of the first four warps: 16 B meta + 8 B values ->
-//     128 int8 through the per-lane 64-entry group table) straight into shared memory in the
-//     canonical K-major 128-byte-swizzled operand layout (the A operand),
-//   * copies the matching 128-byte slices of up to 256 activation rows into the same layout
-//     (the B operand, second four warps),
+//   * expands its 128 units (two threads per unit: 16 B meta + 8 B values -> 128 int8 through
+//     the per-lane 64-entry group table) straight into shared memory in the canonical K-major
+//     128-byte-swizzled operand layout (the A operand),
+//   * brings the matching 128-byte slices of up to 256 activation rows into the same layout with
+//     16-byte asynchronous copies issued one step ahead (the B operand),
 //   * and one thread issues four tcgen05.mma.kind::i8 (M=128, N=batch tile, K=32 each) that
 //     accumulate int32 in tensor memory.  tcgen05.commit signals an mbarrier when the MMAs that
 //     read a stage are done, which is what lets the next expansion reuse it: expansion of step
@@ -119,64 +119,77 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const TcArgs a) 
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_d = *tmem_slot;
 
-    // first unit of this thread's weight row (threads 0..127 expand row tid of the tile)
-    const bool expander = tid < kTileM;
-    const int wrow = row0 + tid;
-    const bool wvalid = expander && wrow < a.rows;
-    uint4 m = make_uint4(0, 0, 0, 0);
-    uint2 v = make_uint2(0, 0);
-    if (wvalid) {
-        m = ld_stream_v4(a.meta + static_cast<size_t>(wrow) * a.meta_stride);
-        v = ld_stream_v2(a.values + static_cast<size_t>(wrow) * a.values_stride);
-    }
+    // Expansion: thread t and thread t+128 share weight row (t & 127) of the tile; each expands
+    // one half of the row's unit (64 columns = 16 groups = four 16-byte chunks) per step.
+    const int trow = tid & (kTileM - 1), thalf = tid >> 7;
+    const int wrow = row0 + trow;
+    const bool wvalid = wrow < a.rows;
+    uint2 m = make_uint2(0, 0);  // the two meta words of this half
+    uint32_t v = 0;              // its 32 sign bits
+    auto load_half = [&](int kc, uint2& mm, uint32_t& vv) {
+        mm = ld_stream_v2(a.meta + static_cast<size_t>(wrow) * a.meta_stride + kc * 4 + thalf * 2);
+        vv = __ldg(a.values + static_cast<size_t>(wrow) * a.values_stride + kc * 2 + thalf);
+    };
+    if (wvalid) load_half(0, m, v);
 
     grid_dep_wait();  // X may be a predecessor's output
 
+    // Activations: 16-byte asynchronous copies (cp.async) into the swizzled B tile, issued one
+    // step ahead of their use; rows beyond n are zero-filled by a zero source size.
+    auto issue_b = [&](int kc) {
+        uint8_t* sb = stage0 + static_cast<size_t>(kc % kTcStages) * stage_bytes + kTileM * 128;
+        for (int i = tid; i < a.nt * 8; i += kTcThreads) {
+            const int j = i >> 3, c = i & 7;
+            const bool in = n0 + j < a.n;
+            const int8_t* src = a.X + static_cast<size_t>(in ? n0 + j : 0) * a.cols + kc * kTileK + c * 16;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(tc_smem(sb + tc_swz(j, c))), "l"(src),
+                         "r"(in ? 16 : 0)
+                         : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    issue_b(0);
+
     const uint32_t idesc = tc_idesc(kTileM, a.nt);
     bool ok = true;
-    for (int kc = 0; kc < nchunks && ok; ++kc) {
-        const int s = kc % kTcStages, use = kc / kTcStages;
-        // the MMAs that read this stage last time must be done before it is overwritten
-        // (the verdict is made uniform across the block so that nobody is left at a barrier)
-        if (use > 0) ok = __syncthreads_and(tc_wait(tc_smem(bars + s), (use - 1) & 1) ? 1 : 0) != 0;
-        if (!ok) break;
+    for (int kc = 0; kc < nchunks; ++kc) {
+        const int s = kc % kTcStages;
         uint8_t* sa = stage0 + static_cast<size_t>(s) * stage_bytes;
         uint8_t* sb = sa + kTileM * 128;
-        if (expander) {
-            // next unit in flight while this one is expanded
-            uint4 mn = make_uint4(0, 0, 0, 0);
-            uint2 vn = make_uint2(0, 0);
-            if (wvalid && kc + 1 < nchunks) {
-                mn = ld_stream_v4(a.meta + static_cast<size_t>(wrow) * a.meta_stride + (kc + 1) * 4);
-                vn = ld_stream_v2(a.values + static_cast<size_t>(wrow) * a.values_stride + (kc + 1) * 2);
-            }
+        // Stage of the NEXT step: the MMAs that read it last must be done before anything is written
+        // to it (the verdict is made uniform across the block so that nobody is left at a barrier).
+        if (kc + 1 < nchunks) {
+            const int use_next = (kc + 1) / kTcStages;
+            if (use_next > 0)
+                ok = __syncthreads_and(tc_wait(tc_smem(bars + (kc + 1) % kTcStages), (use_next - 1) & 1) ? 1 : 0) != 0;
+            if (!ok) break;
+            issue_b(kc + 1);
+        } else {
+            asm volatile("cp.async.commit_group;" ::: "memory");  // keeps the group count uniform
+        }
+        {
+            // next half-unit in flight while this one is expanded
+            uint2 mn = make_uint2(0, 0);
+            uint32_t vn = 0;
+            if (wvalid && kc + 1 < nchunks) load_half(kc + 1, mn, vn);
             const uint32_t* lutp = lut + lane;
-            const uint32_t mw[4] = {m.x, m.y, m.z, m.w};
+            const uint32_t mw[2] = {m.x, m.y};
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {  // 16-byte chunk c = groups 4c..4c+3
+            for (int c = 0; c < 4; ++c) {  // 16-byte chunk = 4 groups
                 uint32_t w[4];
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
-                    const int grp = 4 * c + g;  // group inside the unit
-                    const uint32_t word = mw[grp >> 3];
-                    const uint32_t vv = (grp < 16) ? v.x : v.y;
-                    const uint32_t idx = ((word >> (4 * (grp & 7))) & 0xFu) | (((vv >> (2 * (grp & 15))) & 0x3u) << 4);
+                    const int grp = 4 * c + g;  // group inside this half (0..15)
+                    const uint32_t idx = ((mw[grp >> 3] >> (4 * (grp & 7))) & 0xFu) | (((v >> (2 * grp)) & 0x3u) << 4);
                     w[g] = wvalid ? lutp[idx * 32] : 0u;
                 }
-                *reinterpret_cast<uint4*>(sa + tc_swz(tid, c)) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4*>(sa + tc_swz(trow, thalf * 4 + c)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
             m = mn;
             v = vn;
-        } else {
-            const int tb = tid - kTileM;
-            for (int i = tb; i < a.nt * 8; i += kTcThreads - kTileM) {
-                const int j = i >> 3, c = i & 7;
-                uint4 t = make_uint4(0, 0, 0, 0);
-                if (n0 + j < a.n)
-                    t = *reinterpret_cast<const uint4*>(a.X + static_cast<size_t>(n0 + j) * a.cols + kc * kTileK + c * 16);
-                *reinterpret_cast<uint4*>(sb + tc_swz(j, c)) = t;
-            }
         }
+        // this step's activations have landed (all groups but the newest are complete)
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
         // generic-proxy writes -> visible to the tensor core (async proxy), then hand over
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -204,6 +217,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const TcArgs a) 
                              : "memory");
         }
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
 
     // ---- epilogue: accumulators -> Y ---------------------------------------------------------
     ok = __syncthreads_and(ok ? 1 : 0) != 0;
