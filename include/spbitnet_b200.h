@@ -49,8 +49,9 @@ const char* spb_version(void);
 int spb_set_pdl(int enabled);
 /* Which GEMV kernel the sparse-ternary entry points use when the layout allows the fast
  * paths: 0 or 1 = pair kernel (default: one dp4a per two groups), 2 = per-group table kernel
- * (one dp4a per group; kept for comparison).  Results are identical on valid bitmaps.
- * Returns the previous setting. */
+ * (one dp4a per group; kept for comparison), 3 = sparse tensor-core kernel (tcgen05.mma.sp; int8
+ * activations, one matrix per launch, cols <= 8192; other calls keep the pair kernel).
+ * Results are identical on valid bitmaps.  Returns the previous setting. */
 int spb_set_gemv_variant(int variant);
 
 /* ---- sparse-ternary kernels: include/spbitnet/sparse_ternary_kernels.h ---------- */
@@ -118,10 +119,12 @@ int spb_sparse_ternary_gemm(const uint32_t* meta, const uint32_t* values, const 
                             int values_row_stride, void* stream);
 
 /* Which form spb_sparse_ternary_gemm uses: 0 = automatic (tcgen05 tensor-core form above 32 batch
- * rows when the layout allows it, SIMT form otherwise), 1 = SIMT form, 2 = tensor-core form for any n.
+ * rows when the layout allows it, SIMT form otherwise), 1 = SIMT form, 2 = dense tensor-core form
+ * (weights expanded to int8 tiles) for any n, 3 = sparse tensor-core form (tcgen05.mma.sp: sign bytes
+ * as the compressed operand, bitmaps as index pairs in tensor memory) for any n.
  * Results are identical.  Returns the previous setting. */
 int spb_set_gemm_variant(int variant);
-/* Number of blocks of the tensor-core form whose bounded device-side wait ran out since the library
+/* Number of blocks of the tensor-core kernels (GEMM and GEMV) whose bounded device-side wait ran out since the library
  * was loaded (their outputs are unspecified); 0 in a healthy run, -1 if the counter cannot be read.
  * Synchronises the device. */
 int spb_gemm_tc_timeouts(void);

@@ -144,7 +144,11 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_generic_kernel(const GemmAr
 int gemm_tc_launch(const uint32_t* meta, const uint32_t* values, const int8_t* X, int32_t* Y, int rows, int cols,
                    int n, int meta_stride, int values_stride, void* stream);
 
-static int g_gemm_variant = 0;  // 0 automatic, 1 SIMT form, 2 tensor-core form whenever the layout allows
+int gemm_tcsp_launch(const uint32_t* meta, const uint32_t* values, const int8_t* X, int32_t* Y, int rows, int cols,
+                     int n, int meta_stride, int values_stride, void* stream);
+
+// 0 automatic, 1 SIMT form, 2 dense tensor-core form, 3 sparse tensor-core form (2 and 3 whenever the layout allows)
+static int g_gemm_variant = 0;
 
 }  // namespace spb
 
@@ -172,6 +176,8 @@ extern "C" int spb_sparse_ternary_gemm(const uint32_t* meta, const uint32_t* val
     const bool fast = cols % 128 == 0 && cols / 128 <= 512 && meta_row_stride % 4 == 0 &&
                       values_row_stride % 2 == 0 && al(meta, 16) && al(values, 8) && al(X, 16);
     // tensor cores above 32 batch rows (measured cross-over with the SIMT form on B200)
+    if (fast && g_gemm_variant == 3)
+        return gemm_tcsp_launch(meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream);
     if (fast && g_gemm_variant != 1 && (n > 32 || g_gemm_variant == 2))
         return gemm_tc_launch(meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream);
     if (!fast) {

@@ -281,6 +281,9 @@ int gemm_tc_launch(const uint32_t* meta, const uint32_t* values, const int8_t* X
     return launch("spb_sparse_ternary_gemm(tcgen05)", gemm_tc_kernel, grid, dim3(kTcThreads), smem, stream, a);
 }
 
+int gemm_tcsp_timeouts();
+int gemv_tcsp_timeouts();
+
 }  // namespace spb
 
 extern "C" int spb_gemm_tc_timeouts(void) {
@@ -289,5 +292,6 @@ extern "C" int spb_gemm_tc_timeouts(void) {
         cudaGetLastError();
         return -1;
     }
-    return v;
+    const int w = spb::gemm_tcsp_timeouts(), g = spb::gemv_tcsp_timeouts();
+    return (w < 0 || g < 0) ? -1 : v + w + g;
 }

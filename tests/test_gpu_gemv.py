@@ -14,12 +14,13 @@ from gpu_util import Guarded, dev, host
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=[1, 2], ids=["pair-kernel", "group-table-kernel"], autouse=True)
+@pytest.fixture(params=[1, 2, 3], ids=["pair-kernel", "group-table-kernel", "sparse-mma-kernel"], autouse=True)
 def gemv_variant(request):
     """Every test in this file runs once per GEMV kernel variant."""
     old = K.set_gemv_variant(request.param)
     yield request.param
     K.set_gemv_variant(old)
+    assert K.gemm_tc_timeouts() == 0
 
 
 def run_gemv(case, x=None, align=0):
@@ -197,9 +198,9 @@ def test_unpack_matches_oracle(rows, cols):
         assert (out.read(np.int8).reshape(rows, cols) == want).all()
 
 
-@pytest.fixture(params=[1, 2], ids=["simt", "tcgen05"])
+@pytest.fixture(params=[1, 2, 3], ids=["simt", "tcgen05", "tcgen05sp"])
 def gemm_variant(request):
-    """1 = SIMT form, 2 = tcgen05 tensor-core form (forced for every n the layout allows)."""
+    """1 = SIMT form, 2 = dense tcgen05 form, 3 = sparse tcgen05 form (forced for every n the layout allows)."""
     old = K.set_gemm_variant(request.param)
     yield request.param
     K.set_gemm_variant(old)
