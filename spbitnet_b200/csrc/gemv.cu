@@ -817,6 +817,11 @@ struct MatDesc {
 
 static int g_gemv_variant = 0;  // 0/1 pair kernel (default), 2 per-group table kernel, 3 sparse tensor-core kernel
 
+bool gemv_mmasp_supported(const uint32_t* meta, const uint32_t* values, const int8_t* x, int rows, int cols,
+                          int meta_stride, int values_stride);
+int gemv_mmasp_launch(const char* name, const uint32_t* meta, const uint32_t* values, const int8_t* x, void* y,
+                      int32_t* y_acc, const float* d_absmax, float gamma, int out_mode, int rows, int cols,
+                      int meta_stride, int values_stride, void* stream);
 bool gemv_tcsp_supported(int rows, int cols);
 int gemv_tcsp_launch(const char* name, const uint32_t* meta, const uint32_t* values, const int8_t* x, void* y,
                      int32_t* y_acc, const float* d_absmax, float gamma, int out_mode, int rows, int cols,
@@ -897,6 +902,13 @@ static int run_gemv(const char* name, const MatDesc* mats, int nmat, const XDesc
     }
     int rc;
     if constexpr (IN == IN_I8) {
+        if (fast && nmat == 1 && g_gemv_variant == 4 &&
+            gemv_mmasp_supported(mats[0].meta, mats[0].values, static_cast<const int8_t*>(xd.x), mats[0].rows, cols,
+                                 mats[0].meta_stride, mats[0].values_stride)) {
+            return gemv_mmasp_launch(name, mats[0].meta, mats[0].values, static_cast<const int8_t*>(xd.x), mats[0].y,
+                                     mats[0].y_acc, xd.d_absmax, mats[0].gamma, OUT, mats[0].rows, cols,
+                                     mats[0].meta_stride, mats[0].values_stride, stream);
+        }
         if (fast && nmat == 1 && g_gemv_variant == 3 && gemv_tcsp_supported(mats[0].rows, cols))
             return gemv_tcsp_launch(name, mats[0].meta, mats[0].values, static_cast<const int8_t*>(xd.x), mats[0].y,
                                     mats[0].y_acc, xd.d_absmax, mats[0].gamma, OUT, mats[0].rows, cols,

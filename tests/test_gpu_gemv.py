@@ -14,7 +14,8 @@ from gpu_util import Guarded, dev, host
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=[1, 2, 3], ids=["pair-kernel", "group-table-kernel", "sparse-mma-kernel"], autouse=True)
+@pytest.fixture(params=[1, 2, 3, 4], ids=["pair-kernel", "group-table-kernel", "sparse-mma-kernel", "warp-mma-kernel"],
+                autouse=True)
 def gemv_variant(request):
     """Every test in this file runs once per GEMV kernel variant."""
     old = K.set_gemv_variant(request.param)
