@@ -184,6 +184,8 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     K.set_gemv_variant(args.variant)
+    if args.no_pdl:
+        K.set_pdl(False)
     if args.only_gemm:
         if rank == 0:
             l2 = torch.cuda.get_device_properties(local).L2_cache_size
@@ -512,6 +514,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--chains", type=int, default=8, help="independent branches per step graph")
     ap.add_argument("--variant", type=int, default=0, help="GEMV kernel: 0 auto, 1 unit, 2 column-owner")
+    ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-decode", action="store_true")

@@ -47,10 +47,13 @@ const char* spb_version(void);
  * weight prefetch of one kernel overlaps the tail of the previous one on the same
  * stream.  0: plain stream-ordered launches.  Returns the previous setting. */
 int spb_set_pdl(int enabled);
-/* Which GEMV kernel the sparse-ternary entry points use when the layout allows the fast
- * paths: 0 or 1 = pair kernel (default: one dp4a per two groups), 2 = per-group table kernel
- * (one dp4a per group; kept for comparison), 3 = sparse tensor-core kernel (tcgen05.mma.sp; int8
- * activations, one matrix per launch, cols <= 8192; other calls keep the pair kernel).
+/* Which GEMV kernel the sparse-ternary entry points use when the layout allows the fast paths:
+ * 0 (default) = automatic: the warp-level sparse MMA kernel (mma.sp m16n8k64: the format is re-encoded
+ *     in registers, not decoded) for int8 activations and one matrix per launch when cols % 256 == 0,
+ *     row strides are multiples of 4 words and meta / values / x are 16-byte aligned; the pair kernel
+ *     otherwise and for the fused half-input forms;
+ * 1 = pair kernel (SIMT: one dp4a per two groups), 2 = per-group table kernel (SIMT: one dp4a per group),
+ * 3 = tcgen05 sparse kernel (tensor memory; kept for comparison), 4 = warp-level sparse MMA kernel.
  * Results are identical on valid bitmaps.  Returns the previous setting. */
 int spb_set_gemv_variant(int variant);
 

@@ -815,7 +815,9 @@ struct MatDesc {
     int rows, meta_stride, values_stride;
 };
 
-static int g_gemv_variant = 0;  // 0/1 pair kernel (default), 2 per-group table kernel, 3 sparse tensor-core kernel
+// 0 automatic (warp-level sparse MMA kernel where the layout allows it, else the pair kernel), 1 pair kernel,
+// 2 per-group table kernel, 3 tcgen05 sparse kernel, 4 warp-level sparse MMA kernel
+static int g_gemv_variant = 0;
 
 bool gemv_mmasp_supported(const uint32_t* meta, const uint32_t* values, const int8_t* x, int rows, int cols,
                           int meta_stride, int values_stride);
@@ -902,7 +904,7 @@ static int run_gemv(const char* name, const MatDesc* mats, int nmat, const XDesc
     }
     int rc;
     if constexpr (IN == IN_I8) {
-        if (fast && nmat == 1 && g_gemv_variant == 4 &&
+        if (fast && nmat == 1 && (g_gemv_variant == 0 || g_gemv_variant == 4) &&
             gemv_mmasp_supported(mats[0].meta, mats[0].values, static_cast<const int8_t*>(xd.x), mats[0].rows, cols,
                                  mats[0].meta_stride, mats[0].values_stride)) {
             return gemv_mmasp_launch(name, mats[0].meta, mats[0].values, static_cast<const int8_t*>(xd.x), mats[0].y,

@@ -14,17 +14,18 @@
 //
 // Work split: a block of eight warps owns RB row blocks of 16 rows and the whole K extent, KS warps
 // per row block, each with a contiguous range of 64-column steps (RB * KS = 8).  The block's raw
-// weight slab (16 * RB rows, 3/16 byte per weight) arrives by one cp.async.bulk per row and array
-// into padded shared-memory rows (conflict-free word reads), so every byte of the block is in
-// flight from its first instructions and nothing is held in registers meanwhile.  Weights never
+// weight slab (16 * RB rows, 3/16 byte per weight) arrives by 16-byte asynchronous copies (cp.async,
+// a warp per row) into padded shared-memory rows (conflict-free word reads), so every byte of the
+// block is in flight from its first instructions and nothing is held in registers meanwhile (a
+// cp.async.bulk per row was measured to take about a microsecond longer to issue).  Weights never
 // depend on a predecessor kernel: the copies are issued before the dependency wait, x is staged
 // after it.  Operand registers of a lane (g = lane / 4, tig = lane % 4), as the instruction defines
 // them: A = four sign nibbles -> compressed columns 4 tig.. and 16 + 4 tig.. of rows g and g + 8;
 // metadata = the index pairs of one whole bitmap word (word tig / 2 of the step, row g + 8 (tig & 1));
 // B = x[64 s + 16 j + 4 tig ..] in register j, the same in all N = 8 columns (only column 0 is
-// read).  Partial sums of the KS warps meet in shared memory.
-// The wait for the copies is bounded; a block whose wait runs out records it and returns without
-// storing.
+// read).  Partial sums of the KS warps meet in shared memory.  There is no spin-wait in the kernel.
+#include <cstdlib>
+
 #include "spb_common.cuh"
 
 namespace spb {
@@ -32,7 +33,6 @@ namespace spb {
 constexpr int kGmThreads = 256;
 constexpr int kGmWarps = kGmThreads / 32;
 constexpr int kGmSignLutBytes = 16 * 32 * 4;  // 2 KB on a 2 KB boundary
-constexpr unsigned kGmWaitLimit = 1u << 22;
 
 enum { GM_OUT_I32 = 0, GM_OUT_F32 = 1, GM_OUT_F16 = 2 };
 
@@ -49,14 +49,31 @@ struct GmArgs {
     int meta_stride, values_stride;
     int steps;      // cols / 64
     int ks;         // warps per row block (power of two <= 8)
+    int ks_log2;
     int rb;         // row blocks per thread block = 8 / ks
     int spw;        // steps per warp
     int mpitch;     // shared-memory row pitch of the bitmap words, in words (= 4 mod 32)
     int vpitch;     // same for the sign words
 };
 
-// Number of blocks whose bounded wait ran out since the library was loaded (0 in a healthy run).
-__device__ int g_gemv_mma_timeouts = 0;
+// Development aid, compiled out unless SPB_GT_TRACE is defined: per-block stamps of the phases
+// (slot = launch id taken from gamma, block index; entries 0 and 15 globaltimer, the rest clock64).
+#ifdef SPB_GT_TRACE
+__device__ long long g_gm_trace[4 * 512 * 16];
+__device__ __forceinline__ unsigned long long gm_globaltimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define GM_STAMP(k)                                                                                        \
+    do {                                                                                                   \
+        if (threadIdx.x == 0)                                                                              \
+            g_gm_trace[((static_cast<int>(a.gamma) & 3) * 512 + blockIdx.x % 512) * 16 + (k)] =            \
+                ((k) == 0 || (k) == 15) ? static_cast<long long>(gm_globaltimer()) : clock64();            \
+    } while (0)
+#else
+#define GM_STAMP(k)
+#endif
 
 // Eight bitmaps (two of four bits set each) -> eight index pairs {low index | high index << 2}.
 //   low  = first set bit:  bit0 = ~b0 & b1,  bit1 = ~b0 & ~b1
@@ -76,12 +93,11 @@ __device__ __forceinline__ uint32_t gm_lds(uint32_t addr) {
 
 __global__ void __launch_bounds__(kGmThreads, 4) gemv_mmasp_kernel(const GmArgs a) {
     extern __shared__ uint8_t gm_raw[];
-    // 2 KB-aligned: [sign table 2 KB][mbarrier 16 B][partial sums 8 warps x 16 ints][x, permuted: cols bytes]
+    // 2 KB-aligned: [sign table 2 KB][16 B unused][partial sums 8 warps x 16 ints][x, permuted: cols bytes]
     //               [bitmap rows: 16 rb x mpitch words][sign rows: 16 rb x vpitch words]
     const uint32_t raw_s = static_cast<uint32_t>(__cvta_generic_to_shared(gm_raw));
     const uint32_t base_s = (raw_s + 2047u) & ~2047u;
     uint8_t* base = gm_raw + (base_s - raw_s);
-    const uint32_t bar_s = base_s + kGmSignLutBytes;
     volatile int* red = reinterpret_cast<volatile int*>(base + kGmSignLutBytes + 16);
     const uint32_t xs_s = base_s + kGmSignLutBytes + 16 + kGmWarps * 16 * 4;
     const uint32_t ms_s = xs_s + static_cast<uint32_t>(a.cols);
@@ -93,29 +109,29 @@ __global__ void __launch_bounds__(kGmThreads, 4) gemv_mmasp_kernel(const GmArgs 
     const int valid = min(nrows_blk, a.rows - row0);  // rows of this block inside the matrix
     const uint32_t mbytes = static_cast<uint32_t>(a.cols >> 3), vbytes = static_cast<uint32_t>(a.cols >> 4);
 
-    grid_dep_launch();
-    if (tid == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_s));
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_s),
-                     "r"(static_cast<uint32_t>(valid) * (mbytes + vbytes))
-                     : "memory");
-    }
-    __syncthreads();
-    // one bulk copy per (row, array): thread t < rows copies bitmap row t, thread 32.. the sign rows
+    GM_STAMP(0);
+    GM_STAMP(1);
+    // The raw slab: 16-byte asynchronous copies, a warp per row (bitmap chunks first, then sign chunks), so
+    // that a row's bytes are fetched by consecutive lanes.
     {
-        const int r = tid & 63, which = tid >> 6;  // which: 0 bitmaps, 1 signs (rows <= 64)
-        if (which < 2 && r < valid) {
-            const size_t grow = static_cast<size_t>(row0 + r);
-            const void* src = which == 0 ? static_cast<const void*>(a.meta + grow * a.meta_stride)
-                                         : static_cast<const void*>(a.values + grow * a.values_stride);
-            const uint32_t dst = which == 0 ? ms_s + static_cast<uint32_t>(r * a.mpitch) * 4u
-                                            : vs_s + static_cast<uint32_t>(r * a.vpitch) * 4u;
-            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                         "l"(src), "r"(which == 0 ? mbytes : vbytes), "r"(bar_s)
-                         : "memory");
+        const int mch = static_cast<int>(mbytes >> 4), cpr = mch + static_cast<int>(vbytes >> 4);  // 16-byte chunks of a row
+        for (int k = lane; k < cpr; k += 32) {  // one pass for up to 32 chunks per row (cols <= 2560), else several
+            const bool is_m = k < mch;
+            const uint8_t* src = is_m ? reinterpret_cast<const uint8_t*>(a.meta) + k * 16
+                                      : reinterpret_cast<const uint8_t*>(a.values) + (k - mch) * 16;
+            const size_t src_pitch = static_cast<size_t>(is_m ? a.meta_stride : a.values_stride) * 4u;
+            const uint32_t dst = is_m ? ms_s + static_cast<uint32_t>(k) * 16u : vs_s + static_cast<uint32_t>(k - mch) * 16u;
+            const uint32_t dst_pitch = static_cast<uint32_t>(is_m ? a.mpitch : a.vpitch) * 4u;
+            src += static_cast<size_t>(row0 + warp) * src_pitch;
+            for (int r = warp; r < valid; r += kGmWarps) {
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + static_cast<uint32_t>(r) * dst_pitch), "l"(src)
+                             : "memory");
+                src += kGmWarps * src_pitch;
+            }
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
     }
+    GM_STAMP(3);
     // sign table under the copy latency: entry (nibble n, lane l) at n * 128 + l * 4, byte b = -1 if bit b of n
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
@@ -125,19 +141,29 @@ __global__ void __launch_bounds__(kGmThreads, 4) gemv_mmasp_kernel(const GmArgs 
     }
 
     const int g = lane >> 2, tig = lane & 3;
-    const int rbi = warp / a.ks, kq = warp - rbi * a.ks;
+    // the warp index through a shuffle, so that everything derived from it (the step range, the loop) is
+    // known to be uniform over the warp
+    const int warp_u = __shfl_sync(0xFFFFFFFFu, warp, 0);
+    const int rbi = warp_u >> a.ks_log2, kq = warp_u & (a.ks - 1);
     const int s_begin = kq * a.spw, s_end = min(a.steps, s_begin + a.spw);
     const uint32_t lane_or = base_s | (static_cast<uint32_t>(lane) << 2);
-    const uint32_t sh = static_cast<uint32_t>(tig) * 4u;
-    // word addresses at step 0: the lane's bitmap word, the sign words of rows g and g + 8 of the row block
-    const uint32_t me_s = ms_s + static_cast<uint32_t>((rbi * 16 + g + 8 * (tig & 1)) * a.mpitch + (tig >> 1)) * 4u;
-    const uint32_t v0_s = vs_s + static_cast<uint32_t>((rbi * 16 + g) * a.vpitch) * 4u;
-    const uint32_t v1_s = v0_s + static_cast<uint32_t>(8 * a.vpitch) * 4u;
-    const uint32_t xq_s = xs_s + static_cast<uint32_t>(tig) * 16u;
+    // rotations that bring sign nibble tig (compressed columns 4 tig..) and nibble 4 + tig (16 + 4 tig..) of a
+    // sign word to bits 7..10, where they index the table
+    const uint32_t rot_lo = (static_cast<uint32_t>(tig) * 4u + 25u) & 31u, rot_hi = (static_cast<uint32_t>(tig) * 4u + 9u) & 31u;
+    // running addresses: the lane's bitmap word, the sign words of rows g and g + 8 of the row block, the x slice
+    uint32_t me_p = ms_s + static_cast<uint32_t>((rbi * 16 + g + 8 * (tig & 1)) * a.mpitch + (tig >> 1) + 2 * s_begin) * 4u;
+    uint32_t v0_p = vs_s + static_cast<uint32_t>((rbi * 16 + g) * a.vpitch + s_begin) * 4u;
+    const uint32_t v_half = static_cast<uint32_t>(8 * a.vpitch) * 4u;
+    uint32_t xq_p = xs_s + static_cast<uint32_t>(tig) * 16u + static_cast<uint32_t>(s_begin) * 64u;
 
     // ---- after the dependency: x, permuted so that a lane's four B registers of a step are 16 contiguous bytes:
     //      xs[step][tig][j][0..3] = x[64 step + 16 j + 4 tig + 0..3] -------------------------------------------
+    GM_STAMP(4);
     grid_dep_wait();
+    // The successor on the stream is let in only now: it then loads and waits while this grid computes, and
+    // no deeper queue of waiting grids builds up (measured: a deep queue slows a long chain of launches).
+    grid_dep_launch();
+    GM_STAMP(5);
     for (int q = tid; q < (a.cols >> 4); q += kGmThreads) {
         const uint4 xv = __ldg(reinterpret_cast<const uint4*>(a.x) + q);
         const uint32_t s = static_cast<uint32_t>(q) >> 2, j = static_cast<uint32_t>(q) & 3u;
@@ -147,51 +173,64 @@ __global__ void __launch_bounds__(kGmThreads, 4) gemv_mmasp_kernel(const GmArgs 
         asm volatile("st.shared.u32 [%0], %1;" ::"r"(d + 32u), "r"(xv.z) : "memory");
         asm volatile("st.shared.u32 [%0], %1;" ::"r"(d + 48u), "r"(xv.w) : "memory");
     }
-    // the weights have landed (bounded wait), the table and x are visible
-    bool ok = false;
-    for (unsigned spin = 0; spin < kGmWaitLimit && !ok; ++spin) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done)
-            : "r"(bar_s), "r"(0u)
-            : "memory");
-        ok = done != 0;
-    }
-    ok = __syncthreads_and(ok ? 1 : 0) != 0;
-    if (!ok) {
-        if (tid == 0) atomicAdd(&g_gemv_mma_timeouts, 1);
-        return;
-    }
-
+    GM_STAMP(6);
+    // the weights have landed, the table and x are visible
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    GM_STAMP(7);
+    // One step = 64 columns of 16 rows.  Metadata register of lane (g, tig): the index pairs of bitmap word
+    // 2 s + (tig >> 1) of row g + 8 (tig & 1).  `off` is a compile-time byte offset from the running addresses.
     int c0 = 0, c1 = 0, c2 = 0, c3 = 0;
-    for (int s = s_begin; s < s_end; ++s) {
-        const uint32_t so = static_cast<uint32_t>(s);
-        // metadata register of lane (g, tig): the eight groups of bitmap word 2 s + (tig >> 1) of row g + 8 (tig & 1)
-        const uint32_t e = gm_index_pairs(gm_lds(me_s + so * 8u));
-        const uint32_t t0 = gm_lds(v0_s + so * 4u) >> sh, t1 = gm_lds(v1_s + so * 4u) >> sh;
-        const uint32_t a0 = gm_lds(((t0 << 7) & 0x780u) | lane_or), a1 = gm_lds(((t1 << 7) & 0x780u) | lane_or);
-        const uint32_t a2 = gm_lds(((t0 >> 9) & 0x780u) | lane_or), a3 = gm_lds(((t1 >> 9) & 0x780u) | lane_or);
+    auto step = [&](uint32_t w0, uint32_t w1, uint32_t me_off, uint32_t x_off) {
+        const uint32_t e = gm_index_pairs(gm_lds(me_p + me_off));
+        const uint32_t a0 = gm_lds((__funnelshift_r(w0, w0, rot_lo) & 0x780u) | lane_or);
+        const uint32_t a1 = gm_lds((__funnelshift_r(w1, w1, rot_lo) & 0x780u) | lane_or);
+        const uint32_t a2 = gm_lds((__funnelshift_r(w0, w0, rot_hi) & 0x780u) | lane_or);
+        const uint32_t a3 = gm_lds((__funnelshift_r(w1, w1, rot_hi) & 0x780u) | lane_or);
         uint32_t b0, b1, b2, b3;
-        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(xq_s + so * 64u));
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(xq_p + x_off));
         asm volatile(
             "mma.sp::ordered_metadata.sync.aligned.m16n8k64.row.col.s32.s8.s8.s32 "
             "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9, %10, %11}, {%0, %1, %2, %3}, %12, 0x0;"
             : "+r"(c0), "+r"(c1), "+r"(c2), "+r"(c3)
             : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(b2), "r"(b3), "r"(e));
+    };
+    auto advance = [&](uint32_t steps) {
+        me_p += 8u * steps;
+        v0_p += 4u * steps;
+        xq_p += 64u * steps;
+    };
+    int st = s_begin;
+    for (; st < s_end && (st & 3) != 0; ++st) {  // up to the next multiple of four steps
+        step(gm_lds(v0_p), gm_lds(v0_p + v_half), 0u, 0u);
+        advance(1u);
     }
+    for (; st + 4 <= s_end; st += 4) {  // four steps share one 16-byte read of each row's sign words
+        uint4 w0, w1;
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w0.x), "=r"(w0.y), "=r"(w0.z), "=r"(w0.w) : "r"(v0_p));
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w1.x), "=r"(w1.y), "=r"(w1.z), "=r"(w1.w) : "r"(v0_p + v_half));
+        step(w0.x, w1.x, 0u, 0u);
+        step(w0.y, w1.y, 8u, 64u);
+        step(w0.z, w1.z, 16u, 128u);
+        step(w0.w, w1.w, 24u, 192u);
+        advance(4u);
+    }
+    for (; st < s_end; ++st) {
+        step(gm_lds(v0_p), gm_lds(v0_p + v_half), 0u, 0u);
+        advance(1u);
+    }
+    GM_STAMP(8);
     // column 0 of the tile: lanes with tig == 0 hold rows g (c0) and g + 8 (c2)
     if (tig == 0) {
-        red[warp * 16 + g] = c0;
-        red[warp * 16 + g + 8] = c2;
+        red[warp_u * 16 + g] = c0;
+        red[warp_u * 16 + g + 8] = c2;
     }
     __syncthreads();
+    GM_STAMP(9);
     if (tid < nrows_blk && tid < valid) {
         const int rblk = tid >> 4, r = tid & 15;
         int acc = 0;
-        for (int k = 0; k < a.ks; ++k) acc += red[(rblk * a.ks + k) * 16 + r];
+        for (int k = 0; k < a.ks; ++k) acc += red[((rblk << a.ks_log2) + k) * 16 + r];
         const int row = row0 + tid;
         if (a.out_mode == GM_OUT_I32) {
             static_cast<int32_t*>(a.y)[row] = acc;
@@ -205,6 +244,7 @@ __global__ void __launch_bounds__(kGmThreads, 4) gemv_mmasp_kernel(const GmArgs 
             }
         }
     }
+    GM_STAMP(15);
 }
 
 // Whether the layout can take this kernel: whole 16-byte sign rows (cols % 256 == 0), 16-byte aligned
@@ -223,9 +263,20 @@ int gemv_mmasp_launch(const char* name, const uint32_t* meta, const uint32_t* va
     a.meta = meta; a.values = values; a.x = x; a.y = y; a.y_acc = y_acc; a.d_absmax = d_absmax; a.gamma = gamma;
     a.out_mode = out_mode; a.rows = rows; a.cols = cols; a.meta_stride = meta_stride; a.values_stride = values_stride;
     a.steps = cols / 64;
+    // Warps per row block: long step ranges per warp amortise a warp's fixed cost (measured: about 20 steps
+    // per warp is best at 6912 x 2560), but a small matrix still has to give every SM a few warps.
+    static const int ks_env = [] {
+        const char* e = getenv("SPB_GEMV_MMA_KS");
+        return e ? atoi(e) : 0;
+    }();
+    const int row_blocks = (rows + 15) / 16;
     a.ks = 8;
+    while (a.ks > 1 && a.steps / a.ks < 16) a.ks >>= 1;
+    while (a.ks < 8 && row_blocks * a.ks < 2 * sm_count() && a.steps / (2 * a.ks) >= 8) a.ks <<= 1;
+    if (ks_env == 1 || ks_env == 2 || ks_env == 4 || ks_env == 8) a.ks = ks_env;
     while (a.ks > a.steps) a.ks >>= 1;
     a.rb = kGmWarps / a.ks;
+    a.ks_log2 = a.ks == 8 ? 3 : a.ks == 4 ? 2 : a.ks == 2 ? 1 : 0;
     a.spw = (a.steps + a.ks - 1) / a.ks;
     auto pitch = [](int words) { return words + ((4 - words % 32) + 32) % 32; };  // smallest >= words that is 4 mod 32
     a.mpitch = pitch(cols / 32);
@@ -241,13 +292,10 @@ int gemv_mmasp_launch(const char* name, const uint32_t* meta, const uint32_t* va
     return launch(name, gemv_mmasp_kernel, dim3(blocks), dim3(kGmThreads), smem, stream, a);
 }
 
-int gemv_mmasp_timeouts() {
-    int v = 0;
-    if (cudaMemcpyFromSymbol(&v, g_gemv_mma_timeouts, sizeof v) != cudaSuccess) {
-        cudaGetLastError();
-        return -1;
-    }
-    return v;
+#ifdef SPB_GT_TRACE
+extern "C" int spb_debug_gm_trace(long long* out) {
+    return cudaMemcpyFromSymbol(out, g_gm_trace, sizeof(long long) * 4 * 512 * 16) == cudaSuccess ? 0 : -1;
 }
+#endif
 
 }  // namespace spb

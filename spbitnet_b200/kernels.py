@@ -33,7 +33,7 @@ def set_pdl(enabled: bool) -> bool:
 
 
 def set_gemv_variant(variant: int) -> int:
-    """0 automatic, 1 unit kernel (latency form), 2 column-owner kernel (throughput form)."""
+    """0 automatic, 1 pair kernel, 2 per-group table kernel, 3 tcgen05 sparse kernel, 4 warp-level sparse MMA kernel."""
     return load().spb_set_gemv_variant(int(variant))
 
 
