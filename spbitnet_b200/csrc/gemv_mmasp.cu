@@ -24,6 +24,9 @@
 // metadata = the index pairs of one whole bitmap word (word tig / 2 of the step, row g + 8 (tig & 1));
 // B = x[64 s + 16 j + 4 tig ..] in register j, the same in all N = 8 columns (only column 0 is
 // read).  Partial sums of the KS warps meet in shared memory.  There is no spin-wait in the kernel.
+// Tried and dropped (slower): a form in which a warp keeps the x slices of four steps in registers and
+// walks over the row blocks (fewer shared-memory reads, but thin warps); a two-deep software pipeline
+// of the step loop; cp.async.bulk for the slab.  What pays is long step ranges per warp.
 #include <cstdlib>
 
 #include "spb_common.cuh"
@@ -259,6 +262,7 @@ bool gemv_mmasp_supported(const uint32_t* meta, const uint32_t* values, const in
 int gemv_mmasp_launch(const char* name, const uint32_t* meta, const uint32_t* values, const int8_t* x, void* y,
                       int32_t* y_acc, const float* d_absmax, float gamma, int out_mode, int rows, int cols,
                       int meta_stride, int values_stride, void* stream) {
+    auto pitch = [](int words) { return words + ((4 - words % 32) + 32) % 32; };  // smallest >= words that is 4 mod 32
     GmArgs a{};
     a.meta = meta; a.values = values; a.x = x; a.y = y; a.y_acc = y_acc; a.d_absmax = d_absmax; a.gamma = gamma;
     a.out_mode = out_mode; a.rows = rows; a.cols = cols; a.meta_stride = meta_stride; a.values_stride = values_stride;
@@ -278,7 +282,6 @@ int gemv_mmasp_launch(const char* name, const uint32_t* meta, const uint32_t* va
     a.rb = kGmWarps / a.ks;
     a.ks_log2 = a.ks == 8 ? 3 : a.ks == 4 ? 2 : a.ks == 2 ? 1 : 0;
     a.spw = (a.steps + a.ks - 1) / a.ks;
-    auto pitch = [](int words) { return words + ((4 - words % 32) + 32) % 32; };  // smallest >= words that is 4 mod 32
     a.mpitch = pitch(cols / 32);
     a.vpitch = pitch(cols / 64);
     const size_t smem = 2048 + kGmSignLutBytes + 16 + kGmWarps * 16 * 4 + static_cast<size_t>(cols) +
