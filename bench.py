@@ -34,8 +34,8 @@ sys.path.insert(0, str(ROOT))
 METRIC = "sparse_ternary_gemv_hbm_gbs_6912x2560"
 UNIT = "GB/s"
 NOMINAL_HBM_GBS = 8000.0
-# DRAM bytes one 6912x2560 GEMV launch moved under ncu (read 3.352 MB, write 0: y stays in L2)
-NCU_DRAM_BYTES_PER_LAUNCH = 3.352e6
+# DRAM bytes one 6912x2560 GEMV launch moved under ncu (read 3.337 MB, write 0: y stays in L2)
+NCU_DRAM_BYTES_PER_LAUNCH = 3.337e6
 
 
 def measured_peaks():
@@ -407,7 +407,7 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_kind": peak_kind, "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
                          "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this "
-                                           "kernel at 6912x2560 (profiles/gemv_pairs_6912x2560_ncu_full.md)",
+                                           "kernel at 6912x2560 (profiles/gemv_mmasp_6912x2560_ncu_full.md)",
                          "algorithmic_bytes_per_launch": per, "us_per_launch": per_launch_us,
                          "frac_of_8tbs": achieved / NOMINAL_HBM_GBS},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(x_host.numel()),
@@ -459,11 +459,17 @@ def bench_gemm(args, l2_bytes):
                         K.sparse_ternary_gemm_gpu(metas[i], vals[i], X, Y, r, c, n, case["meta_stride"], case["values_stride"])
                 run()
                 torch.cuda.synchronize()
+                # one CUDA graph of the `copies` calls (stream-ordered), so that the host's launch cost is not timed
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    run()
+                g.replay()
+                torch.cuda.synchronize()
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 reps = 3
                 e0.record()
                 for _ in range(reps):
-                    run()
+                    g.replay()
                 e1.record()
                 torch.cuda.synchronize()
                 us = e0.elapsed_time(e1) * 1e3 / (reps * copies)
@@ -473,8 +479,9 @@ def bench_gemm(args, l2_bytes):
             out[f"{r}x{c}_n{n}"] = row
         del metas, vals
     out["tc_timeouts"] = K.gemm_tc_timeouts()
-    out["what"] = ("spb_sparse_ternary_gemm per call; auto = tcgen05 kind::i8 form from n >= 16, SIMT below; "
-                   "dense_equiv_tops counts 2*M*K*N")
+    out["what"] = ("spb_sparse_ternary_gemm, us per call as a graph of stream-ordered calls over cold weights; auto = "
+                   "warp-level sparse MMA (mma.sp) up to n = 32, tcgen05.mma.sp above; tc_dense = tcgen05 kind::i8 on "
+                   "expanded int8 tiles; dense_equiv_tops counts 2*M*K*N")
     return out
 
 
@@ -513,7 +520,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--chains", type=int, default=8, help="independent branches per step graph")
-    ap.add_argument("--variant", type=int, default=0, help="GEMV kernel: 0 auto, 1 unit, 2 column-owner")
+    ap.add_argument("--variant", type=int, default=0,
+                    help="GEMV kernel: 0 auto (warp-level sparse MMA), 1 SIMT pair, 2 SIMT group table, 3 tcgen05, 4 mma.sp")
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")

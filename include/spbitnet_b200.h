@@ -121,10 +121,12 @@ int spb_sparse_ternary_gemm(const uint32_t* meta, const uint32_t* values, const 
                             int32_t* Y, int rows, int cols, int n, int meta_row_stride,
                             int values_row_stride, void* stream);
 
-/* Which form spb_sparse_ternary_gemm uses: 0 = automatic (tcgen05 tensor-core form above 32 batch
- * rows when the layout allows it, SIMT form otherwise), 1 = SIMT form, 2 = dense tensor-core form
- * (weights expanded to int8 tiles) for any n, 3 = sparse tensor-core form (tcgen05.mma.sp: sign bytes
- * as the compressed operand, bitmaps as index pairs in tensor memory) for any n.
+/* Which form spb_sparse_ternary_gemm uses: 0 (default) = automatic: up to 32 batch rows the warp-level
+ * sparse MMA form (mma.sp m16n8k64, operands re-encoded in registers; needs cols % 256 == 0, row strides
+ * that are multiples of 4 words and 16-byte aligned meta / values / X), above that the tcgen05 sparse form
+ * (tcgen05.mma.sp: sign bytes as the compressed operand, index pairs in tensor memory), the SIMT form where
+ * the layout allows neither; 1 = SIMT form, 2 = tcgen05 dense form (weights expanded to int8 tiles),
+ * 3 = tcgen05 sparse form for any n, 4 = warp-level sparse MMA form where it applies.
  * Results are identical.  Returns the previous setting. */
 int spb_set_gemm_variant(int variant);
 /* Number of blocks of the tensor-core kernels (GEMM and GEMV) whose bounded device-side wait ran out since the library

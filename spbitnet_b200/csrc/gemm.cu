@@ -147,7 +147,14 @@ int gemm_tc_launch(const uint32_t* meta, const uint32_t* values, const int8_t* X
 int gemm_tcsp_launch(const uint32_t* meta, const uint32_t* values, const int8_t* X, int32_t* Y, int rows, int cols,
                      int n, int meta_stride, int values_stride, void* stream);
 
-// 0 automatic, 1 SIMT form, 2 dense tensor-core form, 3 sparse tensor-core form (2 and 3 whenever the layout allows)
+bool gemm_mmasp_supported(const uint32_t* meta, const uint32_t* values, const int8_t* X, int rows, int cols, int n,
+                          int meta_stride, int values_stride);
+int gemm_mmasp_launch(const uint32_t* meta, const uint32_t* values, const int8_t* X, int32_t* Y, int rows, int cols,
+                      int n, int meta_stride, int values_stride, void* stream);
+
+// 0 automatic (up to 32 batch rows: warp-level sparse MMA form; above: tcgen05 sparse form; SIMT where the layout
+// allows neither), 1 SIMT form, 2 tcgen05 dense form, 3 tcgen05 sparse form, 4 warp-level sparse MMA form
+// (2, 3 and 4 whenever the layout allows)
 static int g_gemm_variant = 0;
 
 }  // namespace spb
@@ -175,10 +182,12 @@ extern "C" int spb_sparse_ternary_gemm(const uint32_t* meta, const uint32_t* val
     const size_t x_bytes = static_cast<size_t>(kBatchTile) * cols;
     const bool fast = cols % 128 == 0 && cols / 128 <= 512 && meta_row_stride % 4 == 0 &&
                       values_row_stride % 2 == 0 && al(meta, 16) && al(values, 8) && al(X, 16);
-    // tensor cores above 32 batch rows (measured cross-over with the SIMT form on B200)
-    if (fast && g_gemm_variant == 3)
+    if ((g_gemm_variant == 0 || g_gemm_variant == 4) &&
+        gemm_mmasp_supported(meta, values, X, rows, cols, n, meta_row_stride, values_row_stride))
+        return gemm_mmasp_launch(meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream);
+    if (fast && (g_gemm_variant == 3 || ((g_gemm_variant == 0 || g_gemm_variant == 4) && n > 32)))
         return gemm_tcsp_launch(meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream);
-    if (fast && g_gemm_variant != 1 && (n > 32 || g_gemm_variant == 2))
+    if (fast && g_gemm_variant == 2)
         return gemm_tc_launch(meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream);
     if (!fast) {
         const long long warps = static_cast<long long>(rows) * n;

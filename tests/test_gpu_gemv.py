@@ -199,9 +199,10 @@ def test_unpack_matches_oracle(rows, cols):
         assert (out.read(np.int8).reshape(rows, cols) == want).all()
 
 
-@pytest.fixture(params=[1, 2, 3], ids=["simt", "tcgen05", "tcgen05sp"])
+@pytest.fixture(params=[0, 1, 2, 3], ids=["auto", "simt", "tcgen05", "tcgen05sp"])
 def gemm_variant(request):
-    """1 = SIMT form, 2 = dense tcgen05 form, 3 = sparse tcgen05 form (forced for every n the layout allows)."""
+    """0 = automatic (warp-level sparse MMA up to 32 batch rows, sparse tcgen05 above), 1 = SIMT form,
+    2 = dense tcgen05 form, 3 = sparse tcgen05 form (forced for every n the layout allows)."""
     old = K.set_gemm_variant(request.param)
     yield request.param
     K.set_gemm_variant(old)
@@ -210,7 +211,8 @@ def gemm_variant(request):
 
 @pytest.mark.parametrize("rows,cols,n", [(64, 256, 16), (64, 256, 1), (37, 132, 5), (300, 2560, 4), (96, 6912, 19),
                                           (2048, 2048, 32), (128, 512, 64), (128, 128, 16), (129, 384, 257),
-                                          (1000, 1024, 300), (256, 2560, 256)])
+                                          (1000, 1024, 300), (256, 2560, 256), (100, 256, 8), (500, 2560, 9),
+                                          (333, 512, 24), (64, 6912, 32), (2560, 6912, 17), (48, 768, 3)])
 def test_gemm_matches_oracle(rows, cols, n, gemm_variant):
     # tests/test_cusparselt.cu:127-274: exact int32 vs the CPU int8 GEMM
     case = synth.gemm_case(rows, cols, n, seed=n)
