@@ -450,8 +450,8 @@ def bench_gemm(args, l2_bytes):
             X = torch.randint(-127, 128, (n, c), dtype=torch.int8, device="cuda")
             Y = torch.empty((n, r), dtype=torch.int32, device="cuda")
             row = {}
-            for name, variant in (("auto", 0), ("simt", 1), ("tc_dense", 2), ("tc_sparse", 3)):
-                if (variant == 1 and n > 64) or (variant >= 2 and n < 16):
+            for name, variant in (("auto", 0), ("simt", 1), ("tc_dense", 2), ("tc_sparse", 3), ("mma_sp", 4)):
+                if (variant == 1 and n > 64) or (variant in (2, 3) and n < 16) or (variant == 4 and n > 256):
                     continue
                 K.set_gemm_variant(variant)
                 def run():

@@ -148,7 +148,7 @@ int gemm_tcsp_launch(const uint32_t* meta, const uint32_t* values, const int8_t*
                      int n, int meta_stride, int values_stride, void* stream);
 
 bool gemm_mmasp_supported(const uint32_t* meta, const uint32_t* values, const int8_t* X, int rows, int cols, int n,
-                          int meta_stride, int values_stride);
+                          int meta_stride, int values_stride, int max_n);
 int gemm_mmasp_launch(const uint32_t* meta, const uint32_t* values, const int8_t* X, int32_t* Y, int rows, int cols,
                       int n, int meta_stride, int values_stride, void* stream);
 
@@ -156,6 +156,7 @@ int gemm_mmasp_launch(const uint32_t* meta, const uint32_t* values, const int8_t
 // allows neither), 1 SIMT form, 2 tcgen05 dense form, 3 tcgen05 sparse form, 4 warp-level sparse MMA form
 // (2, 3 and 4 whenever the layout allows)
 static int g_gemm_variant = 0;
+constexpr int kMmaSpAutoMaxN = 32;
 
 }  // namespace spb
 
@@ -182,8 +183,12 @@ extern "C" int spb_sparse_ternary_gemm(const uint32_t* meta, const uint32_t* val
     const size_t x_bytes = static_cast<size_t>(kBatchTile) * cols;
     const bool fast = cols % 128 == 0 && cols / 128 <= 512 && meta_row_stride % 4 == 0 &&
                       values_row_stride % 2 == 0 && al(meta, 16) && al(values, 8) && al(X, 16);
+    // up to 32 batch rows the warp-level form always wins; up to 64 it still does when the tcgen05 form, with
+    // its tiles of 128 weight rows, would leave most SMs idle (measured at 2560x6912: 18.8 against 30.1 us)
+    const int mma_auto_max_n = (rows + 127) / 128 < sm_count() / 4 ? 64 : kMmaSpAutoMaxN;
     if ((g_gemm_variant == 0 || g_gemm_variant == 4) &&
-        gemm_mmasp_supported(meta, values, X, rows, cols, n, meta_row_stride, values_row_stride))
+        gemm_mmasp_supported(meta, values, X, rows, cols, n, meta_row_stride, values_row_stride,
+                             g_gemm_variant == 4 ? 4096 : mma_auto_max_n))
         return gemm_mmasp_launch(meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream);
     if (fast && (g_gemm_variant == 3 || ((g_gemm_variant == 0 || g_gemm_variant == 4) && n > 32)))
         return gemm_tcsp_launch(meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream);

@@ -213,12 +213,12 @@ __global__ void __launch_bounds__(kGqThreads, 2) gemm_mmasp_kernel(const GqArgs 
     }
 }
 
-// Whether the small-batch form applies: up to 32 activation rows, whole 16-byte sign rows (cols % 256 == 0),
+// Whether the small-batch form applies: up to max_n activation rows, whole 16-byte sign rows (cols % 256 == 0),
 // 16-byte aligned rows everywhere.
 bool gemm_mmasp_supported(const uint32_t* meta, const uint32_t* values, const int8_t* X, int rows, int cols, int n,
-                          int meta_stride, int values_stride) {
+                          int meta_stride, int values_stride, int max_n) {
     auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
-    return rows > 0 && n > 0 && n <= 8 * kGqMaxTiles && cols > 0 && cols % 256 == 0 && cols <= 16384 &&
+    return rows > 0 && n > 0 && n <= max_n && cols > 0 && cols % 256 == 0 && cols <= 16384 &&
            meta_stride % 4 == 0 && values_stride % 4 == 0 && al16(meta) && al16(values) && al16(X);
 }
 
