@@ -246,7 +246,7 @@ int gemm_mmasp_launch(const uint32_t* meta, const uint32_t* values, const int8_t
     // fit in about 100 KB next to the slab, else fewer and more blocks along y
     const int tiles = (n + 7) / 8;
     const size_t slab = static_cast<size_t>(16 * a.rb) * (a.mpitch + a.vpitch) * 4;
-    int nt = tiles;
+    int nt = tiles < kGqMaxTiles ? tiles : kGqMaxTiles;
     auto xbytes = [&](int t) {
         const size_t act = static_cast<size_t>(8 * t) * a.xpitch, part = static_cast<size_t>(kGqWarps) * 16 * 8 * t * 4;
         return act > part ? act : part;

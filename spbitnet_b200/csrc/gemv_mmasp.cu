@@ -35,7 +35,11 @@ namespace spb {
 
 constexpr int kGmThreads = 256;
 constexpr int kGmWarps = kGmThreads / 32;
-constexpr int kGmSignLutBytes = 16 * 32 * 4;  // 2 KB on a 2 KB boundary
+// Blocks per SM the register allocation is held to: 48 registers; shared memory (38 KB per block of 64 rows at
+// 2560 columns) allows the same five.
+#ifndef SPB_GEMV_MMA_MIN_BLOCKS
+#define SPB_GEMV_MMA_MIN_BLOCKS 5
+#endif
 
 enum { GM_OUT_I32 = 0, GM_OUT_F32 = 1, GM_OUT_F16 = 2 };
 
@@ -55,7 +59,7 @@ struct GmArgs {
     int ks_log2;
     int rb;         // row blocks per thread block = 8 / ks
     int spw;        // steps per warp
-    int mpitch;     // shared-memory row pitch of the bitmap words, in words (= 4 mod 32)
+    int mpitch;     // shared-memory row pitch of the bitmap words, in words (an odd multiple of 4)
     int vpitch;     // same for the sign words
 };
 
@@ -93,16 +97,21 @@ __device__ __forceinline__ uint32_t gm_lds(uint32_t addr) {
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
 }
+// table read: `off` = (nibble << 7) | (lane << 2); the table's own address is added by the load instruction
+__device__ __forceinline__ uint32_t gm_tab(uint32_t tab_s, uint32_t off) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(tab_s + off));
+    return v;
+}
 
-__global__ void __launch_bounds__(kGmThreads, 4) gemv_mmasp_kernel(const GmArgs a) {
-    extern __shared__ uint8_t gm_raw[];
-    // 2 KB-aligned: [sign table 2 KB][16 B unused][partial sums 8 warps x 16 ints][x, permuted: cols bytes]
-    //               [bitmap rows: 16 rb x mpitch words][sign rows: 16 rb x vpitch words]
-    const uint32_t raw_s = static_cast<uint32_t>(__cvta_generic_to_shared(gm_raw));
-    const uint32_t base_s = (raw_s + 2047u) & ~2047u;
-    uint8_t* base = gm_raw + (base_s - raw_s);
-    volatile int* red = reinterpret_cast<volatile int*>(base + kGmSignLutBytes + 16);
-    const uint32_t xs_s = base_s + kGmSignLutBytes + 16 + kGmWarps * 16 * 4;
+__global__ void __launch_bounds__(kGmThreads, SPB_GEMV_MMA_MIN_BLOCKS) gemv_mmasp_kernel(const GmArgs a) {
+    // static: the sign table (entry (nibble n, lane l) at word n * 32 + l), the partial sums of the eight warps
+    __shared__ __align__(16) uint32_t sgn_tab[16 * 32];
+    __shared__ int red[kGmWarps * 16];
+    // dynamic: [x, permuted: cols bytes][bitmap rows: 16 rb x mpitch words][sign rows: 16 rb x vpitch words]
+    extern __shared__ __align__(16) uint8_t gm_raw[];
+    const uint32_t tab_s = static_cast<uint32_t>(__cvta_generic_to_shared(sgn_tab));
+    const uint32_t xs_s = static_cast<uint32_t>(__cvta_generic_to_shared(gm_raw));
     const uint32_t ms_s = xs_s + static_cast<uint32_t>(a.cols);
     const int nrows_blk = 16 * a.rb;
     const uint32_t vs_s = ms_s + static_cast<uint32_t>(nrows_blk * a.mpitch) * 4u;
@@ -140,7 +149,7 @@ __global__ void __launch_bounds__(kGmThreads, 4) gemv_mmasp_kernel(const GmArgs 
     for (int j = 0; j < 2; ++j) {
         const uint32_t i = tid + j * kGmThreads;
         const uint32_t t = ((i >> 5) * 0x00204081u) & 0x01010101u;
-        asm volatile("st.shared.u32 [%0], %1;" ::"r"(base_s + i * 4u), "r"((t * 0xFEu) | 0x01010101u) : "memory");
+        sgn_tab[i] = (t * 0xFEu) | 0x01010101u;
     }
 
     const int g = lane >> 2, tig = lane & 3;
@@ -149,7 +158,7 @@ __global__ void __launch_bounds__(kGmThreads, 4) gemv_mmasp_kernel(const GmArgs 
     const int warp_u = __shfl_sync(0xFFFFFFFFu, warp, 0);
     const int rbi = warp_u >> a.ks_log2, kq = warp_u & (a.ks - 1);
     const int s_begin = kq * a.spw, s_end = min(a.steps, s_begin + a.spw);
-    const uint32_t lane_or = base_s | (static_cast<uint32_t>(lane) << 2);
+    const uint32_t lane_or = static_cast<uint32_t>(lane) << 2;  // byte offset of the lane's column of the table
     // rotations that bring sign nibble tig (compressed columns 4 tig..) and nibble 4 + tig (16 + 4 tig..) of a
     // sign word to bits 7..10, where they index the table
     const uint32_t rot_lo = (static_cast<uint32_t>(tig) * 4u + 25u) & 31u, rot_hi = (static_cast<uint32_t>(tig) * 4u + 9u) & 31u;
@@ -186,10 +195,10 @@ __global__ void __launch_bounds__(kGmThreads, 4) gemv_mmasp_kernel(const GmArgs 
     int c0 = 0, c1 = 0, c2 = 0, c3 = 0;
     auto step = [&](uint32_t w0, uint32_t w1, uint32_t me_off, uint32_t x_off) {
         const uint32_t e = gm_index_pairs(gm_lds(me_p + me_off));
-        const uint32_t a0 = gm_lds((__funnelshift_r(w0, w0, rot_lo) & 0x780u) | lane_or);
-        const uint32_t a1 = gm_lds((__funnelshift_r(w1, w1, rot_lo) & 0x780u) | lane_or);
-        const uint32_t a2 = gm_lds((__funnelshift_r(w0, w0, rot_hi) & 0x780u) | lane_or);
-        const uint32_t a3 = gm_lds((__funnelshift_r(w1, w1, rot_hi) & 0x780u) | lane_or);
+        const uint32_t a0 = gm_tab(tab_s, (__funnelshift_r(w0, w0, rot_lo) & 0x780u) | lane_or);
+        const uint32_t a1 = gm_tab(tab_s, (__funnelshift_r(w1, w1, rot_lo) & 0x780u) | lane_or);
+        const uint32_t a2 = gm_tab(tab_s, (__funnelshift_r(w0, w0, rot_hi) & 0x780u) | lane_or);
+        const uint32_t a3 = gm_tab(tab_s, (__funnelshift_r(w1, w1, rot_hi) & 0x780u) | lane_or);
         uint32_t b0, b1, b2, b3;
         asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(xq_p + x_off));
         asm volatile(
@@ -262,7 +271,9 @@ bool gemv_mmasp_supported(const uint32_t* meta, const uint32_t* values, const in
 int gemv_mmasp_launch(const char* name, const uint32_t* meta, const uint32_t* values, const int8_t* x, void* y,
                       int32_t* y_acc, const float* d_absmax, float gamma, int out_mode, int rows, int cols,
                       int meta_stride, int values_stride, void* stream) {
-    auto pitch = [](int words) { return words + ((4 - words % 32) + 32) % 32; };  // smallest >= words that is 4 mod 32
+    // smallest pitch >= words that is an odd multiple of four words: eight consecutive rows then start on eight
+    // different groups of four banks, and rows stay 16-byte aligned
+    auto pitch = [](int words) { return words % 8 == 4 ? words : words + ((4 - words % 8) + 8) % 8; };
     GmArgs a{};
     a.meta = meta; a.values = values; a.x = x; a.y = y; a.y_acc = y_acc; a.d_absmax = d_absmax; a.gamma = gamma;
     a.out_mode = out_mode; a.rows = rows; a.cols = cols; a.meta_stride = meta_stride; a.values_stride = values_stride;
@@ -284,7 +295,7 @@ int gemv_mmasp_launch(const char* name, const uint32_t* meta, const uint32_t* va
     a.spw = (a.steps + a.ks - 1) / a.ks;
     a.mpitch = pitch(cols / 32);
     a.vpitch = pitch(cols / 64);
-    const size_t smem = 2048 + kGmSignLutBytes + 16 + kGmWarps * 16 * 4 + static_cast<size_t>(cols) +
+    const size_t smem = static_cast<size_t>(cols) +
                         static_cast<size_t>(16 * a.rb) * (a.mpitch + a.vpitch) * 4;
     cudaError_t err = cudaFuncSetAttribute(gemv_mmasp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (err != cudaSuccess) {
