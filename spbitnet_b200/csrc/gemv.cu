@@ -746,6 +746,164 @@ __global__ void __launch_bounds__(kThreads, (IN >= IN_RESNORM) ? 2 : 4) gemv_pai
     }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// The tensor-core form with the activation producers in front (see gemv_mmasp.cu for the scheme and the
+// operand layouts of mma.sp m16n8k64): up to kMaxMats matrices per launch, any IN_* producer, any OUT_*.
+// A block owns 16 * rb rows of one matrix and the whole K extent; its raw slab arrives by 16-byte
+// cp.async before the dependency wait; after it the block produces the int8 activation vector exactly as
+// the SIMT kernel does (produce_x), re-orders it for the B registers and runs the step loop.
+struct MmaGeom {
+    int steps;    // cols / 64
+    int ks;       // warps per row block (power of two <= 8)
+    int ks_log2;
+    int rb;       // row blocks per thread block = 8 / ks
+    int spw;      // steps per warp
+    int mpitch;   // shared-memory row pitch of the bitmap words, in words (an odd multiple of 4)
+    int vpitch;   // same for the sign words
+};
+
+__device__ __forceinline__ uint32_t mma_index_pairs(uint32_t m) {
+    // eight bitmaps (two of four bits set each) -> eight index pairs {low index | high index << 2}
+    const uint32_t mr = m >> 1, ml = m << 1;
+    const uint32_t t1 = (0x11111111u & (~m & mr)) | (~0x11111111u & (mr | ~m));
+    const uint32_t t2 = (0x22222222u & (~ml & ~m)) | (~0x22222222u & (m | ml));
+    return (t1 & 0x55555555u) | (t2 & 0xAAAAAAAAu);
+}
+
+template <int IN, int OUT>
+__global__ void __launch_bounds__(kThreads, (IN >= IN_RESNORM) ? 2 : 4) gemv_mma_kernel(const GemvArgs a, const MmaGeom geo) {
+    __shared__ __align__(16) uint32_t sgn_tab[16 * 32];  // entry (nibble n, lane l) at word n * 32 + l
+    __shared__ int redi[8 * 16];
+    // dynamic: [x int8, swizzled as produce_x writes it: cols][half scratch of the normalising producers: 2 cols]
+    //          [red: 64 floats][x in B-register order: cols][bitmap rows][sign rows]
+    extern __shared__ __align__(128) uint8_t msmem[];
+    const int hb = (IN >= IN_RESNORM) ? 2 * a.cols : 0;
+    uint4* xs_sw = reinterpret_cast<uint4*>(msmem);
+    float* red = reinterpret_cast<float*>(msmem + a.cols + hb);
+    const uint32_t dyn_s = smem_u32(msmem);
+    const uint32_t tab_s = smem_u32(sgn_tab);
+    const uint32_t xs_s = dyn_s + static_cast<uint32_t>(a.cols + hb) + 256u;
+    const uint32_t ms_s = xs_s + static_cast<uint32_t>(a.cols);
+    const int nrows_blk = 16 * geo.rb;
+    const uint32_t vs_s = ms_s + static_cast<uint32_t>(nrows_blk * geo.mpitch) * 4u;
+
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xFFFFFFFFu, tid >> 5, 0);  // through a shuffle: known to be uniform over the warp
+    int mi = 0;
+    if (a.nmat > 1 && static_cast<int>(blockIdx.x) >= a.mat[1].blk_begin) mi = 1;
+    if (a.nmat > 2 && static_cast<int>(blockIdx.x) >= a.mat[2].blk_begin) mi = 2;
+    const GemvMat& M = a.mat[mi];
+    const int row0 = (blockIdx.x - M.blk_begin) * nrows_blk;
+    const int valid = min(nrows_blk, M.rows - row0);
+
+    // the raw slab: a warp per row, consecutive lanes on consecutive 16-byte chunks (bitmaps, then signs)
+    {
+        const int mch = a.cols >> 7, cpr = mch + (a.cols >> 8);
+        for (int k = lane; k < cpr; k += 32) {
+            const bool is_m = k < mch;
+            const uint8_t* src = is_m ? reinterpret_cast<const uint8_t*>(M.meta) + k * 16
+                                      : reinterpret_cast<const uint8_t*>(M.values) + (k - mch) * 16;
+            const size_t src_pitch = static_cast<size_t>(is_m ? M.meta_stride : M.values_stride) * 4u;
+            const uint32_t dst = is_m ? ms_s + static_cast<uint32_t>(k) * 16u : vs_s + static_cast<uint32_t>(k - mch) * 16u;
+            const uint32_t dst_pitch = static_cast<uint32_t>(is_m ? geo.mpitch : geo.vpitch) * 4u;
+            src += static_cast<size_t>(row0 + warp) * src_pitch;
+            for (int r = warp; r < valid; r += 8) {
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + static_cast<uint32_t>(r) * dst_pitch), "l"(src)
+                             : "memory");
+                src += 8 * src_pitch;
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {  // byte b of an entry = -1 if bit b of the nibble is set, else +1
+        const uint32_t i = tid + j * kThreads;
+        const uint32_t t = ((i >> 5) * 0x00204081u) & 0x01010101u;
+        sgn_tab[i] = (t * 0xFEu) | 0x01010101u;
+    }
+
+    const int g = lane >> 2, tig = lane & 3;
+    const int rbi = warp >> geo.ks_log2, kq = warp & (geo.ks - 1);
+    const int s_begin = kq * geo.spw, s_end = min(geo.steps, s_begin + geo.spw);
+    const uint32_t lane_or = static_cast<uint32_t>(lane) << 2;
+    const uint32_t rot_lo = (static_cast<uint32_t>(tig) * 4u + 25u) & 31u, rot_hi = (static_cast<uint32_t>(tig) * 4u + 9u) & 31u;
+    uint32_t me_p = ms_s + static_cast<uint32_t>((rbi * 16 + g + 8 * (tig & 1)) * geo.mpitch + (tig >> 1) + 2 * s_begin) * 4u;
+    uint32_t v0_p = vs_s + static_cast<uint32_t>((rbi * 16 + g) * geo.vpitch + s_begin) * 4u;
+    const uint32_t v_half = static_cast<uint32_t>(8 * geo.vpitch) * 4u;
+    uint32_t xq_p = xs_s + static_cast<uint32_t>(tig) * 16u + static_cast<uint32_t>(s_begin) * 64u;
+
+    // ---- after the dependency: the activation vector --------------------------------------------------
+    grid_dep_wait();
+    grid_dep_launch();  // the successor is let in only now (see gemv_mmasp.cu)
+    const float absmax = produce_x<IN, OUT>(a, xs_sw, reinterpret_cast<__half*>(xs_sw) + (a.cols >> 1), red,
+                                             blockIdx.x == 0);
+    __syncthreads();
+    // x in B-register order: xs[step][tig][j][0..3] = x[64 step + 16 j + 4 tig ..+3]
+    for (int q = tid; q < (a.cols >> 4); q += kThreads) {
+        const int c = q >> 3, i = q & 7;
+        const uint4 xv = xs_sw[(c << 3) + (i ^ (c & 7))];
+        const uint32_t d = xs_s + (static_cast<uint32_t>(q) >> 2) * 64u + (static_cast<uint32_t>(q) & 3u) * 4u;
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(d), "r"(xv.x) : "memory");
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(d + 16u), "r"(xv.y) : "memory");
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(d + 32u), "r"(xv.z) : "memory");
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(d + 48u), "r"(xv.w) : "memory");
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();  // the slab, the table and x are visible
+
+    int c0 = 0, c1 = 0, c2 = 0, c3 = 0;
+    auto step = [&](uint32_t w0, uint32_t w1, uint32_t me_off, uint32_t x_off) {
+        const uint32_t e = mma_index_pairs(lds32(me_p + me_off));
+        const uint32_t a0 = lds32(tab_s + ((__funnelshift_r(w0, w0, rot_lo) & 0x780u) | lane_or));
+        const uint32_t a1 = lds32(tab_s + ((__funnelshift_r(w1, w1, rot_lo) & 0x780u) | lane_or));
+        const uint32_t a2 = lds32(tab_s + ((__funnelshift_r(w0, w0, rot_hi) & 0x780u) | lane_or));
+        const uint32_t a3 = lds32(tab_s + ((__funnelshift_r(w1, w1, rot_hi) & 0x780u) | lane_or));
+        uint32_t b0, b1, b2, b3;
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(xq_p + x_off));
+        asm volatile(
+            "mma.sp::ordered_metadata.sync.aligned.m16n8k64.row.col.s32.s8.s8.s32 "
+            "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9, %10, %11}, {%0, %1, %2, %3}, %12, 0x0;"
+            : "+r"(c0), "+r"(c1), "+r"(c2), "+r"(c3)
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(b2), "r"(b3), "r"(e));
+    };
+    auto advance = [&](uint32_t steps) {
+        me_p += 8u * steps;
+        v0_p += 4u * steps;
+        xq_p += 64u * steps;
+    };
+    int st = s_begin;
+    for (; st < s_end && (st & 3) != 0; ++st) {
+        step(lds32(v0_p), lds32(v0_p + v_half), 0u, 0u);
+        advance(1u);
+    }
+    for (; st + 4 <= s_end; st += 4) {  // four steps share one 16-byte read of each row's sign words
+        uint4 w0, w1;
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w0.x), "=r"(w0.y), "=r"(w0.z), "=r"(w0.w) : "r"(v0_p));
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w1.x), "=r"(w1.y), "=r"(w1.z), "=r"(w1.w) : "r"(v0_p + v_half));
+        step(w0.x, w1.x, 0u, 0u);
+        step(w0.y, w1.y, 8u, 64u);
+        step(w0.z, w1.z, 16u, 128u);
+        step(w0.w, w1.w, 24u, 192u);
+        advance(4u);
+    }
+    for (; st < s_end; ++st) {
+        step(lds32(v0_p), lds32(v0_p + v_half), 0u, 0u);
+        advance(1u);
+    }
+    if (tig == 0) {  // column 0 of the tile: rows g (c0) and g + 8 (c2)
+        redi[warp * 16 + g] = c0;
+        redi[warp * 16 + g + 8] = c2;
+    }
+    __syncthreads();
+    const float dq = (OUT != OUT_I32) ? dequant_scale(M.gamma, absmax) : 0.0f;
+    if (tid < valid) {
+        const int rblk = tid >> 4, r = tid & 15;
+        int acc = 0;
+        for (int k = 0; k < geo.ks; ++k) acc += redi[((rblk << geo.ks_log2) + k) * 16 + r];
+        store_out(M, row0 + tid, acc, dq, OUT);
+    }
+}
+
 // Any cols % 4 == 0, any stride, any alignment: a warp per row, a group per lane per
 // step, activations straight from global memory.  Correctness path for layouts the
 // unit kernel does not take; not tuned.
@@ -903,6 +1061,46 @@ static int run_gemv(const char* name, const MatDesc* mats, int nmat, const XDesc
         blocks += (m.rows + rpc - 1) / rpc;
     }
     int rc;
+    // tensor-core form with producers: every matrix must have 16-byte aligned rows in both arrays
+    // (opt-in: in a dependent chain, which is what a decode step is, the SIMT kernel is quicker because it expands
+    // its weights before the dependency wait; measured 530 against 614 tok/s)
+    bool mma_ok = fast && g_gemv_variant == 4 && cols % 256 == 0 && cols <= 16384 && !(IN == IN_I8 && nmat == 1);
+    for (int i = 0; i < nmat && mma_ok; ++i)
+        mma_ok = mats[i].rows == 0 || (mats[i].meta_stride % 4 == 0 && mats[i].values_stride % 4 == 0 &&
+                                       aligned(mats[i].meta, 16) && aligned(mats[i].values, 16));
+    if (mma_ok) {
+        MmaGeom geo{};
+        geo.steps = cols / 64;
+        int row_blocks = 0;
+        for (int i = 0; i < nmat; ++i) row_blocks += (mats[i].rows + 15) / 16;
+        geo.ks = 8;
+        while (geo.ks > 1 && geo.steps / geo.ks < 16) geo.ks >>= 1;
+        while (geo.ks < 8 && row_blocks * geo.ks < 2 * sms && geo.steps / (2 * geo.ks) >= 8) geo.ks <<= 1;
+        while (geo.ks > geo.steps) geo.ks >>= 1;
+        geo.rb = 8 / geo.ks;
+        geo.ks_log2 = geo.ks == 8 ? 3 : geo.ks == 4 ? 2 : geo.ks == 2 ? 1 : 0;
+        geo.spw = (geo.steps + geo.ks - 1) / geo.ks;
+        auto pitch = [](int words) { return words % 8 == 4 ? words : words + ((4 - words % 8) + 8) % 8; };
+        geo.mpitch = pitch(cols / 32);
+        geo.vpitch = pitch(cols / 64);
+        a.rpc = 16 * geo.rb;
+        int nblk = 0;
+        for (int i = 0; i < nmat; ++i) {
+            a.mat[i].blk_begin = nblk;
+            nblk += (mats[i].rows + a.rpc - 1) / a.rpc;
+        }
+        const size_t msmem = static_cast<size_t>(cols) * (IN >= IN_RESNORM ? 3 : 1) + 256 + cols +
+                             static_cast<size_t>(16 * geo.rb) * (geo.mpitch + geo.vpitch) * 4;
+        if (msmem <= 200 * 1024) {
+            if ((rc = ensure_smem(gemv_mma_kernel<IN, OUT>, msmem))) return rc;
+            return launch(name, gemv_mma_kernel<IN, OUT>, dim3(nblk), dim3(kThreads), msmem, stream, a, geo);
+        }
+        a.rpc = rpc;  // does not fit: back to the SIMT form
+        for (int i = 0, b = 0; i < nmat; ++i) {
+            a.mat[i].blk_begin = b;
+            b += (mats[i].rows + rpc - 1) / rpc;
+        }
+    }
     if constexpr (IN == IN_I8) {
         if (fast && nmat == 1 && (g_gemv_variant == 0 || g_gemv_variant == 4) &&
             gemv_mmasp_supported(mats[0].meta, mats[0].values, static_cast<const int8_t*>(xd.x), mats[0].rows, cols,
