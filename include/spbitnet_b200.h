@@ -233,6 +233,17 @@ int spb_unpack_to_int8_host(const uint32_t* meta, const uint32_t* values, int ro
  * give an unspecified (but memory-safe) result otherwise. */
 int spb_validate_packed(const uint32_t* meta, int rows, int cols, int meta_row_stride);
 
+/* Conversion on the GPU (the pruning + quantisation + packing steps of python/convert_model.py:88-138,
+ * 141-207, 270-283 in one kernel): weights is a device float32 matrix (rows x cols, weights_row_stride
+ * floats between rows, cols % 4 == 0); meta / values receive the packed arrays, byte-identical to what the
+ * converter writes (two largest |w| per group of four, the higher index on ties; a kept weight is -1 exactly
+ * when w < 0).  abs_sum, if not NULL, is a device double that the kernel ADDS sum |w| to (zero it first):
+ * gamma = abs_sum / (rows * cols).  The sum is accumulated in double precision and may differ from numpy's
+ * float32 mean in the last bits.  The reference converts on the CPU only; this entry point has no GPU
+ * counterpart there. */
+int spb_prune_pack_gpu(const float* weights, int rows, int cols, size_t weights_row_stride, uint32_t* meta,
+                       uint32_t* values, int meta_row_stride, int values_row_stride, double* abs_sum, void* stream);
+
 /* ---- engine: include/spbitnet/inference.h:23-70, src/inference.cu ----------------- */
 
 typedef struct spb_engine spb_engine;

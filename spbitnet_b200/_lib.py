@@ -89,6 +89,7 @@ SIGNATURES = {
     "spb_pack_with_pruning": (_i, [_p, _i, _i, _p, _p]),
     "spb_unpack_to_int8_host": (_i, [_p, _p, _i, _i, _i, _i, _p]),
     "spb_validate_packed": (_i, [_p, _i, _i, _i]),
+    "spb_prune_pack_gpu": (_i, [_p, _i, _i, C.c_size_t, _p, _p, _i, _i, _p, _p]),
     "spb_engine_create": (_p, [C.POINTER(ModelConfig)]),
     "spb_engine_destroy": (None, [_p]),
     "spb_engine_set_linear": (_i, [_p, _i, _i, _p, _p, _f, _i, _i, _i, _i]),

@@ -24,6 +24,8 @@ class DeviceModel:
         self.device = dev
         self.embed = torch.from_numpy(model["embed"].view(np.int16)).to(dev).view(torch.float16)
         self.final_norm = torch.from_numpy(model["final_norm"]).to(dev)
+        head = model.get("lm_head")  # absent or None: tied to the embedding table
+        self.lm_head = None if head is None else torch.from_numpy(head.view(np.int16)).to(dev).view(torch.float16)
         self.layers = []
         cache = {}
         for layer in model["layers"]:
@@ -34,7 +36,7 @@ class DeviceModel:
                     meta = torch.from_numpy(t["meta"].view(np.int32)).to(dev)
                     values = torch.from_numpy(t["values"].view(np.int32)).to(dev)
                     lin.append(dict(t, d_meta=meta, d_values=values))
-                norms = [torch.from_numpy(n).to(dev) for n in layer["norm"]]
+                norms = [None if n is None else torch.from_numpy(n).to(dev) for n in layer["norm"]]
                 cache[key] = {"linear": lin, "norm": norms}
             self.layers.append(cache[key])
 
@@ -57,10 +59,11 @@ class InferenceEngine:
                                                       C.c_void_p(t["d_values"].data_ptr()), float(t["gamma"]),
                                                       t["rows"], t["cols"], t["meta_stride"], t["values_stride"]))
             for i, n in enumerate(layer["norm"]):
-                if i >= 2 and not use_sub_norm:
+                if n is None or (i >= 2 and not use_sub_norm):
                     continue
                 check(self._lib.spb_engine_set_norm(self._h, l, i, C.c_void_p(n.data_ptr())))
-        check(self._lib.spb_engine_set_globals(self._h, C.c_void_p(model.embed.data_ptr()), C.c_void_p(0),
+        head = C.c_void_p(model.lm_head.data_ptr() if model.lm_head is not None else 0)
+        check(self._lib.spb_engine_set_globals(self._h, C.c_void_p(model.embed.data_ptr()), head,
                                                C.c_void_p(model.final_norm.data_ptr())))
 
     def forward(self, token_id: int) -> int:

@@ -190,3 +190,23 @@ def residual_add_gpu(a, b, output, size, stream=None):
 
 def half_gemv_gpu(W, x, y, rows, cols, stream=None):
     check(load().spb_half_gemv(_p(W), _p(x), _p(y), rows, cols, _stream(stream)))
+
+
+# ---- conversion on the GPU (no counterpart among the reference's GPU wrappers) -----------------
+
+def prune_pack_gpu(weights, stream=None):
+    """Magnitude 2:4 pruning + sign extraction + packing of a CUDA float32 matrix, byte-identical to
+    python/convert_model.py (generate_24_mask, quantize_ternary_absmean, the zero-at-mask fix,
+    pack_sparse_ternary).  Returns (meta, values, gamma): int32 CUDA tensors holding the uint32 words,
+    and gamma = mean |w| accumulated in double precision."""
+    import torch
+    assert weights.is_cuda and weights.dtype == torch.float32 and weights.dim() == 2 and weights.stride(1) == 1
+    rows, cols = weights.shape
+    ms, vs = (cols // 4 + 7) // 8, (cols // 4 + 15) // 16
+    meta = torch.zeros((rows, ms), dtype=torch.int32, device=weights.device)
+    values = torch.zeros((rows, vs), dtype=torch.int32, device=weights.device)
+    abs_sum = torch.zeros(1, dtype=torch.float64, device=weights.device)
+    check(load().spb_prune_pack_gpu(_p(weights), rows, cols, weights.stride(0), _p(meta), _p(values), ms, vs,
+                                    _p(abs_sum), _stream(stream)))
+    gamma = float(abs_sum.item()) / max(1, rows * cols)
+    return meta, values, gamma

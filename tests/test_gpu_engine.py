@@ -122,3 +122,17 @@ def test_full_2b4t_shape_against_the_reference_cuda_kernels():
         tok = int(torch.argmax(ref.forward(tok)).item())
         ref_tokens.append(tok)
     assert (ours.generate(prompt, 64) == np.array(ref_tokens, np.int32)).all()
+
+
+def test_model_directory_round_trip_gives_the_same_tokens(tmp_path):
+    # a model written in the reference's directory format and read back decodes like the in-memory one,
+    # with an untied head as well
+    from spbitnet_b200 import model_io
+    model = synth.random_model(synth.TINY, seed=11)
+    prompt = np.array([3, 17, 200, 45], np.int32)
+    want = InferenceEngine(DeviceModel(model)).generate(prompt, 12)
+    back = model_io.load_model_dir(model_io.save_model_dir(model, tmp_path / "m"))
+    assert list(InferenceEngine(DeviceModel(back)).generate(prompt, 12)) == list(want)
+    model["lm_head"] = model["embed"].copy()  # same values, separate tensor: the untied path must agree
+    back = model_io.load_model_dir(model_io.save_model_dir(model, tmp_path / "u"))
+    assert list(InferenceEngine(DeviceModel(back)).generate(prompt, 12)) == list(want)
