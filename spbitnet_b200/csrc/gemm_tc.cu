@@ -157,7 +157,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const TcArgs a) 
         uint8_t* sa = stage0 + static_cast<size_t>(s) * stage_bytes;
         uint8_t* sb = sa + kTileM * 128;
         // Stage of the NEXT step: the MMAs that read it last must be done before anything is written
-        // to it (the verdict is made uniform across the block so that nobody is left at a barrier).
+        // to it (the outcome is made uniform across the block so that nobody is left at a barrier).
         if (kc + 1 < nchunks) {
             const int use_next = (kc + 1) / kTcStages;
             if (use_next > 0)

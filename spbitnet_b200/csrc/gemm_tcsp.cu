@@ -221,7 +221,7 @@ __global__ void __launch_bounds__(kSpThreads, 1) gemm_tcsp_kernel(const SpArgs a
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
         // The stage of the NEXT step must have been released by the MMAs that read it last before its
-        // activations are copied in and, one iteration later, its weights expanded (the verdict is made
+        // activations are copied in and, one iteration later, its weights expanded (the outcome is made
         // uniform so that nobody is left at a barrier).  Waiting here, after the expansion, lets the
         // MMAs of the previous step run under this step's expansion even with two stages.
         if (kc + 1 < nsteps) {

@@ -1191,6 +1191,10 @@ bool bitlinear_group_is_fast(const BitLinearGroup& g) {
 
 using namespace spb;
 
+namespace spb {
+int gemv_variant_setting() { return g_gemv_variant; }
+}  // namespace spb
+
 extern "C" int spb_set_gemv_variant(int variant) {
     const int old = g_gemv_variant;
     g_gemv_variant = variant;

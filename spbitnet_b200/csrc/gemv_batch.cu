@@ -26,6 +26,9 @@
 
 namespace spb {
 
+int gemv_variant_setting();
+int gemv_batch_mma_launch(const spb_gemv_item* d_items, int n, int max_rows, int max_cols, void* stream);
+
 constexpr int kBThreads = 256;
 constexpr int kMaxStages = 4;
 constexpr int kMaxItems = 256;  // descriptors held in shared memory per launch
@@ -277,6 +280,9 @@ extern "C" int spb_sparse_ternary_gemv_batch(const spb_gemv_item* d_items, int n
     if (max_cols % 256 != 0 || max_cols > 128 * kBThreads)
         return fail(SPB_E_UNSUPPORTED, "%s: max_cols=%d (multiple of 256, at most %d)", name, max_cols, 128 * kBThreads);
     if ((reinterpret_cast<uintptr_t>(d_items) & 15) != 0) return fail(SPB_E_INVALID, "%s: d_items must be 16-byte aligned", name);
+    // automatic: the tensor-core form (gemv_batch_mma.cu); the SIMT form below when a SIMT GEMV kernel is selected
+    if (gemv_variant_setting() == 0 || gemv_variant_setting() >= 3)
+        return gemv_batch_mma_launch(d_items, n, max_rows, max_cols, stream);
     const int grid = 2 * sm_count();
     const int rpc = (max_rows + grid - 1) / grid;
     BatchGeom g{};

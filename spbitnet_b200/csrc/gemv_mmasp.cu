@@ -61,7 +61,6 @@ struct GmArgs {
     int spw;        // steps per warp
     int mpitch;     // shared-memory row pitch of the bitmap words, in words (an odd multiple of 4)
     int vpitch;     // same for the sign words
-    int debug;
 };
 
 // Development aid, compiled out unless SPB_GT_TRACE is defined: per-block stamps of the phases
@@ -136,7 +135,7 @@ __global__ void __launch_bounds__(kGmThreads, SPB_GEMV_MMA_MIN_BLOCKS) gemv_mmas
             const uint32_t dst = is_m ? ms_s + static_cast<uint32_t>(k) * 16u : vs_s + static_cast<uint32_t>(k - mch) * 16u;
             const uint32_t dst_pitch = static_cast<uint32_t>(is_m ? a.mpitch : a.vpitch) * 4u;
             src += static_cast<size_t>(row0 + warp) * src_pitch;
-            for (int r = warp; r < valid && !(a.debug & 1); r += kGmWarps) {
+            for (int r = warp; r < valid; r += kGmWarps) {
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + static_cast<uint32_t>(r) * dst_pitch), "l"(src)
                              : "memory");
                 src += kGmWarps * src_pitch;
@@ -213,7 +212,7 @@ __global__ void __launch_bounds__(kGmThreads, SPB_GEMV_MMA_MIN_BLOCKS) gemv_mmas
         v0_p += 4u * steps;
         xq_p += 64u * steps;
     };
-    int st = (a.debug & 2) ? s_end : s_begin;
+    int st = s_begin;
     for (; st < s_end && (st & 3) != 0; ++st) {  // up to the next multiple of four steps
         step(gm_lds(v0_p), gm_lds(v0_p + v_half), 0u, 0u);
         advance(1u);
@@ -279,8 +278,6 @@ int gemv_mmasp_launch(const char* name, const uint32_t* meta, const uint32_t* va
     a.meta = meta; a.values = values; a.x = x; a.y = y; a.y_acc = y_acc; a.d_absmax = d_absmax; a.gamma = gamma;
     a.out_mode = out_mode; a.rows = rows; a.cols = cols; a.meta_stride = meta_stride; a.values_stride = values_stride;
     a.steps = cols / 64;
-    static const int dbg_env = [] { const char* e = getenv("SPB_GEMV_MMA_DEBUG"); return e ? atoi(e) : 0; }();
-    a.debug = dbg_env;
     // Warps per row block: long step ranges per warp amortise a warp's fixed cost (measured: about 20 steps
     // per warp is best at 6912 x 2560), but a small matrix still has to give every SM a few warps.
     static const int ks_env = [] {

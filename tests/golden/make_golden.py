@@ -1,8 +1,8 @@
 #!/usr/bin/env python3
 """Generates the golden vectors under tests/golden/ from the reference itself.
 
-Run in a container that has the reference checkout (default /root/reference) and a built
-oracle/_ref:   python tests/golden/make_golden.py [--ref /root/reference]
+Run where the reference checkout is present (pass its location with --ref) and oracle/_ref is built:
+    python tests/golden/make_golden.py [--ref <reference checkout>]
 
 Sources of truth used here:
   * python/convert_model.py   generate_24_mask, quantize_ternary_absmean, pack_sparse_ternary
