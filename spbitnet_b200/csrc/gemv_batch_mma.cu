@@ -189,16 +189,38 @@ __global__ void __launch_bounds__(kBmThreads, 3) gemv_batch_mma_kernel(const spb
             step(bm_lds(v0_p), bm_lds(v0_p + v_half), 0u, 0u);
             advance(1u);
         }
-        for (; st + 4 <= s_end; st += 4) {  // four steps share one 16-byte read of each row's sign words
-            uint4 w0, w1;
-            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w0.x), "=r"(w0.y), "=r"(w0.z), "=r"(w0.w) : "r"(v0_p));
+        for (; st + 4 <= s_end; st += 4) {
+            // Four steps at a time, written phase by phase so that all independent shared-memory reads are in
+            // flight together: raw words (sign words of four steps are one 16-byte read per row), then the
+            // table reads, then the four MMAs.
+            uint32_t w0[4], w1[4], mw[4], B[4][4], A[4][4];
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w0[0]), "=r"(w0[1]), "=r"(w0[2]), "=r"(w0[3]) : "r"(v0_p));
             asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(w1.x), "=r"(w1.y), "=r"(w1.z), "=r"(w1.w)
+                         : "=r"(w1[0]), "=r"(w1[1]), "=r"(w1[2]), "=r"(w1[3])
                          : "r"(v0_p + v_half));
-            step(w0.x, w1.x, 0u, 0u);
-            step(w0.y, w1.y, 8u, 64u);
-            step(w0.z, w1.z, 16u, 128u);
-            step(w0.w, w1.w, 24u, 192u);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) mw[i] = bm_lds(me_p + 8u * i);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) B[i][j] = bm_lds(xq_p + 64u * i + 16u * j);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                A[i][0] = bm_lds(tab_s + ((__funnelshift_r(w0[i], w0[i], rot_lo) & 0x780u) | lane_or));
+                A[i][1] = bm_lds(tab_s + ((__funnelshift_r(w1[i], w1[i], rot_lo) & 0x780u) | lane_or));
+                A[i][2] = bm_lds(tab_s + ((__funnelshift_r(w0[i], w0[i], rot_hi) & 0x780u) | lane_or));
+                A[i][3] = bm_lds(tab_s + ((__funnelshift_r(w1[i], w1[i], rot_hi) & 0x780u) | lane_or));
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t e = bm_index_pairs(mw[i]);
+                asm volatile(
+                    "mma.sp::ordered_metadata.sync.aligned.m16n8k64.row.col.s32.s8.s8.s32 "
+                    "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9, %10, %11}, {%0, %1, %2, %3}, %12, 0x0;"
+                    : "+r"(c0), "+r"(c1), "+r"(c2), "+r"(c3)
+                    : "r"(A[i][0]), "r"(A[i][1]), "r"(A[i][2]), "r"(A[i][3]), "r"(B[i][0]), "r"(B[i][1]), "r"(B[i][2]),
+                      "r"(B[i][3]), "r"(e));
+            }
             advance(4u);
         }
         for (; st < s_end; ++st) {
