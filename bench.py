@@ -432,6 +432,43 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def oracle_unpack(case, r, c):
+    import oracle
+    return oracle.unpack_to_int8(case["meta"], case["values"], r, c)
+
+
+def library_gemm(Wd, X, r, c, n):
+    """Library kernels on a dense int8 copy of the same weights (comparison only; weights stay resident in L2):
+    cuBLASLt int8 (torch._int_mm) and cuSPARSELt 2:4 (torch._cslt_sparse_mm), which is the reference's batched path."""
+    import torch
+    res = {}
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(20):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / 20
+        return {"us": round(us, 2), "dense_equiv_tops": round(2.0 * r * c * n / us / 1e6, 2)}
+    try:
+        Wt = Wd.t()
+        res["lib_cublaslt_dense"] = timed(lambda: torch._int_mm(X, Wt))
+    except Exception as exc:
+        res["lib_cublaslt_dense"] = {"error": str(exc)[:120]}
+    try:
+        comp = torch._cslt_compress(Wd)
+        Xt = X.t()
+        res["lib_cusparselt"] = timed(lambda: torch._cslt_sparse_mm(comp, Xt, out_dtype=torch.int32))
+    except Exception as exc:
+        res["lib_cusparselt"] = {"error": str(exc)[:120]}
+    return res
+
+
 def bench_gemm(args, l2_bytes):
     """Batched product (prefill) at the two FFN shapes, N in {1,4,16,64,256,1024}: us per call over a
     rotating set of weight copies larger than L2, weight-stream GB/s and dense-equivalent int8 TOP/s."""
@@ -446,6 +483,7 @@ def bench_gemm(args, l2_bytes):
         values = torch.from_numpy(case["values"].view(np.int32)).cuda()
         metas = torch.stack([meta.roll(i, 0) for i in range(copies)]).contiguous()
         vals = torch.stack([values.roll(i, 0) for i in range(copies)]).contiguous()
+        Wd = torch.from_numpy(oracle_unpack(case, r, c)).cuda()  # dense int8 copy, what the reference hands to cuSPARSELt
         for n in synth.GEMM_BATCHES:
             X = torch.randint(-127, 128, (n, c), dtype=torch.int8, device="cuda")
             Y = torch.empty((n, r), dtype=torch.int32, device="cuda")
@@ -476,12 +514,15 @@ def bench_gemm(args, l2_bytes):
                 row[name] = {"us": round(us, 2), "weight_gbs": round(per / us / 1e3, 1),
                              "dense_equiv_tops": round(2.0 * r * c * n / us / 1e6, 2)}
             K.set_gemm_variant(0)
+            if n >= 64:
+                row.update(library_gemm(Wd, X, r, c, n))
             out[f"{r}x{c}_n{n}"] = row
         del metas, vals
     out["tc_timeouts"] = K.gemm_tc_timeouts()
     out["what"] = ("spb_sparse_ternary_gemm, us per call as a graph of stream-ordered calls over cold weights; auto = "
                    "warp-level sparse MMA (mma.sp) up to n = 32, tcgen05.mma.sp above; tc_dense = tcgen05 kind::i8 on "
-                   "expanded int8 tiles; dense_equiv_tops counts 2*M*K*N")
+                   "expanded int8 tiles; lib_* = library kernels on a dense int8 copy of the weights that stays in L2 "
+                   "(comparison only); dense_equiv_tops counts 2*M*K*N")
     return out
 
 
