@@ -14,10 +14,18 @@
 //     (sign nibble -> four bytes) and writes them as four 16-byte chunks of the K-major
 //     128-byte-swizzled A tile.
 // One thread then issues four tcgen05.mma.sp.kind::i8 (M=128, N=batch tile, K=64 each) per
-// 256-column step; accumulators are int32 in tensor memory.  Activations arrive by 16-byte
-// asynchronous copies one step ahead.  A ring of stages (operand tiles + metadata slots) is
-// recycled through tcgen05.commit on one mbarrier per stage.
+// 256-column step; accumulators are int32 in tensor memory.  The activation tiles of a step
+// arrive one step ahead by two tensor-map bulk copies (cp.async.bulk.tensor.2d, box 128 bytes x
+// batch tile, 128-byte swizzle and zero fill past n done by the copy engine, completion on a
+// "full" mbarrier per stage); the tensor map of X is encoded on the host per call through the
+// driver entry point, and 16-byte cp.async by all threads remain as the fall-back.  The weight
+// words of a thread are loaded four steps ahead.  A ring of stages (operand tiles + metadata
+// slots) is recycled through tcgen05.commit on one mbarrier per stage.
 // Every wait is bounded; on expiry the block records it, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include <cstring>
+
 #include "spb_common.cuh"
 
 namespace spb {
@@ -95,14 +103,20 @@ __device__ __forceinline__ uint32_t sp_index_pairs(uint32_t m) {
     return (t1 & 0x55555555u) | (t2 & 0xAAAAAAAAu);
 }
 
-__global__ void __launch_bounds__(kSpThreads, 1) gemm_tcsp_kernel(const SpArgs a) {
+// TMAB: the activation tiles come in by two tensor-map bulk copies per step (cp.async.bulk.tensor, 128-byte
+// swizzle written by the copy engine, rows past n zero-filled by it) issued by one thread, instead of 16-byte
+// cp.async by everybody (4096 of them per step at 256 batch rows: they kept the load/store unit busy for about
+// 3000 cycles per step).
+template <bool TMAB>
+__global__ void __launch_bounds__(kSpThreads, 1) gemm_tcsp_kernel(const SpArgs a, const __grid_constant__ CUtensorMap tmap_x) {
     extern __shared__ uint8_t sp_raw[];
-    // [sign table 2 KB][barriers + tmem slot 64 B] ... 1024-aligned: [stage: A 16 KB | B0 nt*128 | B1 nt*128] x stages
+    // [sign table 2 KB][barriers + tmem slot 128 B] ... 1024-aligned: [stage: A 16 KB | B0 nt*128 | B1 nt*128] x stages
     uint32_t* sgn = reinterpret_cast<uint32_t*>(sp_raw);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sp_raw + kSpSignLutBytes);  // stage[0..S), done
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sp_raw + kSpSignLutBytes + 8 * (kSpMaxStages + 1));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sp_raw + kSpSignLutBytes);  // free[0..4), done, full[5..9)
+    uint64_t* full = bars + kSpMaxStages + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sp_raw + kSpSignLutBytes + 96);
     const uint32_t raw_s = sp_smem(sp_raw);
-    const uint32_t stage0_s = (raw_s + kSpSignLutBytes + 64 + 1023) & ~1023u;
+    const uint32_t stage0_s = (raw_s + kSpSignLutBytes + 128 + 1023) & ~1023u;
     uint8_t* stage0 = sp_raw + (stage0_s - raw_s);
     const int b_bytes = a.nt * 128;  // one of the two activation sub-tiles
     const int stage_bytes = kSpABytes + 2 * b_bytes;
@@ -123,7 +137,7 @@ __global__ void __launch_bounds__(kSpThreads, 1) gemm_tcsp_kernel(const SpArgs a
         sgn[i] = w;
     }
     if (tid == 0) {
-        for (int s = 0; s <= kSpMaxStages; ++s)
+        for (int s = 0; s < 2 * kSpMaxStages + 1; ++s)
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sp_smem(bars + s)));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -156,6 +170,14 @@ __global__ void __launch_bounds__(kSpThreads, 1) gemm_tcsp_kernel(const SpArgs a
         }
     };
     load_unit(0, m, v, uvalid);
+    // three more steps in flight: a step takes about as long as one trip to DRAM, so a single step of
+    // look-ahead left every step waiting for its weights
+    uint4 m1 = make_uint4(0, 0, 0, 0), m2 = m1, m3 = m1;
+    uint2 v1 = make_uint2(0, 0), v2 = v1, v3 = v1;
+    bool u1 = false, u2 = false, u3 = false;
+    if (1 < nsteps) load_unit(1, m1, v1, u1);
+    if (2 < nsteps) load_unit(2, m2, v2, u2);
+    if (3 < nsteps) load_unit(3, m3, v3, u3);
 
     grid_dep_wait();  // X may be a predecessor's output
 
@@ -163,17 +185,33 @@ __global__ void __launch_bounds__(kSpThreads, 1) gemm_tcsp_kernel(const SpArgs a
     // ahead of their use; rows beyond n and columns beyond cols are zero-filled (zero source size).
     auto issue_b = [&](int step) {
         uint8_t* sb = stage0 + static_cast<size_t>(step % S) * stage_bytes + kSpABytes;
-        for (int i = tid; i < a.nt * 16; i += kSpThreads) {
-            const int j = i >> 4, c = i & 15;
-            const int col = step * kSpStepK + c * 16;
-            const bool in = n0 + j < a.n && col < a.cols;
-            const int8_t* src = a.X + static_cast<size_t>(in ? n0 + j : 0) * a.cols + (in ? col : 0);
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
-                             sp_smem(sb + (c >> 3) * b_bytes + sp_swz(j, c & 7))),
-                         "l"(src), "r"(in ? 16 : 0)
-                         : "memory");
+        if constexpr (TMAB) {
+            if (tid == 0) {
+                const uint32_t fb = sp_smem(full + step % S);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(fb),
+                             "r"(static_cast<uint32_t>(2 * b_bytes))
+                             : "memory");
+#pragma unroll
+                for (int h = 0; h < 2; ++h)  // columns [256 step + 128 h, +128) of batch rows [n0, n0 + nt)
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                            sp_smem(sb + h * b_bytes)),
+                        "l"(reinterpret_cast<uint64_t>(&tmap_x)), "r"(step * kSpStepK + 128 * h), "r"(n0), "r"(fb)
+                        : "memory");
+            }
+        } else {
+            for (int i = tid; i < a.nt * 16; i += kSpThreads) {
+                const int j = i >> 4, c = i & 15;
+                const int col = step * kSpStepK + c * 16;
+                const bool in = n0 + j < a.n && col < a.cols;
+                const int8_t* src = a.X + static_cast<size_t>(in ? n0 + j : 0) * a.cols + (in ? col : 0);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
+                                 sp_smem(sb + (c >> 3) * b_bytes + sp_swz(j, c & 7))),
+                             "l"(src), "r"(in ? 16 : 0)
+                             : "memory");
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");
     };
     issue_b(0);
 
@@ -189,7 +227,7 @@ __global__ void __launch_bounds__(kSpThreads, 1) gemm_tcsp_kernel(const SpArgs a
             uint4 mn = make_uint4(0, 0, 0, 0);
             uint2 vn = make_uint2(0, 0);
             bool nvalid = false;
-            if (kc + 1 < nsteps) load_unit(kc + 1, mn, vn, nvalid);
+            if (kc + 4 < nsteps) load_unit(kc + 4, mn, vn, nvalid);
             // metadata: index pairs of this unit's 32 groups -> four tensor-memory columns of the row
             uint32_t e0 = 0x44444444u, e1 = 0x44444444u, e2 = 0x44444444u, e3 = 0x44444444u;
             if (uvalid) {
@@ -215,9 +253,10 @@ __global__ void __launch_bounds__(kSpThreads, 1) gemm_tcsp_kernel(const SpArgs a
                 }
                 *reinterpret_cast<uint4*>(sa + sp_swz(trow, thalf * 4 + c)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
-            m = mn;
-            v = vn;
-            uvalid = nvalid;
+            m = m1; v = v1; uvalid = u1;
+            m1 = m2; v1 = v2; u1 = u2;
+            m2 = m3; v2 = v3; u2 = u3;
+            m3 = mn; v3 = vn; u3 = nvalid;
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
         // The stage of the NEXT step must have been released by the MMAs that read it last before its
@@ -230,19 +269,22 @@ __global__ void __launch_bounds__(kSpThreads, 1) gemm_tcsp_kernel(const SpArgs a
                 ok = __syncthreads_and(sp_wait(sp_smem(bars + (kc + 1) % S), (use_next - 1) & 1) ? 1 : 0) != 0;
             if (!ok) break;
             issue_b(kc + 1);
-        } else {
+        } else if constexpr (!TMAB) {
             asm volatile("cp.async.commit_group;" ::: "memory");  // keeps the group count uniform
         }
-        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        if constexpr (!TMAB) asm volatile("cp.async.wait_group 1;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
         if (tid == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            bool landed = true;
+            if constexpr (TMAB) landed = sp_wait(sp_smem(full + s), static_cast<uint32_t>(kc / S) & 1u);  // this step's activations
+            if (!landed) atomicAdd(&g_tcsp_timeouts, 1);
             const uint64_t da = sp_smem_desc(sp_smem(sa));
             const uint64_t db0 = sp_smem_desc(sp_smem(sb)), db1 = sp_smem_desc(sp_smem(sb + b_bytes));
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {  // 64 logical columns each: 32 B of A, 64 B of X, two metadata columns
+            for (int k = 0; k < 4 && landed; ++k) {  // 64 logical columns each: 32 B of A, 64 B of X, two metadata columns
                 const uint32_t acc = (kc > 0 || k > 0) ? 1u : 0u;
                 const uint64_t db = ((k & 2) ? db1 : db0) + static_cast<uint64_t>(4 * (k & 1));
                 const uint32_t te = tmem_e + static_cast<uint32_t>(s * 8 + 2 * k);
@@ -263,7 +305,7 @@ __global__ void __launch_bounds__(kSpThreads, 1) gemm_tcsp_kernel(const SpArgs a
                              : "memory");
         }
     }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    if constexpr (!TMAB) asm volatile("cp.async.wait_group 0;" ::: "memory");
 
     // ---- epilogue: accumulators -> Y ---------------------------------------------------------
     ok = __syncthreads_and(ok ? 1 : 0) != 0;
@@ -318,14 +360,41 @@ int gemm_tcsp_launch(const uint32_t* meta, const uint32_t* values, const int8_t*
     a.stages = max(2, min(kSpMaxStages, (200 * 1024) / stage_bytes));
     a.tmem_cols = 32;
     while (a.tmem_cols < a.nt + 8 * a.stages) a.tmem_cols <<= 1;
-    const size_t smem = kSpSignLutBytes + 64 + 1024 + static_cast<size_t>(a.stages) * stage_bytes;
-    cudaError_t err = cudaFuncSetAttribute(gemm_tcsp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    const size_t smem = kSpSignLutBytes + 128 + 1024 + static_cast<size_t>(a.stages) * stage_bytes;
+    // tensor map of X for the activation tiles: uint8 [n rows][cols], box 128 bytes x nt rows, 128-byte swizzle
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static const EncodeFn encode = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess) {
+            cudaGetLastError();
+            p = nullptr;
+        }
+        return reinterpret_cast<EncodeFn>(p);
+    }();
+    alignas(64) CUtensorMap tmap;
+    bool use_tma = encode != nullptr && cols % 128 == 0;
+    if (use_tma) {
+        const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(n)};
+        const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(cols)};
+        const cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(a.nt)};
+        const cuuint32_t estr[2] = {1u, 1u};
+        use_tma = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(X), gdim, gstride, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    }
+    if (!use_tma) memset(&tmap, 0, sizeof tmap);
+    void (*kernel)(SpArgs, CUtensorMap) = use_tma ? gemm_tcsp_kernel<true> : gemm_tcsp_kernel<false>;
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (err != cudaSuccess) {
         cudaGetLastError();
         return fail(SPB_E_CUDA, "gemm_tcsp: %s", cudaGetErrorString(err));
     }
     const dim3 grid((rows + kSpTileM - 1) / kSpTileM, (n + a.nt - 1) / a.nt);
-    return launch("spb_sparse_ternary_gemm(tcgen05.sp)", gemm_tcsp_kernel, grid, dim3(kSpThreads), smem, stream, a);
+    return launch("spb_sparse_ternary_gemm(tcgen05.sp)", kernel, grid, dim3(kSpThreads), smem, stream, a, tmap);
 }
 
 int gemm_tcsp_timeouts() {
