@@ -144,6 +144,8 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_generic_kernel(const GemmAr
 int gemm_tc_launch(const uint32_t* meta, const uint32_t* values, const int8_t* X, int32_t* Y, int rows, int cols,
                    int n, int meta_stride, int values_stride, void* stream);
 
+int gemm_tcsp_ws_launch(const uint32_t* meta, const uint32_t* values, const int8_t* X, int32_t* Y, int rows, int cols,
+                        int n, int meta_stride, int values_stride, void* stream);
 int gemm_tcsp_launch(const uint32_t* meta, const uint32_t* values, const int8_t* X, int32_t* Y, int rows, int cols,
                      int n, int meta_stride, int values_stride, void* stream);
 
@@ -190,7 +192,11 @@ extern "C" int spb_sparse_ternary_gemm(const uint32_t* meta, const uint32_t* val
         gemm_mmasp_supported(meta, values, X, rows, cols, n, meta_row_stride, values_row_stride,
                              g_gemm_variant == 4 ? 4096 : mma_auto_max_n))
         return gemm_mmasp_launch(meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream);
-    if (fast && (g_gemm_variant == 3 || ((g_gemm_variant == 0 || g_gemm_variant == 4) && n > 32)))
+    if (fast && (g_gemm_variant == 0 || g_gemm_variant == 4)) {  // warp-specialised tcgen05 sparse form
+        const int rc = gemm_tcsp_ws_launch(meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream);
+        if (rc != SPB_E_UNSUPPORTED) return rc;  // no tensor map of X on this system: the plain form below
+    }
+    if (fast && (g_gemm_variant == 3 || g_gemm_variant == 0 || g_gemm_variant == 4))
         return gemm_tcsp_launch(meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream);
     if (fast && g_gemm_variant == 2)
         return gemm_tc_launch(meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream);

@@ -283,6 +283,7 @@ int gemm_tc_launch(const uint32_t* meta, const uint32_t* values, const int8_t* X
 
 int gemm_tcsp_timeouts();
 int gemv_tcsp_timeouts();
+int gemm_tcsp_ws_timeouts();
 
 }  // namespace spb
 
@@ -292,6 +293,6 @@ extern "C" int spb_gemm_tc_timeouts(void) {
         cudaGetLastError();
         return -1;
     }
-    const int w = spb::gemm_tcsp_timeouts(), g = spb::gemv_tcsp_timeouts();
-    return (w < 0 || g < 0) ? -1 : v + w + g;
+    const int w = spb::gemm_tcsp_timeouts(), g = spb::gemv_tcsp_timeouts(), s = spb::gemm_tcsp_ws_timeouts();
+    return (w < 0 || g < 0 || s < 0) ? -1 : v + w + g + s;
 }
