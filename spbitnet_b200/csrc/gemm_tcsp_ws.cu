@@ -22,6 +22,7 @@
 // and the block returns.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <cstring>
 
 #include "spb_common.cuh"
@@ -331,7 +332,16 @@ int gemm_tcsp_ws_launch(const uint32_t* meta, const uint32_t* values, const int8
     a.meta = meta; a.values = values; a.Y = Y;
     a.rows = rows; a.cols = cols; a.n = n;
     a.meta_stride = meta_stride; a.values_stride = values_stride;
-    a.nt = min(256, (n + 15) / 16 * 16);
+    static const int nt_env = [] {
+        const char* e = getenv("SPB_GEMM_WS_NT");
+        return e ? atoi(e) : 0;
+    }();
+    // batch rows per block: 256, or 128 / 64 when the wider tile would leave more than half of the SMs without a
+    // block (a step costs about the same whatever the tile width, so more, narrower blocks finish sooner)
+    const int mtiles = (rows + kWsTileM - 1) / kWsTileM;
+    int nt = 256;
+    while (nt > 64 && mtiles * ((n + nt - 1) / nt) < sm_count() / 2) nt >>= 1;
+    a.nt = min(nt_env > 0 ? nt_env : nt, (n + 15) / 16 * 16);
     const int stage_bytes = kWsABytes + 2 * a.nt * 128;
     a.stages = max(2, min(kWsMaxStages, (200 * 1024) / stage_bytes));
     a.tmem_cols = 32;
