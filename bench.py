@@ -547,7 +547,25 @@ def bench_decode(args):
     dt = time.perf_counter() - t0
     steps = len(prompt) - 1 + n_gen
     weight_bytes = dm.sparse_bytes() + model["embed"].nbytes
-    return {"tok_s": steps / dt, "ms_per_token": 1e3 * dt / steps, "generated": int(len(toks)),
+    # the same job with the prompt fed as one batch (BitLinear layers as the batched product)
+    eng.reset()
+    eng.set_prefill_chunk(256)
+    eng.generate(prompt, 2)
+    eng.reset()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    toks_b = eng.generate(prompt, n_gen)
+    dt_b = time.perf_counter() - t0
+    eng.reset()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    eng.prefill(prompt)
+    dt_p = time.perf_counter() - t0
+    eng.set_prefill_chunk(0)
+    batched = {"tok_s": steps / dt_b, "ms_total": 1e3 * dt_b, "prefill_ms": 1e3 * dt_p,
+               "prefill_tok_s": len(prompt) / dt_p, "same_tokens_as_serial": bool((toks_b == toks).all()),
+               "decode_only_tok_s": (n_gen - 1) / max(dt_b - dt_p, 1e-9)}
+    return {"tok_s": steps / dt, "batched_prompt": batched, "ms_per_token": 1e3 * dt / steps, "generated": int(len(toks)),
             "prompt": int(len(prompt)), "weight_mb_per_token": round(weight_bytes / 1e6, 1),
             "hbm_gbs": weight_bytes * steps / dt / 1e9,
             "what": "prefill (token-serial, as the reference) + decode, wall clock around generate() incl. prompt "

@@ -100,6 +100,8 @@ SIGNATURES = {
     "spb_engine_seq_len": (_i, [_p]),
     "spb_engine_generate": (_i, [_p, _p, _i, _i, _i, _p]),
     "spb_engine_copy_logits": (_i, [_p, _p]),
+    "spb_engine_prefill": (_i, [_p, _p, _i, _p]),
+    "spb_engine_set_prefill_chunk": (_i, [_p, _i]),
 }
 
 _lib = None

@@ -14,7 +14,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libspbitnet_b200.so"
 SOURCES = ["core.cu", "gemv.cu", "gemv_batch.cu", "gemv_batch_mma.cu", "gemv_tcsp.cu", "gemv_mmasp.cu", "gemm.cu", "gemm_tc.cu", "gemm_tcsp.cu", "gemm_tcsp_ws.cu", "gemm_mmasp.cu", "unpack.cu", "decode_ops.cu", "attention.cu", "fused_ops.cu",
-           "engine.cu", "noalloc.cu", "pack.cu", "format_host.cpp"]
+           "prefill.cu", "engine.cu", "noalloc.cu", "pack.cu", "format_host.cpp"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-Xcompiler", "-fPIC", "-shared"]
 

@@ -67,6 +67,17 @@ struct spb_engine {
     bool fused = false;               // vector ops run inside the BitLinear launches
     bool force_unfused = false;
     int seq_len = 0;
+
+    // batched prefill: buffers for `pf_cap` tokens at a time, allocated by the first call that needs them
+    int prefill_chunk = 0;  // 0 = generate() feeds the prompt token by token, as the reference does
+    int pf_cap = 0;
+    uint8_t* pf_pool = nullptr;
+    __half *pf_x = nullptr, *pf_q = nullptr, *pf_k = nullptr, *pf_v = nullptr, *pf_attn = nullptr, *pf_o = nullptr;
+    __half *pf_gate = nullptr, *pf_up = nullptr, *pf_down = nullptr;
+    int8_t* pf_xq = nullptr;
+    int32_t* pf_acc = nullptr;
+    float* pf_absmax = nullptr;  // two arrays of pf_cap
+    int* pf_tokens = nullptr;
 };
 
 namespace {
@@ -211,6 +222,122 @@ int ensure_graph(spb_engine* e, bool record_tokens, int n_prompt) {
     return SPB_OK;
 }
 
+// ---- batched prefill -------------------------------------------------------------------------------
+// T prompt tokens go through a layer together: the BitLinear layers run as the batched product
+// (spb_sparse_ternary_gemm, one activation row per token, integer-exact) followed by a per-row dequantise,
+// the vector ops as one block per token, attention as one block per (head, token) over the positions up to
+// the token's own.  Every rounding point of the token-serial step is kept, so the integer accumulators and
+// the quantised activations are the ones forward() produces token by token; only the attention sums are
+// formed in a different order (the split-KV kernel is not used here).
+
+constexpr int kPrefillMaxChunk = 256;
+
+int ensure_prefill_buffers(spb_engine* e, int cap) {
+    if (e->pf_cap >= cap) return SPB_OK;
+    if (e->pf_pool) {
+        SPB_CUDA(cudaStreamSynchronize(e->stream));
+        cudaFree(e->pf_pool);
+        e->pf_pool = nullptr;
+        e->pf_cap = 0;
+    }
+    const spb_model_config& c = e->cfg;
+    const size_t T = static_cast<size_t>(cap);
+    const size_t H = c.hidden_size, qdim = static_cast<size_t>(c.num_attention_heads) * c.head_dim;
+    const size_t kvdim = static_cast<size_t>(c.num_key_value_heads) * c.head_dim, inter = c.intermediate_size;
+    const size_t maxdim = std::max(std::max(H, qdim), inter);
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return o; };
+    const size_t o_x = take(2 * T * H), o_q = take(2 * T * qdim), o_k = take(2 * T * kvdim), o_v = take(2 * T * kvdim);
+    const size_t o_attn = take(2 * T * qdim), o_o = take(2 * T * H), o_gate = take(2 * T * inter);
+    const size_t o_up = take(2 * T * inter), o_down = take(2 * T * H), o_xq = take(T * maxdim);
+    const size_t o_acc = take(4 * T * maxdim), o_abs = take(4 * 2 * T), o_tok = take(4 * T);
+    SPB_CUDA(cudaMalloc(&e->pf_pool, off));
+    uint8_t* p = e->pf_pool;
+    e->pf_x = reinterpret_cast<__half*>(p + o_x);
+    e->pf_q = reinterpret_cast<__half*>(p + o_q);
+    e->pf_k = reinterpret_cast<__half*>(p + o_k);
+    e->pf_v = reinterpret_cast<__half*>(p + o_v);
+    e->pf_attn = reinterpret_cast<__half*>(p + o_attn);
+    e->pf_o = reinterpret_cast<__half*>(p + o_o);
+    e->pf_gate = reinterpret_cast<__half*>(p + o_gate);
+    e->pf_up = reinterpret_cast<__half*>(p + o_up);
+    e->pf_down = reinterpret_cast<__half*>(p + o_down);
+    e->pf_xq = reinterpret_cast<int8_t*>(p + o_xq);
+    e->pf_acc = reinterpret_cast<int32_t*>(p + o_acc);
+    e->pf_absmax = reinterpret_cast<float*>(p + o_abs);
+    e->pf_tokens = reinterpret_cast<int*>(p + o_tok);
+    e->pf_cap = cap;
+    return SPB_OK;
+}
+
+// out[t] = BitLinear(L) of the T quantised rows in pf_xq with the row scales `absmax`
+int prefill_linear(spb_engine* e, const Linear& L, const float* absmax, __half* out, int T) {
+    int rc = spb_sparse_ternary_gemm(L.meta, L.values, e->pf_xq, e->pf_acc, L.rows, L.cols, T, L.ms, L.vs, e->stream);
+    if (rc) return rc;
+    return dequantize_rows(e->pf_acc, out, absmax, L.gamma, L.rows, T, e->stream);
+}
+
+// Tokens d_tokens[0..T) at positions start..start+T-1 (T <= pf_cap); *d_pos must hold `start`.  With `last`
+// the logits of the final token are formed as well.
+int enqueue_prefill_chunk(spb_engine* e, int T, bool last) {
+    const spb_model_config& c = e->cfg;
+    const int H = c.hidden_size, hd = c.head_dim, nh = c.num_attention_heads, nkv = c.num_key_value_heads;
+    const int inter = c.intermediate_size;
+    void* s = e->stream;
+    float* am0 = e->pf_absmax;
+    float* am1 = e->pf_absmax + e->pf_cap;
+    int rc;
+    if ((rc = embed_rows(e->embed, e->pf_tokens, e->pf_x, H, T, s))) return rc;
+    const float attn_scale = 1.0f / sqrtf(static_cast<float>(hd));
+    for (int l = 0; l < c.num_hidden_layers; ++l) {
+        const Layer& L = e->layers[l];
+        __half* kc = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(e->kcache) + l * e->kv_bytes_per_layer);
+        __half* vc = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(e->vcache) + l * e->kv_bytes_per_layer);
+        if ((rc = residual_norm_quant(l == 0 ? nullptr : e->pf_down, nullptr, e->pf_x, L.norm[0], nullptr, e->pf_xq,
+                                      am0, H, c.rms_norm_eps, s, T))) return rc;
+        if ((rc = prefill_linear(e, L.lin[0], am0, e->pf_q, T))) return rc;
+        if ((rc = prefill_linear(e, L.lin[1], am0, e->pf_k, T))) return rc;
+        if ((rc = prefill_linear(e, L.lin[2], am0, e->pf_v, T))) return rc;
+        if ((rc = rope_scatter(e->pf_q, e->pf_k, e->pf_v, kc, vc, nh, nkv, hd, c.max_position_embeddings,
+                               c.rope_theta, e->d_pos, s, T))) return rc;
+        if ((rc = decode_attention_pos(e->pf_q, kc, vc, e->pf_attn, nh, nkv, hd, c.max_position_embeddings,
+                                       attn_scale, e->d_pos, s, T))) return rc;
+        if ((rc = absmax_quantize_rows(e->pf_attn, e->pf_xq, am1, nh * hd, T, s))) return rc;
+        if ((rc = prefill_linear(e, L.lin[3], am1, e->pf_o, T))) return rc;
+        if ((rc = residual_norm_quant(e->pf_o, L.norm[2], e->pf_x, L.norm[1], nullptr, e->pf_xq, am0, H,
+                                      c.rms_norm_eps, s, T))) return rc;
+        if ((rc = prefill_linear(e, L.lin[4], am0, e->pf_gate, T))) return rc;
+        if ((rc = prefill_linear(e, L.lin[5], am0, e->pf_up, T))) return rc;
+        if ((rc = relu2_norm_quant(e->pf_gate, e->pf_up, L.norm[3], nullptr, e->pf_xq, am1, inter, c.rms_norm_eps,
+                                   s, T))) return rc;
+        if ((rc = prefill_linear(e, L.lin[6], am1, e->pf_down, T))) return rc;
+    }
+    if (!last) return SPB_OK;
+    // only the final token's logits are ever read: last residual add + final norm + lm_head on its row
+    const size_t row = static_cast<size_t>(T - 1) * H;
+    if ((rc = residual_norm_quant(c.num_hidden_layers ? e->pf_down + row : nullptr, nullptr, e->pf_x + row,
+                                  e->final_norm, e->xfinal, e->xq, e->absmax, H, c.rms_norm_eps, s))) return rc;
+    return spb_half_gemv(e->lm_head ? e->lm_head : e->embed, e->xfinal, e->logits, c.vocab_size, H, s);
+}
+
+// Runs tokens[0..n) (HOST array) through the model from position e->seq_len in chunks; leaves the logits of
+// the last one in e->logits, *d_pos = e->seq_len = old + n.  Validated by the caller.
+int prefill_tokens(spb_engine* e, const int* tokens, int n) {
+    const int chunk = std::min(e->prefill_chunk > 0 ? e->prefill_chunk : kPrefillMaxChunk, kPrefillMaxChunk);
+    int rc = ensure_prefill_buffers(e, std::min(chunk, std::max(n, 1)));
+    if (rc) return rc;
+    const int cap = std::min(chunk, e->pf_cap);
+    for (int done = 0; done < n; done += cap) {
+        const int T = std::min(cap, n - done);
+        // the token ids are consumed by the first kernel of the chunk; the copy is ordered before it on the stream
+        SPB_CUDA(cudaMemcpyAsync(e->pf_tokens, tokens + done, sizeof(int) * T, cudaMemcpyHostToDevice, e->stream));
+        if ((rc = set_int(e->d_pos, e->seq_len, e->stream))) return rc;
+        if ((rc = enqueue_prefill_chunk(e, T, done + T == n))) return rc;
+        e->seq_len += T;  // the next chunk's copy into pf_tokens is ordered after this chunk's kernels by the stream
+    }
+    return set_int(e->d_pos, e->seq_len, e->stream);
+}
+
 }  // namespace
 
 extern "C" spb_engine* spb_engine_create(const spb_model_config* cfg) {
@@ -286,6 +413,7 @@ extern "C" void spb_engine_destroy(spb_engine* e) {
     cudaStreamSynchronize(e->stream);
     drop_graph(e);
     if (e->d_prompt) cudaFree(e->d_prompt);
+    if (e->pf_pool) cudaFree(e->pf_pool);
     cudaFree(e->pool);
     cudaStreamDestroy(e->stream);
     delete e;
@@ -348,6 +476,30 @@ extern "C" int spb_engine_forward(spb_engine* e, int token_id, const float** d_l
     return SPB_OK;
 }
 
+extern "C" int spb_engine_prefill(spb_engine* e, const int* tokens, int n, const float** d_logits) {
+    int rc = check_ready(e);
+    if (rc) return rc;
+    if (!tokens || n < 1) return fail(SPB_E_INVALID, "spb_engine_prefill: no tokens");
+    if (e->seq_len + n > e->cfg.max_position_embeddings)
+        return fail(SPB_E_INVALID, "spb_engine_prefill: %d positions exceed the KV cache (%d)", e->seq_len + n,
+                    e->cfg.max_position_embeddings);
+    for (int i = 0; i < n; ++i)
+        if (tokens[i] < 0 || tokens[i] >= e->cfg.vocab_size)
+            return fail(SPB_E_INVALID, "spb_engine_prefill: token %d outside the vocabulary", tokens[i]);
+    if ((rc = prefill_tokens(e, tokens, n))) return rc;
+    SPB_CUDA(cudaStreamSynchronize(e->stream));
+    if (d_logits) *d_logits = e->logits;
+    return SPB_OK;
+}
+
+extern "C" int spb_engine_set_prefill_chunk(spb_engine* e, int chunk) {
+    if (!e) return fail(SPB_E_INVALID, "spb_engine_set_prefill_chunk: null handle");
+    if (chunk < 0) return fail(SPB_E_INVALID, "spb_engine_set_prefill_chunk: negative chunk");
+    const int prev = e->prefill_chunk;
+    e->prefill_chunk = std::min(chunk, kPrefillMaxChunk);
+    return prev;
+}
+
 extern "C" int spb_engine_reset(spb_engine* e) {
     if (!e) return fail(SPB_E_INVALID, "spb_engine_reset: null handle");
     const size_t kv_total = e->kv_bytes_per_layer * e->cfg.num_hidden_layers;
@@ -394,6 +546,40 @@ extern "C" int spb_engine_generate(spb_engine* e, const int* prompt, int n_promp
     SPB_CUDA(cudaMemcpyAsync(e->d_prompt + start, prompt, sizeof(int) * n_prompt, cudaMemcpyHostToDevice, e->stream));
     if ((rc = ensure_graph(e, true, need))) return rc;
     int produced = 0;
+    if (e->prefill_chunk > 0 && n_prompt >= 2) {
+        // The prompt as a batch; the first generated token comes from its last logits, the rest from the
+        // per-token graph.  Positions and recorded tokens end up where the token-serial loop puts them.
+        if (max_tokens == 0) {
+            if ((rc = prefill_tokens(e, prompt, n_prompt - 1))) return rc;
+            SPB_CUDA(cudaStreamSynchronize(e->stream));
+            return 0;
+        }
+        if ((rc = prefill_tokens(e, prompt, n_prompt))) return rc;
+        if ((rc = set_int(e->d_pos, e->seq_len - 1, e->stream))) return rc;
+        if ((rc = argmax_advance(e->logits, e->cfg.vocab_size, e->bval, e->bidx, e->argmax_blocks, e->d_next, e->d_out,
+                                 e->d_pos, e->stream))) return rc;
+        const int first_slot = start + n_prompt - 1;
+        if (eos_token_id < 0) {
+            for (int s = 1; s < max_tokens; ++s) SPB_CUDA(cudaGraphLaunch(e->graph, e->stream));
+            e->seq_len += max_tokens - 1;
+            SPB_CUDA(cudaMemcpyAsync(out_tokens, e->d_out + first_slot, sizeof(int) * max_tokens, cudaMemcpyDeviceToHost,
+                                     e->stream));
+            SPB_CUDA(cudaStreamSynchronize(e->stream));
+            return max_tokens;
+        }
+        for (int t = 0; t < max_tokens; ++t) {
+            if (t > 0) {
+                SPB_CUDA(cudaGraphLaunch(e->graph, e->stream));
+                e->seq_len++;
+            }
+            SPB_CUDA(cudaMemcpyAsync(out_tokens + t, e->d_out + first_slot + t, sizeof(int), cudaMemcpyDeviceToHost,
+                                     e->stream));
+            SPB_CUDA(cudaStreamSynchronize(e->stream));
+            produced = t + 1;
+            if (out_tokens[t] == eos_token_id) break;
+        }
+        return produced;
+    }
     if (eos_token_id < 0) {
         for (int s = 0; s < steps; ++s) SPB_CUDA(cudaGraphLaunch(e->graph, e->stream));
         e->seq_len += steps;

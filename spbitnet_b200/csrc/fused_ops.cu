@@ -54,6 +54,14 @@ __global__ void __launch_bounds__(1024) residual_norm_quant_kernel(
     grid_dep_launch();
     grid_dep_wait();
     const int tid = threadIdx.x, nt = blockDim.x;
+    {   // one block per vector: block b works on the b-th vector of n elements (prefill batches; decode has one)
+        const size_t off = static_cast<size_t>(blockIdx.x) * n;
+        if (delta) delta += off;
+        x += off;
+        if (xn_out) xn_out += off;
+        xq += off;
+        d_absmax += blockIdx.x;
+    }
     if (delta) {
         float sub_scale = 1.0f;
         if (sub_w) {
@@ -101,6 +109,14 @@ __global__ void __launch_bounds__(1024) relu2_norm_quant_kernel(
     grid_dep_launch();
     grid_dep_wait();
     const int tid = threadIdx.x, nt = blockDim.x;
+    {   // one block per vector, as in residual_norm_quant_kernel
+        const size_t off = static_cast<size_t>(blockIdx.x) * n;
+        gate += off;
+        up += off;
+        if (h_out) h_out += off;
+        hq += off;
+        d_absmax += blockIdx.x;
+    }
     float s = 0.0f;
     for (int i = tid; i < n; i += nt) {
         const float r = fmaxf(0.0f, __half2float(gate[i]));
@@ -136,7 +152,11 @@ __global__ void __launch_bounds__(256) rope_scatter_kernel(__half* __restrict__ 
                                                            const int* __restrict__ d_pos) {
     grid_dep_launch();
     grid_dep_wait();
-    const int pos = *d_pos;
+    // blockIdx.y = token of a prefill batch (0 in decode): its vectors follow one another, its position is *d_pos + y
+    const int pos = *d_pos + blockIdx.y;
+    q += static_cast<size_t>(blockIdx.y) * num_heads * head_dim;
+    k += static_cast<size_t>(blockIdx.y) * num_kv_heads * head_dim;
+    v += static_cast<size_t>(blockIdx.y) * num_kv_heads * head_dim;
     const int hp = head_dim / 2;
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     const int q_pairs = num_heads * hp, k_pairs = num_kv_heads * hp;
@@ -180,7 +200,10 @@ __global__ void __launch_bounds__(256) decode_attention_pos_kernel(
     __shared__ float sh[32];
     grid_dep_launch();
     grid_dep_wait();
-    const int seq_len = *d_pos + 1;
+    // blockIdx.y = token of a prefill batch (0 in decode): it sees the positions up to its own
+    const int seq_len = *d_pos + blockIdx.y + 1;
+    Q += static_cast<size_t>(blockIdx.y) * num_heads * head_dim;
+    out += static_cast<size_t>(blockIdx.y) * num_heads * head_dim;
     float* sc = dsm;
     float* part = dsm + ((max_seq_len + 31) & ~31);
     const int head = blockIdx.x;
@@ -338,32 +361,32 @@ static int fused_threads(int n) {
 }
 
 int residual_norm_quant(const void* delta, const float* sub_w, void* x, const float* w, void* xn_out,
-                        int8_t* xq, float* d_absmax, int n, float eps, void* stream) {
+                        int8_t* xq, float* d_absmax, int n, float eps, void* stream, int vectors) {
     const size_t smem = sizeof(float) * static_cast<size_t>(n);
     if (smem > 200 * 1024) return fail(SPB_E_UNSUPPORTED, "residual_norm_quant: n=%d too large", n);
     if (smem > 48 * 1024) cudaFuncSetAttribute(residual_norm_quant_kernel,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    return launch("residual_norm_quant", residual_norm_quant_kernel, dim3(1), dim3(fused_threads(n)), smem,
+    return launch("residual_norm_quant", residual_norm_quant_kernel, dim3(vectors), dim3(fused_threads(n)), smem,
                   stream, static_cast<const __half*>(delta), sub_w, static_cast<__half*>(x), w,
                   static_cast<__half*>(xn_out), xq, d_absmax, n, eps);
 }
 
 int relu2_norm_quant(const void* gate, const void* up, const float* sub_w, void* h_out, int8_t* hq,
-                     float* d_absmax, int n, float eps, void* stream) {
+                     float* d_absmax, int n, float eps, void* stream, int vectors) {
     const size_t smem = sizeof(float) * static_cast<size_t>(n);
     if (smem > 200 * 1024) return fail(SPB_E_UNSUPPORTED, "relu2_norm_quant: n=%d too large", n);
     if (smem > 48 * 1024) cudaFuncSetAttribute(relu2_norm_quant_kernel,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    return launch("relu2_norm_quant", relu2_norm_quant_kernel, dim3(1), dim3(fused_threads(n)), smem, stream,
+    return launch("relu2_norm_quant", relu2_norm_quant_kernel, dim3(vectors), dim3(fused_threads(n)), smem, stream,
                   static_cast<const __half*>(gate), static_cast<const __half*>(up), sub_w,
                   static_cast<__half*>(h_out), hq, d_absmax, n, eps);
 }
 
 int rope_scatter(void* q, const void* k, const void* v, void* kcache, void* vcache, int num_heads,
                  int num_kv_heads, int head_dim, int max_seq_len, float theta, const int* d_pos,
-                 void* stream) {
+                 void* stream, int vectors) {
     const int threads = (num_heads + num_kv_heads) * (head_dim / 2) + num_kv_heads * head_dim / 2;
-    return launch("rope_scatter", rope_scatter_kernel, dim3((threads + 255) / 256), dim3(256), 0, stream,
+    return launch("rope_scatter", rope_scatter_kernel, dim3((threads + 255) / 256, vectors), dim3(256), 0, stream,
                   static_cast<__half*>(q), static_cast<const __half*>(k), static_cast<const __half*>(v),
                   static_cast<__half*>(kcache), static_cast<__half*>(vcache), num_heads, num_kv_heads,
                   head_dim, max_seq_len, theta, d_pos);
@@ -371,12 +394,12 @@ int rope_scatter(void* q, const void* k, const void* v, void* kcache, void* vcac
 
 int decode_attention_pos(const void* Q, const void* K, const void* V, void* out, int num_heads,
                          int num_kv_heads, int head_dim, int max_seq_len, float scale, const int* d_pos,
-                         void* stream) {
+                         void* stream, int vectors) {
     const size_t smem = sizeof(float) * (((max_seq_len + 31) & ~31) + 8 * static_cast<size_t>(head_dim));
     if (smem > 200 * 1024) return fail(SPB_E_UNSUPPORTED, "decode_attention: max_seq_len %d too long", max_seq_len);
     if (smem > 48 * 1024) cudaFuncSetAttribute(decode_attention_pos_kernel,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    return launch("decode_attention_pos", decode_attention_pos_kernel, dim3(num_heads), dim3(256), smem,
+    return launch("decode_attention_pos", decode_attention_pos_kernel, dim3(num_heads, vectors), dim3(256), smem,
                   stream, static_cast<const __half*>(Q), static_cast<const __half*>(K),
                   static_cast<const __half*>(V), static_cast<__half*>(out), num_heads, num_kv_heads,
                   head_dim, max_seq_len, scale, d_pos);

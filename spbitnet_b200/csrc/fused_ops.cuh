@@ -1,19 +1,21 @@
 // Host launchers of the fused decode-step kernels (fused_ops.cu); engine-internal.
+// `vectors` > 1 runs the op on that many consecutive vectors (the tokens of a prefill batch): vector b of every
+// operand starts b * its length after the first, d_absmax is an array, and token b sits at position *d_pos + b.
 #pragma once
 #include "spb_common.cuh"
 
 namespace spb {
 
 int residual_norm_quant(const void* delta, const float* sub_w, void* x, const float* w, void* xn_out,
-                        int8_t* xq, float* d_absmax, int n, float eps, void* stream);
+                        int8_t* xq, float* d_absmax, int n, float eps, void* stream, int vectors = 1);
 int relu2_norm_quant(const void* gate, const void* up, const float* sub_w, void* h_out, int8_t* hq,
-                     float* d_absmax, int n, float eps, void* stream);
+                     float* d_absmax, int n, float eps, void* stream, int vectors = 1);
 int rope_scatter(void* q, const void* k, const void* v, void* kcache, void* vcache, int num_heads,
                  int num_kv_heads, int head_dim, int max_seq_len, float theta, const int* d_pos,
-                 void* stream);
+                 void* stream, int vectors = 1);
 int decode_attention_pos(const void* Q, const void* K, const void* V, void* out, int num_heads,
                          int num_kv_heads, int head_dim, int max_seq_len, float scale, const int* d_pos,
-                         void* stream);
+                         void* stream, int vectors = 1);
 // attention.cu: split-KV decode attention.  seq_len comes from *d_pos + 1 when d_pos is given.
 int decode_attention_split(const void* Q, const void* K, const void* V, void* out, int num_heads,
                            int num_kv_heads, int head_dim, int max_seq_len, int seq_len, const int* d_pos,
@@ -24,6 +26,11 @@ int embed_token(const void* embed, void* x, int hidden, const int* d_prompt, int
 int argmax_advance(const float* logits, int n, float* bval, int* bidx, int nblocks, int* d_next,
                    int* d_out, int* d_pos, void* stream);
 int set_int(int* dst, int value, void* stream);
+// prefill.cu: row-batched forms, one block per token of the batch
+int embed_rows(const void* embed, const int* d_tokens, void* x, int hidden, int vectors, void* stream);
+int absmax_quantize_rows(const void* in, int8_t* out, float* d_absmax, int n, int vectors, void* stream);
+int dequantize_rows(const int32_t* acc, void* out, const float* d_absmax, float gamma, int rows, int vectors,
+                    void* stream);
 
 // gemv.cu: up to three BitLinear layers that consume the same activation vector, one launch.
 struct BitLinearGroup {

@@ -72,6 +72,22 @@ class InferenceEngine:
         check(self._lib.spb_engine_forward(self._h, int(token_id), C.byref(out)))
         return out.value
 
+    def prefill(self, tokens) -> int:
+        """The tokens as one batch from the current position (what forward() token by token does, with the
+        BitLinear layers as the batched product); returns the device address of the last token's logits."""
+        t = np.ascontiguousarray(tokens, np.int32)
+        out = C.c_void_p(0)
+        check(self._lib.spb_engine_prefill(self._h, C.c_void_p(t.ctypes.data), len(t), C.byref(out)))
+        return out.value
+
+    def set_prefill_chunk(self, chunk: int) -> int:
+        """generate() feeds the prompt token by token when 0 (the reference's loop, default), else in batches
+        of up to `chunk` tokens.  Returns the previous setting."""
+        prev = self._lib.spb_engine_set_prefill_chunk(self._h, int(chunk))
+        if prev < 0:
+            check(prev)
+        return prev
+
     def logits(self) -> np.ndarray:
         h = np.empty(self.model.config["vocab_size"], np.float32)
         check(self._lib.spb_engine_copy_logits(self._h, C.c_void_p(h.ctypes.data)))
