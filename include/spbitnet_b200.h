@@ -121,6 +121,19 @@ int spb_sparse_ternary_gemm(const uint32_t* meta, const uint32_t* values, const 
                             int32_t* Y, int rows, int cols, int n, int meta_row_stride,
                             int values_row_stride, void* stream);
 
+/* BitLinear over a batch of quantised activation rows: the product above followed by dequantize_gpu
+ * (src/kernels/inference_kernels.cu:162-171) per activation row, i.e. what n calls of spb_sparse_bitlinear_q8
+ * give.  Xq: n rows of cols int8 (absmax_quantize_gpu outputs); d_absmax: their n scales (device);
+ * output: n rows of `rows` half, output[j*rows + r] = half(float(acc) * (gamma * d_absmax[j] / 127)).
+ * The default forms write the scaled output from their own epilogues; the other forms (set by
+ * spb_set_gemm_variant, or taken for layouts the tensor-core forms do not cover) need acc_workspace, a device
+ * buffer of n * rows int32 whose contents are overwritten, and answer SPB_E_UNSUPPORTED when it is NULL.
+ * The reference has no batched BitLinear; its prefill calls fused_sparse_bitlinear_gpu once per token
+ * (src/main.cpp:266-267, src/inference.cu:106-117). */
+int spb_sparse_bitlinear_gemm(const uint32_t* meta, const uint32_t* values, const int8_t* Xq, void* output,
+                              const float* d_absmax, float gamma, int32_t* acc_workspace, int rows, int cols,
+                              int n, int meta_row_stride, int values_row_stride, void* stream);
+
 /* Which form spb_sparse_ternary_gemm uses: 0 (default) = automatic: up to 32 batch rows the warp-level
  * sparse MMA form (mma.sp m16n8k64, operands re-encoded in registers; needs cols % 256 == 0, row strides
  * that are multiples of 4 words and 16-byte aligned meta / values / X), above that the tcgen05 sparse form

@@ -61,6 +61,7 @@ SIGNATURES = {
     "spb_gemv_batch_check": (_i, [_p, _i]),
     "spb_sparse_ternary_gemv_batch": (_i, [_p, _i, _i, _i, _p]),
     "spb_sparse_ternary_gemm": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
+    "spb_sparse_bitlinear_gemm": (_i, [_p, _p, _p, _p, _p, C.c_float, _p, _i, _i, _i, _i, _i, _p]),
     "spb_set_gemm_variant": (_i, [_i]),
     "spb_gemm_tc_timeouts": (_i, []),
     "spb_rms_norm": (_i, [_p, _p, _p, _i, _f, _p]),

@@ -14,7 +14,8 @@
 
 namespace spb {
 
-constexpr int kChunk = 128;      // positions per block
+constexpr int kChunk = 64;       // positions per block
+constexpr int kRowsPerWarp = kChunk / 8;  // kAttnThreads / 32 warps share a chunk
 constexpr int kAttnThreads = 256;
 constexpr int kMaxGroup = 8;     // query heads per KV head held in registers
 
@@ -29,7 +30,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_split_kernel(
     const __half* __restrict__ Q, const __half* __restrict__ K, const __half* __restrict__ V,
     float* __restrict__ scratch, int num_kv_heads, int head_dim, int max_seq_len, int nsplit_max,
     float scale, int seq_len_arg, const int* __restrict__ d_pos) {
-    extern __shared__ float asm_[];  // [G][kChunk] scores, then [2][G][head_dim] partial outputs
+    extern __shared__ float asm_[];  // [G][kChunk] scores, then [8 warps][G][head_dim] partial outputs
     grid_dep_launch();
     grid_dep_wait();
     const int seq_len = d_pos ? (*d_pos + 1) : seq_len_arg;
@@ -44,7 +45,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_split_kernel(
     const __half* vbase = V + (static_cast<size_t>(kvh) * max_seq_len + p0) * head_dim;
     const int ndl = (head_dim + 31) / 32;  // dims per lane, at most 8 (head_dim <= 256)
 
-    // ---- scores: warp w takes positions w, w+8, ...; four rows in flight per step ---------
+    // ---- scores: warp w takes positions w, w+8, ...: all of a warp's rows are in flight at once -------
     float qreg[G][8];
 #pragma unroll
     for (int g = 0; g < G; ++g)
@@ -54,11 +55,12 @@ __global__ void __launch_bounds__(kAttnThreads) attn_split_kernel(
             qreg[g][i] = (i < ndl && d < head_dim)
                              ? __half2float(Q[(static_cast<size_t>(kvh) * G + g) * head_dim + d]) : 0.0f;
         }
-    for (int j0 = warp; j0 < np; j0 += 4 * nw) {
-        float kv[4][8];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int j = j0 + u * nw;
+    for (int half = 0; half < 2; ++half) {
+        float kv[kRowsPerWarp / 2][8];
+#pragma unroll
+        for (int u = 0; u < kRowsPerWarp / 2; ++u) {
+            const int j = warp + (half * (kRowsPerWarp / 2) + u) * nw;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const int d = lane + 32 * i;
@@ -67,8 +69,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_split_kernel(
             }
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int j = j0 + u * nw;
+        for (int u = 0; u < kRowsPerWarp / 2; ++u) {
+            const int j = warp + (half * (kRowsPerWarp / 2) + u) * nw;
 #pragma unroll
             for (int g = 0; g < G; ++g) {
                 float acc = 0.0f;
@@ -104,27 +106,53 @@ __global__ void __launch_bounds__(kAttnThreads) attn_split_kernel(
     }
     __syncthreads();
 
-    // ---- sum_j e[g][j] * V[j][d]: the block is two halves of positions x head_dim dims ----------
+    // ---- sum_j e[g][j] * V[j][d]: warp w takes positions w, w+8, ... (four rows in flight), lane l the dims
+    //      l, l+32, ...; the eight partial sums meet in shared memory ------------------------------------
     {
-        const int halves = (kAttnThreads >= 2 * head_dim) ? 2 : 1;
-        const int d = tid % head_dim, hsel = tid / head_dim;
-        float acc[G];
+        float acc[G][8];
 #pragma unroll
-        for (int g = 0; g < G; ++g) acc[g] = 0.0f;
-        if (hsel < halves) {
-            for (int j = hsel; j < np; j += halves) {
-                const float vv = __half2float(vbase[static_cast<size_t>(j) * head_dim + d]);
+        for (int g = 0; g < G; ++g)
 #pragma unroll
-                for (int g = 0; g < G; ++g) acc[g] += sc[g * kChunk + j] * vv;
+            for (int i = 0; i < 8; ++i) acc[g][i] = 0.0f;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            float vv[kRowsPerWarp / 2][8];
+#pragma unroll
+            for (int u = 0; u < kRowsPerWarp / 2; ++u) {
+                const int j = warp + (half * (kRowsPerWarp / 2) + u) * nw;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int d = lane + 32 * i;
+                    vv[u][i] = (i < ndl && d < head_dim && j < np)
+                                   ? __half2float(vbase[static_cast<size_t>(j) * head_dim + d]) : 0.0f;
+                }
             }
 #pragma unroll
-            for (int g = 0; g < G; ++g) po[(hsel * G + g) * head_dim + d] = acc[g];
+            for (int u = 0; u < kRowsPerWarp / 2; ++u) {
+                const int j = warp + (half * (kRowsPerWarp / 2) + u) * nw;
+                if (j < np) {
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        const float e = sc[g * kChunk + j];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) acc[g][i] += e * vv[u][i];
+                    }
+                }
+            }
         }
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int d = lane + 32 * i;
+                if (i < ndl && d < head_dim) po[(warp * G + g) * head_dim + d] = acc[g][i];
+            }
         __syncthreads();
         for (int t = tid; t < G * head_dim; t += kAttnThreads) {
             const int g = t / head_dim, dd = t - g * head_dim;
-            float o = po[g * head_dim + dd];
-            if (halves == 2) o += po[(G + g) * head_dim + dd];
+            float o = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kAttnThreads / 32; ++w) o += po[(w * G + g) * head_dim + dd];
             scratch[(static_cast<size_t>(kvh * G + g) * nsplit_max + split) * (head_dim + 2) + 2 + dd] = o;
         }
     }
@@ -164,7 +192,7 @@ int decode_attention_split(const void* Q, const void* K, const void* V, void* ou
         return fail(SPB_E_UNSUPPORTED, "%s: group %d / head_dim %d outside the kernel's range", name, G, head_dim);
     const int nsplit_max = (max_seq_len + kChunk - 1) / kChunk;
     const int nsplit = d_pos ? nsplit_max : (seq_len + kChunk - 1) / kChunk;
-    const size_t smem = sizeof(float) * (static_cast<size_t>(G) * kChunk + 2 * G * head_dim);
+    const size_t smem = sizeof(float) * (static_cast<size_t>(G) * kChunk + (kAttnThreads / 32) * G * head_dim);
     const dim3 grid(num_kv_heads, nsplit);
     const __half* q = static_cast<const __half*>(Q);
     const __half* k = static_cast<const __half*>(K);
@@ -172,6 +200,9 @@ int decode_attention_split(const void* Q, const void* K, const void* V, void* ou
     int rc = SPB_OK;
 #define SPB_ATTN_CASE(GG)                                                                              \
     case GG:                                                                                           \
+        if (smem > 48 * 1024)                                                                          \
+            cudaFuncSetAttribute(attn_split_kernel<GG>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                                 static_cast<int>(smem));                                              \
         rc = launch(name, attn_split_kernel<GG>, grid, dim3(kAttnThreads), smem, stream, q, k, v, scratch, \
                     num_kv_heads, head_dim, max_seq_len, nsplit_max, scale, seq_len, d_pos);               \
         break;

@@ -78,6 +78,11 @@ struct spb_engine {
     int32_t* pf_acc = nullptr;
     float* pf_absmax = nullptr;  // two arrays of pf_cap
     int* pf_tokens = nullptr;
+    // a chunk of T tokens replayed as a CUDA graph once the same (T, last) has been asked for twice in a row
+    struct PrefillGraph { int T; bool last; cudaGraphExec_t exec; };
+    std::vector<PrefillGraph> pf_graphs;
+    int pf_prev_T = 0;
+    bool pf_prev_last = false;
 };
 
 namespace {
@@ -194,6 +199,9 @@ void drop_graph(spb_engine* e) {
         cudaGraphExecDestroy(e->graph);
         e->graph = nullptr;
     }
+    for (auto& g : e->pf_graphs) cudaGraphExecDestroy(g.exec);
+    e->pf_graphs.clear();
+    e->pf_prev_T = 0;
 }
 
 int ensure_graph(spb_engine* e, bool record_tokens, int n_prompt) {
@@ -236,6 +244,9 @@ int ensure_prefill_buffers(spb_engine* e, int cap) {
     if (e->pf_cap >= cap) return SPB_OK;
     if (e->pf_pool) {
         SPB_CUDA(cudaStreamSynchronize(e->stream));
+        for (auto& g : e->pf_graphs) cudaGraphExecDestroy(g.exec);  // they hold the old addresses
+        e->pf_graphs.clear();
+        e->pf_prev_T = 0;
         cudaFree(e->pf_pool);
         e->pf_pool = nullptr;
         e->pf_cap = 0;
@@ -272,9 +283,8 @@ int ensure_prefill_buffers(spb_engine* e, int cap) {
 
 // out[t] = BitLinear(L) of the T quantised rows in pf_xq with the row scales `absmax`
 int prefill_linear(spb_engine* e, const Linear& L, const float* absmax, __half* out, int T) {
-    int rc = spb_sparse_ternary_gemm(L.meta, L.values, e->pf_xq, e->pf_acc, L.rows, L.cols, T, L.ms, L.vs, e->stream);
-    if (rc) return rc;
-    return dequantize_rows(e->pf_acc, out, absmax, L.gamma, L.rows, T, e->stream);
+    return spb_sparse_bitlinear_gemm(L.meta, L.values, e->pf_xq, out, absmax, L.gamma, e->pf_acc, L.rows, L.cols, T, L.ms,
+                                     L.vs, e->stream);
 }
 
 // Tokens d_tokens[0..T) at positions start..start+T-1 (T <= pf_cap); *d_pos must hold `start`.  With `last`
@@ -320,6 +330,41 @@ int enqueue_prefill_chunk(spb_engine* e, int T, bool last) {
     return spb_half_gemv(e->lm_head ? e->lm_head : e->embed, e->xfinal, e->logits, c.vocab_size, H, s);
 }
 
+// A chunk is some 500 launches; issued one by one the host is slower than the GPU.  All of a chunk's operands sit at
+// fixed addresses (batch buffers, device-resident position), so the chunk is captured as a graph when the same
+// (T, last) comes twice in a row (full chunks of a long prompt, prompts of one length) and replayed from then on.
+int run_prefill_chunk(spb_engine* e, int T, bool last) {
+    for (const auto& g : e->pf_graphs)
+        if (g.T == T && g.last == last) {
+            SPB_CUDA(cudaGraphLaunch(g.exec, e->stream));
+            return SPB_OK;
+        }
+    const bool repeat = e->pf_prev_T == T && e->pf_prev_last == last;
+    e->pf_prev_T = T;
+    e->pf_prev_last = last;
+    if (!repeat) return enqueue_prefill_chunk(e, T, last);
+    SPB_CUDA(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
+    const int rc = enqueue_prefill_chunk(e, T, last);
+    cudaGraph_t g = nullptr;
+    cudaError_t err = cudaStreamEndCapture(e->stream, &g);
+    if (rc) {
+        if (g) cudaGraphDestroy(g);
+        return rc;
+    }
+    if (err != cudaSuccess) return cuda_fail("cudaStreamEndCapture", err);
+    cudaGraphExec_t exec = nullptr;
+    err = cudaGraphInstantiate(&exec, g, 0);
+    cudaGraphDestroy(g);
+    if (err != cudaSuccess) return cuda_fail("cudaGraphInstantiate", err);
+    if (e->pf_graphs.size() >= 4) {
+        cudaGraphExecDestroy(e->pf_graphs.front().exec);
+        e->pf_graphs.erase(e->pf_graphs.begin());
+    }
+    e->pf_graphs.push_back({T, last, exec});
+    SPB_CUDA(cudaGraphLaunch(exec, e->stream));
+    return SPB_OK;
+}
+
 // Runs tokens[0..n) (HOST array) through the model from position e->seq_len in chunks; leaves the logits of
 // the last one in e->logits, *d_pos = e->seq_len = old + n.  Validated by the caller.
 int prefill_tokens(spb_engine* e, const int* tokens, int n) {
@@ -332,7 +377,7 @@ int prefill_tokens(spb_engine* e, const int* tokens, int n) {
         // the token ids are consumed by the first kernel of the chunk; the copy is ordered before it on the stream
         SPB_CUDA(cudaMemcpyAsync(e->pf_tokens, tokens + done, sizeof(int) * T, cudaMemcpyHostToDevice, e->stream));
         if ((rc = set_int(e->d_pos, e->seq_len, e->stream))) return rc;
-        if ((rc = enqueue_prefill_chunk(e, T, done + T == n))) return rc;
+        if ((rc = run_prefill_chunk(e, T, done + T == n))) return rc;
         e->seq_len += T;  // the next chunk's copy into pf_tokens is ordered after this chunk's kernels by the stream
     }
     return set_int(e->d_pos, e->seq_len, e->stream);

@@ -145,14 +145,17 @@ int gemm_tc_launch(const uint32_t* meta, const uint32_t* values, const int8_t* X
                    int n, int meta_stride, int values_stride, void* stream);
 
 int gemm_tcsp_ws_launch(const uint32_t* meta, const uint32_t* values, const int8_t* X, int32_t* Y, int rows, int cols,
-                        int n, int meta_stride, int values_stride, void* stream);
+                        int n, int meta_stride, int values_stride, void* stream, const GemmEpilogue* ep);
+// prefill.cu
+int dequantize_rows(const int32_t* acc, void* out, const float* d_absmax, float gamma, int rows, int vectors,
+                    void* stream);
 int gemm_tcsp_launch(const uint32_t* meta, const uint32_t* values, const int8_t* X, int32_t* Y, int rows, int cols,
                      int n, int meta_stride, int values_stride, void* stream);
 
 bool gemm_mmasp_supported(const uint32_t* meta, const uint32_t* values, const int8_t* X, int rows, int cols, int n,
                           int meta_stride, int values_stride, int max_n);
 int gemm_mmasp_launch(const uint32_t* meta, const uint32_t* values, const int8_t* X, int32_t* Y, int rows, int cols,
-                      int n, int meta_stride, int values_stride, void* stream);
+                      int n, int meta_stride, int values_stride, void* stream, const GemmEpilogue* ep);
 
 // 0 automatic (up to 32 batch rows: warp-level sparse MMA form; above: tcgen05 sparse form; SIMT where the layout
 // allows neither), 1 SIMT form, 2 tcgen05 dense form, 3 tcgen05 sparse form, 4 warp-level sparse MMA form
@@ -170,19 +173,46 @@ extern "C" int spb_set_gemm_variant(int variant) {
     return old;
 }
 
+// The batched product.  With `ep` the output is the scaled half matrix: the two default forms write it from their
+// own epilogues (Y unused); every other form leaves the sums in Y, which must then be a workspace of n * rows
+// int32, and a per-row dequantise follows on the same stream.
+static int gemm_dispatch(const char* name, const uint32_t* meta, const uint32_t* values, const int8_t* X, int32_t* Y,
+                         int rows, int cols, int n, int meta_row_stride, int values_row_stride, void* stream,
+                         const GemmEpilogue* ep);
+static int gemm_dispatch_int(const char* name, const uint32_t* meta, const uint32_t* values, const int8_t* X, int32_t* Y,
+                             int rows, int cols, int n, int meta_row_stride, int values_row_stride, void* stream,
+                             bool fast);
+
 extern "C" int spb_sparse_ternary_gemm(const uint32_t* meta, const uint32_t* values, const int8_t* X,
                                        int32_t* Y, int rows, int cols, int n, int meta_row_stride,
                                        int values_row_stride, void* stream) {
     const char* name = "spb_sparse_ternary_gemm";
     if (rows < 0 || cols < 0 || n < 0) return fail(SPB_E_INVALID, "%s: negative size", name);
     if (rows == 0 || cols == 0 || n == 0) return SPB_OK;
+    if (!Y) return fail(SPB_E_INVALID, "%s: null pointer", name);
+    return gemm_dispatch(name, meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream, nullptr);
+}
+
+extern "C" int spb_sparse_bitlinear_gemm(const uint32_t* meta, const uint32_t* values, const int8_t* Xq, void* output,
+                                         const float* d_absmax, float gamma, int32_t* acc_workspace, int rows,
+                                         int cols, int n, int meta_row_stride, int values_row_stride, void* stream) {
+    const char* name = "spb_sparse_bitlinear_gemm";
+    if (rows < 0 || cols < 0 || n < 0) return fail(SPB_E_INVALID, "%s: negative size", name);
+    if (rows == 0 || cols == 0 || n == 0) return SPB_OK;
+    if (!output || !d_absmax) return fail(SPB_E_INVALID, "%s: null pointer", name);
+    const GemmEpilogue ep{static_cast<__half*>(output), d_absmax, gamma};
+    return gemm_dispatch(name, meta, values, Xq, acc_workspace, rows, cols, n, meta_row_stride, values_row_stride,
+                         stream, &ep);
+}
+
+static int gemm_dispatch(const char* name, const uint32_t* meta, const uint32_t* values, const int8_t* X, int32_t* Y,
+                         int rows, int cols, int n, int meta_row_stride, int values_row_stride, void* stream,
+                         const GemmEpilogue* ep) {
     if (cols % 4 != 0) return fail(SPB_E_INVALID, "%s: cols=%d is not a multiple of 4", name, cols);
-    if (!meta || !values || !X || !Y) return fail(SPB_E_INVALID, "%s: null pointer", name);
+    if (!meta || !values || !X) return fail(SPB_E_INVALID, "%s: null pointer", name);
     if (meta_row_stride < (cols / 4 + 7) / 8 || values_row_stride < (cols / 4 + 15) / 16)
         return fail(SPB_E_INVALID, "%s: row stride shorter than a row", name);
-    GemmArgs a{meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, 0, 0};
     auto al = [](const void* p, size_t k) { return (reinterpret_cast<uintptr_t>(p) & (k - 1)) == 0; };
-    const size_t x_bytes = static_cast<size_t>(kBatchTile) * cols;
     const bool fast = cols % 128 == 0 && cols / 128 <= 512 && meta_row_stride % 4 == 0 &&
                       values_row_stride % 2 == 0 && al(meta, 16) && al(values, 8) && al(X, 16);
     // up to 32 batch rows the warp-level form always wins; up to 64 it still does when the tcgen05 form, with
@@ -191,11 +221,27 @@ extern "C" int spb_sparse_ternary_gemm(const uint32_t* meta, const uint32_t* val
     if ((g_gemm_variant == 0 || g_gemm_variant == 4) &&
         gemm_mmasp_supported(meta, values, X, rows, cols, n, meta_row_stride, values_row_stride,
                              g_gemm_variant == 4 ? 4096 : mma_auto_max_n))
-        return gemm_mmasp_launch(meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream);
+        return gemm_mmasp_launch(meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream, ep);
     if (fast && (g_gemm_variant == 0 || g_gemm_variant == 4)) {  // warp-specialised tcgen05 sparse form
-        const int rc = gemm_tcsp_ws_launch(meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream);
+        const int rc = gemm_tcsp_ws_launch(meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream, ep);
         if (rc != SPB_E_UNSUPPORTED) return rc;  // no tensor map of X on this system: the plain form below
     }
+    if (ep) {  // the remaining forms write int32 sums: run them into the workspace, then scale row by row
+        if (!Y) return fail(SPB_E_UNSUPPORTED, "%s: this layout needs acc_workspace (n * rows int32)", name);
+        const int rc = gemm_dispatch_int(name, meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream,
+                                         fast);
+        if (rc) return rc;
+        return dequantize_rows(Y, ep->out, ep->absmax, ep->gamma, rows, n, stream);
+    }
+    return gemm_dispatch_int(name, meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream, fast);
+}
+
+// The forms without a fused epilogue: plain tcgen05 sparse, tcgen05 dense, SIMT.
+static int gemm_dispatch_int(const char* name, const uint32_t* meta, const uint32_t* values, const int8_t* X, int32_t* Y,
+                             int rows, int cols, int n, int meta_row_stride, int values_row_stride, void* stream,
+                             bool fast) {
+    GemmArgs a{meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, 0, 0};
+    const size_t x_bytes = static_cast<size_t>(kBatchTile) * cols;
     if (fast && (g_gemm_variant == 3 || g_gemm_variant == 0 || g_gemm_variant == 4))
         return gemm_tcsp_launch(meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream);
     if (fast && g_gemm_variant == 2)

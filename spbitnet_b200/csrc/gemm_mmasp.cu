@@ -39,6 +39,7 @@ struct GqArgs {
     int mpitch;   // shared-memory row pitch of the bitmap words, in words (= 4 mod 32)
     int vpitch;   // same for the sign words
     int xpitch;   // shared-memory pitch of an activation row, bytes (cols + 64)
+    GemmEpilogue ep;  // ep.out set: scaled half output instead of Y
 };
 
 __device__ __forceinline__ uint32_t gq_index_pairs(uint32_t m) {
@@ -208,7 +209,11 @@ __global__ void __launch_bounds__(kGqThreads, 2) gemm_mmasp_kernel(const GqArgs 
             const int rblk = r >> 4, rr = r & 15;
             int sum = 0;
             for (int k = 0; k < a.ks; ++k) sum += red[(((rblk << a.ks_log2) + k) * 16 + rr) * NC + jc];
-            a.Y[static_cast<size_t>(j0 + jc) * a.rows + row0 + r] = sum;
+            const size_t o = static_cast<size_t>(j0 + jc) * a.rows + row0 + r;
+            if (a.ep.out)
+                a.ep.out[o] = __float2half_rn(__fmul_rn(static_cast<float>(sum), dequant_scale(a.ep.gamma, a.ep.absmax[j0 + jc])));
+            else
+                a.Y[o] = sum;
         }
     }
 }
@@ -223,10 +228,11 @@ bool gemm_mmasp_supported(const uint32_t* meta, const uint32_t* values, const in
 }
 
 int gemm_mmasp_launch(const uint32_t* meta, const uint32_t* values, const int8_t* X, int32_t* Y, int rows, int cols,
-                      int n, int meta_stride, int values_stride, void* stream) {
+                      int n, int meta_stride, int values_stride, void* stream, const GemmEpilogue* ep) {
     const char* name = "spb_sparse_ternary_gemm(mma.sp)";
     GqArgs a{};
     a.meta = meta; a.values = values; a.X = X; a.Y = Y;
+    if (ep) a.ep = *ep;
     a.rows = rows; a.cols = cols; a.n = n;
     a.meta_stride = meta_stride; a.values_stride = values_stride;
     a.steps = cols / 64;

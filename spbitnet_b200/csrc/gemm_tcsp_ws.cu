@@ -47,6 +47,7 @@ struct WsArgs {
     int nt;         // batch rows per block: multiple of 16, at most 256
     int stages;     // ring depth (2..kWsMaxStages)
     int tmem_cols;  // power of two >= nt + 8 * stages
+    GemmEpilogue ep;  // ep.out set: scaled half output instead of Y
 };
 
 __device__ int g_tcsp_ws_timeouts = 0;  // roles whose bounded wait ran out (0 in a healthy run)
@@ -308,7 +309,14 @@ __global__ void __launch_bounds__(kWsThreads, 1) gemm_tcsp_ws_kernel(const WsArg
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const int j = n0 + c0 + i;
-                        if (c0 + i < a.nt && j < a.n) a.Y[static_cast<size_t>(j) * a.rows + row] = static_cast<int32_t>(r[i]);
+                        if (c0 + i < a.nt && j < a.n) {
+                            const size_t o = static_cast<size_t>(j) * a.rows + row;
+                            if (a.ep.out)
+                                a.ep.out[o] = __float2half_rn(__fmul_rn(static_cast<float>(static_cast<int32_t>(r[i])),
+                                                                        dequant_scale(a.ep.gamma, a.ep.absmax[j])));
+                            else
+                                a.Y[o] = static_cast<int32_t>(r[i]);
+                        }
                     }
                 }
             }
@@ -327,9 +335,10 @@ __global__ void __launch_bounds__(kWsThreads, 1) gemm_tcsp_ws_kernel(const WsArg
 // Launch of the warp-specialised form; the caller has checked the layout (cols % 128 == 0, aligned rows and X).
 // Returns SPB_E_UNSUPPORTED when the tensor map of X cannot be made (the caller then takes the plain form).
 int gemm_tcsp_ws_launch(const uint32_t* meta, const uint32_t* values, const int8_t* X, int32_t* Y, int rows, int cols,
-                        int n, int meta_stride, int values_stride, void* stream) {
+                        int n, int meta_stride, int values_stride, void* stream, const GemmEpilogue* ep) {
     WsArgs a{};
     a.meta = meta; a.values = values; a.Y = Y;
+    if (ep) a.ep = *ep;
     a.rows = rows; a.cols = cols; a.n = n;
     a.meta_stride = meta_stride; a.values_stride = values_stride;
     static const int nt_env = [] {

@@ -93,6 +93,14 @@ __device__ __forceinline__ float dequant_scale(float gamma, float absmax) {
     return __fdiv_rn(__fmul_rn(gamma, absmax), 127.0f);
 }
 
+// Optional BitLinear epilogue of the batched product: with `out` set, output row j is written as
+// half(float(acc) * dequant_scale(gamma, absmax[j])) (dequantize_gpu per activation row) instead of the int32 sums.
+struct GemmEpilogue {
+    __half* out;          // [n, rows] half, or nullptr
+    const float* absmax;  // n row scales
+    float gamma;
+};
+
 
 // ---------------------------------------------------------------------------
 // (bitmap | signs << 4) -> the four int8 weights of a group, packed little-endian

@@ -108,6 +108,16 @@ def sparse_ternary_gemm_gpu(meta, values, X, Y, rows, cols, n, meta_row_stride, 
                                          values_row_stride, _stream(stream)))
 
 
+def sparse_bitlinear_gemm_gpu(meta, values, Xq, output, d_absmax, gamma, rows, cols, n, meta_row_stride,
+                              values_row_stride, acc_workspace=None, stream=None):
+    """BitLinear over n quantised activation rows (no counterpart in the reference, whose prefill is token-serial):
+    output[j] = half(float(W @ Xq[j]) * (gamma * d_absmax[j] / 127)).  acc_workspace: n * rows int32, needed only by
+    the forms without a fused epilogue."""
+    ws = _p(acc_workspace) if acc_workspace is not None else None
+    check(load().spb_sparse_bitlinear_gemm(_p(meta), _p(values), _p(Xq), _p(output), _p(d_absmax), float(gamma), ws,
+                                           rows, cols, n, meta_row_stride, values_row_stride, _stream(stream)))
+
+
 # ---- inference_kernels.h ----------------------------------------------------------------
 
 def rms_norm_gpu(input, weight, output, size, eps, stream=None):

@@ -8,8 +8,53 @@ import oracle
 from spbitnet_b200 import synth
 from spbitnet_b200 import kernels as K
 from spbitnet_b200.engine import DeviceModel, InferenceEngine
+from gpu_util import Guarded, dev
 
 pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(params=[0, 1, 3], ids=["auto", "simt", "tcgen05sp"])
+def gemm_variant(request):
+    old = K.set_gemm_variant(request.param)
+    yield request.param
+    K.set_gemm_variant(old)
+
+
+@pytest.mark.parametrize("rows,cols,n", [(256, 256, 1), (640, 2560, 5), (2560, 2560, 40), (6912, 2560, 130),
+                                          (2560, 6912, 64), (129, 384, 33), (100, 260, 7), (300, 1024, 257)])
+def test_batched_bitlinear_is_gemm_then_dequantize(rows, cols, n, gemm_variant):
+    # half outputs bit-identical to the oracle's dequantize of the oracle's integer product, row by row
+    case = synth.gemm_case(rows, cols, n, seed=n)
+    rng = np.random.default_rng(n)
+    absmax = rng.uniform(0.5, 4.0, n).astype(np.float32)
+    absmax[0] = 0.0  # an all-zero activation row: scale 0, outputs +0
+    gamma = np.float32(0.0371)
+    acc = oracle.sparse_gemm(case["meta"], case["values"], case["X"], rows, cols)
+    want = np.stack([oracle.dequantize(acc[j], absmax[j], gamma) for j in range(n)])
+    out = Guarded(n * rows * 2)
+    ws = Guarded(n * rows * 4)
+    K.sparse_bitlinear_gemm_gpu(dev(case["meta"]), dev(case["values"]), dev(case["X"]), out.ptr, dev(absmax), gamma,
+                                rows, cols, n, case["meta_stride"], case["values_stride"], acc_workspace=ws.ptr)
+    got = out.read(np.float16).reshape(n, rows)
+    assert (got.view(np.uint16) == want.view(np.uint16)).all()
+    assert K.gemm_tc_timeouts() == 0
+
+
+def test_batched_bitlinear_without_workspace():
+    # the default forms need no workspace; a layout that falls to the SIMT form answers "unsupported" without one
+    case = synth.gemm_case(2560, 2560, 48, seed=1)
+    absmax = np.ones(48, np.float32)
+    out = Guarded(48 * 2560 * 2)
+    K.sparse_bitlinear_gemm_gpu(dev(case["meta"]), dev(case["values"]), dev(case["X"]), out.ptr, dev(absmax), 1.0,
+                                2560, 2560, 48, case["meta_stride"], case["values_stride"])
+    acc = oracle.sparse_gemm(case["meta"], case["values"], case["X"], 2560, 2560)
+    want = np.stack([oracle.dequantize(acc[j], 1.0, 1.0) for j in range(48)])
+    assert (out.read(np.float16).reshape(48, 2560).view(np.uint16) == want.view(np.uint16)).all()
+    odd = synth.gemm_case(100, 260, 7, seed=2)
+    out2 = Guarded(7 * 100 * 2)
+    with pytest.raises(Exception):
+        K.sparse_bitlinear_gemm_gpu(dev(odd["meta"]), dev(odd["values"]), dev(odd["X"]), out2.ptr, dev(absmax), 1.0,
+                                    100, 260, 7, odd["meta_stride"], odd["values_stride"])
 
 
 def _serial_logits(eng, tokens):
@@ -55,6 +100,28 @@ def test_prefill_in_two_calls_equals_one_call():
     assert eng.seq_len == 20
     # the second call's tokens attend to the first call's cache entries; the arithmetic per token is the same
     assert (one == two).all()
+
+
+def test_repeated_prefill_replays_a_graph_with_the_same_result():
+    # the first call launches kernel by kernel, the second captures a graph, the third replays it
+    model = synth.random_model(synth.TINY, seed=14)
+    eng = InferenceEngine(DeviceModel(model))
+    tokens = np.random.default_rng(1).integers(0, synth.TINY["vocab_size"], 11).astype(np.int32)
+    outs = []
+    for _ in range(4):
+        eng.reset()
+        eng.prefill(tokens)
+        outs.append(eng.logits())
+    assert all((o == outs[0]).all() for o in outs[1:])
+    # a replayed chunk at another start position (the position lives in device memory)
+    eng.reset()
+    eng.prefill(tokens[:5])
+    eng.prefill(tokens)      # 11 tokens at positions 5..15, graph of T = 11
+    a = eng.logits()
+    eng.reset()
+    for t in list(tokens[:5]) + list(tokens):
+        eng.forward(int(t))
+    assert np.abs(a - eng.logits()).max() < 1e-2
 
 
 @pytest.mark.parametrize("chunk", [3, 8, 256])
