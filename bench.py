@@ -193,6 +193,12 @@ def run_ours(args):
         if world > 1:
             dist.destroy_process_group()
         return
+    if args.only_prefill:
+        if rank == 0:
+            print(json.dumps({"metric": "prefill_tok_s_2b4t_shape", "prefill": bench_prefill(args), "n_gpus": world}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
     if args.only_decode:
         if rank == 0:
             print(json.dumps({"metric": "decode_tok_s_2b4t_shape", "decode": bench_decode(args), "n_gpus": world}))
@@ -572,6 +578,34 @@ def bench_decode(args):
                     "H2D and token D2H; random-init 2B-4T shape, layer weights generated once and uploaded per layer"}
 
 
+def bench_prefill(args):
+    """The prompt as one batch through a random-init 2B-4T-shape model (engine.prefill), wall clock per call."""
+    import torch
+    from spbitnet_b200 import synth
+    from spbitnet_b200.engine import DeviceModel, InferenceEngine
+    cfg = dict(synth.BITNET_2B)
+    if args.decode_layers > 0:
+        cfg["num_hidden_layers"] = args.decode_layers
+    model = synth.random_model(cfg, seed=0, shared_layer=True)
+    eng = InferenceEngine(DeviceModel(model))
+    n = args.prefill_tokens
+    prompt = np.random.default_rng(0).integers(0, cfg["vocab_size"], n).astype(np.int32)
+    for _ in range(3):  # direct launches, graph capture, first replay
+        eng.reset()
+        eng.prefill(prompt)
+    times = []
+    for _ in range(5):
+        eng.reset()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        eng.prefill(prompt)
+        times.append(time.perf_counter() - t0)
+    dt = float(np.median(times))
+    return {"tokens": n, "layers": cfg["num_hidden_layers"], "ms": 1e3 * dt, "tok_s": n / dt,
+            "what": "engine.prefill(prompt): token ids H2D, all layers over the batch, logits of the last token; "
+                    "median of 5 calls after 3 warm-up calls"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -588,6 +622,8 @@ def main():
     ap.add_argument("--no-gemm", action="store_true")
     ap.add_argument("--only-gemm", action="store_true", help="only the batched-product section (profiling aid)")
     ap.add_argument("--only-decode", action="store_true", help="skip the GEMV sections (profiling aid)")
+    ap.add_argument("--only-prefill", action="store_true", help="only the batched-prefill timing (profiling aid)")
+    ap.add_argument("--prefill-tokens", type=int, default=128)
     ap.add_argument("--decode-layers", type=int, default=0, help="override the layer count of the decode model")
     ap.add_argument("--decode-tokens", type=int, default=256)
     args = ap.parse_args()
