@@ -59,3 +59,107 @@ def test_row_sharded_bitlinear_two_gpus():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert all(ok for _, ok in results)
+
+
+def _engine_worker(rank, world, port, out_q):
+    import time
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import oracle
+        from spbitnet_b200 import sharding, synth
+        from spbitnet_b200.engine import DeviceModel, InferenceEngine
+        ok, notes = True, {}
+        configs = [
+            dict(synth.TINY),
+            # five KV heads over two ranks (3 + 2), odd vocabulary (501 + 500 rows of the lm_head)
+            dict(hidden_size=640, num_hidden_layers=2, num_attention_heads=10, num_key_value_heads=5, head_dim=64,
+                 intermediate_size=1280, vocab_size=1001, max_position_embeddings=32, rms_norm_eps=1e-5,
+                 rope_theta=10000.0),
+        ]
+        for ci, cfg in enumerate(configs):
+            model = synth.random_model(cfg, seed=21 + ci)
+            sharded = sharding.ShardedEngine(model)
+            single = sharding.ShardedEngine(model, single=True)
+            fused = InferenceEngine(DeviceModel(model))
+            prompt = np.random.default_rng(ci).integers(0, cfg["vocab_size"], 5).astype(np.int32)
+            toks = [int(t) for t in prompt]
+            gen = []
+            for step in range(11):
+                tok = toks[step] if step < len(toks) else gen[-1]
+                a = sharded.forward(tok)
+                b = single.forward(tok)
+                fused.forward(tok)
+                c = fused.logits()
+                ah = a.cpu().numpy()
+                # same ops on row slices, concatenated: bit-identical to one rank
+                ok = ok and bool((ah.view(np.uint32) == b.cpu().numpy().view(np.uint32)).all())
+                # against the production engine (fused kernels, split attention): the engine's logits tolerance
+                ok = ok and float(np.abs(ah - c).max()) < 1e-2 and int(np.argmax(ah)) == int(np.argmax(c))
+                if step >= len(toks) - 1:
+                    gen.append(int(np.argmax(ah)))
+            if rank == 0:
+                want, _ = oracle.Engine(model).generate(prompt, 6)
+                ok = ok and gen[:6] == [int(t) for t in want]
+        # timing at the 2B-4T width (4 layers, small vocabulary): the sharded step against the same step on one rank
+        cfg = dict(synth.BITNET_2B, num_hidden_layers=4, vocab_size=8192, max_position_embeddings=128)
+        model = synth.random_model(cfg, seed=5, shared_layer=True)
+        for name, eng in (("sharded", sharding.ShardedEngine(model)), ("one_rank", sharding.ShardedEngine(model, single=True))):
+            for t in range(3):
+                eng.forward(t)
+            torch.cuda.synchronize()
+            dist.barrier()
+            t0 = time.perf_counter()
+            for t in range(20):
+                eng.forward(t)
+            torch.cuda.synchronize()
+            notes[name + "_ms_per_token"] = round((time.perf_counter() - t0) / 20 * 1e3, 3)
+        out_q.put((rank, ok, notes))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_row_sharded_engine_two_gpus():
+    """Whole decode step row-sharded over two GPUs (q/k/v by KV heads, the other matrices and the lm_head by rows,
+    all-gathers only): logits bit-identical to the same step on one rank, within 1e-2 of the production engine,
+    greedy tokens equal to the oracle's."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_engine_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=600) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    print("row-sharded engine timing:", [n for _, _, n in results])
+    assert all(ok for _, ok, _ in results)
+
+
+def test_sharded_engine_on_one_rank_matches_the_engine():
+    """The op-by-op step the sharded engine is made of (single=True: no process group) against the production engine
+    and the oracle; runs on any box."""
+    import oracle
+    from spbitnet_b200 import sharding, synth
+    from spbitnet_b200.engine import DeviceModel, InferenceEngine
+    model = synth.random_model(synth.TINY, seed=31)
+    eng = sharding.ShardedEngine(model, single=True)
+    fused = InferenceEngine(DeviceModel(model))
+    cpu = oracle.Engine(model)
+    for tok in [3, 400, 17, 99, 250, 1]:
+        a = eng.forward(tok).cpu().numpy()
+        fused.forward(tok)
+        want = cpu.forward(tok)
+        assert np.abs(a - want).max() < 1e-2
+        assert np.abs(a - fused.logits()).max() < 1e-2
+        assert int(np.argmax(a)) == oracle.argmax(want)
+    prompt = np.array([5, 17, 200], np.int32)
+    eng.reset()
+    want_tokens, _ = cpu.__class__(model).generate(prompt, 6)
+    assert (eng.generate(prompt, 6) == want_tokens).all()

@@ -72,3 +72,20 @@ def test_all_gather_of_row_slices_gloo(world, rows, mult):
         assert p.exitcode == 0
     assert sorted(r[0] for r in results) == list(range(world))
     assert all(ok and n == rows for _, ok, n in results)
+
+
+def test_head_split_keeps_query_heads_with_their_kv_head():
+    # the sharded engine splits q by (query heads per KV head) * head_dim rows and k/v by head_dim rows: on every
+    # rank the query heads must be exactly those of the rank's KV heads, also when the KV heads do not divide evenly
+    from spbitnet_b200 import sharding
+    for nh, nkv, hd, world in [(20, 5, 128, 2), (20, 5, 128, 4), (64, 8, 128, 8), (4, 2, 64, 2), (10, 5, 64, 3)]:
+        g = nh // nkv
+        covered = 0
+        for r in range(world):
+            q0, q1 = sharding.row_range(nh * hd, world, r, g * hd)
+            k0, k1 = sharding.row_range(nkv * hd, world, r, hd)
+            kv0, kv1 = sharding.row_range(nkv, world, r)
+            assert (k0, k1) == (kv0 * hd, kv1 * hd)
+            assert (q0, q1) == (kv0 * g * hd, kv1 * g * hd)
+            covered += kv1 - kv0
+        assert covered == nkv
