@@ -57,7 +57,8 @@ __device__ __forceinline__ uint32_t gq_lds(uint32_t addr) {
 }
 
 // NT = tiles of eight activation rows per block.
-template <int NT>
+// HALF_OUT: the epilogue writes the scaled half output (a.ep) instead of the int32 sums
+template <int NT, bool HALF_OUT>
 __global__ void __launch_bounds__(kGqThreads, 2) gemm_mmasp_kernel(const GqArgs a) {
     extern __shared__ uint8_t gq_raw[];
     // 2 KB-aligned: [sign table 2 KB][bitmap rows: 16 rb x mpitch words][sign rows: 16 rb x vpitch words]
@@ -210,7 +211,7 @@ __global__ void __launch_bounds__(kGqThreads, 2) gemm_mmasp_kernel(const GqArgs 
             int sum = 0;
             for (int k = 0; k < a.ks; ++k) sum += red[(((rblk << a.ks_log2) + k) * 16 + rr) * NC + jc];
             const size_t o = static_cast<size_t>(j0 + jc) * a.rows + row0 + r;
-            if (a.ep.out)
+            if (HALF_OUT)
                 a.ep.out[o] = __float2half_rn(__fmul_rn(static_cast<float>(sum), dequant_scale(a.ep.gamma, a.ep.absmax[j0 + jc])));
             else
                 a.Y[o] = sum;
@@ -260,7 +261,8 @@ int gemm_mmasp_launch(const uint32_t* meta, const uint32_t* values, const int8_t
     while (nt > 1 && (nt == 3 || 2048 + kGqSignLutBytes + slab + xbytes(nt) > 110 * 1024)) --nt;
     const size_t smem = 2048 + kGqSignLutBytes + slab + xbytes(nt);
     if (smem > 200 * 1024) return fail(SPB_E_UNSUPPORTED, "%s: %d columns do not fit", name, cols);
-    void (*kernel)(GqArgs) = nt == 1 ? gemm_mmasp_kernel<1> : nt == 2 ? gemm_mmasp_kernel<2> : gemm_mmasp_kernel<4>;
+    void (*kernel)(GqArgs) = nt == 1 ? gemm_mmasp_kernel<1, false> : nt == 2 ? gemm_mmasp_kernel<2, false> : gemm_mmasp_kernel<4, false>;
+    if (a.ep.out) kernel = nt == 1 ? gemm_mmasp_kernel<1, true> : nt == 2 ? gemm_mmasp_kernel<2, true> : gemm_mmasp_kernel<4, true>;
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (err != cudaSuccess) {
         cudaGetLastError();

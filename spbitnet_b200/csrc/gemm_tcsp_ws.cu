@@ -96,6 +96,8 @@ __device__ __forceinline__ uint32_t ws_index_pairs(uint32_t m) {
     return (t1 & 0x55555555u) | (t2 & 0xAAAAAAAAu);
 }
 
+// HALF_OUT: the epilogue writes the scaled half output (a.ep) instead of the int32 sums
+template <bool HALF_OUT>
 __global__ void __launch_bounds__(kWsThreads, 1) gemm_tcsp_ws_kernel(const WsArgs a, const __grid_constant__ CUtensorMap tmap_x) {
     extern __shared__ uint8_t ws_raw[];
     // [sign table 2 KB][barriers + tmem slot 128 B] ... 1024-aligned: [stage: A 16 KB | B0 nt*128 | B1 nt*128] x stages
@@ -311,7 +313,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) gemm_tcsp_ws_kernel(const WsArg
                         const int j = n0 + c0 + i;
                         if (c0 + i < a.nt && j < a.n) {
                             const size_t o = static_cast<size_t>(j) * a.rows + row;
-                            if (a.ep.out)
+                            if (HALF_OUT)
                                 a.ep.out[o] = __float2half_rn(__fmul_rn(static_cast<float>(static_cast<int32_t>(r[i])),
                                                                         dequant_scale(a.ep.gamma, a.ep.absmax[j])));
                             else
@@ -380,13 +382,14 @@ int gemm_tcsp_ws_launch(const uint32_t* meta, const uint32_t* values, const int8
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return SPB_E_UNSUPPORTED;
-    cudaError_t err = cudaFuncSetAttribute(gemm_tcsp_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    void (*kernel)(WsArgs, CUtensorMap) = a.ep.out ? gemm_tcsp_ws_kernel<true> : gemm_tcsp_ws_kernel<false>;
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (err != cudaSuccess) {
         cudaGetLastError();
         return fail(SPB_E_CUDA, "gemm_tcsp_ws: %s", cudaGetErrorString(err));
     }
     const dim3 grid((rows + kWsTileM - 1) / kWsTileM, (n + a.nt - 1) / a.nt);
-    return launch("spb_sparse_ternary_gemm(tcgen05.sp, warp-specialised)", gemm_tcsp_ws_kernel, grid, dim3(kWsThreads), smem,
+    return launch("spb_sparse_ternary_gemm(tcgen05.sp, warp-specialised)", kernel, grid, dim3(kWsThreads), smem,
                   stream, a, tmap);
 }
 
