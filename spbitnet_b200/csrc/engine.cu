@@ -83,6 +83,9 @@ struct spb_engine {
     std::vector<PrefillGraph> pf_graphs;
     int pf_prev_T = 0;
     bool pf_prev_last = false;
+    // side streams for the products of a layer that do not depend on one another (k, v beside q; up beside gate)
+    cudaStream_t pf_side[2] = {nullptr, nullptr};
+    cudaEvent_t pf_fork = nullptr, pf_join[2] = {nullptr, nullptr};
 };
 
 namespace {
@@ -261,8 +264,15 @@ int ensure_prefill_buffers(spb_engine* e, int cap) {
     const size_t o_x = take(2 * T * H), o_q = take(2 * T * qdim), o_k = take(2 * T * kvdim), o_v = take(2 * T * kvdim);
     const size_t o_attn = take(2 * T * qdim), o_o = take(2 * T * H), o_gate = take(2 * T * inter);
     const size_t o_up = take(2 * T * inter), o_down = take(2 * T * H), o_xq = take(T * maxdim);
-    const size_t o_acc = take(4 * T * maxdim), o_abs = take(4 * 2 * T), o_tok = take(4 * T);
+    const size_t o_acc = take(3 * 4 * T * maxdim), o_abs = take(4 * 2 * T), o_tok = take(4 * T);
     SPB_CUDA(cudaMalloc(&e->pf_pool, off));
+    if (!e->pf_fork) {
+        SPB_CUDA(cudaEventCreateWithFlags(&e->pf_fork, cudaEventDisableTiming));
+        for (int i = 0; i < 2; ++i) {
+            SPB_CUDA(cudaStreamCreateWithFlags(&e->pf_side[i], cudaStreamNonBlocking));
+            SPB_CUDA(cudaEventCreateWithFlags(&e->pf_join[i], cudaEventDisableTiming));
+        }
+    }
     uint8_t* p = e->pf_pool;
     e->pf_x = reinterpret_cast<__half*>(p + o_x);
     e->pf_q = reinterpret_cast<__half*>(p + o_q);
@@ -282,9 +292,30 @@ int ensure_prefill_buffers(spb_engine* e, int cap) {
 }
 
 // out[t] = BitLinear(L) of the T quantised rows in pf_xq with the row scales `absmax`
-int prefill_linear(spb_engine* e, const Linear& L, const float* absmax, __half* out, int T) {
-    return spb_sparse_bitlinear_gemm(L.meta, L.values, e->pf_xq, out, absmax, L.gamma, e->pf_acc, L.rows, L.cols, T, L.ms,
-                                     L.vs, e->stream);
+int prefill_linear(spb_engine* e, const Linear& L, const float* absmax, __half* out, int T, cudaStream_t stream,
+                   int32_t* acc) {
+    return spb_sparse_bitlinear_gemm(L.meta, L.values, e->pf_xq, out, absmax, L.gamma, acc, L.rows, L.cols, T, L.ms,
+                                     L.vs, stream);
+}
+
+// Up to three BitLinear layers on the same quantised rows: the first on the engine's stream, the others on side
+// streams between a fork and a join event (graph capture turns these into parallel branches), so that products
+// with few row tiles share the machine.  Each gets its own third of the int32 workspace.
+int prefill_linear_group(spb_engine* e, const Linear* const* L, __half* const* out, int n, const float* absmax, int T) {
+    const spb_model_config& c = e->cfg;
+    const size_t maxdim = std::max(std::max(static_cast<size_t>(c.hidden_size),
+                                            static_cast<size_t>(c.num_attention_heads) * c.head_dim),
+                                   static_cast<size_t>(c.intermediate_size));
+    const size_t third = static_cast<size_t>(e->pf_cap) * maxdim;  // pf_acc holds three of these
+    SPB_CUDA(cudaEventRecord(e->pf_fork, e->stream));
+    for (int i = 1; i < n; ++i) {
+        SPB_CUDA(cudaStreamWaitEvent(e->pf_side[i - 1], e->pf_fork, 0));
+        if (int rc = prefill_linear(e, *L[i], absmax, out[i], T, e->pf_side[i - 1], e->pf_acc + i * third)) return rc;
+        SPB_CUDA(cudaEventRecord(e->pf_join[i - 1], e->pf_side[i - 1]));
+    }
+    if (int rc = prefill_linear(e, *L[0], absmax, out[0], T, e->stream, e->pf_acc)) return rc;
+    for (int i = 1; i < n; ++i) SPB_CUDA(cudaStreamWaitEvent(e->stream, e->pf_join[i - 1], 0));
+    return SPB_OK;
 }
 
 // Tokens d_tokens[0..T) at positions start..start+T-1 (T <= pf_cap); *d_pos must hold `start`.  With `last`
@@ -305,22 +336,27 @@ int enqueue_prefill_chunk(spb_engine* e, int T, bool last) {
         __half* vc = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(e->vcache) + l * e->kv_bytes_per_layer);
         if ((rc = residual_norm_quant(l == 0 ? nullptr : e->pf_down, nullptr, e->pf_x, L.norm[0], nullptr, e->pf_xq,
                                       am0, H, c.rms_norm_eps, s, T))) return rc;
-        if ((rc = prefill_linear(e, L.lin[0], am0, e->pf_q, T))) return rc;
-        if ((rc = prefill_linear(e, L.lin[1], am0, e->pf_k, T))) return rc;
-        if ((rc = prefill_linear(e, L.lin[2], am0, e->pf_v, T))) return rc;
+        {
+            const Linear* g[3] = {&L.lin[0], &L.lin[1], &L.lin[2]};
+            __half* o[3] = {e->pf_q, e->pf_k, e->pf_v};
+            if ((rc = prefill_linear_group(e, g, o, 3, am0, T))) return rc;
+        }
         if ((rc = rope_scatter(e->pf_q, e->pf_k, e->pf_v, kc, vc, nh, nkv, hd, c.max_position_embeddings,
                                c.rope_theta, e->d_pos, s, T))) return rc;
         if ((rc = decode_attention_pos(e->pf_q, kc, vc, e->pf_attn, nh, nkv, hd, c.max_position_embeddings,
                                        attn_scale, e->d_pos, s, T))) return rc;
         if ((rc = absmax_quantize_rows(e->pf_attn, e->pf_xq, am1, nh * hd, T, s))) return rc;
-        if ((rc = prefill_linear(e, L.lin[3], am1, e->pf_o, T))) return rc;
+        if ((rc = prefill_linear(e, L.lin[3], am1, e->pf_o, T, e->stream, e->pf_acc))) return rc;
         if ((rc = residual_norm_quant(e->pf_o, L.norm[2], e->pf_x, L.norm[1], nullptr, e->pf_xq, am0, H,
                                       c.rms_norm_eps, s, T))) return rc;
-        if ((rc = prefill_linear(e, L.lin[4], am0, e->pf_gate, T))) return rc;
-        if ((rc = prefill_linear(e, L.lin[5], am0, e->pf_up, T))) return rc;
+        {
+            const Linear* g[2] = {&L.lin[4], &L.lin[5]};
+            __half* o[2] = {e->pf_gate, e->pf_up};
+            if ((rc = prefill_linear_group(e, g, o, 2, am0, T))) return rc;
+        }
         if ((rc = relu2_norm_quant(e->pf_gate, e->pf_up, L.norm[3], nullptr, e->pf_xq, am1, inter, c.rms_norm_eps,
                                    s, T))) return rc;
-        if ((rc = prefill_linear(e, L.lin[6], am1, e->pf_down, T))) return rc;
+        if ((rc = prefill_linear(e, L.lin[6], am1, e->pf_down, T, e->stream, e->pf_acc))) return rc;
     }
     if (!last) return SPB_OK;
     // only the final token's logits are ever read: last residual add + final norm + lm_head on its row
@@ -459,6 +495,11 @@ extern "C" void spb_engine_destroy(spb_engine* e) {
     drop_graph(e);
     if (e->d_prompt) cudaFree(e->d_prompt);
     if (e->pf_pool) cudaFree(e->pf_pool);
+    for (int i = 0; i < 2; ++i) {
+        if (e->pf_side[i]) cudaStreamDestroy(e->pf_side[i]);
+        if (e->pf_join[i]) cudaEventDestroy(e->pf_join[i]);
+    }
+    if (e->pf_fork) cudaEventDestroy(e->pf_fork);
     cudaFree(e->pool);
     cudaStreamDestroy(e->stream);
     delete e;
