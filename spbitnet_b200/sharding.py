@@ -92,9 +92,15 @@ class ShardedEngine:
     in the reference's order, so the logits are bit-identical to the same engine on one rank (single=True).
     The reference itself is single-GPU; this class has no counterpart there."""
 
-    def __init__(self, model: dict, group=None, single: bool = False):
+    def __init__(self, model: dict, group=None, single: bool = False, device=None, kernels=None):
+        """device: where the tensors live (default: the current CUDA device).  kernels: the module providing the
+        per-op entry points (default: spbitnet_b200.kernels, i.e. the CUDA library; the CPU tests pass an
+        oracle-backed stand-in together with device="cpu" to exercise the split and the collectives under gloo)."""
         import torch
         import torch.distributed as dist
+        if kernels is None:
+            from . import kernels
+        self.K = kernels
         self.group = group
         self.world = 1 if single else dist.get_world_size(group)
         self.rank = 0 if single else dist.get_rank(group)
@@ -109,7 +115,7 @@ class ShardedEngine:
         self.group_heads = self.nh // self.nkv
         kv0, kv1 = row_range(self.nkv, self.world, self.rank)
         self.nkv_loc, self.nh_loc = kv1 - kv0, (kv1 - kv0) * self.group_heads
-        dev = torch.device("cuda", torch.cuda.current_device())
+        dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.dev = dev
 
         def up(a, dt=None):
@@ -159,7 +165,7 @@ class ShardedEngine:
     def _bitlinear(self, lin, n_in):
         """Local rows of BitLinear(lin) on the quantised activation in self.xq / self.absmax."""
         import torch
-        from . import kernels as K
+        K = self.K
         out = torch.empty(max(lin["local_rows"], 1), dtype=torch.float16, device=self.dev)
         if lin["local_rows"]:
             K.sparse_bitlinear_q8_gpu(lin["meta"], lin["values"], self.xq, out, self.absmax, lin["gamma"],
@@ -169,7 +175,7 @@ class ShardedEngine:
     def forward(self, token_id: int):
         """One token; returns the full logits (vocab_size float32, device tensor) on every rank."""
         import torch
-        from . import kernels as K
+        K = self.K
         if self.seq_len >= self.max_seq:
             raise ValueError("KV cache full")
         c, H, hd = self.cfg, self.H, self.hd

@@ -89,3 +89,50 @@ def test_head_split_keeps_query_heads_with_their_kv_head():
             assert (q0, q1) == (kv0 * g * hd, kv1 * g * hd)
             covered += kv1 - kv0
         assert covered == nkv
+
+
+def _engine_worker(rank, world, port, out_q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import cpu_kernels
+        # five KV heads over the ranks (uneven), odd vocabulary
+        cfg = dict(hidden_size=320, num_hidden_layers=2, num_attention_heads=10, num_key_value_heads=5, head_dim=32,
+                   intermediate_size=512, vocab_size=301, max_position_embeddings=16, rms_norm_eps=1e-5,
+                   rope_theta=10000.0)
+        model = synth.random_model(cfg, seed=7)
+        eng = sharding.ShardedEngine(model, device="cpu", kernels=cpu_kernels)
+        one = sharding.ShardedEngine(model, single=True, device="cpu", kernels=cpu_kernels)
+        cpu = oracle.Engine(model)
+        ok = True
+        tok = 5
+        for step in range(6):
+            a = eng.forward(tok).numpy()
+            b = one.forward(tok).numpy()
+            want = cpu.forward(tok)
+            ok = ok and a.shape == (cfg["vocab_size"],)
+            ok = ok and bool((a.view(np.uint32) == b.view(np.uint32)).all())   # the split changes no bit
+            ok = ok and float(np.abs(a - want).max()) < 1e-4 and int(np.argmax(a)) == oracle.argmax(want)
+            tok = int(np.argmax(a))
+        out_q.put((rank, ok, eng.nkv_loc))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_row_sharded_decode_step_gloo(world):
+    """sharding.ShardedEngine (KV-head split of q/k/v, row split of the other matrices and of the lm_head, four
+    all-gathers per layer) under gloo with oracle-backed stand-ins for the per-op kernels: logits bit-identical to the
+    same step on one rank and equal to the oracle engine's."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_engine_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(ok for _, ok, _ in results)
+    assert sum(n for _, _, n in results) == 5
