@@ -368,6 +368,12 @@ int gemm_tcsp_ws_launch(const uint32_t* meta, const uint32_t* values, const int8
     a.stages = max(2, min(kWsMaxStages, (200 * 1024) / stage_bytes));
     // two groups pay off except at 128 batch rows per block (measured at 6912x2560, n = 256: 12.4 against 11.9 us)
     a.groups = a.nt == 128 ? 1 : 2;
+    // A group must not run more than one ring revolution ahead of the MMA warp, or its parity wait on a stage's
+    // "free" barrier would be satisfied by the previous completion of the same parity.  A group's wait for step k
+    // confirms the commit of step k - stages; its next step is k + groups, whose wait needs the commit of
+    // k + groups - 2 * stages to be over: true when groups <= stages.  (Three groups on two stages were tried and
+    // ran into exactly this.)
+    a.groups = min(a.groups, a.stages);
     a.tmem_cols = 32;
     while (a.tmem_cols < a.nt + 8 * a.stages) a.tmem_cols <<= 1;
     const size_t smem = kWsSignLutBytes + 128 + 1024 + static_cast<size_t>(a.stages) * stage_bytes;
