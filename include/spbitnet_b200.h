@@ -304,12 +304,14 @@ int spb_engine_copy_logits(spb_engine* e, float* h_logits);
  * rows; norms, quantisation, RoPE and the KV scatter run per row with the rounding points of the
  * token-serial step, so integer accumulators and int8 activations are identical and the logits of the last
  * token (the only ones formed; *d_logits, device, vocab_size floats) agree with the token-serial ones within
- * the attention kernels' summation order.  Tokens are processed at most 256 at a time; the first call
- * allocates the batch buffers (about 80 KB per token of the chunk at the 2B-4T shape).  Synchronises the
- * engine's stream before returning. */
+ * the attention kernels' summation order.  Tokens are processed at most 1024 at a time (or the chunk set by
+ * spb_engine_set_prefill_chunk); the first call that needs them allocates the batch buffers (about 150 KB per
+ * token of the chunk at the 2B-4T shape, sized by the longest chunk seen).  Synchronises the engine's stream
+ * before returning. */
 int spb_engine_prefill(spb_engine* e, const int* tokens, int n, const float** d_logits);
 /* How spb_engine_generate feeds the prompt: 0 (default) = token by token like the reference's loop;
- * c > 0 = as batches of up to min(c, 256) tokens through the prefill path above.  Returns the previous
+ * c > 0 = as batches of up to min(c, 1024) tokens through the prefill path above (spb_engine_prefill uses
+ * the same chunk when it is set, else 1024).  Returns the previous
  * setting, or a negative status. */
 int spb_engine_set_prefill_chunk(spb_engine* e, int chunk);
 

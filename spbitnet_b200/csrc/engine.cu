@@ -241,7 +241,7 @@ int ensure_graph(spb_engine* e, bool record_tokens, int n_prompt) {
 // the quantised activations are the ones forward() produces token by token; only the attention sums are
 // formed in a different order (the split-KV kernel is not used here).
 
-constexpr int kPrefillMaxChunk = 256;
+constexpr int kPrefillMaxChunk = 1024;  // larger batches amortise the re-encoding of a weight tile over more activation rows
 
 int ensure_prefill_buffers(spb_engine* e, int cap) {
     if (e->pf_cap >= cap) return SPB_OK;

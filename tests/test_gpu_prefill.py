@@ -180,10 +180,16 @@ def test_prefill_at_the_2b4t_width():
     tokens = np.random.default_rng(0).integers(0, cfg["vocab_size"], 300).astype(np.int32)  # two chunks: 256 + 44
     want = _serial_logits(eng, tokens)
     eng.reset()
+    eng.set_prefill_chunk(256)
     eng.prefill(tokens)
     got = eng.logits()
     assert np.abs(got - want).max() < 1e-2
     assert int(np.argmax(got)) == int(np.argmax(want))
+    eng.reset()
+    eng.set_prefill_chunk(0)
+    eng.prefill(tokens)      # one chunk of 300
+    one = eng.logits()
+    assert np.abs(one - want).max() < 1e-2 and int(np.argmax(one)) == int(np.argmax(want))
     assert K.gemm_tc_timeouts() == 0
     # greedy continuation identical
     eng.reset()
