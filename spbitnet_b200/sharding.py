@@ -118,7 +118,7 @@ class ShardedEngine:
         dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.dev = dev
 
-        def up(a, dt=None):
+        def up(a):
             t = torch.from_numpy(np.ascontiguousarray(a).view(np.int16) if a.dtype == np.float16 else np.ascontiguousarray(a))
             t = t.to(dev)
             return t.view(torch.float16) if a.dtype == np.float16 else t
@@ -162,7 +162,7 @@ class ShardedEngine:
             return local
         return all_gather_rows(local, rows, multiple, self.group)
 
-    def _bitlinear(self, lin, n_in):
+    def _bitlinear(self, lin):
         """Local rows of BitLinear(lin) on the quantised activation in self.xq / self.absmax."""
         import torch
         K = self.K
@@ -187,7 +187,7 @@ class ShardedEngine:
             lin, norm = L["lin"], L["norm"]
             K.rms_norm_gpu(x, norm[0], self.xn, H, eps)
             K.absmax_quantize_gpu(self.xn, self.xq, self.absmax, H)
-            q, k, v = (self._bitlinear(lin[i], H) for i in range(3))
+            q, k, v = (self._bitlinear(lin[i]) for i in range(3))
             attn_loc = torch.empty(max(self.nh_loc * hd, 1), dtype=torch.float16, device=self.dev)
             if self.nkv_loc:
                 K.rope_gpu(q, self.nh_loc, hd, pos, theta)
@@ -198,13 +198,13 @@ class ShardedEngine:
                                        self.max_seq, pos + 1, scale)
             attn = self._gather(attn_loc[: self.nh_loc * hd], self.nh * hd, self.mult[0])
             K.absmax_quantize_gpu(attn, self.xq, self.absmax, self.nh * hd)
-            o = self._gather(self._bitlinear(lin[3], self.nh * hd), H).contiguous()
+            o = self._gather(self._bitlinear(lin[3]), H).contiguous()
             if norm[2] is not None:
                 K.rms_norm_gpu(o, norm[2], o, H, eps)
             K.residual_add_gpu(o, x, x, H)
             K.rms_norm_gpu(x, norm[1], self.xn, H, eps)
             K.absmax_quantize_gpu(self.xn, self.xq, self.absmax, H)
-            gate, upv = self._bitlinear(lin[4], H), self._bitlinear(lin[5], H)
+            gate, upv = self._bitlinear(lin[4]), self._bitlinear(lin[5])
             n_loc = lin[4]["local_rows"]
             m_loc = torch.empty(max(n_loc, 1), dtype=torch.float32, device=self.dev)
             if n_loc:
@@ -215,7 +215,7 @@ class ShardedEngine:
             else:
                 K.float_to_half_gpu(m, self.xn, self.inter)
             K.absmax_quantize_gpu(self.xn, self.xq, self.absmax, self.inter)
-            down = self._gather(self._bitlinear(lin[6], self.inter), H).contiguous()
+            down = self._gather(self._bitlinear(lin[6]), H).contiguous()
             K.residual_add_gpu(down, x, x, H)
         K.rms_norm_gpu(x, self.final_norm, self.xn, H, eps)
         loc = torch.empty(max(self.head_loc.shape[0], 1), dtype=torch.float32, device=self.dev)
