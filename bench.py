@@ -34,6 +34,7 @@ sys.path.insert(0, str(ROOT))
 METRIC = "sparse_ternary_gemv_hbm_gbs_6912x2560"
 UNIT = "GB/s"
 NOMINAL_HBM_GBS = 8000.0
+NOMINAL_SPARSE_INT8_TOPS = 9000.0  # dense-equivalent; 4.5 POP/s dense int8 x 2
 # DRAM bytes one 6912x2560 GEMV launch moved under ncu (read 3.337 MB, write 0: y stays in L2)
 NCU_DRAM_BYTES_PER_LAUNCH = 3.337e6
 
@@ -101,68 +102,113 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------------------
-# reference arm: the reference's CPU implementation on the host cores
+# reference arm: the reference's CPU implementation on the host cores.  Imports nothing of the product:
+# the seeded inputs are drawn here with numpy (the rules of spbitnet_b200.synth, restated).
 # ---------------------------------------------------------------------------------------
 
-def cpu_gemv_baseline(rows, cols, threads, budget_s, use_ref=True):
-    """Times the reference's CPU GEMV (unpack_to_int8 + int32 dot, as its tests run it) on the
-    metric shape.  Returns (GB/s, kind, reps, seconds)."""
-    import oracle
-    from spbitnet_b200 import synth
-    rng = np.random.default_rng(0)
-    w, mask = synth.ternary_weights_and_mask(rows, cols, rng)
+METRIC_ROWS, METRIC_COLS = 6912, 2560
+
+
+def gemv_bytes(rows, cols):
+    """The reference's byte count of one GEMV (benchmarks/bench_kernels.cu:248): both weight streams + x + y."""
+    return rows * 4 * ((cols // 4 + 7) // 8 + (cols // 4 + 15) // 16) + cols + 4 * rows
+
+
+def ternary_case_numpy(rows, cols, seed=0):
+    """(weights int8 {-1,0,1}, keep-mask with two per group, x int8): P(0)=0.42, P(+1)=P(-1)=0.29; per group of
+    four keep at most two non-zeros chosen uniformly, then zeros by ascending index until two are marked."""
+    rng = np.random.default_rng(seed)
+    u = rng.random((rows, cols))
+    w = np.where(u < 0.42, 0, np.where(u < 0.71, 1, -1)).astype(np.int8)
+    keys = rng.random((rows, cols))
+    g = cols // 4
+    nz = w.reshape(rows, g, 4) != 0
+    order_key = np.where(nz, keys.reshape(rows, g, 4), 2.0 + np.arange(4)[None, None, :])
+    order = np.argsort(order_key, axis=-1, kind="stable")
+    keep = np.zeros((rows, g, 4), bool)
+    np.put_along_axis(keep, order[:, :, :2], True, axis=-1)
     x = rng.integers(-127, 128, cols, dtype=np.int8)
-    nbytes = synth.gemv_algorithmic_bytes(rows, cols)
-    if use_ref and oracle.ref() is not None:
-        kind = "reference"
-        run = lambda reps: oracle.ref_cpu_sparse_gemv(w, mask, x, threads=threads, repeats=reps)
-    else:
-        kind = "port"
-        meta, values = synth.pack_numpy(w, mask)
-        def run(reps):
-            for _ in range(reps):
-                oracle.sparse_gemv(meta, values, x, rows, cols, threads=threads)
-    t0 = time.perf_counter()
-    run(1)
-    one = time.perf_counter() - t0
-    reps = max(1, int(budget_s / max(one, 1e-4)))
-    t0 = time.perf_counter()
-    run(reps)
-    dt = time.perf_counter() - t0
-    return nbytes * reps / dt / 1e9, kind, reps, dt
+    return w, keep.reshape(rows, cols), x
+
+
+class CpuGemv:
+    """The CPU GEMV of the reference (unpack_to_int8 + int32 dot, tests/test_sparse_ternary.cu:17-33) on the
+    metric shape: through oracle/_ref (the reference's own header) when built, else the C port."""
+
+    def __init__(self, rows, cols, threads):
+        import oracle
+        self.rows, self.cols, self.threads = rows, cols, threads
+        w, mask, self.x = ternary_case_numpy(rows, cols, 0)
+        self.bytes = gemv_bytes(rows, cols)
+        if oracle.ref() is not None:
+            self.kind = "reference"
+            self.ctx = oracle.RefCpuGemv(w, mask, threads)
+            self.run = lambda reps, dot_only=False: self.ctx.run(self.x, reps, dot_only)
+        else:
+            self.kind = "port"
+            meta, values = oracle.pack_from_dense(w, mask)
+            def run(reps, dot_only=False):
+                for _ in range(reps):
+                    oracle.sparse_gemv(meta, values, self.x, rows, cols, threads=threads)
+            self.run = run
+
+    def timed(self, budget_s, dot_only=False):
+        """(GB/s, repeats, seconds) of about budget_s seconds of back-to-back GEMVs."""
+        t0 = time.perf_counter()
+        self.run(1, dot_only)
+        one = time.perf_counter() - t0
+        reps = max(1, int(budget_s / max(one, 1e-4)))
+        t0 = time.perf_counter()
+        self.run(reps, dot_only)
+        dt = time.perf_counter() - t0
+        return self.bytes * reps / dt / 1e9, reps, dt
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    from spbitnet_b200 import synth
-    rows, cols = synth.METRIC_SHAPE
+    rows, cols = METRIC_ROWS, METRIC_COLS
     threads = os.cpu_count() or 1
-    # each step: `reps` GEMVs of the metric shape on all host threads
-    gbs1, kind, reps, _ = cpu_gemv_baseline(rows, cols, threads, 0.5)
-    for _ in range(max(args.warmup - 1, 0)):
-        cpu_gemv_baseline(rows, cols, threads, 0.2)
+    cpu = CpuGemv(rows, cols, threads)
+    for _ in range(max(args.warmup, 0)):
+        cpu.timed(0.2)
     vals, t_total = [], 0.0
-    for _ in range(args.steps):
-        g, kind, r, dt = cpu_gemv_baseline(rows, cols, threads, 1.0)
+    for _ in range(args.steps):  # each step: about a second of GEMVs of the metric shape on all host threads
+        g, r, dt = cpu.timed(1.0)
         vals.append((g, r, dt))
         t_total += dt
-    total_bytes = sum(synth.gemv_algorithmic_bytes(rows, cols) * r for _, r, _ in vals)
-    value = total_bytes / t_total / 1e9
+    n_gemv = sum(r for _, r, _ in vals)
+    value = cpu.bytes * n_gemv / t_total / 1e9
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t_total / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": "gemv 6912x2560 batch 1, reference CPU path (unpack_to_int8 + int32 dot)",
-                   "shape": [rows, cols]},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind,
-                         "sample": f"{sum(r for _, r, _ in vals)} GEMVs of 6912x2560 in {t_total:.2f} s, row loop "
-                                   f"split over {threads} threads"},
+        "config": {"workload": "gemv shape sweep, batch 1; headline 6912x2560", "shape": [rows, cols],
+                   "path": "reference CPU path: unpack_to_int8 + int32 dot, rows split over the host threads"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": cpu.kind,
+                         "sample": f"{n_gemv} GEMVs of 6912x2560 in {t_total:.2f} s; every thread unpacks and "
+                                   f"multiplies its own slice of the rows ({threads} threads)"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line))
+
+
+def cpu_baselines(budget_s=4.0):
+    """The CPU baselines of the metric shape, timed on this host: the reference's scalar GEMV as written (one
+    thread), its dot product alone on pre-unpacked weights (one thread / all threads), and the same GEMV with the
+    row loop split over all threads.  A baseline, not a target."""
+    threads = os.cpu_count() or 1
+    one, many = CpuGemv(METRIC_ROWS, METRIC_COLS, 1), CpuGemv(METRIC_ROWS, METRIC_COLS, threads)
+    c1, r1, d1 = one.timed(budget_s)
+    c2a, _, _ = one.timed(budget_s / 2, dot_only=True) if one.kind == "reference" else (None, 0, 0)
+    c2b, _, _ = many.timed(budget_s / 2, dot_only=True) if many.kind == "reference" else (None, 0, 0)
+    c3, r3, d3 = many.timed(budget_s)
+    return {"value": c3, "unit": UNIT, "cores": threads, "kind": many.kind,
+            "sample": f"{r3} GEMVs of 6912x2560 in {d3:.2f} s, unpack + dot with the rows split over {threads} threads",
+            "one_thread_unpack_and_dot": c1, "one_thread_sample": f"{r1} GEMVs in {d1:.2f} s",
+            "dot_only_one_thread": c2a, "dot_only_all_threads": c2b}
 
 
 # ---------------------------------------------------------------------------------------
@@ -201,7 +247,7 @@ def run_ours(args):
         return
     if args.only_decode:
         if rank == 0:
-            print(json.dumps({"metric": "decode_tok_s_2b4t_shape", "decode": bench_decode(args), "n_gpus": world}))
+            print(json.dumps({"metric": "decode_tok_s_2b4t_shape", "decode": bench_decode(args, with_cpu=not args.no_cpu), "n_gpus": world}))
         if world > 1:
             dist.destroy_process_group()
         return
@@ -383,61 +429,77 @@ def run_ours(args):
         y_host.copy_(ys, non_blocking=True)
     ms_e2e_serial = time_device(e2e_step, args.steps, args.warmup)
 
-    # ---- the other shapes of the sweep (rank 0 only, short) --------------------------------
+    # ---- the shapes of the sweep (rank 0 only, short): ours, and the reference's own kernel recompiled for
+    #      sm_100a, each as the same graph of launches (same branches, same weight copies, same x and y) -------
+    import ctypes as C
+    refcuda = oracle.refcuda() if rank == 0 else None
+
+    def capture_ref(metas, vals, xs, ys, r, c, ms, vs, copies, chains):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            main = torch.cuda.current_stream()
+            for st in branch_streams[:chains]:
+                st.wait_stream(main)
+            for i in range(copies):
+                st = branch_streams[i % chains]
+                refcuda.refcuda_gemv(C.c_void_p(metas[i].data_ptr()), C.c_void_p(vals[i].data_ptr()),
+                                     C.c_void_p(xs[i % xs.shape[0]].data_ptr()), C.c_void_p(ys[i].data_ptr()), r, c,
+                                     ms, vs, C.c_void_p(st.cuda_stream))
+            for st in branch_streams[:chains]:
+                main.wait_stream(st)
+        return g
+
+    def time_graph(g, reps, launches):
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / (reps * launches)
+
     sweep = {}
     if rank == 0 and not args.no_sweep:
         for (r, c) in synth.GEMV_SHAPES:
             cs, cp, mt, vl, pb = make_set(r, c, max(2 * l2_bytes, 256 << 20), seed=0)
-            xx = torch.from_numpy(rng.integers(-127, 128, (8, c), dtype=np.int8)).cuda()
+            xh = rng.integers(-127, 128, (8, c), dtype=np.int8)
+            xx = torch.from_numpy(xh).cuda()
             yy = torch.zeros((cp, r), dtype=torch.int32, device="cuda")
             launch_pass(mt, vl, xx, yy, r, c, cs["meta_stride"], cs["values_stride"], cp)
             torch.cuda.synchronize()
+            want0 = oracle.sparse_gemv(cs["meta"], cs["values"], xh[0], r, c, threads=os.cpu_count() or 1)
+            if not (yy[0].cpu().numpy() == want0).all():
+                raise SystemExit(f"bench: {r}x{c} GEMV differs from the oracle; refusing to time it")
             g2 = capture(mt, vl, xx, yy, r, c, cs["meta_stride"], cs["values_stride"], cp, args.chains)
-            for _ in range(3):
-                g2.replay()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(5):
-                g2.replay()
-            e1.record()
-            torch.cuda.synchronize()
-            us = e0.elapsed_time(e1) * 1e3 / (5 * cp)
+            us = time_graph(g2, 5, cp)
             gbs = pb / (us * 1e-6) / 1e9
-            sweep[f"{r}x{c}"] = {"us_per_gemv": round(us, 3), "gbs": round(gbs, 1),
-                                 "frac_measured": round(gbs / peak, 4), "frac_8tbs": round(gbs / NOMINAL_HBM_GBS, 4)}
+            row = {"us_per_gemv": round(us, 3), "gbs": round(gbs, 1),
+                   "frac_measured": round(gbs / peak, 4), "frac_8tbs": round(gbs / NOMINAL_HBM_GBS, 4)}
+            if refcuda is not None:
+                yy.zero_()
+                g3 = capture_ref(mt, vl, xx, yy, r, c, cs["meta_stride"], cs["values_stride"], cp, args.chains)
+                us_ref = time_graph(g3, 3, cp)
+                ok = bool((yy[0].cpu().numpy() == want0).all())
+                row["reference_kernel"] = {"us_per_gemv": round(us_ref, 3), "gbs": round(pb / (us_ref * 1e-6) / 1e9, 1),
+                                           "frac_measured": round(pb / (us_ref * 1e-6) / 1e9 / peak, 4),
+                                           "matches_oracle": ok, "speedup": round(us_ref / us, 2)}
+                del g3
+            sweep[f"{r}x{c}"] = row
             del mt, vl, yy, g2
 
-    # ---- reference CUDA kernel on the same GPU (when the checker library is present) --------
     ref_cuda = None
-    if rank == 0:
-        try:
-            import ctypes as C
-            rc = oracle.refcuda()
-            if rc is not None:
-                sp = C.c_void_p(torch.cuda.current_stream().cuda_stream)
-                def ref_pass():
-                    for i in range(copies):
-                        rc.refcuda_gemv(C.c_void_p(metas[i].data_ptr()), C.c_void_p(vals[i].data_ptr()),
-                                        C.c_void_p(xs[i].data_ptr()), C.c_void_p(ys[i].data_ptr()), rows, cols,
-                                        ms_, vs_, sp)
-                ms_ref = time_device(ref_pass, 2, 1) if world == 1 else None
-                if ms_ref:
-                    ref_cuda = {"us_per_gemv": ms_ref * 1e3 / (2 * copies),
-                                "gbs": step_bytes * 2 / (ms_ref * 1e-3) / 1e9,
-                                "what": "reference sparse_ternary_gemv_kernel recompiled for sm_100a, same buffers"}
-        except Exception as exc:  # the checker is optional
-            ref_cuda = {"error": str(exc)}
+    if refcuda is not None and "6912x2560" in sweep:
+        ref_cuda = dict(sweep["6912x2560"].get("reference_kernel", {}),
+                        what="reference sparse_ternary_gemv_kernel (src/kernels/sparse_ternary.cu:116-168) recompiled "
+                             "for sm_100a, the same graph of launches over the same buffers as ours")
 
-    # ---- CPU baseline (rank 0, N == 1) -------------------------------------------------------
+    # ---- CPU baselines (rank 0, N == 1) ------------------------------------------------------
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        threads = os.cpu_count() or 1
-        g1, kind, reps1, dt1 = cpu_gemv_baseline(rows, cols, 1, 4.0)
-        gN, kind, repsN, dtN = cpu_gemv_baseline(rows, cols, threads, 4.0)
-        cpu = {"value": gN, "unit": UNIT, "cores": threads, "kind": kind,
-               "sample": f"{repsN} GEMVs of 6912x2560 in {dtN:.2f} s on {threads} threads "
-                         f"(1 thread: {g1:.3f} GB/s over {reps1} GEMVs)"}
+        cpu = cpu_baselines()
 
     gemm = None
     if rank == 0 and not args.no_gemm:
@@ -446,13 +508,20 @@ def run_ours(args):
         except Exception as exc:
             gemm = {"error": repr(exc)}
 
-    # ---- decode throughput on the 2B-4T-shape model (secondary figure) ----------------------
+    # ---- decode throughput on the 2B-4T-shape model: every rank runs its own replica -----------------
     decode = None
-    if rank == 0 and not args.no_decode:
+    if not args.no_decode:
         try:
-            decode = bench_decode(args)
+            decode = bench_decode(args, with_reference=(rank == 0), with_cpu=(rank == 0 and world == 1 and not args.no_cpu))
         except Exception as exc:
             decode = {"error": repr(exc)}
+        if world > 1:
+            mine = torch.tensor([decode.get("tok_s", 0.0)], device="cuda", dtype=torch.float64)
+            allv = [torch.zeros_like(mine) for _ in range(world)]
+            dist.all_gather(allv, mine)
+            per_rank = [float(v.item()) for v in allv]
+            decode["replicas"] = {"n": world, "tok_s_total": sum(per_rank), "tok_s_per_rank": per_rank,
+                                  "what": "independent greedy-decode replicas, one per GPU, no communication"}
 
     if rank == 0:
         line = {
@@ -502,44 +571,100 @@ def oracle_unpack(case, r, c):
     return oracle.unpack_to_int8(case["meta"], case["values"], r, c)
 
 
-def library_gemm(Wd, X, r, c, n):
-    """Library kernels on a dense int8 copy of the same weights (comparison only; weights stay resident in L2):
-    cuBLASLt int8 (torch._int_mm) and cuSPARSELt 2:4 (torch._cslt_sparse_mm), which is the reference's batched path."""
+def _time_us(fn, reps=20, warm=3):
     import torch
-    res = {}
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / reps
 
-    def timed(fn):
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(20):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / 20
-        return {"us": round(us, 2), "dense_equiv_tops": round(2.0 * r * c * n / us / 1e6, 2)}
+
+def library_gemm(Wd, X, r, c, n, want):
+    """Library kernels on a dense int8 copy of the same weights (comparison only; that copy stays resident in L2):
+    cuBLASLt dense int8 (torch._int_mm) and cuSPARSELt 2:4 through oracle/cslt_shim.cpp, which follows the
+    reference's CuSparseLtGemm: plan and compress once, then one cusparseLtMatmul per call, timed alone as a CUDA
+    graph of 20 calls, result checked against the oracle."""
+    import torch
+    import oracle
+    res = {}
     try:
         Wt = Wd.t()
-        res["lib_cublaslt_dense"] = timed(lambda: torch._int_mm(X, Wt))
+        us = _time_us(lambda: torch._int_mm(X, Wt))
+        res["lib_cublaslt_dense"] = {"us": round(us, 2), "dense_equiv_tops": round(2.0 * r * c * n / us / 1e6, 2)}
     except Exception as exc:
         res["lib_cublaslt_dense"] = {"error": str(exc)[:120]}
     try:
-        comp = torch._cslt_compress(Wd)
-        Xt = X.t()
-        res["lib_cusparselt"] = timed(lambda: torch._cslt_sparse_mm(comp, Xt, out_dtype=torch.int32))
+        if oracle.cslt() is None:
+            raise RuntimeError("oracle/libspb_cslt.so not built or cuSPARSELt missing")
+        gemm = oracle.CusparseLtGemm(r, c, n)
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            gemm.prepare(Wd.data_ptr(), side.cuda_stream)
+            D = torch.zeros((n, r), dtype=torch.int32, device="cuda")
+            gemm.execute(X.data_ptr(), D.data_ptr(), side.cuda_stream)
+            side.synchronize()
+            ok = bool((D[:want.shape[0]].cpu().numpy() == want).all())
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for _ in range(20):
+                    gemm.execute(X.data_ptr(), D.data_ptr(), side.cuda_stream)
+            us = _time_us(g.replay, reps=5, warm=2) / 20
+        torch.cuda.synchronize()
+        res["lib_cusparselt"] = {"us": round(us, 2), "dense_equiv_tops": round(2.0 * r * c * n / us / 1e6, 2),
+                                 "matches_oracle": ok}
+        gemm.close()
     except Exception as exc:
-        res["lib_cusparselt"] = {"error": str(exc)[:120]}
+        res["lib_cusparselt"] = {"error": str(exc)[:160]}
     return res
 
 
-def bench_gemm(args, l2_bytes):
-    """Batched product (prefill) at the two FFN shapes, N in {1,4,16,64,256,1024}: us per call over a
-    rotating set of weight copies larger than L2, weight-stream GB/s and dense-equivalent int8 TOP/s."""
+def sparse_int8_peak():
+    """Empirical sparse-int8 tensor peak of this GPU: the library's own 2:4 kernel (cuSPARSELt through the shim) on
+    a problem large enough to be compute-bound, in dense-equivalent TOP/s (2*M*K*N per call).  None when the
+    library is missing."""
     import torch
+    import oracle
+    try:
+        if oracle.cslt() is None:
+            return None
+        m = k = 8192
+        n = 8192
+        W = torch.zeros((m, k), dtype=torch.int8, device="cuda")
+        W.view(m, k // 4, 4)[:, :, :2] = 1  # a valid 2:4 pattern
+        X = torch.randint(-127, 128, (n, k), dtype=torch.int8, device="cuda")
+        D = torch.empty((n, m), dtype=torch.int32, device="cuda")
+        gemm = oracle.CusparseLtGemm(m, k, n)
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            gemm.prepare(W.data_ptr(), side.cuda_stream)
+            us = _time_us(lambda: gemm.execute(X.data_ptr(), D.data_ptr(), side.cuda_stream), reps=10, warm=3)
+        torch.cuda.synchronize()
+        gemm.close()
+        return {"dense_equiv_tops": round(2.0 * m * k * n / us / 1e6, 1), "us": round(us, 1),
+                "what": "cuSPARSELt int8 2:4, 8192 x 8192 x 8192, CUDA events over 10 calls"}
+    except Exception as exc:
+        return {"error": str(exc)[:160]}
+
+
+def bench_gemm(args, l2_bytes):
+    """Batched product (prefill) at the two FFN shapes, N in {1,4,16,64,256,1024}: us per call over a rotating set
+    of weight copies larger than L2, weight-stream GB/s and dense-equivalent int8 TOP/s.  Every form's result is
+    compared with the CPU oracle on a few activation rows before it is timed."""
+    import torch
+    import oracle
     from spbitnet_b200 import kernels as K, synth
     out = {}
+    peak_hbm, _ = measured_peaks()
+    sp_peak = sparse_int8_peak()
+    out["sparse_int8_peak"] = sp_peak
+    peak_tops = (sp_peak or {}).get("dense_equiv_tops") or NOMINAL_SPARSE_INT8_TOPS
+    threads = os.cpu_count() or 1
     for (r, c) in synth.GEMM_SHAPES:
         case = synth.gemv_case(r, c, seed=0)
         per = r * 4 * (case["meta_stride"] + case["values_stride"])
@@ -548,59 +673,72 @@ def bench_gemm(args, l2_bytes):
         values = torch.from_numpy(case["values"].view(np.int32)).cuda()
         metas = torch.stack([meta.roll(i, 0) for i in range(copies)]).contiguous()
         vals = torch.stack([values.roll(i, 0) for i in range(copies)]).contiguous()
+        last_meta, last_values = np.roll(case["meta"], copies - 1, 0), np.roll(case["values"], copies - 1, 0)
         Wd = torch.from_numpy(oracle_unpack(case, r, c)).cuda()  # dense int8 copy, what the reference hands to cuSPARSELt
         for n in synth.GEMM_BATCHES:
             X = torch.randint(-127, 128, (n, c), dtype=torch.int8, device="cuda")
             Y = torch.empty((n, r), dtype=torch.int32, device="cuda")
+            Xh = X.cpu().numpy()
+            probe = sorted({0, n // 2, n - 1})
+            want = {j: oracle.sparse_gemv(last_meta, last_values, Xh[j], r, c, threads=threads) for j in probe}
             row = {}
-            for name, variant in (("auto", 0), ("simt", 1), ("tc_dense", 2), ("tc_sparse", 3), ("mma_sp", 4)):
-                if (variant == 1 and n > 64) or (variant in (2, 3) and n < 16) or (variant == 4 and n > 256):
+            for name, variant in (("auto", 0), ("simt", 1), ("tc_sparse", 3), ("mma_sp", 4)):
+                if (variant == 1 and n > 64) or (variant == 3 and n < 16) or (variant == 4 and n > 256):
                     continue
                 K.set_gemm_variant(variant)
                 def run():
                     for i in range(copies):
                         K.sparse_ternary_gemm_gpu(metas[i], vals[i], X, Y, r, c, n, case["meta_stride"], case["values_stride"])
+                Y.zero_()
                 run()
                 torch.cuda.synchronize()
+                Yh = Y.cpu().numpy()  # the product with the last weight copy
+                if any(not (Yh[j] == want[j]).all() for j in probe):
+                    raise SystemExit(f"bench: batched product {r}x{c} n={n} ({name}) differs from the oracle; refusing to time it")
                 # one CUDA graph of the `copies` calls (stream-ordered), so that the host's launch cost is not timed
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g):
                     run()
-                g.replay()
-                torch.cuda.synchronize()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                reps = 3
-                e0.record()
-                for _ in range(reps):
-                    g.replay()
-                e1.record()
-                torch.cuda.synchronize()
-                us = e0.elapsed_time(e1) * 1e3 / (reps * copies)
+                us = _time_us(g.replay, reps=3, warm=1) / copies
+                tops = 2.0 * r * c * n / us / 1e6
+                gbs = (per + n * c + 4.0 * n * r) / us / 1e3
                 row[name] = {"us": round(us, 2), "weight_gbs": round(per / us / 1e3, 1),
-                             "dense_equiv_tops": round(2.0 * r * c * n / us / 1e6, 2)}
+                             "dense_equiv_tops": round(tops, 2)}
+                if name == "auto":
+                    # the binding roof of this n: weights + X + Y over HBM, or 2*M*K*N over the sparse-int8 peak
+                    t_hbm, t_tc = (per + n * c + 4.0 * n * r) / (peak_hbm * 1e3), 2.0 * r * c * n / (peak_tops * 1e6)
+                    bound = "hbm" if t_hbm >= t_tc else "tensor"
+                    row["roofline"] = {"bound": bound, "achieved": round(gbs if bound == "hbm" else tops, 1),
+                                       "peak": peak_hbm if bound == "hbm" else peak_tops,
+                                       "unit": "GB/s" if bound == "hbm" else "TOP/s (dense-equivalent)",
+                                       "frac": round((t_hbm if bound == "hbm" else t_tc) / us, 4)}
             K.set_gemm_variant(0)
-            if n >= 64:
-                row.update(library_gemm(Wd, X, r, c, n))
+            if n >= 16:
+                # the libraries run on copy 0 of the weights
+                w0 = oracle.sparse_gemv(case["meta"], case["values"], Xh[0], r, c, threads=threads)
+                row.update(library_gemm(Wd, X, r, c, n, w0[None, :]))
             out[f"{r}x{c}_n{n}"] = row
         del metas, vals
     out["tc_timeouts"] = K.gemm_tc_timeouts()
-    out["what"] = ("spb_sparse_ternary_gemm, us per call as a graph of stream-ordered calls over cold weights; auto = "
-                   "warp-level sparse MMA (mma.sp) up to n = 32, tcgen05.mma.sp above; tc_dense = tcgen05 kind::i8 on "
-                   "expanded int8 tiles; lib_* = library kernels on a dense int8 copy of the weights that stays in L2 "
-                   "(comparison only); dense_equiv_tops counts 2*M*K*N")
+    out["what"] = ("spb_sparse_ternary_gemm, us per call as a graph of stream-ordered calls over cold weights, each form "
+                   "checked against the CPU oracle first; auto = warp-level sparse MMA (mma.sp) up to n = 32, tcgen05.mma.sp "
+                   "above; lib_* = library kernels on a dense int8 copy of the weights that stays in L2 (comparison only: "
+                   "cuBLASLt dense int8, and cuSPARSELt 2:4 planned and compressed once as the reference does); "
+                   "dense_equiv_tops counts 2*M*K*N; roofline.peak for the tensor bound is sparse_int8_peak (measured "
+                   "with the library) or the nominal 9000")
     return out
 
 
-def bench_decode(args):
-    """Greedy decode of a random-init BitNet-2B-4T-shape model: 128-token prompt, 256 generated."""
+def bench_decode(args, with_reference=True, with_cpu=False):
+    """Greedy decode of a random-init BitNet-2B-4T-shape model (every matrix of every layer with its own seed,
+    generated on the GPU): 128-token prompt, 256 generated."""
     import torch
     from spbitnet_b200 import synth
-    from spbitnet_b200.engine import DeviceModel, InferenceEngine
+    from spbitnet_b200.engine import InferenceEngine
     cfg = dict(synth.BITNET_2B)
     if args.decode_layers > 0:
         cfg["num_hidden_layers"] = args.decode_layers
-    model = synth.random_model(cfg, seed=0, shared_layer=True)
-    dm = DeviceModel(model)
+    dm = synth.DeviceRandomModel(cfg, seed=0)
     eng = InferenceEngine(dm)
     prompt = np.random.default_rng(0).integers(0, cfg["vocab_size"], 128).astype(np.int32)
     n_gen = args.decode_tokens
@@ -611,7 +749,7 @@ def bench_decode(args):
     toks = eng.generate(prompt, n_gen)
     dt = time.perf_counter() - t0
     steps = len(prompt) - 1 + n_gen
-    weight_bytes = dm.sparse_bytes() + model["embed"].nbytes
+    weight_bytes = dm.sparse_bytes() + dm.embed.numel() * 2
     # the same job with the prompt fed as one batch (BitLinear layers as the batched product)
     eng.reset()
     eng.set_prefill_chunk(256)
@@ -630,23 +768,71 @@ def bench_decode(args):
     batched = {"tok_s": steps / dt_b, "ms_total": 1e3 * dt_b, "prefill_ms": 1e3 * dt_p,
                "prefill_tok_s": len(prompt) / dt_p, "same_tokens_as_serial": bool((toks_b == toks).all()),
                "decode_only_tok_s": (n_gen - 1) / max(dt_b - dt_p, 1e-9)}
-    return {"tok_s": steps / dt, "batched_prompt": batched, "ms_per_token": 1e3 * dt / steps, "generated": int(len(toks)),
-            "prompt": int(len(prompt)), "weight_mb_per_token": round(weight_bytes / 1e6, 1),
-            "hbm_gbs": weight_bytes * steps / dt / 1e9,
-            "what": "prefill (token-serial, as the reference) + decode, wall clock around generate() incl. prompt "
-                    "H2D and token D2H; random-init 2B-4T shape, layer weights generated once and uploaded per layer"}
+    peak, _ = measured_peaks()
+    out = {"tok_s": steps / dt, "batched_prompt": batched, "ms_per_token": 1e3 * dt / steps, "generated": int(len(toks)),
+           "prompt": int(len(prompt)), "weight_mb_per_token": round(weight_bytes / 1e6, 1),
+           "hbm_gbs": weight_bytes * steps / dt / 1e9, "hbm_frac_measured": weight_bytes * steps / dt / 1e9 / peak,
+           "what": "prefill (token-serial, as the reference) + decode, wall clock around generate() incl. prompt "
+                   "H2D and token D2H; random-init 2B-4T shape, every matrix of every layer drawn with its own seed"}
+    if with_reference:
+        try:
+            out["reference_engine_same_gpu"] = bench_reference_engine(dm, prompt)
+        except Exception as exc:
+            out["reference_engine_same_gpu"] = {"error": repr(exc)[:160]}
+    if with_cpu:
+        try:
+            out["cpu_forward"] = bench_cpu_forward(dm)
+        except Exception as exc:
+            out["cpu_forward"] = {"error": repr(exc)[:160]}
+    return out
+
+
+def bench_reference_engine(dm, prompt, n_tokens=48):
+    """The reference's forward pass op by op (src/inference.cu:123-283: ~28 launches + 2 copies per layer on the
+    null stream, host arg-max as src/main.cpp:280-287) with the reference's own CUDA kernels recompiled for sm_100a,
+    on the same device weights: tok/s over n_tokens greedy tokens after a 16-token prompt."""
+    import torch
+    import oracle
+    if oracle.refcuda() is None:
+        return None
+    from oracle import ref_cuda_engine
+    ref = ref_cuda_engine.RefCudaEngine(dm)
+    for t in prompt[:16]:
+        ref.forward(int(t))
+    tok = int(prompt[16])
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(n_tokens):
+        tok = int(torch.argmax(ref.forward(tok)).item())
+    dt = time.perf_counter() - t0
+    return {"tok_s": n_tokens / dt, "ms_per_token": 1e3 * dt / n_tokens, "tokens": n_tokens,
+            "what": "reference kernels (src/kernels/*.cu for sm_100a) in the reference's op order, launched from "
+                    "Python through ctypes on the null stream, arg-max on the device; positions 16.."}
+
+
+def bench_cpu_forward(dm):
+    """The reference's forward pass on the host cores (the C port of src/inference.cu:123-283 in oracle/, one
+    thread; python/baseline_pytorch.py InferenceEngine.forward is its Python twin): seconds per token at the
+    model's full shape, one warm-up token and one timed token."""
+    import oracle
+    cpu = oracle.Engine(dm.to_host())
+    cpu.forward(11)
+    t0 = time.perf_counter()
+    cpu.forward(12)
+    dt = time.perf_counter() - t0
+    return {"tok_s": 1.0 / dt, "s_per_token": dt, "cores": 1, "kind": "port",
+            "sample": "one decode token at position 1 after one warm-up token, full model"}
 
 
 def bench_prefill(args):
     """The prompt as one batch through a random-init 2B-4T-shape model (engine.prefill), wall clock per call."""
     import torch
     from spbitnet_b200 import synth
-    from spbitnet_b200.engine import DeviceModel, InferenceEngine
+    from spbitnet_b200.engine import InferenceEngine
     cfg = dict(synth.BITNET_2B)
     if args.decode_layers > 0:
         cfg["num_hidden_layers"] = args.decode_layers
-    model = synth.random_model(cfg, seed=0, shared_layer=True)
-    eng = InferenceEngine(DeviceModel(model))
+    eng = InferenceEngine(synth.DeviceRandomModel(cfg, seed=0))
     n = args.prefill_tokens
     prompt = np.random.default_rng(0).integers(0, cfg["vocab_size"], n).astype(np.int32)
     for _ in range(3):  # direct launches, graph capture, first replay

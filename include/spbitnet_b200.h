@@ -52,8 +52,8 @@ int spb_set_pdl(int enabled);
  *     in registers, not decoded) for int8 activations and one matrix per launch when cols % 256 == 0,
  *     row strides are multiples of 4 words and meta / values / x are 16-byte aligned; the pair kernel
  *     otherwise and for the fused half-input forms;
- * 1 = pair kernel (SIMT: one dp4a per two groups), 2 = per-group table kernel (SIMT: one dp4a per group),
- * 3 = tcgen05 sparse kernel (tensor memory; kept for comparison), 4 = warp-level sparse MMA kernel.
+ * 1 = pair kernel (SIMT: one dp4a per two groups), 4 = warp-level sparse MMA kernel wherever the layout allows
+ * it, the fused half-input and multi-matrix forms included.  Other values behave like 0.
  * Results are identical on valid bitmaps.  Returns the previous setting. */
 int spb_set_gemv_variant(int variant);
 
@@ -76,7 +76,8 @@ int spb_sparse_ternary_gemv(const uint32_t* meta, const uint32_t* values, const 
  * d_items is a DEVICE array of n items that the caller uploads once (a decode step's list is
  * static); it must be 16-byte aligned and satisfy spb_gemv_batch_check, which validates the HOST
  * copy: cols a multiple of 256 (at most 32768), row strides multiples of 4 words, meta/values/x
- * 16-byte aligned.  max_rows / max_cols bound the items (they size shared memory). */
+ * 16-byte aligned.  max_rows / max_cols bound the items (max_cols sizes shared memory); an item
+ * with more than max_cols columns is skipped by the kernel (its y is left untouched), never copied. */
 typedef struct {
     const uint32_t* meta;
     const uint32_t* values;
@@ -138,14 +139,23 @@ int spb_sparse_bitlinear_gemm(const uint32_t* meta, const uint32_t* values, cons
  * sparse MMA form (mma.sp m16n8k64, operands re-encoded in registers; needs cols % 256 == 0, row strides
  * that are multiples of 4 words and 16-byte aligned meta / values / X), above that the tcgen05 sparse form
  * (tcgen05.mma.sp: sign bytes as the compressed operand, index pairs in tensor memory), the SIMT form where
- * the layout allows neither; 1 = SIMT form, 2 = tcgen05 dense form (weights expanded to int8 tiles),
- * 3 = tcgen05 sparse form for any n, 4 = warp-level sparse MMA form where it applies.
- * Results are identical.  Returns the previous setting. */
+ * the layout allows neither; 1 = SIMT form, 3 = tcgen05 sparse form for any n, 4 = warp-level sparse MMA
+ * form where it applies.  Other values behave like 0.  Results are identical.  Returns the previous setting. */
 int spb_set_gemm_variant(int variant);
-/* Number of blocks of the tensor-core kernels (GEMM and GEMV) whose bounded device-side wait ran out since the library
- * was loaded (their outputs are unspecified); 0 in a healthy run, -1 if the counter cannot be read.
- * Synchronises the device. */
+/* Number of bounded device-side waits of the tcgen05 product that ran out since the library was loaded, over all
+ * GPUs of the process; 0 in a healthy run, -1 if the counter cannot be read.  Synchronises the current device.
+ * A block whose wait ran out skips its epilogue and frees its tensor memory, so the outputs of that call are
+ * unspecified.  The kernel entry points are asynchronous and cannot report this themselves: callers of
+ * spb_sparse_ternary_gemm / spb_sparse_bitlinear_gemm that need the guarantee compare this counter before and
+ * after (once the stream is synchronised).  The engine does so at its own synchronisation points
+ * (spb_engine_prefill, spb_engine_generate, spb_engine_copy_logits) and returns SPB_E_TIMEOUT when it moved. */
 int spb_gemm_tc_timeouts(void);
+/* Testing aid, no counterpart in the reference: launches one block that allocates tensor memory, waits with the
+ * product kernel's bounded wait (limit_cycles, clamped to [1000, 40000000] SM clocks) on a barrier that nobody
+ * arrives at, counts the run-out like the product kernel, frees its tensor memory and returns; then synchronises
+ * the stream.  Returns SPB_E_TIMEOUT (the expected answer: the wait ran out and was reported) or SPB_E_CUDA.
+ * Nothing is left in flight and the context stays usable. */
+int spb_debug_bounded_wait_selftest(long long limit_cycles, void* stream);
 
 /* ---- transformer kernels: include/spbitnet/inference_kernels.h ------------------- */
 

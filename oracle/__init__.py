@@ -19,6 +19,7 @@ _ORACLE = HERE / "libspb_oracle.so"
 _TESTGEN = HERE / "libspb_testgen.so"
 _REF = HERE / "_ref" / "libspb_ref.so"
 _REFCUDA = HERE / "_ref" / "libspb_refcuda.so"
+_CSLT = HERE / "libspb_cslt.so"
 
 
 def build(quiet: bool = True) -> None:
@@ -57,6 +58,14 @@ def ref():
 def refcuda():
     """The reference CUDA kernels for sm_100a, or None."""
     return _load(_REFCUDA)
+
+
+def cslt():
+    """The cuSPARSELt comparison shim (cslt_shim.cpp), or None when it was not built."""
+    try:
+        return _load(_CSLT)
+    except OSError:  # the shim is there but libcusparseLt is not
+        return None
 
 
 def _p(a):
@@ -390,3 +399,140 @@ def ref_cpu_sparse_gemv(w, mask, x, threads: int = 1, repeats: int = 1):
     y = np.empty(w.shape[0], np.int32)
     r.ref_cpu_sparse_gemv(_p(w), _p(m), w.shape[0], w.shape[1], _p(x), _p(y), int(threads), int(repeats))
     return y
+
+
+class RefCpuGemv:
+    """The reference's CPU GEMV (tests/test_sparse_ternary.cu:17-33) over `slices` row slices, one thread each,
+    packed once.  run(x, repeats, dot_only): dot_only=False unpacks and multiplies every repeat (the reference's
+    cpu_sparse_gemv), dot_only=True multiplies pre-unpacked rows."""
+
+    def __init__(self, w, mask, slices: int = 1):
+        self._r = ref()
+        if self._r is None:
+            raise RuntimeError("oracle/_ref/libspb_ref.so is not built")
+        self._r.ref_gemv_ctx_create.restype = C.c_void_p
+        self._r.ref_gemv_ctx_run.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]
+        self._r.ref_gemv_ctx_destroy.argtypes = [C.c_void_p]
+        w = np.ascontiguousarray(w, np.int8)
+        m = np.ascontiguousarray(mask).astype(np.uint8)
+        self.rows, self.cols = w.shape
+        self._h = C.c_void_p(self._r.ref_gemv_ctx_create(_p(w), _p(m), self.rows, self.cols, int(slices)))
+
+    def run(self, x, repeats: int = 1, dot_only: bool = False):
+        x = np.ascontiguousarray(x, np.int8)
+        y = np.empty(self.rows, np.int32)
+        self._r.ref_gemv_ctx_run(self._h, _p(x), _p(y), int(repeats), 1 if dot_only else 0)
+        return y
+
+    def __del__(self):
+        try:
+            if self._h:
+                self._r.ref_gemv_ctx_destroy(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+
+class CusparseLtGemm:
+    """spbitnet::CuSparseLtGemm (include/spbitnet/cusparselt_backend.h:28-77) through cslt_shim.cpp: plan at
+    construction, prepare(dense int8 [m, k] device pointer) once, execute(B, D) per call.  Pointers are device
+    addresses (ints); stream is a CUDA stream handle (int) or None."""
+
+    def __init__(self, m: int, k: int, n: int):
+        self._l = cslt()
+        if self._l is None:
+            raise RuntimeError("oracle/libspb_cslt.so is not built or cuSPARSELt is missing")
+        l = self._l
+        l.cslt_last_error.restype = C.c_char_p
+        l.cslt_create.argtypes = [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_void_p)]
+        l.cslt_destroy.argtypes = [C.c_void_p]
+        l.cslt_prepare.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        l.cslt_execute.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+        l.cslt_pruned.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        self.m, self.k, self.n = m, k, n
+        self._h = C.c_void_p()
+        self._check(l.cslt_create(m, k, n, C.byref(self._h)))
+
+    def _check(self, rc):
+        if rc:
+            raise RuntimeError(f"cuSPARSELt shim error {rc}: {self._l.cslt_last_error().decode()}")
+
+    def prepare(self, d_weights: int, stream=None):
+        self._check(self._l.cslt_prepare(self._h, C.c_void_p(d_weights), C.c_void_p(stream or 0)))
+
+    def execute(self, d_B: int, d_D: int, stream=None):
+        self._check(self._l.cslt_execute(self._h, C.c_void_p(d_B), C.c_void_p(d_D), C.c_void_p(stream or 0)))
+
+    def pruned(self, d_out: int, stream=None):
+        self._check(self._l.cslt_pruned(self._h, C.c_void_p(d_out), C.c_void_p(stream or 0)))
+
+    def close(self):
+        if self._h:
+            self._l.cslt_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+_DROPIN = HERE / "_ref" / "libspb_dropin.so"
+DROPIN_GEMV_TEST = HERE / "_ref" / "dropin_gemv_test"
+
+
+def dropin():
+    """The reference's own engine + loader built over this repository's kernels (ref_dropin_shim.cu), or None."""
+    try:
+        return _load(_DROPIN)
+    except OSError:
+        return None
+
+
+class DropInEngine:
+    """spbitnet::Model::load + spbitnet::InferenceEngine (the reference's unmodified host code) running on the
+    sm_100a library through the drop-in headers.  forward(token) returns the logits as a host array."""
+
+    def __init__(self, model_dir):
+        self._l = dropin()
+        if self._l is None:
+            raise RuntimeError("oracle/_ref/libspb_dropin.so is not built")
+        l = self._l
+        l.dropin_create.restype = C.c_void_p
+        l.dropin_create.argtypes = [C.c_char_p]
+        l.dropin_last_error.restype = C.c_char_p
+        for name in ("dropin_destroy", "dropin_reset"):
+            getattr(l, name).argtypes = [C.c_void_p]
+        l.dropin_vocab.argtypes = [C.c_void_p]
+        l.dropin_seq_len.argtypes = [C.c_void_p]
+        l.dropin_forward.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+        h = l.dropin_create(str(model_dir).encode())
+        if not h:
+            raise RuntimeError(l.dropin_last_error().decode())
+        self._h = C.c_void_p(h)
+        self.vocab = l.dropin_vocab(self._h)
+
+    def forward(self, token: int) -> np.ndarray:
+        out = np.empty(self.vocab, np.float32)
+        if self._l.dropin_forward(self._h, int(token), _p(out)):
+            raise RuntimeError(self._l.dropin_last_error().decode())
+        return out
+
+    def reset(self):
+        self._l.dropin_reset(self._h)
+
+    @property
+    def seq_len(self):
+        return self._l.dropin_seq_len(self._h)
+
+    def close(self):
+        if self._h:
+            self._l.dropin_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

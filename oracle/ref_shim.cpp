@@ -79,4 +79,61 @@ void ref_cpu_sparse_gemv(const int8_t* w, const uint8_t* mask, int rows, int col
     }
 }
 
+// The same CPU GEMV with the row range cut into `slices` contiguous parts, one thread each, every part a
+// SparseTernaryTensor of its own (packed once, outside any timing) that its thread unpacks with the reference's
+// unpack_to_int8 and multiplies with the loop of tests/test_sparse_ternary.cu:24-32.  No algorithmic change:
+// slices = 1 is the function above without the repeated allocation.
+//   mode 0: every repeat unpacks and multiplies (the reference's cpu_sparse_gemv, partitioned);
+//   mode 1: the slices are unpacked once up front and every repeat only multiplies (dot product only).
+struct RefGemvCtx {
+    int rows, cols;
+    std::vector<SparseTernaryTensor> part;
+    std::vector<int> r0;
+    std::vector<std::vector<int8_t>> dense;
+};
+
+void* ref_gemv_ctx_create(const int8_t* w, const uint8_t* mask, int rows, int cols, int slices) {
+    if (slices < 1) slices = 1;
+    if (slices > rows) slices = rows;
+    auto* ctx = new RefGemvCtx{rows, cols, {}, {}, {}};
+    for (int i = 0; i < slices; ++i) {
+        const int a = static_cast<int>(static_cast<long>(rows) * i / slices);
+        const int b = static_cast<int>(static_cast<long>(rows) * (i + 1) / slices);
+        ctx->r0.push_back(a);
+        ctx->part.push_back(SparseTernaryTensor::pack_from_dense(w + static_cast<size_t>(a) * cols,
+                                                                 mask + static_cast<size_t>(a) * cols, b - a, cols));
+        ctx->dense.emplace_back(static_cast<size_t>(b - a) * cols);
+    }
+    ctx->r0.push_back(rows);
+    return ctx;
+}
+
+void ref_gemv_ctx_destroy(void* p) { delete static_cast<RefGemvCtx*>(p); }
+
+void ref_gemv_ctx_run(void* p, const int8_t* x, int32_t* y, int repeats, int mode) {
+    RefGemvCtx* ctx = static_cast<RefGemvCtx*>(p);
+    const int cols = ctx->cols, slices = static_cast<int>(ctx->part.size());
+    auto body = [&](int i) {
+        int8_t* dense = ctx->dense[i].data();
+        const int nrows = ctx->r0[i + 1] - ctx->r0[i];
+        if (mode == 1) ctx->part[i].unpack_to_int8(dense);
+        for (int rep = 0; rep < repeats; ++rep) {
+            if (mode == 0) ctx->part[i].unpack_to_int8(dense);
+            for (int r = 0; r < nrows; ++r) {
+                int32_t sum = 0;
+                for (int c = 0; c < cols; ++c)
+                    sum += static_cast<int32_t>(dense[static_cast<size_t>(r) * cols + c]) * static_cast<int32_t>(x[c]);
+                y[ctx->r0[i] + r] = sum;
+            }
+        }
+    };
+    if (slices == 1) {
+        body(0);
+        return;
+    }
+    std::vector<std::thread> pool;
+    for (int i = 0; i < slices; ++i) pool.emplace_back(body, i);
+    for (auto& th : pool) th.join();
+}
+
 }  // extern "C"

@@ -64,6 +64,7 @@ SIGNATURES = {
     "spb_sparse_bitlinear_gemm": (_i, [_p, _p, _p, _p, _p, C.c_float, _p, _i, _i, _i, _i, _i, _p]),
     "spb_set_gemm_variant": (_i, [_i]),
     "spb_gemm_tc_timeouts": (_i, []),
+    "spb_debug_bounded_wait_selftest": (_i, [C.c_longlong, _p]),
     "spb_rms_norm": (_i, [_p, _p, _p, _i, _f, _p]),
     "spb_absmax_quantize": (_i, [_p, _p, _p, _i, _p]),
     "spb_absmax_reduce": (_i, [_p, _p, _i, _p]),

@@ -8,15 +8,18 @@ import os
 import shutil
 import subprocess
 import sys
+from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libspbitnet_b200.so"
-SOURCES = ["core.cu", "gemv.cu", "gemv_batch.cu", "gemv_batch_mma.cu", "gemv_tcsp.cu", "gemv_mmasp.cu", "gemm.cu", "gemm_tc.cu", "gemm_tcsp.cu", "gemm_tcsp_ws.cu", "gemm_mmasp.cu", "unpack.cu", "decode_ops.cu", "attention.cu", "fused_ops.cu",
-           "prefill.cu", "engine.cu", "noalloc.cu", "pack.cu", "format_host.cpp"]
-NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
-              "-Xcompiler", "-fPIC", "-shared"]
+SOURCES = ["core.cu", "gemv.cu", "gemv_batch_mma.cu", "gemv_mmasp.cu", "gemm.cu", "gemm_tcsp_ws.cu", "gemm_mmasp.cu", "unpack.cu",
+           "decode_ops.cu", "attention.cu", "fused_ops.cu", "prefill.cu", "engine.cu", "noalloc.cu", "pack.cu", "format_host.cpp"]
+COMPILE_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+                 "-Xcompiler", "-fPIC"]
+LINK_FLAGS = ["-shared", "-gencode", "arch=compute_100a,code=sm_100a"]
+OBJ = CSRC / "build"
 
 
 def _nvcc() -> str:
@@ -34,23 +37,42 @@ def needs_build() -> bool:
     if not LIB.exists():
         return True
     t = LIB.stat().st_mtime
-    deps = list(CSRC.glob("*")) + [HERE.parent / "include" / "spbitnet_b200.h"]
+    deps = [p for p in CSRC.glob("*") if p.is_file()] + [HERE.parent / "include" / "spbitnet_b200.h"]
     return any(p.stat().st_mtime > t for p in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    if not force and not needs_build():
-        return LIB
-    cmd = [_nvcc(), *NVCC_FLAGS, "-o", str(LIB), *map(str, sources())]
+def _compile_one(nvcc: str, src: Path, obj: Path, verbose: bool) -> str:
+    cmd = [nvcc, *COMPILE_FLAGS, "-c", "-o", str(obj), str(src)]
     if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
-        print(" ".join(cmd))
+        cmd[1:1] = ["-Xptxas", "-v"]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
-        raise RuntimeError(f"nvcc failed:\n{res.stdout}\n{res.stderr}")
+        raise RuntimeError(f"nvcc failed on {src.name}:\n{res.stdout}\n{res.stderr}")
+    return res.stderr
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """One object file per source, compiled in parallel and only when the source or a header is newer than
+    the object; then one link.  Objects live in csrc/build/ (not tracked)."""
+    if not force and not needs_build():
+        return LIB
+    nvcc = _nvcc()
+    OBJ.mkdir(exist_ok=True)
+    headers = [p for p in CSRC.glob("*.cuh")] + [HERE.parent / "include" / "spbitnet_b200.h"]
+    newest_header = max(p.stat().st_mtime for p in headers)
+    jobs = []
+    for src in sources():
+        obj = OBJ / (src.name + ".o")
+        if force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, newest_header):
+            jobs.append((src, obj))
+    with ThreadPoolExecutor(max_workers=max(1, min(len(jobs), os.cpu_count() or 1))) as pool:
+        logs = list(pool.map(lambda j: _compile_one(nvcc, j[0], j[1], verbose), jobs))
     if verbose:
-        print(res.stderr)
+        print("\n".join(logs))
+    objs = [str(OBJ / (s.name + ".o")) for s in sources()]
+    res = subprocess.run([nvcc, *LINK_FLAGS, "-o", str(LIB), *objs], capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
     return LIB
 
 

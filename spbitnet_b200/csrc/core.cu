@@ -3,6 +3,8 @@
 
 #include <atomic>
 #include <cstring>
+#include <mutex>
+#include <vector>
 
 namespace spb {
 
@@ -32,7 +34,55 @@ int sm_count() {
     return cached[dev];
 }
 
+int ensure_dynamic_smem_impl(const char* name, const void* kernel, size_t bytes) {
+    struct Entry { const void* kernel; int device; size_t bytes; };
+    static std::mutex mu;
+    static std::vector<Entry> seen;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) dev = 0;
+    std::lock_guard<std::mutex> lock(mu);
+    Entry* hit = nullptr;
+    for (Entry& e : seen)
+        if (e.kernel == kernel && e.device == dev) hit = &e;
+    if (hit && hit->bytes >= bytes) return SPB_OK;
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return fail(SPB_E_CUDA, "%s: cudaFuncSetAttribute(%zu B of shared memory): %s", name, bytes, cudaGetErrorString(err));
+    }
+    if (hit) hit->bytes = bytes;
+    else seen.push_back(Entry{kernel, dev, bytes});
+    return SPB_OK;
+}
+
+int* timeout_counter() {
+    static int* counter = [] {
+        int* p = nullptr;
+        if (cudaHostAlloc(reinterpret_cast<void**>(&p), sizeof(int), cudaHostAllocPortable | cudaHostAllocMapped) != cudaSuccess) {
+            cudaGetLastError();
+            return static_cast<int*>(nullptr);
+        }
+        *p = 0;
+        return p;
+    }();
+    return counter;
+}
+
+int timeouts_now() {
+    int* p = timeout_counter();
+    return p ? *static_cast<volatile int*>(p) : 0;
+}
+
 }  // namespace spb
+
+extern "C" int spb_gemm_tc_timeouts(void) {
+    if (!spb::timeout_counter()) return -1;
+    if (cudaDeviceSynchronize() != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    return spb::timeouts_now();
+}
 
 extern "C" const char* spb_last_error_string(void) { return spb::t_error; }
 

@@ -67,6 +67,7 @@ struct spb_engine {
     bool fused = false;               // vector ops run inside the BitLinear launches
     bool force_unfused = false;
     int seq_len = 0;
+    int timeouts_seen = 0;  // value of the library's bounded-wait counter when the engine last looked
 
     // batched prefill: buffers for `pf_cap` tokens at a time, allocated by the first call that needs them
     int prefill_chunk = 0;  // 0 = generate() feeds the prompt token by token, as the reference does
@@ -104,6 +105,42 @@ int cuda_fail(const char* what, cudaError_t err) {
     } while (0)
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Makes the engine's device current for the duration of an entry point and restores the caller's afterwards, so
+// that launches, late allocations and graph work land on the GPU the engine was created on.
+class DeviceScope {
+public:
+    explicit DeviceScope(int device) {
+        if (cudaGetDevice(&prev_) != cudaSuccess) prev_ = -1;
+        if (prev_ != device) {
+            ok_ = cudaSetDevice(device) == cudaSuccess;
+            switched_ = ok_;
+        }
+    }
+    ~DeviceScope() {
+        if (switched_ && prev_ >= 0) cudaSetDevice(prev_);
+    }
+    bool ok() const { return ok_; }
+
+private:
+    int prev_ = -1;
+    bool ok_ = true, switched_ = false;
+};
+
+#define SPB_ON_ENGINE_DEVICE(e)                                                             \
+    DeviceScope device_scope__((e)->device);                                                \
+    if (!device_scope__.ok()) return fail(SPB_E_CUDA, "engine: cannot make device %d current", (e)->device)
+
+// Called after the engine's stream has been synchronised: a tensor-core block of the batched product whose bounded
+// wait ran out has skipped its epilogue, so whatever was computed since the last look is not to be trusted.
+int check_timeouts(spb_engine* e, const char* where) {
+    const int now = timeouts_now();
+    if (now == e->timeouts_seen) return SPB_OK;
+    const int n = now - e->timeouts_seen;
+    e->timeouts_seen = now;
+    return fail(SPB_E_TIMEOUT, "%s: %d bounded device-side wait(s) of the tensor-core product ran out; the outputs of "
+                "this call are unspecified", where, n);
+}
 
 BitLinearGroup make_group(const Linear* const* L, __half* const* out, int n) {
     BitLinearGroup g{};
@@ -486,11 +523,13 @@ extern "C" spb_engine* spb_engine_create(const spb_model_config* cfg) {
     e->d_pos = reinterpret_cast<int*>(p + o_ints);
     e->d_next = e->d_pos + 1;
     e->d_out = reinterpret_cast<int*>(p + o_out);
+    e->timeouts_seen = timeouts_now();
     return e;
 }
 
 extern "C" void spb_engine_destroy(spb_engine* e) {
     if (!e) return;
+    DeviceScope scope(e->device);
     cudaStreamSynchronize(e->stream);
     drop_graph(e);
     if (e->d_prompt) cudaFree(e->d_prompt);
@@ -549,6 +588,7 @@ extern "C" int spb_engine_forward(spb_engine* e, int token_id, const float** d_l
     if (rc) return rc;
     if (token_id < 0 || token_id >= e->cfg.vocab_size) return fail(SPB_E_INVALID, "spb_engine_forward: token %d outside the vocabulary", token_id);
     if (e->seq_len >= e->cfg.max_position_embeddings) return fail(SPB_E_INVALID, "spb_engine_forward: KV cache full (%d)", e->seq_len);
+    SPB_ON_ENGINE_DEVICE(e);
     if ((rc = ensure_graph(e, false, 0))) return rc;
     if ((rc = set_int(e->d_next, token_id, e->stream))) return rc;
     SPB_CUDA(cudaGraphLaunch(e->graph, e->stream));
@@ -572,8 +612,10 @@ extern "C" int spb_engine_prefill(spb_engine* e, const int* tokens, int n, const
     for (int i = 0; i < n; ++i)
         if (tokens[i] < 0 || tokens[i] >= e->cfg.vocab_size)
             return fail(SPB_E_INVALID, "spb_engine_prefill: token %d outside the vocabulary", tokens[i]);
+    SPB_ON_ENGINE_DEVICE(e);
     if ((rc = prefill_tokens(e, tokens, n))) return rc;
     SPB_CUDA(cudaStreamSynchronize(e->stream));
+    if ((rc = check_timeouts(e, "spb_engine_prefill"))) return rc;
     if (d_logits) *d_logits = e->logits;
     return SPB_OK;
 }
@@ -588,6 +630,7 @@ extern "C" int spb_engine_set_prefill_chunk(spb_engine* e, int chunk) {
 
 extern "C" int spb_engine_reset(spb_engine* e) {
     if (!e) return fail(SPB_E_INVALID, "spb_engine_reset: null handle");
+    SPB_ON_ENGINE_DEVICE(e);
     const size_t kv_total = e->kv_bytes_per_layer * e->cfg.num_hidden_layers;
     SPB_CUDA(cudaMemsetAsync(e->kcache, 0, kv_total, e->stream));
     SPB_CUDA(cudaMemsetAsync(e->vcache, 0, kv_total, e->stream));
@@ -601,15 +644,30 @@ extern "C" int spb_engine_seq_len(const spb_engine* e) { return e ? e->seq_len :
 
 extern "C" int spb_engine_copy_logits(spb_engine* e, float* h_logits) {
     if (!e || !h_logits) return fail(SPB_E_INVALID, "spb_engine_copy_logits: null pointer");
+    SPB_ON_ENGINE_DEVICE(e);
     SPB_CUDA(cudaMemcpyAsync(h_logits, e->logits, sizeof(float) * e->cfg.vocab_size, cudaMemcpyDeviceToHost, e->stream));
     SPB_CUDA(cudaStreamSynchronize(e->stream));
-    return SPB_OK;
+    return check_timeouts(e, "spb_engine_copy_logits");
 }
+
+static int generate_impl(spb_engine* e, const int* prompt, int n_prompt, int max_tokens, int eos_token_id,
+                         int* out_tokens);
 
 extern "C" int spb_engine_generate(spb_engine* e, const int* prompt, int n_prompt, int max_tokens,
                                    int eos_token_id, int* out_tokens) {
     int rc = check_ready(e);
     if (rc) return rc;
+    SPB_ON_ENGINE_DEVICE(e);
+    const int produced = generate_impl(e, prompt, n_prompt, max_tokens, eos_token_id, out_tokens);
+    if (produced < 0) return produced;
+    // every path of generate_impl ends with the stream synchronised
+    if ((rc = check_timeouts(e, "spb_engine_generate"))) return rc;
+    return produced;
+}
+
+static int generate_impl(spb_engine* e, const int* prompt, int n_prompt, int max_tokens, int eos_token_id,
+                         int* out_tokens) {
+    int rc;
     if (!prompt || n_prompt < 1 || max_tokens < 0 || (max_tokens > 0 && !out_tokens))
         return fail(SPB_E_INVALID, "spb_engine_generate: bad arguments");
     const int start = e->seq_len;

@@ -141,25 +141,19 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_generic_kernel(const GemmAr
     if (lane == 0) a.Y[static_cast<size_t>(j) * a.rows + row] = acc;
 }
 
-int gemm_tc_launch(const uint32_t* meta, const uint32_t* values, const int8_t* X, int32_t* Y, int rows, int cols,
-                   int n, int meta_stride, int values_stride, void* stream);
-
 int gemm_tcsp_ws_launch(const uint32_t* meta, const uint32_t* values, const int8_t* X, int32_t* Y, int rows, int cols,
                         int n, int meta_stride, int values_stride, void* stream, const GemmEpilogue* ep);
 // prefill.cu
 int dequantize_rows(const int32_t* acc, void* out, const float* d_absmax, float gamma, int rows, int vectors,
                     void* stream);
-int gemm_tcsp_launch(const uint32_t* meta, const uint32_t* values, const int8_t* X, int32_t* Y, int rows, int cols,
-                     int n, int meta_stride, int values_stride, void* stream);
-
 bool gemm_mmasp_supported(const uint32_t* meta, const uint32_t* values, const int8_t* X, int rows, int cols, int n,
                           int meta_stride, int values_stride, int max_n);
 int gemm_mmasp_launch(const uint32_t* meta, const uint32_t* values, const int8_t* X, int32_t* Y, int rows, int cols,
                       int n, int meta_stride, int values_stride, void* stream, const GemmEpilogue* ep);
 
 // 0 automatic (up to 32 batch rows: warp-level sparse MMA form; above: tcgen05 sparse form; SIMT where the layout
-// allows neither), 1 SIMT form, 2 tcgen05 dense form, 3 tcgen05 sparse form, 4 warp-level sparse MMA form
-// (2, 3 and 4 whenever the layout allows)
+// allows neither), 1 SIMT form, 3 tcgen05 sparse form, 4 warp-level sparse MMA form (3 and 4 whenever the layout
+// allows)
 static int g_gemm_variant = 0;
 constexpr int kMmaSpAutoMaxN = 32;
 
@@ -222,11 +216,11 @@ static int gemm_dispatch(const char* name, const uint32_t* meta, const uint32_t*
         gemm_mmasp_supported(meta, values, X, rows, cols, n, meta_row_stride, values_row_stride,
                              g_gemm_variant == 4 ? 4096 : mma_auto_max_n))
         return gemm_mmasp_launch(meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream, ep);
-    if (fast && (g_gemm_variant == 0 || g_gemm_variant == 4)) {  // warp-specialised tcgen05 sparse form
+    if (fast && g_gemm_variant != 1) {  // warp-specialised tcgen05 sparse form
         const int rc = gemm_tcsp_ws_launch(meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream, ep);
-        if (rc != SPB_E_UNSUPPORTED) return rc;  // no tensor map of X on this system: the plain form below
+        if (rc != SPB_E_UNSUPPORTED) return rc;  // no tensor map of X on this system: the SIMT form below
     }
-    if (ep) {  // the remaining forms write int32 sums: run them into the workspace, then scale row by row
+    if (ep) {  // the SIMT forms write int32 sums: run them into the workspace, then scale row by row
         if (!Y) return fail(SPB_E_UNSUPPORTED, "%s: this layout needs acc_workspace (n * rows int32)", name);
         const int rc = gemm_dispatch_int(name, meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream,
                                          fast);
@@ -236,16 +230,12 @@ static int gemm_dispatch(const char* name, const uint32_t* meta, const uint32_t*
     return gemm_dispatch_int(name, meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream, fast);
 }
 
-// The forms without a fused epilogue: plain tcgen05 sparse, tcgen05 dense, SIMT.
+// The SIMT forms (no fused epilogue).
 static int gemm_dispatch_int(const char* name, const uint32_t* meta, const uint32_t* values, const int8_t* X, int32_t* Y,
                              int rows, int cols, int n, int meta_row_stride, int values_row_stride, void* stream,
                              bool fast) {
     GemmArgs a{meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, 0, 0};
     const size_t x_bytes = static_cast<size_t>(kBatchTile) * cols;
-    if (fast && (g_gemm_variant == 3 || g_gemm_variant == 0 || g_gemm_variant == 4))
-        return gemm_tcsp_launch(meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream);
-    if (fast && g_gemm_variant == 2)
-        return gemm_tc_launch(meta, values, X, Y, rows, cols, n, meta_row_stride, values_row_stride, stream);
     if (!fast) {
         const long long warps = static_cast<long long>(rows) * n;
         const unsigned grid = static_cast<unsigned>((warps * 32 + kGemmThreads - 1) / kGemmThreads);
@@ -266,13 +256,6 @@ static int gemm_dispatch_int(const char* name, const uint32_t* meta, const uint3
     const dim3 grid((rows + a.rpc - 1) / a.rpc, (n + kBatchTile - 1) / kBatchTile);
     const size_t smem = kLutBytes + ((a.rpc * kBatchTile * 4 + 15) & ~15) + x_bytes;
     auto kernel = passes <= 1 ? gemm_units_kernel<1> : gemm_units_kernel<2>;
-    if (smem > 48 * 1024) {
-        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               static_cast<int>(smem));
-        if (err != cudaSuccess) {
-            cudaGetLastError();
-            return fail(SPB_E_CUDA, "%s: %s", name, cudaGetErrorString(err));
-        }
-    }
+    if (int rc = ensure_dynamic_smem(name, kernel, smem)) return rc;
     return launch(name, kernel, dim3(grid), dim3(kGemmThreads), smem, stream, a);
 }

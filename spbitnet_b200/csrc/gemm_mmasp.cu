@@ -263,11 +263,7 @@ int gemm_mmasp_launch(const uint32_t* meta, const uint32_t* values, const int8_t
     if (smem > 200 * 1024) return fail(SPB_E_UNSUPPORTED, "%s: %d columns do not fit", name, cols);
     void (*kernel)(GqArgs) = nt == 1 ? gemm_mmasp_kernel<1, false> : nt == 2 ? gemm_mmasp_kernel<2, false> : gemm_mmasp_kernel<4, false>;
     if (a.ep.out) kernel = nt == 1 ? gemm_mmasp_kernel<1, true> : nt == 2 ? gemm_mmasp_kernel<2, true> : gemm_mmasp_kernel<4, true>;
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (err != cudaSuccess) {
-        cudaGetLastError();
-        return fail(SPB_E_CUDA, "%s: %s", name, cudaGetErrorString(err));
-    }
+    if (int rc = ensure_dynamic_smem(name, kernel, smem)) return rc;
     const dim3 grid((rows + 16 * a.rb - 1) / (16 * a.rb), (tiles + nt - 1) / nt);
     return launch(name, kernel, grid, dim3(kGqThreads), smem, stream, a);
 }

@@ -2,13 +2,12 @@
 //
 //   Y[j, r] = sum_c W[r, c] * X[j, c]      W: rows x cols compressed 2:4 ternary, X: n x cols int8
 //
-// Same operands and layouts as gemm_tcsp.cu (sign bytes as the compressed A tile in shared memory,
-// index pairs as metadata in tensor memory, activation tiles by tensor-map bulk copies, int32
-// accumulators in tensor memory).  What differs is who does what.  In gemm_tcsp.cu one thread issues
-// the copies and the MMAs between two block-wide barriers per step, and a trace showed a step costing
-// about 2450 cycles of which the re-encoding is 500: the rest is that thread's serial chain (barrier,
-// fences, waits, 800 cycles to issue four MMAs) with 255 threads parked.  Here the block has three roles
-// that only meet at mbarriers:
+// Operands: the sign bytes (+1 / -1) of a tile as the compressed A operand in shared memory (K-major, 128-byte
+// swizzle), the index pairs as metadata in tensor memory (one byte per 8 columns, lane = weight row), the
+// activation tiles by tensor-map bulk copies, int32 accumulators in tensor memory.  A first form in which one
+// thread issued the copies and the MMAs between two block-wide barriers per step cost about 2450 cycles per
+// step of which the re-encoding was 500 (the rest: that thread's serial chain with 255 threads parked).  Here
+// the block has three roles that only meet at mbarriers:
 //   warps 0-7 and 12-19      re-encode, as two groups of 256 threads that take alternate steps: wait for a
 //                            free stage, write the A tile and the metadata of a step, arrive on the
 //                            stage's "a_full" barrier;
@@ -23,7 +22,6 @@
 // and the block returns.
 #include <cuda.h>
 
-#include <cstdlib>
 #include <cstring>
 
 #include "spb_common.cuh"
@@ -53,9 +51,13 @@ struct WsArgs {
     int tmem_cols;  // power of two >= nt + 8 * stages
     int groups;     // re-encoding groups in use: 2 (alternate steps), or 1 (warps 12-19 idle)
     GemmEpilogue ep;  // ep.out set: scaled half output instead of Y
+    int* timeouts;        // counter of waits that ran out (pinned host memory, system-scope atomics), may be null
+    long long wait_cycles;  // bound of every wait in the kernel
 };
 
-__device__ int g_tcsp_ws_timeouts = 0;  // roles whose bounded wait ran out (0 in a healthy run)
+__device__ __forceinline__ void ws_count_timeout(int* counter) {
+    if (counter) atomicAdd_system(counter, 1);
+}
 
 __device__ __forceinline__ uint32_t ws_smem(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -74,8 +76,8 @@ __device__ __forceinline__ uint32_t ws_idesc(int m, int n) {
     return (1u << 2) | (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
            (static_cast<uint32_t>(m >> 4) << 24);
 }
-// Bounded by time, not by polls (a poll may suspend for a while): about 20 ms at 2 GHz.
-__device__ __forceinline__ bool ws_wait(uint32_t mbar, uint32_t parity) {
+// Bounded by time, not by polls (a poll may suspend for a while): kWsWaitCycles is about 20 ms at 2 GHz.
+__device__ __forceinline__ bool ws_wait(uint32_t mbar, uint32_t parity, long long limit) {
     const long long t0 = clock64();
     for (;;) {
         uint32_t done;
@@ -87,7 +89,7 @@ __device__ __forceinline__ bool ws_wait(uint32_t mbar, uint32_t parity) {
             : "r"(mbar), "r"(parity)
             : "memory");
         if (done) return true;
-        if (clock64() - t0 > kWsWaitCycles) return false;
+        if (clock64() - t0 > limit) return false;
     }
 }
 __device__ __forceinline__ uint32_t ws_swz(int r, int c) {
@@ -161,7 +163,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) gemm_tcsp_ws_kernel(const WsArg
             int issued = 0;
             for (int kc = 0; kc < nsteps && ok; ++kc) {
                 const int s = kc % S;
-                if (kc >= S) ok = ws_wait(ws_smem(free_b + s), static_cast<uint32_t>(kc / S - 1) & 1u);
+                if (kc >= S) ok = ws_wait(ws_smem(free_b + s), static_cast<uint32_t>(kc / S - 1) & 1u, a.wait_cycles);
                 if (!ok) break;
                 const uint32_t fb = ws_smem(b_full + s);
                 uint8_t* sb = stage0 + static_cast<size_t>(s) * stage_bytes + kWsABytes;
@@ -179,8 +181,8 @@ __global__ void __launch_bounds__(kWsThreads, 1) gemm_tcsp_ws_kernel(const WsArg
             }
             // nothing of this block's copies may be in flight when it leaves: the last S issued steps
             for (int kc = max(0, issued - S); kc < issued; ++kc)
-                if (!ws_wait(ws_smem(b_full + kc % S), static_cast<uint32_t>(kc / S) & 1u)) ok = false;
-            if (!ok) atomicAdd(&g_tcsp_ws_timeouts, 1);
+                if (!ws_wait(ws_smem(b_full + kc % S), static_cast<uint32_t>(kc / S) & 1u, a.wait_cycles)) ok = false;
+            if (!ok) ws_count_timeout(a.timeouts);
         }
     } else if (warp == 8) {
         // ---- MMA warp: four tcgen05.mma.sp per step, as soon as both operands of the stage are there ----------
@@ -189,7 +191,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) gemm_tcsp_ws_kernel(const WsArg
             for (int kc = 0; kc < nsteps; ++kc) {
                 const int s = kc % S;
                 const uint32_t par = static_cast<uint32_t>(kc / S) & 1u;
-                ok = ws_wait(ws_smem(a_full + s), par) && ws_wait(ws_smem(b_full + s), par);
+                ok = ws_wait(ws_smem(a_full + s), par, a.wait_cycles) && ws_wait(ws_smem(b_full + s), par, a.wait_cycles);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t sa = stage0_s + static_cast<uint32_t>(s) * stage_bytes;
@@ -215,7 +217,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) gemm_tcsp_ws_kernel(const WsArg
                     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(ws_smem(done_b))
                                  : "memory");
             }
-            if (!ok) atomicAdd(&g_tcsp_ws_timeouts, 1);
+            if (!ok) ws_count_timeout(a.timeouts);
         }
     } else if (warp < 8 || (warp >= kWsGroup1Warp && a.groups == 2)) {
         // ---- re-encoding warps, two groups of eight that take alternate steps (a step's re-encoding is a chain of
@@ -253,7 +255,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) gemm_tcsp_ws_kernel(const WsArg
             uint2 vn = make_uint2(0, 0);
             bool nvalid = false;
             if (kc + 4 * gs < nsteps) load_unit(kc + 4 * gs, mn, vn, nvalid);
-            if (kc >= S) ok = ws_wait(ws_smem(free_b + s), static_cast<uint32_t>(kc / S - 1) & 1u);
+            if (kc >= S) ok = ws_wait(ws_smem(free_b + s), static_cast<uint32_t>(kc / S - 1) & 1u, a.wait_cycles);
             ok = __all_sync(0xFFFFFFFFu, ok ? 1 : 0) != 0;  // tcgen05.st below is warp-wide
             if (!ok) break;
             // metadata: index pairs of this unit's 32 groups -> four tensor-memory columns of the row
@@ -296,7 +298,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) gemm_tcsp_ws_kernel(const WsArg
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ws_smem(a_full + s)) : "memory");
         }
         // ---- epilogue: accumulators -> Y -------------------------------------------------------------
-        if (ok) ok = ws_wait(ws_smem(done_b), 0);
+        if (ok) ok = ws_wait(ws_smem(done_b), 0, a.wait_cycles);
         ok = __all_sync(0xFFFFFFFFu, ok ? 1 : 0) != 0;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
@@ -334,7 +336,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) gemm_tcsp_ws_kernel(const WsArg
                 }
             }
         } else if (lane == 0) {
-            atomicAdd(&g_tcsp_ws_timeouts, 1);
+            ws_count_timeout(a.timeouts);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -343,6 +345,32 @@ __global__ void __launch_bounds__(kWsThreads, 1) gemm_tcsp_ws_kernel(const WsArg
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d),
                      "r"(static_cast<uint32_t>(a.tmem_cols))
                      : "memory");
+}
+
+// One block that allocates tensor memory, waits with ws_wait on a barrier nobody arrives at, reports the run-out
+// like the product kernel does, frees the tensor memory and returns.  No copy is in flight at any time.
+__global__ void __launch_bounds__(128, 1) ws_wait_selftest_kernel(int* timeouts, long long limit) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ uint32_t tmem_slot;
+    const int warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(ws_smem(&bar)));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ws_smem(&tmem_slot)), "r"(32u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&tmem_slot);
+    if (threadIdx.x == 0 && !ws_wait(ws_smem(&bar), 0u, limit)) ws_count_timeout(timeouts);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(32u) : "memory");
 }
 
 // Launch of the warp-specialised form; the caller has checked the layout (cols % 128 == 0, aligned rows and X).
@@ -354,16 +382,12 @@ int gemm_tcsp_ws_launch(const uint32_t* meta, const uint32_t* values, const int8
     if (ep) a.ep = *ep;
     a.rows = rows; a.cols = cols; a.n = n;
     a.meta_stride = meta_stride; a.values_stride = values_stride;
-    static const int nt_env = [] {
-        const char* e = getenv("SPB_GEMM_WS_NT");
-        return e ? atoi(e) : 0;
-    }();
     // batch rows per block: 256, or 128 / 64 when the wider tile would leave more than half of the SMs without a
     // block (a step costs about the same whatever the tile width, so more, narrower blocks finish sooner)
     const int mtiles = (rows + kWsTileM - 1) / kWsTileM;
     int nt = 256;
     while (nt > 64 && mtiles * ((n + nt - 1) / nt) < sm_count() / 2) nt >>= 1;
-    a.nt = min(nt_env > 0 ? nt_env : nt, (n + 15) / 16 * 16);
+    a.nt = min(nt, (n + 15) / 16 * 16);
     const int stage_bytes = kWsABytes + 2 * a.nt * 128;
     a.stages = max(2, min(kWsMaxStages, (200 * 1024) / stage_bytes));
     // two groups pay off except at 128 batch rows per block (measured at 6912x2560, n = 256: 12.4 against 11.9 us)
@@ -402,23 +426,27 @@ int gemm_tcsp_ws_launch(const uint32_t* meta, const uint32_t* values, const int8
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return SPB_E_UNSUPPORTED;
     void (*kernel)(WsArgs, CUtensorMap) = a.ep.out ? gemm_tcsp_ws_kernel<true> : gemm_tcsp_ws_kernel<false>;
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (err != cudaSuccess) {
-        cudaGetLastError();
-        return fail(SPB_E_CUDA, "gemm_tcsp_ws: %s", cudaGetErrorString(err));
-    }
+    if (int rc = ensure_dynamic_smem("gemm_tcsp_ws", kernel, smem)) return rc;
+    a.timeouts = timeout_counter();
+    a.wait_cycles = kWsWaitCycles;
     const dim3 grid((rows + kWsTileM - 1) / kWsTileM, (n + a.nt - 1) / a.nt);
     return launch("spb_sparse_ternary_gemm(tcgen05.sp, warp-specialised)", kernel, grid, dim3(kWsThreads), smem,
                   stream, a, tmap);
 }
 
-int gemm_tcsp_ws_timeouts() {
-    int v = 0;
-    if (cudaMemcpyFromSymbol(&v, g_tcsp_ws_timeouts, sizeof v) != cudaSuccess) {
-        cudaGetLastError();
-        return -1;
-    }
-    return v;
-}
-
 }  // namespace spb
+
+extern "C" int spb_debug_bounded_wait_selftest(long long limit_cycles, void* stream) {
+    using namespace spb;
+    int* counter = timeout_counter();
+    if (!counter) return fail(SPB_E_CUDA, "spb_debug_bounded_wait_selftest: no timeout counter");
+    const long long limit = limit_cycles < 1000 ? 1000 : limit_cycles > kWsWaitCycles ? kWsWaitCycles : limit_cycles;
+    const int before = timeouts_now();
+    ws_wait_selftest_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream)>>>(counter, limit);
+    cudaError_t err = cudaGetLastError();
+    if (err == cudaSuccess) err = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    if (err != cudaSuccess) return fail(SPB_E_CUDA, "spb_debug_bounded_wait_selftest: %s", cudaGetErrorString(err));
+    if (timeouts_now() != before)
+        return fail(SPB_E_TIMEOUT, "spb_debug_bounded_wait_selftest: the wait ran out after %lld cycles, as it must", limit);
+    return SPB_OK;
+}

@@ -12,9 +12,9 @@
 //     (quantising it on the way when the input is half), in 16-byte chunks whose
 //     position is XOR-swizzled so that the per-thread 128-byte reads are
 //     conflict free;
-//   * turns (bitmap, sign pair) into the four int8 weights of a group with a
-//     64-entry table replicated once per lane in shared memory (bank = lane, no
-//     conflicts) and consumes a group with one dp4a;
+//   * gathers the four non-zero x bytes of two groups with one PRMT whose selector comes from a
+//     per-lane table indexed by the two bitmaps, takes their signs from a second per-lane table
+//     and consumes two groups with one dp4a (the pair kernel below);
 //   * reduces the per-thread partials of a row with a segmented shuffle scan.
 // A "unit" is 128 consecutive columns of one row: 16 B of meta + 8 B of values.
 #include "fused_ops.cuh"
@@ -78,128 +78,13 @@ __device__ __forceinline__ void store_out(const GemvMat& m, int row, int acc, fl
     }
 }
 
-// Block = rpc rows of one matrix = rpc * upr units, one unit per thread.
-//   phase A (independent of any predecessor): stream the unit's 24 bytes of weights, build the
-//            per-lane table, expand the unit to 32 packed int8x4 weight words in registers;
-//   phase B (after the dependency wait): stage x, 8 x LDS.128 + 32 x dp4a, reduce, store.
-template <int IN, int OUT>
-__global__ void __launch_bounds__(kThreads) gemv_units_kernel(const GemvArgs a) {
-    extern __shared__ __align__(16) uint8_t smem[];
-    uint32_t* lut = reinterpret_cast<uint32_t*>(smem);
-    int* rowacc = reinterpret_cast<int*>(smem + kLutBytes);
-    uint4* xs = reinterpret_cast<uint4*>(smem + kLutBytes + ((a.rpc * 4 + 15) & ~15));
-
-    const int tid = threadIdx.x, lane = tid & 31;
-    int mi = 0;
-    if (a.nmat > 1 && static_cast<int>(blockIdx.x) >= a.mat[1].blk_begin) mi = 1;
-    if (a.nmat > 2 && static_cast<int>(blockIdx.x) >= a.mat[2].blk_begin) mi = 2;
-    const GemvMat& M = a.mat[mi];
-    const int r_lo = (blockIdx.x - M.blk_begin) * a.rpc;
-    const int nrows = min(a.rpc, M.rows - r_lo);
-    const int nunits = nrows * a.upr;
-
-    grid_dep_launch();
-
-    // ---- phase A ------------------------------------------------------------------------
-    const bool valid = tid < nunits;
-    int rl = -1, cb = a.upr;
-    uint4 m = make_uint4(0, 0, 0, 0);
-    uint2 v = make_uint2(0, 0);
-    if (valid) {
-        rl = tid / a.upr;
-        cb = tid - rl * a.upr;
-        const size_t row = static_cast<size_t>(r_lo + rl);
-        m = ld_stream_v4(M.meta + row * M.meta_stride + cb * 4);
-        v = ld_stream_v2(M.values + row * M.values_stride + cb * 2);
-    }
-    fill_lane_lut(lut, tid, kThreads);
-    for (int e = tid; e < nrows; e += kThreads) rowacc[e] = 0;
-    __syncthreads();
-
-    uint32_t wt[32];
-    {
-        const uint32_t* lutp = lut + lane;
-        const uint32_t mw[4] = {m.x, m.y, m.z, m.w};
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const uint32_t vv = (w < 2) ? v.x : v.y;
-            const uint32_t sg = (w & 1) ? (vv >> 16) : vv;  // the 16 sign bits of this meta word
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-                const uint32_t idx = ((mw[w] >> (4 * g)) & 0xFu) | (((sg >> (2 * g)) & 0x3u) << 4);
-                wt[w * 8 + g] = lutp[idx * 32];
-            }
-        }
-    }
-
-    // ---- phase B ------------------------------------------------------------------------
-    grid_dep_wait();
-    const int nchunks = a.cols >> 4;
-    float absmax = 0.0f;
-    if (IN == IN_F16 || OUT != OUT_I32) absmax = *a.d_absmax;
-    if (IN == IN_I8) {
-        const uint4* xg = static_cast<const uint4*>(a.x);
-        for (int q = tid; q < nchunks; q += kThreads) {
-            const int c = q >> 3, i = q & 7;
-            xs[(c << 3) + (i ^ (c & 7))] = xg[q];
-        }
-    } else {
-        const float scale = quant_scale(absmax);
-        const uint4* xg = static_cast<const uint4*>(a.x);
-        for (int q = tid; q < nchunks; q += kThreads) {
-            const uint4 lo = xg[2 * q], hi = xg[2 * q + 1];
-            const uint32_t hw[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-            uint32_t out[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                uint32_t packed = 0;
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const __half2 h2 = *reinterpret_cast<const __half2*>(&hw[2 * k + e]);
-                    const int q0 = quantize_one(__low2float(h2), scale);
-                    const int q1 = quantize_one(__high2float(h2), scale);
-                    packed |= (static_cast<uint32_t>(q0) & 0xFFu) << (16 * e);
-                    packed |= (static_cast<uint32_t>(q1) & 0xFFu) << (16 * e + 8);
-                }
-                out[k] = packed;
-            }
-            const int c = q >> 3, i = q & 7;
-            xs[(c << 3) + (i ^ (c & 7))] = make_uint4(out[0], out[1], out[2], out[3]);
-        }
-    }
-    __syncthreads();
-
-    int part = 0;
-    if (valid) {
-        const uint4* xb = xs + (cb << 3);
-        const int sw = cb & 7;
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-            const uint4 xv = xb[ch ^ sw];
-            part = __dp4a(static_cast<int>(wt[ch * 4 + 0]), static_cast<int>(xv.x), part);
-            part = __dp4a(static_cast<int>(wt[ch * 4 + 1]), static_cast<int>(xv.y), part);
-            part = __dp4a(static_cast<int>(wt[ch * 4 + 2]), static_cast<int>(xv.z), part);
-            part = __dp4a(static_cast<int>(wt[ch * 4 + 3]), static_cast<int>(xv.w), part);
-        }
-    }
-    // segmented reduction: the units of a row sit in consecutive lanes
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-        const int other = __shfl_down_sync(0xFFFFFFFFu, part, off);
-        if (lane + off < 32 && cb + off < a.upr) part += other;
-    }
-    if (valid && (cb == 0 || lane == 0)) atomicAdd(&rowacc[rl], part);
-    __syncthreads();
-
-    const float dq = (OUT != OUT_I32) ? dequant_scale(M.gamma, absmax) : 0.0f;
-    for (int t = tid; t < nrows; t += kThreads) store_out(M, r_lo + t, rowacc[t], dq, OUT);
-}
-
 // ---------------------------------------------------------------------------
 // Pair kernel (the default).
 //
-// Same block/unit mapping and the same two phases as the kernel above, but two groups (one
-// meta byte, one sign nibble) are consumed at a time:
+// Block = rpc rows of one matrix = rpc * upr units, one unit per thread, two phases:
+//   phase A (independent of any predecessor): stream the unit's 24 bytes of weights, copy the tables;
+//   phase B (after the dependency wait): stage x, expand, multiply-add, reduce, store.
+// Two groups (one meta byte, one sign nibble) are consumed at a time:
 //   sel = sel_lut[meta byte & 0x77] : PRMT selector that gathers the four non-zero columns
 //   sgn = sgn_lut[sign nibble]      : their four signs as int8 +-1
 //   acc = dp4a(prmt(x_lo, x_hi, sel), sgn, acc)
@@ -952,14 +837,7 @@ __global__ void __launch_bounds__(kThreads) gemv_generic_kernel(const GemvArgs a
 // ---------------------------------------------------------------------------
 template <typename K>
 static int ensure_smem(K kernel, size_t bytes) {
-    if (bytes <= 48 * 1024) return SPB_OK;
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(bytes));
-    if (err != cudaSuccess) {
-        cudaGetLastError();
-        return fail(SPB_E_CUDA, "cudaFuncSetAttribute(%zu B): %s", bytes, cudaGetErrorString(err));
-    }
-    return SPB_OK;
+    return ensure_dynamic_smem("sparse-ternary GEMV", kernel, bytes);
 }
 
 static bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
@@ -974,7 +852,7 @@ struct MatDesc {
 };
 
 // 0 automatic (warp-level sparse MMA kernel where the layout allows it, else the pair kernel), 1 pair kernel,
-// 2 per-group table kernel, 3 tcgen05 sparse kernel, 4 warp-level sparse MMA kernel
+// 4 warp-level sparse MMA kernel (also for the fused-producer forms)
 static int g_gemv_variant = 0;
 
 bool gemv_mmasp_supported(const uint32_t* meta, const uint32_t* values, const int8_t* x, int rows, int cols,
@@ -982,10 +860,6 @@ bool gemv_mmasp_supported(const uint32_t* meta, const uint32_t* values, const in
 int gemv_mmasp_launch(const char* name, const uint32_t* meta, const uint32_t* values, const int8_t* x, void* y,
                       int32_t* y_acc, const float* d_absmax, float gamma, int out_mode, int rows, int cols,
                       int meta_stride, int values_stride, void* stream);
-bool gemv_tcsp_supported(int rows, int cols);
-int gemv_tcsp_launch(const char* name, const uint32_t* meta, const uint32_t* values, const int8_t* x, void* y,
-                     int32_t* y_acc, const float* d_absmax, float gamma, int out_mode, int rows, int cols,
-                     int meta_stride, int values_stride, void* stream);
 
 // Where the activation vector of a launch comes from (see the IN_* producers).
 struct XDesc {
@@ -1109,18 +983,9 @@ static int run_gemv(const char* name, const MatDesc* mats, int nmat, const XDesc
                                      mats[0].y_acc, xd.d_absmax, mats[0].gamma, OUT, mats[0].rows, cols,
                                      mats[0].meta_stride, mats[0].values_stride, stream);
         }
-        if (fast && nmat == 1 && g_gemv_variant == 3 && gemv_tcsp_supported(mats[0].rows, cols))
-            return gemv_tcsp_launch(name, mats[0].meta, mats[0].values, static_cast<const int8_t*>(xd.x), mats[0].y,
-                                    mats[0].y_acc, xd.d_absmax, mats[0].gamma, OUT, mats[0].rows, cols,
-                                    mats[0].meta_stride, mats[0].values_stride, stream);
     }
     if constexpr (IN <= IN_F16) {
         if (!fast) return launch(name, gemv_generic_kernel<IN, OUT>, dim3(blocks), dim3(kThreads), 0, stream, a);
-        if (g_gemv_variant == 2) {  // the per-group table kernel, kept for comparison
-            const size_t smem = kLutBytes + ((rpc * 4 + 15) & ~15) + static_cast<size_t>(cols);
-            if ((rc = ensure_smem(gemv_units_kernel<IN, OUT>, smem))) return rc;
-            return launch(name, gemv_units_kernel<IN, OUT>, dim3(blocks), dim3(kThreads), smem, stream, a);
-        }
     }
     const size_t smem = kSelBytes + kSgnBytes + 256 + ((a.upr * (rpc | 1) * 4 + 15) & ~15) +
                         static_cast<size_t>(cols) * (IN >= IN_RESNORM ? 3 : 1);
@@ -1190,10 +1055,6 @@ bool bitlinear_group_is_fast(const BitLinearGroup& g) {
 }  // namespace spb
 
 using namespace spb;
-
-namespace spb {
-int gemv_variant_setting() { return g_gemv_variant; }
-}  // namespace spb
 
 extern "C" int spb_set_gemv_variant(int variant) {
     const int old = g_gemv_variant;

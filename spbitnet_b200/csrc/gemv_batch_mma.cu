@@ -23,6 +23,7 @@ constexpr int kBmMaxItems = 256;  // descriptors held in shared memory per launc
 struct BmGeom {
     int stage_bytes;  // one half of the double buffer: slab + x, 16-byte aligned
     int x_off;        // offset of the x vector inside a stage
+    int max_cols;     // the stages are sized for items of up to this many columns; wider items are skipped
 };
 
 struct BmTile {
@@ -88,7 +89,8 @@ __global__ void __launch_bounds__(kBmThreads, 3) gemv_batch_mma_kernel(const spb
         BmTile t{-1, 0, 0};
         while (walk_item < n) {
             const int kl = bm_ks_log2(desc[walk_item].cols), tr = 128 >> kl;
-            const int nt = (desc[walk_item].rows + tr - 1) / tr;
+            // an item wider than the stages were sized for has no tiles: it is skipped, never copied
+            const int nt = desc[walk_item].cols > geo.max_cols ? 0 : (desc[walk_item].rows + tr - 1) / tr;
             if (gt < walk_base + nt) {
                 t.item = walk_item;
                 t.row0 = (gt - walk_base) * tr;
@@ -265,13 +267,10 @@ int gemv_batch_mma_launch(const spb_gemv_item* d_items, int n, int max_rows, int
     BmGeom geo{};
     geo.x_off = static_cast<int>((slab + 15) & ~static_cast<size_t>(15));
     geo.stage_bytes = geo.x_off + max_cols;
+    geo.max_cols = max_cols;
     const size_t smem = 2 * static_cast<size_t>(geo.stage_bytes);
     if (smem > 200 * 1024) return fail(SPB_E_UNSUPPORTED, "%s: %d columns need more shared memory than a block may take", name, max_cols);
-    cudaError_t err = cudaFuncSetAttribute(gemv_batch_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (err != cudaSuccess) {
-        cudaGetLastError();
-        return fail(SPB_E_CUDA, "%s: %s", name, cudaGetErrorString(err));
-    }
+    if (int rc = ensure_dynamic_smem(name, gemv_batch_mma_kernel, smem)) return rc;
     const size_t per_block = smem + 16 * 1024;  // + static shared memory (table, descriptors) and the reserve
     int per_sm = static_cast<int>((227 * 1024) / per_block);
     per_sm = per_sm < 1 ? 1 : per_sm > 3 ? 3 : per_sm;
@@ -285,3 +284,35 @@ int gemv_batch_mma_launch(const spb_gemv_item* d_items, int n, int max_rows, int
 }
 
 }  // namespace spb
+
+using namespace spb;
+
+extern "C" int spb_gemv_batch_check(const spb_gemv_item* h_items, int n) {
+    if (n < 0 || (n > 0 && !h_items)) return fail(SPB_E_INVALID, "spb_gemv_batch_check: bad list");
+    for (int i = 0; i < n; ++i) {
+        const spb_gemv_item& I = h_items[i];
+        auto al = [](const void* p, size_t k) { return (reinterpret_cast<uintptr_t>(p) & (k - 1)) == 0; };
+        if (I.rows <= 0 || I.cols <= 0 || I.cols % 256 != 0 || I.cols > 32768)
+            return fail(SPB_E_UNSUPPORTED, "item %d: %dx%d (cols must be a multiple of 256, at most 32768)", i, I.rows,
+                        I.cols);
+        if (!I.meta || !I.values || !I.x || !I.y) return fail(SPB_E_INVALID, "item %d: null pointer", i);
+        if (I.meta_row_stride < I.cols / 32 || I.values_row_stride < I.cols / 64 || I.meta_row_stride % 4 ||
+            I.values_row_stride % 4)
+            return fail(SPB_E_UNSUPPORTED, "item %d: row strides must cover a row and be multiples of 4 words", i);
+        if (!al(I.meta, 16) || !al(I.values, 16) || !al(I.x, 16) || !al(I.y, 4))
+            return fail(SPB_E_UNSUPPORTED, "item %d: meta, values and x must be 16-byte aligned", i);
+    }
+    return SPB_OK;
+}
+
+extern "C" int spb_sparse_ternary_gemv_batch(const spb_gemv_item* d_items, int n, int max_rows, int max_cols,
+                                             void* stream) {
+    const char* name = "spb_sparse_ternary_gemv_batch";
+    if (n < 0 || max_rows < 0 || max_cols < 0) return fail(SPB_E_INVALID, "%s: negative size", name);
+    if (n == 0 || max_rows == 0 || max_cols == 0) return SPB_OK;
+    if (!d_items) return fail(SPB_E_INVALID, "%s: null pointer", name);
+    if (max_cols % 256 != 0 || max_cols > 32768)
+        return fail(SPB_E_UNSUPPORTED, "%s: max_cols=%d (multiple of 256, at most 32768)", name, max_cols);
+    if ((reinterpret_cast<uintptr_t>(d_items) & 15) != 0) return fail(SPB_E_INVALID, "%s: d_items must be 16-byte aligned", name);
+    return gemv_batch_mma_launch(d_items, n, max_rows, max_cols, stream);
+}

@@ -27,8 +27,6 @@
 // Tried and dropped (slower): a form in which a warp keeps the x slices of four steps in registers and
 // walks over the row blocks (fewer shared-memory reads, but thin warps); a two-deep software pipeline
 // of the step loop; cp.async.bulk for the slab.  What pays is long step ranges per warp.
-#include <cstdlib>
-
 #include "spb_common.cuh"
 
 namespace spb {
@@ -62,25 +60,6 @@ struct GmArgs {
     int mpitch;     // shared-memory row pitch of the bitmap words, in words (an odd multiple of 4)
     int vpitch;     // same for the sign words
 };
-
-// Development aid, compiled out unless SPB_GT_TRACE is defined: per-block stamps of the phases
-// (slot = launch id taken from gamma, block index; entries 0 and 15 globaltimer, the rest clock64).
-#ifdef SPB_GT_TRACE
-__device__ long long g_gm_trace[4 * 512 * 16];
-__device__ __forceinline__ unsigned long long gm_globaltimer() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define GM_STAMP(k)                                                                                        \
-    do {                                                                                                   \
-        if (threadIdx.x == 0)                                                                              \
-            g_gm_trace[((static_cast<int>(a.gamma) & 3) * 512 + blockIdx.x % 512) * 16 + (k)] =            \
-                ((k) == 0 || (k) == 15) ? static_cast<long long>(gm_globaltimer()) : clock64();            \
-    } while (0)
-#else
-#define GM_STAMP(k)
-#endif
 
 // Eight bitmaps (two of four bits set each) -> eight index pairs {low index | high index << 2}.
 //   low  = first set bit:  bit0 = ~b0 & b1,  bit1 = ~b0 & ~b1
@@ -120,9 +99,6 @@ __global__ void __launch_bounds__(kGmThreads, SPB_GEMV_MMA_MIN_BLOCKS) gemv_mmas
     const int row0 = blockIdx.x * nrows_blk;
     const int valid = min(nrows_blk, a.rows - row0);  // rows of this block inside the matrix
     const uint32_t mbytes = static_cast<uint32_t>(a.cols >> 3), vbytes = static_cast<uint32_t>(a.cols >> 4);
-
-    GM_STAMP(0);
-    GM_STAMP(1);
     // The raw slab: 16-byte asynchronous copies, a warp per row (bitmap chunks first, then sign chunks), so
     // that a row's bytes are fetched by consecutive lanes.
     {
@@ -143,7 +119,6 @@ __global__ void __launch_bounds__(kGmThreads, SPB_GEMV_MMA_MIN_BLOCKS) gemv_mmas
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
-    GM_STAMP(3);
     // sign table under the copy latency: entry (nibble n, lane l) at n * 128 + l * 4, byte b = -1 if bit b of n
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
@@ -170,12 +145,10 @@ __global__ void __launch_bounds__(kGmThreads, SPB_GEMV_MMA_MIN_BLOCKS) gemv_mmas
 
     // ---- after the dependency: x, permuted so that a lane's four B registers of a step are 16 contiguous bytes:
     //      xs[step][tig][j][0..3] = x[64 step + 16 j + 4 tig + 0..3] -------------------------------------------
-    GM_STAMP(4);
     grid_dep_wait();
     // The successor on the stream is let in only now: it then loads and waits while this grid computes, and
     // no deeper queue of waiting grids builds up (measured: a deep queue slows a long chain of launches).
     grid_dep_launch();
-    GM_STAMP(5);
     for (int q = tid; q < (a.cols >> 4); q += kGmThreads) {
         const uint4 xv = __ldg(reinterpret_cast<const uint4*>(a.x) + q);
         const uint32_t s = static_cast<uint32_t>(q) >> 2, j = static_cast<uint32_t>(q) & 3u;
@@ -185,11 +158,9 @@ __global__ void __launch_bounds__(kGmThreads, SPB_GEMV_MMA_MIN_BLOCKS) gemv_mmas
         asm volatile("st.shared.u32 [%0], %1;" ::"r"(d + 32u), "r"(xv.z) : "memory");
         asm volatile("st.shared.u32 [%0], %1;" ::"r"(d + 48u), "r"(xv.w) : "memory");
     }
-    GM_STAMP(6);
     // the weights have landed, the table and x are visible
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
-    GM_STAMP(7);
     // One step = 64 columns of 16 rows.  Metadata register of lane (g, tig): the index pairs of bitmap word
     // 2 s + (tig >> 1) of row g + 8 (tig & 1).  `off` is a compile-time byte offset from the running addresses.
     int c0 = 0, c1 = 0, c2 = 0, c3 = 0;
@@ -231,14 +202,12 @@ __global__ void __launch_bounds__(kGmThreads, SPB_GEMV_MMA_MIN_BLOCKS) gemv_mmas
         step(gm_lds(v0_p), gm_lds(v0_p + v_half), 0u, 0u);
         advance(1u);
     }
-    GM_STAMP(8);
     // column 0 of the tile: lanes with tig == 0 hold rows g (c0) and g + 8 (c2)
     if (tig == 0) {
         red[warp_u * 16 + g] = c0;
         red[warp_u * 16 + g + 8] = c2;
     }
     __syncthreads();
-    GM_STAMP(9);
     if (tid < nrows_blk && tid < valid) {
         const int rblk = tid >> 4, r = tid & 15;
         int acc = 0;
@@ -256,7 +225,6 @@ __global__ void __launch_bounds__(kGmThreads, SPB_GEMV_MMA_MIN_BLOCKS) gemv_mmas
             }
         }
     }
-    GM_STAMP(15);
 }
 
 // Whether the layout can take this kernel: whole 16-byte sign rows (cols % 256 == 0), 16-byte aligned
@@ -280,15 +248,10 @@ int gemv_mmasp_launch(const char* name, const uint32_t* meta, const uint32_t* va
     a.steps = cols / 64;
     // Warps per row block: long step ranges per warp amortise a warp's fixed cost (measured: about 20 steps
     // per warp is best at 6912 x 2560), but a small matrix still has to give every SM a few warps.
-    static const int ks_env = [] {
-        const char* e = getenv("SPB_GEMV_MMA_KS");
-        return e ? atoi(e) : 0;
-    }();
     const int row_blocks = (rows + 15) / 16;
     a.ks = 8;
     while (a.ks > 1 && a.steps / a.ks < 16) a.ks >>= 1;
     while (a.ks < 8 && row_blocks * a.ks < 2 * sm_count() && a.steps / (2 * a.ks) >= 8) a.ks <<= 1;
-    if (ks_env == 1 || ks_env == 2 || ks_env == 4 || ks_env == 8) a.ks = ks_env;
     while (a.ks > a.steps) a.ks >>= 1;
     a.rb = kGmWarps / a.ks;
     a.ks_log2 = a.ks == 8 ? 3 : a.ks == 4 ? 2 : a.ks == 2 ? 1 : 0;
@@ -297,19 +260,10 @@ int gemv_mmasp_launch(const char* name, const uint32_t* meta, const uint32_t* va
     a.vpitch = pitch(cols / 64);
     const size_t smem = static_cast<size_t>(cols) +
                         static_cast<size_t>(16 * a.rb) * (a.mpitch + a.vpitch) * 4;
-    cudaError_t err = cudaFuncSetAttribute(gemv_mmasp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (err != cudaSuccess) {
-        cudaGetLastError();
-        return fail(SPB_E_CUDA, "%s: %s", name, cudaGetErrorString(err));
-    }
+    if (int rc = ensure_dynamic_smem(name, gemv_mmasp_kernel, smem)) return rc;
     const unsigned blocks = static_cast<unsigned>((rows + 16 * a.rb - 1) / (16 * a.rb));
     return launch(name, gemv_mmasp_kernel, dim3(blocks), dim3(kGmThreads), smem, stream, a);
 }
 
-#ifdef SPB_GT_TRACE
-extern "C" int spb_debug_gm_trace(long long* out) {
-    return cudaMemcpyFromSymbol(out, g_gm_trace, sizeof(long long) * 4 * 512 * 16) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 }  // namespace spb

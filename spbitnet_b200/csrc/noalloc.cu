@@ -27,10 +27,13 @@ std::mutex g_scratch_mutex;
 int scratch_address_for_current_device(float** out) {
     int dev = -1;
     cudaError_t err = cudaGetDevice(&dev);
-    if (err != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    if (err != cudaSuccess) {
         cudaGetLastError();
         return spb::fail(SPB_E_CUDA, "spb_decode_attention_noalloc: cudaGetDevice: %s", cudaGetErrorString(err));
     }
+    if (dev < 0 || dev >= kMaxDevices)
+        return spb::fail(SPB_E_UNSUPPORTED, "spb_decode_attention_noalloc: device %d beyond the %d slots of the address table",
+                         dev, kMaxDevices);
     std::lock_guard<std::mutex> lock(g_scratch_mutex);
     if (!g_scratch_address[dev]) {
         float* p = nullptr;

@@ -23,6 +23,24 @@ bool pdl_enabled();
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// Raises a kernel's dynamic shared-memory limit to at least `bytes` on the current device.  The attribute is
+// per (kernel, device) and only ever grows here, so the largest value set so far is remembered and the runtime
+// is called only when a launch needs more.  Returns SPB_OK or SPB_E_CUDA (message recorded under `name`).
+int ensure_dynamic_smem_impl(const char* name, const void* kernel, size_t bytes);
+template <typename... KArgs>
+int ensure_dynamic_smem(const char* name, void (*kernel)(KArgs...), size_t bytes) {
+    if (bytes <= 48 * 1024) return SPB_OK;
+    return ensure_dynamic_smem_impl(name, reinterpret_cast<const void*>(kernel), bytes);
+}
+
+// Counter of bounded device-side waits that ran out (tensor-core kernels).  It lives in pinned host memory
+// that every GPU of the process can reach (allocated portable and mapped on first use), so a kernel bumps it
+// with a system-scope atomic through the pointer it is given, and the host reads it after a synchronisation
+// without another CUDA call.  nullptr when the allocation failed (kernels then skip the count).
+int* timeout_counter();
+// Current value of the counter (0 when it could not be allocated).
+int timeouts_now();
+
 // Launches `kernel` on `stream`.  With PDL enabled the launch carries
 // cudaLaunchAttributeProgrammaticStreamSerialization, so the grid may start
 // while its predecessor on the stream is still draining; every kernel in this

@@ -27,18 +27,14 @@ class DeviceModel:
         head = model.get("lm_head")  # absent or None: tied to the embedding table
         self.lm_head = None if head is None else torch.from_numpy(head.view(np.int16)).to(dev).view(torch.float16)
         self.layers = []
-        cache = {}
-        for layer in model["layers"]:
-            key = id(layer)
-            if key not in cache or True:
-                lin = []
-                for t in layer["linear"]:
-                    meta = torch.from_numpy(t["meta"].view(np.int32)).to(dev)
-                    values = torch.from_numpy(t["values"].view(np.int32)).to(dev)
-                    lin.append(dict(t, d_meta=meta, d_values=values))
-                norms = [None if n is None else torch.from_numpy(n).to(dev) for n in layer["norm"]]
-                cache[key] = {"linear": lin, "norm": norms}
-            self.layers.append(cache[key])
+        for layer in model["layers"]:  # every layer gets its own device copy, also when the host arrays are shared
+            lin = []
+            for t in layer["linear"]:
+                meta = torch.from_numpy(t["meta"].view(np.int32)).to(dev)
+                values = torch.from_numpy(t["values"].view(np.int32)).to(dev)
+                lin.append(dict(t, d_meta=meta, d_values=values))
+            norms = [None if n is None else torch.from_numpy(n).to(dev) for n in layer["norm"]]
+            self.layers.append({"linear": lin, "norm": norms})
 
     def sparse_bytes(self) -> int:
         return sum(t["d_meta"].numel() * 4 + t["d_values"].numel() * 4 for L in self.layers for t in L["linear"])

@@ -46,6 +46,12 @@ def gemm_tc_timeouts() -> int:
     return load().spb_gemm_tc_timeouts()
 
 
+def debug_bounded_wait_selftest(limit_cycles: int = 4000, stream=None) -> int:
+    """Runs the library's bounded-wait self-test and returns its status code (SPB_E_TIMEOUT is the
+    expected answer: the wait ran out, was counted, and the block returned)."""
+    return load().spb_debug_bounded_wait_selftest(int(limit_cycles), _stream(stream))
+
+
 # ---- sparse_ternary_kernels.h ---------------------------------------------------------
 
 def sparse_ternary_unpack_gpu(meta, values, out, rows, cols, meta_row_stride, values_row_stride, stream=None):

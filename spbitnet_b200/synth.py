@@ -146,3 +146,94 @@ def random_model(cfg: dict, seed: int = 0, layers: int | None = None, shared_lay
             layer["norm"].append((1.0 + 0.02 * rng.standard_normal(n)).astype(np.float32))
         model["layers"].append(layer)
     return model
+
+
+# ---- the same distributions generated on the GPU (torch) ------------------------------------------
+# A 2B-4T-shape model has 210 distinct matrices and a 70B-shape layer 1.2e9 weights; numpy needs seconds per
+# matrix, the GPU milliseconds.  Same draw rules as ternary_weights_and_mask / pack_numpy, with torch's
+# generator (so the bits differ from the numpy ones for the same seed, the distribution does not).
+
+def device_sparse_matrix(rows: int, cols: int, seed, device=None, chunk_rows: int = 2048):
+    """(meta, values) int32 CUDA tensors [rows, cols/32] and [rows, cols/64] of one synthetic matrix.
+    cols must be a multiple of 64.  Generated `chunk_rows` rows at a time to bound temporaries."""
+    import torch
+    if cols % 64:
+        raise ValueError("device_sparse_matrix: cols must be a multiple of 64")
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(int(np.random.SeedSequence(seed).generate_state(1, np.uint64)[0] >> 1))
+    g = cols // 4
+    meta = torch.empty((rows, cols // 32), dtype=torch.int32, device=dev)
+    values = torch.empty((rows, cols // 64), dtype=torch.int32, device=dev)
+    idx = torch.arange(4, device=dev, dtype=torch.float32)
+    sh4 = torch.arange(4, device=dev, dtype=torch.int64)
+    for r0 in range(0, rows, chunk_rows):
+        n = min(chunk_rows, rows - r0)
+        u = torch.rand((n, g, 4), generator=gen, device=dev)
+        neg = u >= 0.71
+        nz = u >= 0.42
+        keys = torch.rand((n, g, 4), generator=gen, device=dev)
+        order_key = torch.where(nz, keys, 2.0 + idx)           # non-zeros first (random), then zeros by index
+        kept = torch.argsort(order_key, dim=-1, stable=True)[..., :2]
+        mask = torch.zeros((n, g, 4), dtype=torch.bool, device=dev)
+        mask.scatter_(-1, kept, True)
+        bitmap = (mask.to(torch.int64) << sh4).sum(-1)                       # [n, g], 4 bits
+        rank = torch.cumsum(mask.to(torch.int64), -1) - 1
+        sneg = (neg & mask).to(torch.int64) << torch.where(mask, rank, torch.zeros_like(rank))
+        signs = sneg.sum(-1)                                                  # [n, g], 2 bits
+        m = (bitmap.view(n, g // 8, 8) << (4 * torch.arange(8, device=dev, dtype=torch.int64))).sum(-1)
+        v = (signs.view(n, g // 16, 16) << (2 * torch.arange(16, device=dev, dtype=torch.int64))).sum(-1)
+        meta[r0:r0 + n] = m.to(torch.int32)      # int64 -> int32 keeps the low 32 bits
+        values[r0:r0 + n] = v.to(torch.int32)
+    return meta, values
+
+
+class DeviceRandomModel:
+    """Random-init model generated on the current CUDA device, in the attribute layout of
+    spbitnet_b200.engine.DeviceModel (config, device, embed, final_norm, lm_head, layers).  Every matrix of
+    every layer has its own seed (seed, layer, matrix); with repeat_layer=True layer 0 is generated once and
+    every further layer is a separate device COPY of it (for shapes where only throughput matters: the HBM
+    traffic is still one distinct copy per layer).  Distributions as in random_model()."""
+
+    def __init__(self, cfg: dict, seed: int = 0, repeat_layer: bool = False, device=None):
+        import torch
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.config, self.device = dict(cfg), dev
+        H, I, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"]
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(1000003 * seed + 17)
+        self.embed = (torch.randn((cfg["vocab_size"], H), generator=gen, device=dev) * 0.02).to(torch.float16)
+        self.final_norm = 1.0 + 0.02 * torch.randn(H, generator=gen, device=dev)
+        self.lm_head = None
+        self.layers = []
+        host = np.random.default_rng([seed, 99])
+        for l in range(L):
+            if repeat_layer and l > 0:
+                first = self.layers[0]
+                lin = [dict(t, d_meta=t["d_meta"].clone(), d_values=t["d_values"].clone()) for t in first["linear"]]
+                self.layers.append({"linear": lin, "norm": [n.clone() for n in first["norm"]]})
+                continue
+            lin = []
+            for i, (r, c) in enumerate(linear_shapes(cfg)):
+                meta, values = device_sparse_matrix(r, c, [seed, l, i], dev)
+                gamma = np.float32(host.uniform(0.5, 2.0) / np.sqrt(c))
+                lin.append({"d_meta": meta, "d_values": values, "gamma": gamma, "rows": r, "cols": c,
+                            "meta_stride": meta.shape[1], "values_stride": values.shape[1]})
+            norms = [1.0 + 0.02 * torch.randn(n, generator=gen, device=dev) for n in (H, H, H, I)]
+            self.layers.append({"linear": lin, "norm": norms})
+
+    def sparse_bytes(self) -> int:
+        return sum(t["d_meta"].numel() * 4 + t["d_values"].numel() * 4 for L in self.layers for t in L["linear"])
+
+    def to_host(self) -> dict:
+        """The model as host numpy arrays in the random_model() layout (what the CPU oracle takes)."""
+        def u32(t):
+            return np.ascontiguousarray(t.cpu().numpy()).view(np.uint32)
+        layers = []
+        for L in self.layers:
+            lin = [{"meta": u32(t["d_meta"]), "values": u32(t["d_values"]), "gamma": t["gamma"], "rows": t["rows"],
+                    "cols": t["cols"], "meta_stride": t["meta_stride"], "values_stride": t["values_stride"]}
+                   for t in L["linear"]]
+            layers.append({"linear": lin, "norm": [n.cpu().numpy() for n in L["norm"]]})
+        return {"config": dict(self.config), "layers": layers, "final_norm": self.final_norm.cpu().numpy(),
+                "embed": self.embed.view(self.embed.dtype).cpu().numpy()}

@@ -89,12 +89,11 @@ def test_unfused_path_gives_the_same_tokens(monkeypatch):
 def test_full_2b4t_shape_against_the_reference_cuda_kernels():
     """The 30-layer 2B-4T-shape model, 16-token prompt + 64 greedy steps, against the reference's
     own kernels on the same GPU: logits within 1e-2 max-abs, identical tokens."""
-    import ref_cuda_engine
+    from oracle import ref_cuda_engine
     if not ref_cuda_engine.available():
         pytest.skip("oracle/_ref/libspb_refcuda.so not built")
     cfg = dict(synth.BITNET_2B, max_position_embeddings=128)
-    model = synth.random_model(cfg, seed=2, shared_layer=True)
-    dm = DeviceModel(model)
+    dm = synth.DeviceRandomModel(cfg, seed=2)  # all 210 matrices distinct, generated on the GPU
     ours, ref = InferenceEngine(dm), ref_cuda_engine.RefCudaEngine(dm)
     prompt = np.random.default_rng(4).integers(0, cfg["vocab_size"], 16).astype(np.int32)
     for t in prompt[:-1]:

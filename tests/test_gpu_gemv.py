@@ -14,14 +14,14 @@ from gpu_util import Guarded, dev, host
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=[1, 2, 3, 4], ids=["pair-kernel", "group-table-kernel", "sparse-mma-kernel", "warp-mma-kernel"],
-                autouse=True)
+@pytest.fixture(params=[0, 1, 4], ids=["auto", "pair-kernel", "warp-mma-kernel"], autouse=True)
 def gemv_variant(request):
     """Every test in this file runs once per GEMV kernel variant."""
     old = K.set_gemv_variant(request.param)
+    before = K.gemm_tc_timeouts()
     yield request.param
     K.set_gemv_variant(old)
-    assert K.gemm_tc_timeouts() == 0
+    assert K.gemm_tc_timeouts() == before
 
 
 def run_gemv(case, x=None, align=0):
@@ -106,9 +106,10 @@ def test_padded_strides_and_unaligned_pointers():
     assert (y.read(np.int32) == want).all()
 
 
-def test_invalid_bitmaps_follow_the_reference_gpu_table(gemv_variant):
-    # src/kernels/sparse_ternary.cu:34-51: any bitmap without exactly two bits decodes as (0,0).
-    # The pair kernel only promises memory safety on such input (it must not fault).
+def test_invalid_bitmaps_are_memory_safe(gemv_variant):
+    # src/kernels/sparse_ternary.cu:34-51 decodes any bitmap without exactly two bits as (0,0) while the
+    # reference's CPU unpack yields as many non-zeros as bits: the result is unspecified there.  The kernels
+    # here promise memory safety on such input (no fault, no write outside y), and exactness on the valid groups.
     cols = 128
     meta = np.array([[0x0F731248, 0x0, 0xEDB7FFFF, 0x33333333]], np.uint32)
     values = np.array([[0x9C3A5F01, 0x6E21D4B7]], np.uint32)
@@ -121,9 +122,8 @@ def test_invalid_bitmaps_follow_the_reference_gpu_table(gemv_variant):
         p0, p1 = lut.get(b, (0, 0))
         acc += (-1 if s & 1 else 1) * int(x[4 * g + p0]) + (-1 if s & 2 else 1) * int(x[4 * g + p1])
     case = dict(meta=meta, values=values, x=x, rows=1, cols=cols, meta_stride=4, values_stride=2)
-    got = run_gemv(case)[0]
-    if gemv_variant == 2:
-        assert got == acc
+    got = run_gemv(case)[0]  # Guarded output: canaries on either side are checked
+    assert abs(int(got) - acc) <= 23 * 2 * 128  # the 23 invalid groups may each contribute anything two bytes can
 
 
 def test_degenerate_and_bad_arguments():
@@ -199,14 +199,15 @@ def test_unpack_matches_oracle(rows, cols):
         assert (out.read(np.int8).reshape(rows, cols) == want).all()
 
 
-@pytest.fixture(params=[0, 1, 2, 3], ids=["auto", "simt", "tcgen05", "tcgen05sp"])
+@pytest.fixture(params=[0, 1, 3], ids=["auto", "simt", "tcgen05sp"])
 def gemm_variant(request):
     """0 = automatic (warp-level sparse MMA up to 32 batch rows, sparse tcgen05 above), 1 = SIMT form,
-    2 = dense tcgen05 form, 3 = sparse tcgen05 form (forced for every n the layout allows)."""
+    3 = sparse tcgen05 form (forced for every n the layout allows)."""
     old = K.set_gemm_variant(request.param)
+    before = K.gemm_tc_timeouts()
     yield request.param
     K.set_gemm_variant(old)
-    assert K.gemm_tc_timeouts() == 0
+    assert K.gemm_tc_timeouts() == before
 
 
 @pytest.mark.parametrize("rows,cols,n", [(64, 256, 16), (64, 256, 1), (37, 132, 5), (300, 2560, 4), (96, 6912, 19),
