@@ -239,6 +239,13 @@ def run_ours(args):
         if world > 1:
             dist.destroy_process_group()
         return
+    if args.only_sharded:
+        res = bench_sharded(args, rank, world, dist if world > 1 else None)
+        if rank == 0:
+            print(json.dumps({"metric": "sharded_decode_tok_s_70b_shape", "sharded": res, "n_gpus": world}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
     if args.only_prefill:
         if rank == 0:
             print(json.dumps({"metric": "prefill_tok_s_2b4t_shape", "prefill": bench_prefill(args), "n_gpus": world}))
@@ -523,6 +530,14 @@ def run_ours(args):
             decode["replicas"] = {"n": world, "tok_s_total": sum(per_rank), "tok_s_per_rank": per_rank,
                                   "what": "independent greedy-decode replicas, one per GPU, no communication"}
 
+    # ---- the row-sharded 70B-shape decode on all ranks of this run ---------------------------------------
+    sharded = None
+    if not args.no_sharded:
+        try:
+            sharded = bench_sharded(args, rank, world, dist)
+        except Exception as exc:
+            sharded = {"error": repr(exc)[:300]}
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -560,6 +575,7 @@ def run_ours(args):
             "sweep": sweep,
             "gemm": gemm,
             "decode": decode,
+            "sharded": sharded,
         }
         print(json.dumps(line))
     if world > 1:
@@ -824,6 +840,119 @@ def bench_cpu_forward(dm):
             "sample": "one decode token at position 1 after one warm-up token, full model"}
 
 
+def bench_sharded(args, rank, world, dist):
+    """The Llama-70B-shaped ternary model (hidden 8192, 80 layers, 64 / 8 heads, FFN 28672, vocab 128256) row-sharded
+    over the `world` GPUs of this run through spb_shard_engine (slices exchanged by peer stores + flags inside the
+    captured step, no library collective on the data path): decode tok/s at batch 1 and batch 64 after a 512-token
+    random-id prompt, and the fraction of the measured HBM bandwidth every GPU reaches on its own bytes.  With more
+    than one rank a small model is first decoded sharded and on one rank: the logits must be bit-identical and the
+    tokens the CPU oracle's, else nothing is timed."""
+    import torch
+    from spbitnet_b200 import synth
+    from spbitnet_b200.shard_engine import ShardEngine
+    peak, _ = measured_peaks()
+    out = {"world": world}
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- parity gate -------------------------------------------------------------------------------------
+    if world > 1:
+        small = dict(hidden_size=1024, num_hidden_layers=2, num_attention_heads=16, num_key_value_heads=8, head_dim=64,
+                     intermediate_size=2048, vocab_size=4001, max_position_embeddings=64, rms_norm_eps=1e-5,
+                     rope_theta=500000.0)
+        dm = synth.DeviceRandomModel(small, seed=9)
+        verdicts = []
+        for batch in (1, 5):
+            sharded, one = ShardEngine(dm, rank=rank, world=world, batch=batch), ShardEngine(dm, batch=batch)
+            prompts = np.random.default_rng(7).integers(0, small["vocab_size"], (4, batch)).astype(np.int32)
+            same = True
+            for step in range(4):
+                sharded.step(prompts[step])
+                one.step(prompts[step])
+                a, b = sharded.logits(), one.logits()
+                same = same and bool((a.view(np.uint32) == b.view(np.uint32)).all())
+            sharded.reset()
+            one.reset()
+            got = sharded.generate(prompts, 8)
+            same = same and bool((got == one.generate(prompts, 8)).all())
+            if rank == 0 and batch == 1:
+                import oracle
+                want, _ = oracle.Engine(dm.to_host()).generate(prompts[:, 0], 8)
+                same = same and bool((got[:, 0] == want).all())
+            verdicts.append(same)
+            barrier()
+            sharded.close()
+            one.close()
+        flag = torch.tensor([1.0 if all(verdicts) else 0.0], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        out["parity"] = "bit-identical" if flag.item() == 1.0 else "MISMATCH"
+        out["parity_what"] = ("2-layer model (hidden 1024, 8 KV heads, vocab 4001), batch 1 and 5: logits of 4 steps equal "
+                              "bit for bit to the same engine with one rank, 8 greedy tokens equal, batch-1 tokens equal to "
+                              "the CPU oracle's")
+        del dm
+        if out["parity"] != "bit-identical":
+            return out
+    else:
+        out["parity"] = "one rank (nothing to compare)"
+
+    # ---- the 70B-shaped model: layer 0 drawn on the GPU, every further layer a separate copy of its slices -----
+    cfg = dict(synth.LLAMA_70B_SHAPE, max_position_embeddings=args.shard_prompt + args.shard_tokens + 16)
+    if args.shard_layers > 0:
+        cfg["num_hidden_layers"] = args.shard_layers
+    L = cfg["num_hidden_layers"]
+    full = synth.DeviceRandomModel(dict(cfg, num_hidden_layers=1), seed=5)
+    full.config = cfg
+    full.layers = [full.layers[0]] * L  # ShardEngine clones the rank's slices layer by layer
+    results = {}
+    for batch in (1, 64):
+        eng = ShardEngine(full, rank=rank, world=world, batch=batch)
+        rng = np.random.default_rng(11)
+        prompts = rng.integers(0, cfg["vocab_size"], (args.shard_prompt, batch)).astype(np.int32)
+        warm = eng.generate(prompts[:4], 2)  # graph capture, page-in
+        eng.reset()
+        barrier()
+        t0 = time.perf_counter()
+        first = eng.generate(prompts, 1)  # the prompt, step by step as the reference feeds it; one generated token
+        t_prompt = max_over_ranks(time.perf_counter() - t0)
+        barrier()
+        t0 = time.perf_counter()
+        toks = eng.generate(first[-1:], args.shard_tokens)
+        dt = max_over_ranks(time.perf_counter() - t0)
+        step_s = dt / args.shard_tokens
+        kv_bytes = 2 * L * batch * (cfg["num_key_value_heads"] // world if world <= cfg["num_key_value_heads"] else 1) * \
+            (args.shard_prompt + args.shard_tokens // 2) * cfg["head_dim"] * 2
+        my_bytes = eng.weight_bytes() + kv_bytes
+        results[f"batch{batch}"] = {
+            "tok_s": batch * args.shard_tokens / dt, "ms_per_step": 1e3 * step_s,
+            "prompt_s": t_prompt, "prompt_tok_s": batch * (args.shard_prompt - 1) / t_prompt,
+            "per_gpu_bytes_per_step": int(my_bytes), "per_gpu_hbm_gbs": my_bytes / step_s / 1e9,
+            "per_gpu_hbm_frac_measured": my_bytes / step_s / 1e9 / peak,
+            "exchanges_per_step": 4 * L + 1, "tokens_checksum": int(np.asarray(toks, np.int64).sum() % 1000003)}
+        eng.close()
+        del eng
+        torch.cuda.empty_cache()
+    out.update(results)
+    out["model"] = {"shape": "Llama-70B-shaped ternary 2:4", "layers": L, "hidden": cfg["hidden_size"],
+                    "ffn": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "prompt": args.shard_prompt,
+                    "generated": args.shard_tokens,
+                    "weights": "one layer drawn at random, uploaded as a separate copy per layer (the HBM traffic is that "
+                               "of distinct layers)"}
+    out["what"] = ("row-sharded decode: every ternary matrix and the LM head split by output rows over the ranks, slices "
+                   "exchanged inside the captured step by a kernel that stores them into every peer's buffer over NVLink "
+                   "and waits (bounded) for the peers' flags; wall clock around generate(), max over ranks")
+    return out
+
+
 def bench_prefill(args):
     """The prompt as one batch through a random-init 2B-4T-shape model (engine.prefill), wall clock per call."""
     import torch
@@ -865,6 +994,11 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-gemm", action="store_true")
+    ap.add_argument("--no-sharded", action="store_true")
+    ap.add_argument("--only-sharded", action="store_true", help="only the row-sharded 70B-shape decode")
+    ap.add_argument("--shard-layers", type=int, default=0, help="override the layer count of the sharded model")
+    ap.add_argument("--shard-prompt", type=int, default=512)
+    ap.add_argument("--shard-tokens", type=int, default=48)
     ap.add_argument("--only-gemm", action="store_true", help="only the batched-product section (profiling aid)")
     ap.add_argument("--only-decode", action="store_true", help="skip the GEMV sections (profiling aid)")
     ap.add_argument("--only-prefill", action="store_true", help="only the batched-prefill timing (profiling aid)")

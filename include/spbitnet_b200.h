@@ -142,6 +142,10 @@ int spb_sparse_bitlinear_gemm(const uint32_t* meta, const uint32_t* values, cons
  * the layout allows neither; 1 = SIMT form, 3 = tcgen05 sparse form for any n, 4 = warp-level sparse MMA
  * form where it applies.  Other values behave like 0.  Results are identical.  Returns the previous setting. */
 int spb_set_gemm_variant(int variant);
+/* Weight rows per block of the tcgen05 sparse form: 0 (default) = automatic, 1 = 128 rows, 2 = 256 rows (two
+ * accumulators on one activation tile; needs more than 128 batch rows).  Results are identical; a testing and
+ * measurement aid.  Returns the previous setting. */
+int spb_set_gemm_row_halves(int halves);
 /* Number of bounded device-side waits of the tcgen05 product that ran out since the library was loaded, over all
  * GPUs of the process; 0 in a healthy run, -1 if the counter cannot be read.  Synchronises the current device.
  * A block whose wait ran out skips its epilogue and frees its tensor memory, so the outputs of that call are
@@ -324,6 +328,85 @@ int spb_engine_prefill(spb_engine* e, const int* tokens, int n, const float** d_
  * the same chunk when it is set, else 1024).  Returns the previous
  * setting, or a negative status. */
 int spb_engine_set_prefill_chunk(spb_engine* e, int chunk);
+
+/* ---- model directory loader: include/spbitnet/model.h:88-145, src/model.cu:179-311 ---------------------- */
+
+typedef struct spb_model spb_model;
+/* Model::load: reads <dir>/config.json, <dir>/manifest.json and the weight files into ONE device allocation on the
+ * current device (sizes checked against shapes and strides, sparse bitmaps validated).  NULL on failure
+ * (spb_last_error_string says why).  The reference throws std::runtime_error instead. */
+spb_model* spb_model_load(const char* model_dir);
+void spb_model_destroy(spb_model* m);
+/* ModelConfig (model.h:22-38): the fields of spb_model_config plus bos_token_id / eos_token_id (either may be NULL). */
+int spb_model_get_config(const spb_model* m, spb_model_config* cfg, int* bos_token_id, int* eos_token_id);
+size_t spb_model_device_bytes(const spb_model* m);
+/* Attaches every tensor of the model to an engine created with the model's config (the engine borrows them). */
+int spb_model_attach(const spb_model* m, spb_engine* e);
+
+/* ---- tokenizer: include/spbitnet/tokenizer.h, src/tokenizer.cpp (host only) --------------------------- */
+
+typedef struct spb_tokenizer spb_tokenizer;
+/* Tokenizer::load (tokenizer.h:20, src/tokenizer.cpp:287-339): a HuggingFace tokenizer.json (byte-level BPE). */
+spb_tokenizer* spb_tokenizer_load(const char* tokenizer_json_path);
+void spb_tokenizer_destroy(spb_tokenizer* t);
+int spb_tokenizer_vocab_size(const spb_tokenizer* t);
+/* Tokenizer::encode (tokenizer.h:23, src/tokenizer.cpp:341-357): no BOS / EOS added.  Writes at most `capacity`
+ * ids and returns the number the text encodes to (call with capacity 0 to size the buffer), or a negative status. */
+int spb_tokenizer_encode(const spb_tokenizer* t, const char* text, size_t text_bytes, int* ids, int capacity);
+/* Tokenizer::decode / decode_token (tokenizer.h:26-29, src/tokenizer.cpp:359-374): special tokens and ids outside
+ * the vocabulary are skipped.  Writes at most capacity - 1 bytes and a terminating zero; returns the byte length
+ * of the whole text, or a negative status. */
+int spb_tokenizer_decode(const spb_tokenizer* t, const int* ids, int n, char* out, size_t capacity);
+
+/* ---- row-sharded engine: one rank of a tensor-parallel group, one process per GPU ----------------------
+ * No counterpart in the reference (it is single-GPU).  The decode step of InferenceEngine::forward
+ * (src/inference.cu:123-283) with every matrix split by output rows over `world` ranks and no reduction anywhere,
+ * so every rank's integer accumulators, half outputs and logits are bit-identical to the same step on one rank:
+ * q/k/v by whole KV heads (RoPE, KV cache and attention stay local), o / gate / up / down by rows, the LM head by
+ * vocabulary rows; norms, quantisation and residual adds replicated.  The slices meet through an exchange kernel
+ * that stores them into every rank's exchange buffer over NVLink (peer mappings of one CUDA IPC allocation per
+ * rank) and waits, bounded by time, for the peers' sequence-numbered flags: 4 exchanges per layer + 1 per token.
+ * batch > 1 decodes that many independent sequences in lock step with the batched product.
+ * Set-up per rank: create (current device) -> row_range / set_linear (the rank's row slices) / set_norm /
+ * set_globals -> ipc_handle, all-gather the 64-byte handles by any host channel, set_peers -> a host barrier ->
+ * generate / step (every rank calls with the same arguments).  A rank whose wait for a peer runs out reports
+ * SPB_E_TIMEOUT at its next synchronisation and skips all later waits; the engine must then be recreated. */
+typedef struct spb_shard_engine spb_shard_engine;
+/* world 1..8 (at most num_key_value_heads), batch 1..64; hidden_size, intermediate_size and head_dim multiples of 8. */
+spb_shard_engine* spb_shard_engine_create(const spb_model_config* cfg, int rank, int world, int batch);
+void spb_shard_engine_destroy(spb_shard_engine* e);
+/* Rows [start, stop) of the full matrix that this rank owns.  which: 0 q, 1 k, 2 v, 3 o, 4 gate, 5 up, 6 down,
+ * 7 LM head (vocabulary rows). */
+int spb_shard_engine_row_range(const spb_shard_engine* e, int which, int* start, int* stop);
+/* The rank's row slice of a matrix (SparseLinear, include/spbitnet/model.h:46-60): rows = stop - start. */
+int spb_shard_engine_set_linear(spb_shard_engine* e, int layer, int which, const uint32_t* d_meta, const uint32_t* d_values,
+                                float gamma, int rows, int cols, int meta_stride, int values_stride);
+/* Full norm vectors (replicated).  which as spb_engine_set_norm. */
+int spb_shard_engine_set_norm(spb_shard_engine* e, int layer, int which, const float* d_weight);
+/* d_embed: the full embedding table; d_lm_head_rows: this rank's vocabulary rows of the LM head (of the embedding
+ * table when tied); d_final_norm: full. */
+int spb_shard_engine_set_globals(spb_shard_engine* e, const void* d_embed, const void* d_lm_head_rows, const float* d_final_norm);
+/* 64-byte CUDA IPC handle of this rank's exchange buffer (HOST pointer). */
+int spb_shard_engine_ipc_handle(spb_shard_engine* e, void* handle_out);
+/* handles: world x 64 bytes in rank order (HOST); the entry of this rank is ignored. */
+int spb_shard_engine_set_peers(spb_shard_engine* e, const void* handles);
+/* The same for buffers this GPU can already address (ranks in one process with peer access enabled): world device
+ * pointers to buffers of spb_shard_engine_exchange_bytes bytes, zero-filled; the entry of this rank is ignored. */
+int spb_shard_engine_set_peer_pointers(spb_shard_engine* e, void* const* buffers);
+size_t spb_shard_engine_exchange_bytes(const spb_shard_engine* e);
+/* Bound of every wait for a peer (default 5000 ms). */
+int spb_shard_engine_set_timeout_ms(spb_shard_engine* e, int ms);
+int spb_shard_engine_reset(spb_shard_engine* e);
+int spb_shard_engine_seq_len(const spb_shard_engine* e);
+/* One decode step: tokens[batch] (HOST) enter at the current position; synchronises.  Afterwards the rank's logits
+ * rows are available through spb_shard_engine_copy_logits. */
+int spb_shard_engine_step(spb_shard_engine* e, const int* tokens);
+/* h_logits_rows: batch x (stop - start of which = 7) floats (HOST): this rank's vocabulary rows of the last step. */
+int spb_shard_engine_copy_logits(spb_shard_engine* e, float* h_logits_rows);
+/* The greedy loop of src/main.cpp:266-300 for `batch` sequences: prompt is n_prompt x batch token ids (HOST,
+ * position-major), out_tokens max_tokens x batch.  Feeds prompt[0 .. n_prompt-2], then generates max_tokens tokens
+ * from prompt[n_prompt-1]; no EOS stop.  Returns max_tokens or a negative status. */
+int spb_shard_engine_generate(spb_shard_engine* e, const int* prompt, int n_prompt, int max_tokens, int* out_tokens);
 
 #ifdef __cplusplus
 }

@@ -536,3 +536,55 @@ class DropInEngine:
             self.close()
         except Exception:
             pass
+
+
+_REFTOK = HERE / "_ref" / "libspb_reftok.so"
+
+
+class RefTokenizer:
+    """The reference's own spbitnet::Tokenizer (src/tokenizer.cpp, unmodified) through ref_tokenizer_shim.cpp."""
+
+    def __init__(self, path):
+        self._l = _load(_REFTOK)
+        if self._l is None:
+            raise RuntimeError("oracle/_ref/libspb_reftok.so is not built")
+        l = self._l
+        l.reftok_load.restype = C.c_void_p
+        l.reftok_load.argtypes = [C.c_char_p]
+        l.reftok_destroy.argtypes = [C.c_void_p]
+        l.reftok_vocab_size.argtypes = [C.c_void_p]
+        l.reftok_encode.argtypes = [C.c_void_p, C.c_char_p, C.c_size_t, C.c_void_p, C.c_int]
+        l.reftok_decode.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_size_t]
+        h = l.reftok_load(str(path).encode())
+        if not h:
+            raise RuntimeError(f"reference tokenizer could not load {path}")
+        self._h = C.c_void_p(h)
+
+    @staticmethod
+    def available() -> bool:
+        return _REFTOK.exists()
+
+    @property
+    def vocab_size(self):
+        return self._l.reftok_vocab_size(self._h)
+
+    def encode(self, raw: bytes):
+        n = self._l.reftok_encode(self._h, raw, len(raw), None, 0)
+        ids = np.zeros(max(n, 1), np.int32)
+        self._l.reftok_encode(self._h, raw, len(raw), _p(ids), n)
+        return [int(i) for i in ids[:n]]
+
+    def decode(self, ids) -> bytes:
+        a = np.ascontiguousarray(ids, np.int32)
+        n = self._l.reftok_decode(self._h, _p(a), a.size, None, 0)
+        buf = C.create_string_buffer(n + 1)
+        self._l.reftok_decode(self._h, _p(a), a.size, buf, n + 1)
+        return buf.raw[:n]
+
+    def __del__(self):
+        try:
+            if self._h:
+                self._l.reftok_destroy(self._h)
+                self._h = None
+        except Exception:
+            pass

@@ -63,6 +63,7 @@ SIGNATURES = {
     "spb_sparse_ternary_gemm": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "spb_sparse_bitlinear_gemm": (_i, [_p, _p, _p, _p, _p, C.c_float, _p, _i, _i, _i, _i, _i, _p]),
     "spb_set_gemm_variant": (_i, [_i]),
+    "spb_set_gemm_row_halves": (_i, [_i]),
     "spb_gemm_tc_timeouts": (_i, []),
     "spb_debug_bounded_wait_selftest": (_i, [C.c_longlong, _p]),
     "spb_rms_norm": (_i, [_p, _p, _p, _i, _f, _p]),
@@ -104,6 +105,32 @@ SIGNATURES = {
     "spb_engine_copy_logits": (_i, [_p, _p]),
     "spb_engine_prefill": (_i, [_p, _p, _i, _p]),
     "spb_engine_set_prefill_chunk": (_i, [_p, _i]),
+    "spb_model_load": (_p, [C.c_char_p]),
+    "spb_model_destroy": (None, [_p]),
+    "spb_model_get_config": (_i, [_p, C.POINTER(ModelConfig), C.POINTER(_i), C.POINTER(_i)]),
+    "spb_model_device_bytes": (C.c_size_t, [_p]),
+    "spb_model_attach": (_i, [_p, _p]),
+    "spb_tokenizer_load": (_p, [C.c_char_p]),
+    "spb_tokenizer_destroy": (None, [_p]),
+    "spb_tokenizer_vocab_size": (_i, [_p]),
+    "spb_tokenizer_encode": (_i, [_p, C.c_char_p, C.c_size_t, _p, _i]),
+    "spb_tokenizer_decode": (_i, [_p, _p, _i, _p, C.c_size_t]),
+    "spb_shard_engine_create": (_p, [C.POINTER(ModelConfig), _i, _i, _i]),
+    "spb_shard_engine_destroy": (None, [_p]),
+    "spb_shard_engine_row_range": (_i, [_p, _i, C.POINTER(_i), C.POINTER(_i)]),
+    "spb_shard_engine_set_linear": (_i, [_p, _i, _i, _p, _p, _f, _i, _i, _i, _i]),
+    "spb_shard_engine_set_norm": (_i, [_p, _i, _i, _p]),
+    "spb_shard_engine_set_globals": (_i, [_p, _p, _p, _p]),
+    "spb_shard_engine_ipc_handle": (_i, [_p, _p]),
+    "spb_shard_engine_set_peers": (_i, [_p, _p]),
+    "spb_shard_engine_set_peer_pointers": (_i, [_p, _p]),
+    "spb_shard_engine_exchange_bytes": (C.c_size_t, [_p]),
+    "spb_shard_engine_set_timeout_ms": (_i, [_p, _i]),
+    "spb_shard_engine_reset": (_i, [_p]),
+    "spb_shard_engine_seq_len": (_i, [_p]),
+    "spb_shard_engine_step": (_i, [_p, _p]),
+    "spb_shard_engine_copy_logits": (_i, [_p, _p]),
+    "spb_shard_engine_generate": (_i, [_p, _p, _i, _i, _p]),
 }
 
 _lib = None

@@ -14,8 +14,10 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libspbitnet_b200.so"
+CLI = HERE / "spbitnet_infer"
 SOURCES = ["core.cu", "gemv.cu", "gemv_batch_mma.cu", "gemv_mmasp.cu", "gemm.cu", "gemm_tcsp_ws.cu", "gemm_mmasp.cu", "unpack.cu",
-           "decode_ops.cu", "attention.cu", "fused_ops.cu", "prefill.cu", "engine.cu", "noalloc.cu", "pack.cu", "format_host.cpp"]
+           "decode_ops.cu", "attention.cu", "fused_ops.cu", "prefill.cu", "engine.cu", "sharded.cu", "noalloc.cu", "pack.cu", "format_host.cpp",
+           "tokenizer.cpp", "model_loader.cpp"]
 COMPILE_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
                  "-Xcompiler", "-fPIC"]
 LINK_FLAGS = ["-shared", "-gencode", "arch=compute_100a,code=sm_100a"]
@@ -73,6 +75,13 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     res = subprocess.run([nvcc, *LINK_FLAGS, "-o", str(LIB), *objs], capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+    # the command line (the reference's spbitnet_infer, src/main.cpp) on top of the library
+    cli_src = CSRC / "cli_main.cpp"
+    if force or not CLI.exists() or CLI.stat().st_mtime < max(cli_src.stat().st_mtime, LIB.stat().st_mtime):
+        res = subprocess.run([nvcc, "-O2", "-std=c++17", "-o", str(CLI), str(cli_src), "-L", str(HERE), "-lspbitnet_b200",
+                              "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"], capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"building spbitnet_infer failed:\n{res.stdout}\n{res.stderr}")
     return LIB
 
 

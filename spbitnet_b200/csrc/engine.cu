@@ -523,6 +523,7 @@ extern "C" spb_engine* spb_engine_create(const spb_model_config* cfg) {
     e->d_pos = reinterpret_cast<int*>(p + o_ints);
     e->d_next = e->d_pos + 1;
     e->d_out = reinterpret_cast<int*>(p + o_out);
+    prepare_host_state();
     e->timeouts_seen = timeouts_now();
     return e;
 }

@@ -149,11 +149,15 @@ __global__ void __launch_bounds__(256) rope_scatter_kernel(__half* __restrict__ 
                                                            __half* __restrict__ vcache, int num_heads,
                                                            int num_kv_heads, int head_dim,
                                                            int max_seq_len, float theta,
-                                                           const int* __restrict__ d_pos) {
+                                                           const int* __restrict__ d_pos, size_t seq_stride) {
     grid_dep_launch();
     grid_dep_wait();
-    // blockIdx.y = token of a prefill batch (0 in decode): its vectors follow one another, its position is *d_pos + y
-    const int pos = *d_pos + blockIdx.y;
+    // blockIdx.y = token of a prefill batch (0 in decode): its vectors follow one another, its position is *d_pos + y.
+    // With seq_stride != 0 the vectors are one token each of independent sequences instead: all at position *d_pos,
+    // sequence y's caches seq_stride elements after sequence y - 1's.
+    const int pos = *d_pos + (seq_stride ? 0 : blockIdx.y);
+    kcache += seq_stride * blockIdx.y;
+    vcache += seq_stride * blockIdx.y;
     q += static_cast<size_t>(blockIdx.y) * num_heads * head_dim;
     k += static_cast<size_t>(blockIdx.y) * num_kv_heads * head_dim;
     v += static_cast<size_t>(blockIdx.y) * num_kv_heads * head_dim;
@@ -195,13 +199,16 @@ __global__ void __launch_bounds__(256) rope_scatter_kernel(__half* __restrict__ 
 __global__ void __launch_bounds__(256) decode_attention_pos_kernel(
     const __half* __restrict__ Q, const __half* __restrict__ K, const __half* __restrict__ V,
     __half* __restrict__ out, int num_heads, int num_kv_heads, int head_dim, int max_seq_len,
-    float scale, const int* __restrict__ d_pos) {
+    float scale, const int* __restrict__ d_pos, size_t seq_stride) {
     extern __shared__ float dsm[];
     __shared__ float sh[32];
     grid_dep_launch();
     grid_dep_wait();
-    // blockIdx.y = token of a prefill batch (0 in decode): it sees the positions up to its own
-    const int seq_len = *d_pos + blockIdx.y + 1;
+    // blockIdx.y = token of a prefill batch (0 in decode): it sees the positions up to its own.  With
+    // seq_stride != 0: one token each of independent sequences at position *d_pos, caches seq_stride apart.
+    const int seq_len = *d_pos + (seq_stride ? 0 : blockIdx.y) + 1;
+    K += seq_stride * blockIdx.y;
+    V += seq_stride * blockIdx.y;
     Q += static_cast<size_t>(blockIdx.y) * num_heads * head_dim;
     out += static_cast<size_t>(blockIdx.y) * num_heads * head_dim;
     float* sc = dsm;
@@ -384,17 +391,17 @@ int relu2_norm_quant(const void* gate, const void* up, const float* sub_w, void*
 
 int rope_scatter(void* q, const void* k, const void* v, void* kcache, void* vcache, int num_heads,
                  int num_kv_heads, int head_dim, int max_seq_len, float theta, const int* d_pos,
-                 void* stream, int vectors) {
+                 void* stream, int vectors, size_t seq_stride) {
     const int threads = (num_heads + num_kv_heads) * (head_dim / 2) + num_kv_heads * head_dim / 2;
     return launch("rope_scatter", rope_scatter_kernel, dim3((threads + 255) / 256, vectors), dim3(256), 0, stream,
                   static_cast<__half*>(q), static_cast<const __half*>(k), static_cast<const __half*>(v),
                   static_cast<__half*>(kcache), static_cast<__half*>(vcache), num_heads, num_kv_heads,
-                  head_dim, max_seq_len, theta, d_pos);
+                  head_dim, max_seq_len, theta, d_pos, seq_stride);
 }
 
 int decode_attention_pos(const void* Q, const void* K, const void* V, void* out, int num_heads,
                          int num_kv_heads, int head_dim, int max_seq_len, float scale, const int* d_pos,
-                         void* stream, int vectors) {
+                         void* stream, int vectors, size_t seq_stride) {
     const size_t smem = sizeof(float) * (((max_seq_len + 31) & ~31) + 8 * static_cast<size_t>(head_dim));
     if (smem > 200 * 1024) return fail(SPB_E_UNSUPPORTED, "decode_attention: max_seq_len %d too long", max_seq_len);
     if (smem > 48 * 1024) cudaFuncSetAttribute(decode_attention_pos_kernel,
@@ -402,7 +409,7 @@ int decode_attention_pos(const void* Q, const void* K, const void* V, void* out,
     return launch("decode_attention_pos", decode_attention_pos_kernel, dim3(num_heads, vectors), dim3(256), smem,
                   stream, static_cast<const __half*>(Q), static_cast<const __half*>(K),
                   static_cast<const __half*>(V), static_cast<__half*>(out), num_heads, num_kv_heads,
-                  head_dim, max_seq_len, scale, d_pos);
+                  head_dim, max_seq_len, scale, d_pos, seq_stride);
 }
 
 int embed_token(const void* embed, void* x, int hidden, const int* d_prompt, int n_prompt,

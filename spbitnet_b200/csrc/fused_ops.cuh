@@ -1,6 +1,9 @@
 // Host launchers of the fused decode-step kernels (fused_ops.cu); engine-internal.
 // `vectors` > 1 runs the op on that many consecutive vectors (the tokens of a prefill batch): vector b of every
 // operand starts b * its length after the first, d_absmax is an array, and token b sits at position *d_pos + b.
+// rope_scatter / decode_attention_pos with seq_stride != 0 treat the vectors as one token each of independent
+// sequences instead (batched decode): all at position *d_pos, sequence b's K and V caches b * seq_stride elements
+// after the first sequence's.
 #pragma once
 #include "spb_common.cuh"
 
@@ -12,10 +15,10 @@ int relu2_norm_quant(const void* gate, const void* up, const float* sub_w, void*
                      float* d_absmax, int n, float eps, void* stream, int vectors = 1);
 int rope_scatter(void* q, const void* k, const void* v, void* kcache, void* vcache, int num_heads,
                  int num_kv_heads, int head_dim, int max_seq_len, float theta, const int* d_pos,
-                 void* stream, int vectors = 1);
+                 void* stream, int vectors = 1, size_t seq_stride = 0);
 int decode_attention_pos(const void* Q, const void* K, const void* V, void* out, int num_heads,
                          int num_kv_heads, int head_dim, int max_seq_len, float scale, const int* d_pos,
-                         void* stream, int vectors = 1);
+                         void* stream, int vectors = 1, size_t seq_stride = 0);
 // attention.cu: split-KV decode attention.  seq_len comes from *d_pos + 1 when d_pos is given.
 int decode_attention_split(const void* Q, const void* K, const void* V, void* out, int num_heads,
                            int num_kv_heads, int head_dim, int max_seq_len, int seq_len, const int* d_pos,

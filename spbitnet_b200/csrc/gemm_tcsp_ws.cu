@@ -50,10 +50,15 @@ struct WsArgs {
     int stages;     // ring depth (2..kWsMaxStages)
     int tmem_cols;  // power of two >= nt + 8 * stages
     int groups;     // re-encoding groups in use: 2 (alternate steps), or 1 (warps 12-19 idle)
+    int mh;         // weight-row halves per block: 1 (128 rows), or 2 (256 rows: group g re-encodes rows 128 g .. of every
+                    // step, both halves multiply the same activation tile into their own accumulator)
     GemmEpilogue ep;  // ep.out set: scaled half output instead of Y
     int* timeouts;        // counter of waits that ran out (pinned host memory, system-scope atomics), may be null
     long long wait_cycles;  // bound of every wait in the kernel
 };
+
+// 0 automatic, 1 / 2 force one / two weight-row halves per block (spb_set_gemm_row_halves; testing and measurement)
+static int g_ws_mh = 0;
 
 __device__ __forceinline__ void ws_count_timeout(int* counter) {
     if (counter) atomicAdd_system(counter, 1);
@@ -107,7 +112,7 @@ __device__ __forceinline__ uint32_t ws_index_pairs(uint32_t m) {
 template <bool HALF_OUT>
 __global__ void __launch_bounds__(kWsThreads, 1) gemm_tcsp_ws_kernel(const WsArgs a, const __grid_constant__ CUtensorMap tmap_x) {
     extern __shared__ uint8_t ws_raw[];
-    // [sign table 2 KB][barriers + tmem slot 128 B] ... 1024-aligned: [stage: A 16 KB | B0 nt*128 | B1 nt*128] x stages
+    // [sign table 2 KB][barriers + tmem slot 128 B] ... 1024-aligned: [stage: A 16 KB x mh | B0 nt*128 | B1 nt*128] x stages
     uint32_t* sgn = reinterpret_cast<uint32_t*>(ws_raw);
     uint64_t* bars = reinterpret_cast<uint64_t*>(ws_raw + kWsSignLutBytes);
     uint64_t* a_full = bars;                      // [stage]: 256 arrivals, the re-encoded tile and its metadata are written
@@ -119,12 +124,13 @@ __global__ void __launch_bounds__(kWsThreads, 1) gemm_tcsp_ws_kernel(const WsArg
     const uint32_t stage0_s = (raw_s + kWsSignLutBytes + 128 + 1023) & ~1023u;
     uint8_t* stage0 = ws_raw + (stage0_s - raw_s);
     const int b_bytes = a.nt * 128;  // one of the two activation sub-tiles
-    const int stage_bytes = kWsABytes + 2 * b_bytes;
+    const int a_bytes = a.mh * kWsABytes;
+    const int stage_bytes = a_bytes + 2 * b_bytes;
     const int S = a.stages;
 
     const int tid = threadIdx.x, lane = tid & 31;
     const int warp = __shfl_sync(0xFFFFFFFFu, tid >> 5, 0);
-    const int row0 = blockIdx.x * kWsTileM;
+    const int row0 = blockIdx.x * kWsTileM * a.mh;
     const int n0 = blockIdx.y * a.nt;
     const int upr = a.cols >> 7;
     const int nsteps = (upr + 1) >> 1;
@@ -136,7 +142,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) gemm_tcsp_ws_kernel(const WsArg
     }
     if (tid == 0) {
         for (int s = 0; s < kWsMaxStages; ++s) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(ws_smem(a_full + s)), "r"(kWsExpanders));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(ws_smem(a_full + s)), "r"(kWsExpanders * a.mh));
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(ws_smem(b_full + s)));
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(ws_smem(free_b + s)));
         }
@@ -153,7 +159,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) gemm_tcsp_ws_kernel(const WsArg
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_d = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
-    const uint32_t tmem_e = tmem_d + static_cast<uint32_t>(a.nt);  // metadata slots behind the accumulator
+    const uint32_t tmem_e = tmem_d + static_cast<uint32_t>(a.nt * a.mh);  // metadata slots behind the accumulators
     bool ok = true;
 
     if (warp == 9) {
@@ -166,7 +172,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) gemm_tcsp_ws_kernel(const WsArg
                 if (kc >= S) ok = ws_wait(ws_smem(free_b + s), static_cast<uint32_t>(kc / S - 1) & 1u, a.wait_cycles);
                 if (!ok) break;
                 const uint32_t fb = ws_smem(b_full + s);
-                uint8_t* sb = stage0 + static_cast<size_t>(s) * stage_bytes + kWsABytes;
+                uint8_t* sb = stage0 + static_cast<size_t>(s) * stage_bytes + a_bytes;
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(fb),
                              "r"(static_cast<uint32_t>(2 * b_bytes))
                              : "memory");
@@ -195,21 +201,24 @@ __global__ void __launch_bounds__(kWsThreads, 1) gemm_tcsp_ws_kernel(const WsArg
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t sa = stage0_s + static_cast<uint32_t>(s) * stage_bytes;
-                const uint64_t da = ws_smem_desc(sa);
-                const uint64_t db0 = ws_smem_desc(sa + kWsABytes), db1 = ws_smem_desc(sa + kWsABytes + b_bytes);
+                const uint64_t db0 = ws_smem_desc(sa + a_bytes), db1 = ws_smem_desc(sa + a_bytes + b_bytes);
+                for (int h = 0; h < a.mh; ++h) {  // each half of the weight rows into its own accumulator
+                    const uint64_t da = ws_smem_desc(sa + static_cast<uint32_t>(h) * kWsABytes);
+                    const uint32_t td = tmem_d + static_cast<uint32_t>(h * a.nt);
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {  // 64 logical columns each: 32 B of A, 64 B of X, two metadata columns
-                    const uint32_t acc = (kc > 0 || k > 0) ? 1u : 0u;
-                    const uint64_t db = ((k & 2) ? db1 : db0) + static_cast<uint64_t>(4 * (k & 1));
-                    const uint32_t te = tmem_e + static_cast<uint32_t>(s * 8 + 2 * k);
-                    asm volatile(
-                        "{\n\t.reg .pred p;\n\t"
-                        "setp.ne.b32 p, %4, 0;\n\t"
-                        "tcgen05.mma.sp.cta_group::1.kind::i8 [%0], %1, %2, [%9], %3, {%5, %6, %7, %8}, p;\n\t}"
-                        :
-                        : "r"(tmem_d), "l"(da + 2 * k), "l"(db), "r"(idesc), "r"(acc), "r"(0u), "r"(0u), "r"(0u), "r"(0u),
-                          "r"(te)
-                        : "memory");
+                    for (int k = 0; k < 4; ++k) {  // 64 logical columns each: 32 B of A, 64 B of X, two metadata columns
+                        const uint32_t acc = (kc > 0 || k > 0) ? 1u : 0u;
+                        const uint64_t db = ((k & 2) ? db1 : db0) + static_cast<uint64_t>(4 * (k & 1));
+                        const uint32_t te = tmem_e + static_cast<uint32_t>((s * a.mh + h) * 8 + 2 * k);
+                        asm volatile(
+                            "{\n\t.reg .pred p;\n\t"
+                            "setp.ne.b32 p, %4, 0;\n\t"
+                            "tcgen05.mma.sp.cta_group::1.kind::i8 [%0], %1, %2, [%9], %3, {%5, %6, %7, %8}, p;\n\t}"
+                            :
+                            : "r"(td), "l"(da + 2 * k), "l"(db), "r"(idesc), "r"(acc), "r"(0u), "r"(0u), "r"(0u), "r"(0u),
+                              "r"(te)
+                            : "memory");
+                    }
                 }
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(ws_smem(free_b + s))
                              : "memory");
@@ -228,7 +237,8 @@ __global__ void __launch_bounds__(kWsThreads, 1) gemm_tcsp_ws_kernel(const WsArg
         const int ewarp = warp < 8 ? warp : warp - kWsGroup1Warp + 8;  // 0..15 over both groups
         const int etid = (ewarp & 7) * 32 + lane;                        // 0..255 within the group
         const int trow = etid & (kWsTileM - 1), thalf = etid >> 7;
-        const int wrow = row0 + trow;
+        const int mhalf = a.mh == 2 ? grp : 0;  // which 128 rows of the block this group serves
+        const int wrow = row0 + mhalf * kWsTileM + trow;
         const bool wvalid = wrow < a.rows;
         auto load_unit = [&](int step, uint4& mm, uint2& vv, bool& valid) {
             const int u = 2 * step + thalf;
@@ -242,14 +252,15 @@ __global__ void __launch_bounds__(kWsThreads, 1) gemm_tcsp_ws_kernel(const WsArg
         uint4 m0 = make_uint4(0, 0, 0, 0), m1 = m0, m2 = m0, m3 = m0;
         uint2 v0 = make_uint2(0, 0), v1 = v0, v2 = v0, v3 = v0;
         bool u0 = false, u1 = false, u2 = false, u3 = false;
-        const int gs = a.groups;  // step stride of a group
-        if (grp < nsteps) load_unit(grp, m0, v0, u0);
-        if (grp + gs < nsteps) load_unit(grp + gs, m1, v1, u1);
-        if (grp + 2 * gs < nsteps) load_unit(grp + 2 * gs, m2, v2, u2);
-        if (grp + 3 * gs < nsteps) load_unit(grp + 3 * gs, m3, v3, u3);
+        const int gs = a.mh == 2 ? 1 : a.groups;  // step stride of a group (with two row halves every group takes every step)
+        const int k_first = a.mh == 2 ? 0 : grp;
+        if (k_first < nsteps) load_unit(k_first, m0, v0, u0);
+        if (k_first + gs < nsteps) load_unit(k_first + gs, m1, v1, u1);
+        if (k_first + 2 * gs < nsteps) load_unit(k_first + 2 * gs, m2, v2, u2);
+        if (k_first + 3 * gs < nsteps) load_unit(k_first + 3 * gs, m3, v3, u3);
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const uint32_t sgn_s = raw_s + (static_cast<uint32_t>(lane) << 2);
-        for (int kc = grp; kc < nsteps; kc += gs) {
+        for (int kc = k_first; kc < nsteps; kc += gs) {
             const int s = kc % S;
             uint4 mn = make_uint4(0, 0, 0, 0);
             uint2 vn = make_uint2(0, 0);
@@ -266,12 +277,12 @@ __global__ void __launch_bounds__(kWsThreads, 1) gemm_tcsp_ws_kernel(const WsArg
                 e2 = ws_index_pairs(m0.z);
                 e3 = ws_index_pairs(m0.w);
             }
-            const uint32_t eaddr = tmem_e + lane_base + static_cast<uint32_t>(s * 8 + thalf * 4);
+            const uint32_t eaddr = tmem_e + lane_base + static_cast<uint32_t>((s * a.mh + mhalf) * 8 + thalf * 4);
             asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(eaddr), "r"(e0), "r"(e1), "r"(e2),
                          "r"(e3)
                          : "memory");
             // values: sign nibble -> four bytes of +1 / -1; a unit is four 16-byte chunks of the row
-            const uint32_t sa = stage0_s + static_cast<uint32_t>(s) * stage_bytes;
+            const uint32_t sa = stage0_s + static_cast<uint32_t>(s) * stage_bytes + static_cast<uint32_t>(mhalf) * kWsABytes;
             const uint32_t vw[2] = {v0.x, v0.y};
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
@@ -303,12 +314,15 @@ __global__ void __launch_bounds__(kWsThreads, 1) gemm_tcsp_ws_kernel(const WsArg
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
             grid_dep_wait();  // Y may still be read by a predecessor
-            // warp w reads TMEM lanes 32 * (w % 4) .. + 31 (weight rows); the sixteen warps share the columns
-            const int quarter = ewarp & 3, csel = ewarp >> 2;
-            const int row = row0 + quarter * 32 + lane;
-            for (int c0 = csel * 32; c0 < a.nt; c0 += 64 * gs) {
+            // warp w reads TMEM lanes 32 * (w % 4) .. + 31 (weight rows); the warps that serve the same rows share the
+            // columns (all sixteen with one row half, the eight of a group with two)
+            const int quarter = ewarp & 3;
+            const int csel = a.mh == 2 ? ((ewarp >> 2) & 1) : (ewarp >> 2);
+            const int cstep = a.mh == 2 ? 64 : 64 * a.groups;
+            const int row = row0 + mhalf * kWsTileM + quarter * 32 + lane;
+            for (int c0 = csel * 32; c0 < a.nt; c0 += cstep) {
                 uint32_t r[32];
-                const uint32_t taddr = tmem_d + lane_base + static_cast<uint32_t>(c0);
+                const uint32_t taddr = tmem_d + lane_base + static_cast<uint32_t>(mhalf * a.nt + c0);
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                     "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -373,6 +387,32 @@ __global__ void __launch_bounds__(128, 1) ws_wait_selftest_kernel(int* timeouts,
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(32u) : "memory");
 }
 
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                             const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeFn tensor_map_encoder() {
+    static const EncodeFn encode = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess) {
+            cudaGetLastError();
+            p = nullptr;
+        }
+        return reinterpret_cast<EncodeFn>(p);
+    }();
+    return encode;
+}
+
+// Everything the launchers look up or allocate lazily on the host (driver entry point, the pinned timeout counter,
+// the SM count), done now: an engine calls this at creation so that none of it first happens inside a stream
+// capture, where allocations and look-ups are not allowed.
+void prepare_host_state() {
+    tensor_map_encoder();
+    timeout_counter();
+    sm_count();
+}
+
 // Launch of the warp-specialised form; the caller has checked the layout (cols % 128 == 0, aligned rows and X).
 // Returns SPB_E_UNSUPPORTED when the tensor map of X cannot be made (the caller then takes the plain form).
 int gemm_tcsp_ws_launch(const uint32_t* meta, const uint32_t* values, const int8_t* X, int32_t* Y, int rows, int cols,
@@ -388,10 +428,25 @@ int gemm_tcsp_ws_launch(const uint32_t* meta, const uint32_t* values, const int8
     int nt = 256;
     while (nt > 64 && mtiles * ((n + nt - 1) / nt) < sm_count() / 2) nt >>= 1;
     a.nt = min(nt, (n + 15) / 16 * 16);
-    const int stage_bytes = kWsABytes + 2 * a.nt * 128;
+    // Two row halves per block (256 weight rows on one activation tile, one re-encoding group per half, two
+    // accumulators).  A step then costs about twice as much (the MMA warp issues eight MMAs, each group re-encodes
+    // every step), so it only pays by saving a wave.  Both accumulators and the metadata slots must fit the 512
+    // tensor-memory columns: 240 batch rows.
+    a.mh = 1;
+    if (g_ws_mh != 1 && n > 128) {
+        // automatic: only where the 128-row blocks need a second wave and the 256-row blocks fit into one
+        // (measured: 6912x2560 at n = 1024, 25.2 -> 22.1 us; everywhere else the 128-row form is faster)
+        const int mt2 = (rows + 2 * kWsTileM - 1) / (2 * kWsTileM), nt2 = 240;
+        const int items1 = mtiles * ((n + a.nt - 1) / a.nt), items2 = mt2 * ((n + nt2 - 1) / nt2);
+        if (g_ws_mh == 2 || (items1 > sm_count() && items2 <= sm_count() && items2 >= (3 * sm_count()) / 4)) {
+            a.mh = 2;
+            a.nt = min(nt2, (n + 15) / 16 * 16);
+        }
+    }
+    const int stage_bytes = a.mh * kWsABytes + 2 * a.nt * 128;
     a.stages = max(2, min(kWsMaxStages, (200 * 1024) / stage_bytes));
     // two groups pay off except at 128 batch rows per block (measured at 6912x2560, n = 256: 12.4 against 11.9 us)
-    a.groups = a.nt == 128 ? 1 : 2;
+    a.groups = a.mh == 2 ? 2 : a.nt == 128 ? 1 : 2;
     // A group must not run more than one ring revolution ahead of the MMA warp, or its parity wait on a stage's
     // "free" barrier would be satisfied by the previous completion of the same parity.  A group's wait for step k
     // confirms the commit of step k - stages; its next step is k + groups, whose wait needs the commit of
@@ -399,21 +454,10 @@ int gemm_tcsp_ws_launch(const uint32_t* meta, const uint32_t* values, const int8
     // ran into exactly this.)
     a.groups = min(a.groups, a.stages);
     a.tmem_cols = 32;
-    while (a.tmem_cols < a.nt + 8 * a.stages) a.tmem_cols <<= 1;
+    while (a.tmem_cols < a.mh * (a.nt + 8 * a.stages)) a.tmem_cols <<= 1;
+    if (a.tmem_cols > 512) return fail(SPB_E_UNSUPPORTED, "gemm_tcsp_ws: %d tensor-memory columns", a.tmem_cols);
     const size_t smem = kWsSignLutBytes + 128 + 1024 + static_cast<size_t>(a.stages) * stage_bytes;
-    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-    static const EncodeFn encode = [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess) {
-            cudaGetLastError();
-            p = nullptr;
-        }
-        return reinterpret_cast<EncodeFn>(p);
-    }();
+    const EncodeFn encode = tensor_map_encoder();
     if (!encode) return SPB_E_UNSUPPORTED;
     // tensor map of X: uint8 [n rows][cols], box 128 bytes x nt rows, 128-byte swizzle, zero fill past n
     alignas(64) CUtensorMap tmap;
@@ -429,7 +473,7 @@ int gemm_tcsp_ws_launch(const uint32_t* meta, const uint32_t* values, const int8
     if (int rc = ensure_dynamic_smem("gemm_tcsp_ws", kernel, smem)) return rc;
     a.timeouts = timeout_counter();
     a.wait_cycles = kWsWaitCycles;
-    const dim3 grid((rows + kWsTileM - 1) / kWsTileM, (n + a.nt - 1) / a.nt);
+    const dim3 grid((rows + a.mh * kWsTileM - 1) / (a.mh * kWsTileM), (n + a.nt - 1) / a.nt);
     return launch("spb_sparse_ternary_gemm(tcgen05.sp, warp-specialised)", kernel, grid, dim3(kWsThreads), smem,
                   stream, a, tmap);
 }
@@ -449,4 +493,10 @@ extern "C" int spb_debug_bounded_wait_selftest(long long limit_cycles, void* str
     if (timeouts_now() != before)
         return fail(SPB_E_TIMEOUT, "spb_debug_bounded_wait_selftest: the wait ran out after %lld cycles, as it must", limit);
     return SPB_OK;
+}
+
+extern "C" int spb_set_gemm_row_halves(int halves) {
+    const int old = spb::g_ws_mh;
+    spb::g_ws_mh = halves == 1 || halves == 2 ? halves : 0;
+    return old;
 }

@@ -1,0 +1,883 @@
+// Row-sharded decode engine: one rank of a tensor-parallel group, one process per GPU.
+//
+// The reference is single-GPU (src/inference.cu); this is the one way its decode step partitions without a
+// reduction, so that every integer accumulator and every half output stays bit-identical to the unsharded
+// step: rank r owns a contiguous slice of the output rows of every ternary matrix (q/k/v by whole KV heads,
+// so that RoPE, the KV cache and attention are local; o / gate / up / down by rows; the LM head by vocabulary
+// rows), computes its slice with the ordinary kernels on the full activation vector, and the slices are
+// concatenated on every rank.  Vector ops (norms, quantisation, residual adds) are replicated.  Four
+// exchanges per layer (attention output, o_proj output, gate and up, down output) plus one per token for the
+// arg-max candidates.
+//
+// The exchange is not a library collective.  Every rank exports one device buffer (CUDA IPC) and maps its
+// peers'; an exchange is ONE kernel that
+//   1. copies the rank's slice into the same place of every rank's buffer with ordinary stores through the
+//      peer mappings (NVLink / NVSwitch), its own included,
+//   2. fences (system scope) and, in the last block to finish, stores the exchange's sequence number into
+//      its flag word on every peer,
+//   3. waits until the local flag words of all peers have reached that sequence number, bounded by time:
+//      when the bound runs out the kernel raises a status word that the host reads at its next
+//      synchronisation (SPB_E_TIMEOUT), and every later exchange of the engine skips its wait.
+// No multicast, no bulk-copy engine, no library kernel ever sees a peer pointer; remote data always lands in
+// the consumer's own memory before anything reads it.  Sequence numbers only grow, so flags are never reset.
+// A buffer is reused once per layer: a rank that writes exchange n into a peer has passed its wait of
+// exchange n - 1, so that peer has issued everything up to exchange n - 1, which comes after its last read
+// of this buffer's previous contents (four exchanges earlier).
+//
+// batch = 1 runs the fused GEMV launches of the single-GPU engine on the row slices; batch > 1 decodes that
+// many independent sequences in lock step (same position, own KV caches) with the batched product
+// (spb_sparse_bitlinear_gemm) and the row-batched vector kernels.
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "fused_ops.cuh"
+
+namespace spb {
+
+namespace {
+
+constexpr int kMaxWorld = 8;
+constexpr int kMaxBatch = 64;
+enum { X_ATTN = 0, X_O = 1, X_GU = 2, X_DOWN = 3, X_AMAX = 4, X_KINDS = 5 };
+constexpr size_t kFlagBytesPerKind = 64;
+
+struct XSeg {
+    const uint8_t* src;   // local compact slice: rows x len bytes
+    uint32_t dst_off;     // byte offset of the slice inside every rank's exchange buffer (row 0)
+    uint32_t dst_pitch;   // bytes between rows of the gathered array
+    uint32_t len;         // bytes per row of this rank's slice (a multiple of 4)
+};
+
+struct XArgs {
+    uint8_t* peer[kMaxWorld];  // exchange buffers of all ranks, peer[rank] = the local one
+    XSeg seg[2];
+    int nseg, rows, world, rank;
+    uint32_t flag_off;              // byte offset of this kind's flag words in the exchange buffer
+    unsigned* seqno;                // local: sequence number of this kind's last exchange
+    unsigned* done;                 // local: blocks of the running exchange that have finished copying
+    int* status;                    // pinned host word: 0 healthy, 1 a wait ran out
+    int* broken;                    // the same fact in device memory (read by every later exchange)
+    unsigned long long timeout_ns;  // bound of the wait
+};
+
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+template <typename T>
+__device__ __forceinline__ void xcopy(const XArgs& a, int tid_global, int nthreads) {
+    for (int s = 0; s < a.nseg; ++s) {
+        const XSeg& g = a.seg[s];
+        const uint32_t per_row = g.len / sizeof(T);
+        const uint32_t total = per_row * static_cast<uint32_t>(a.rows);
+        for (uint32_t i = tid_global; i < total; i += nthreads) {
+            const uint32_t row = i / per_row, c = i - row * per_row;
+            const T v = reinterpret_cast<const T*>(g.src + static_cast<size_t>(row) * g.len)[c];
+            const size_t o = static_cast<size_t>(g.dst_off) + static_cast<size_t>(row) * g.dst_pitch + static_cast<size_t>(c) * sizeof(T);
+            for (int p = 0; p < a.world; ++p) *reinterpret_cast<T*>(a.peer[p] + o) = v;
+        }
+    }
+}
+
+// WIDE: every length, offset and pitch is a multiple of 16 bytes (16-byte copies), else 4-byte copies.
+template <bool WIDE>
+__global__ void __launch_bounds__(256) exchange_kernel(const XArgs a) {
+    __shared__ unsigned s_last, s_seq;
+    grid_dep_launch();
+    grid_dep_wait();  // the slice was written by the predecessor
+    const int tid = blockIdx.x * blockDim.x + threadIdx.x, nthreads = gridDim.x * blockDim.x;
+    if (WIDE) xcopy<uint4>(a, tid, nthreads);
+    else xcopy<uint32_t>(a, tid, nthreads);
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned ticket = atomicAdd(a.done, 1u);
+        s_last = ticket == gridDim.x - 1 ? 1u : 0u;
+        if (s_last) {
+            *a.done = 0;
+            s_seq = *a.seqno + 1;
+            *a.seqno = s_seq;
+        }
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence_system();
+    const unsigned seq = s_seq;
+    const int p = threadIdx.x;
+    if (p < a.world && p != a.rank) {
+        st_release_sys(reinterpret_cast<unsigned*>(a.peer[p] + a.flag_off) + a.rank, seq);
+        const unsigned* mine = reinterpret_cast<const unsigned*>(a.peer[a.rank] + a.flag_off) + p;
+        if (*reinterpret_cast<volatile int*>(a.broken) == 0) {
+            const unsigned long long t0 = globaltimer_ns();
+            for (;;) {
+                // sequence numbers only grow; the subtraction keeps the comparison right across a wrap
+                if (static_cast<int>(ld_acquire_sys(mine) - seq) >= 0) break;
+                if (globaltimer_ns() - t0 > a.timeout_ns) {
+                    *reinterpret_cast<volatile int*>(a.broken) = 1;
+                    atomicExch_system(a.status, 1);
+                    break;
+                }
+                __nanosleep(64);
+            }
+        }
+    }
+}
+
+// token of sequence b: prompt[pos * batch + b] while pos < n_prompt, else next[b]; row copy of the embedding
+__global__ void __launch_bounds__(256) shard_embed_kernel(const __half* __restrict__ embed, __half* __restrict__ x,
+                                                          int hidden, const int* __restrict__ d_prompt, int n_prompt,
+                                                          const int* __restrict__ d_next, const int* __restrict__ d_pos,
+                                                          int batch) {
+    grid_dep_launch();
+    grid_dep_wait();
+    const int b = blockIdx.y, pos = *d_pos;
+    const int token = (d_prompt && pos < n_prompt) ? d_prompt[pos * batch + b] : d_next[b];
+    const uint4* row = reinterpret_cast<const uint4*>(embed + static_cast<size_t>(token) * hidden);
+    uint4* dst = reinterpret_cast<uint4*>(x + static_cast<size_t>(b) * hidden);
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < hidden / 8; i += gridDim.x * blockDim.x) dst[i] = row[i];
+}
+
+// First maximum of the rank's logits of sequence blockIdx.x (std::max_element order): (value, global index).
+__global__ void __launch_bounds__(1024) shard_argmax_kernel(const float* __restrict__ logits, int n, int index0,
+                                                            float* __restrict__ out_pairs) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    grid_dep_launch();
+    grid_dep_wait();
+    const float* v = logits + static_cast<size_t>(blockIdx.x) * n;
+    float best = -INFINITY;
+    int besti = 0x7FFFFFFF;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float x = v[i];
+        if (besti == 0x7FFFFFFF || x > best) {  // i grows: a later equal value never replaces an earlier one
+            best = x;
+            besti = i;
+        }
+    }
+    auto take = [](float& a, int& ai, float b, int bi) {
+        if (bi != 0x7FFFFFFF && (ai == 0x7FFFFFFF || b > a || (b == a && bi < ai))) { a = b; ai = bi; }
+    };
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+        take(best, besti, __shfl_xor_sync(0xFFFFFFFFu, best, off), __shfl_xor_sync(0xFFFFFFFFu, besti, off));
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { sv[warp] = best; si[warp] = besti; }
+    __syncthreads();
+    if (warp == 0) {
+        best = sv[lane];
+        besti = si[lane];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1)
+            take(best, besti, __shfl_xor_sync(0xFFFFFFFFu, best, off), __shfl_xor_sync(0xFFFFFFFFu, besti, off));
+        if (lane == 0) {
+            out_pairs[2 * blockIdx.x] = best;
+            reinterpret_cast<int*>(out_pairs)[2 * blockIdx.x + 1] = besti == 0x7FFFFFFF ? besti : besti + index0;
+        }
+    }
+}
+
+// Thread b: the first maximum over the ranks' candidates of sequence b (ranks hold ascending vocabulary ranges, so
+// the lowest rank wins ties), published as the next token; thread 0 then advances the position.
+__global__ void __launch_bounds__(kMaxBatch) shard_pick_kernel(const float* __restrict__ pairs, int world, int batch,
+                                                               int* __restrict__ d_next, int* __restrict__ d_out,
+                                                               int* __restrict__ d_pos) {
+    grid_dep_launch();
+    grid_dep_wait();
+    const int b = threadIdx.x, pos = *d_pos;
+    if (b < batch) {
+        float best = -INFINITY;
+        int besti = 0x7FFFFFFF;
+        for (int r = 0; r < world; ++r) {
+            const float v = pairs[(static_cast<size_t>(b) * world + r) * 2];
+            const int i = reinterpret_cast<const int*>(pairs)[(static_cast<size_t>(b) * world + r) * 2 + 1];
+            if (i != 0x7FFFFFFF && (besti == 0x7FFFFFFF || v > best)) { best = v; besti = i; }
+        }
+        d_next[b] = besti;
+        if (d_out) d_out[static_cast<size_t>(pos) * batch + b] = besti;
+    }
+    __syncthreads();
+    if (b == 0) *d_pos = pos + 1;
+}
+
+// LM head for a batch: logits[b][r] = sum_k W[r][k] * x[b][k], fp16 inputs, fp32 accumulation on the warp-level
+// tensor-core MMA (m16n8k16).  A warp owns 16 rows of W and all NT * 8 batch columns; per 32 columns every lane
+// reads 16 bytes of its two rows and of each batch column it serves.  Which four of a lane's eight values go
+// into which MMA step is the same for W and x, so the products pair up correctly (a dot product does not care
+// about the order of its terms; the fp32 sums differ from a sequential loop in the last bits only).
+template <int NT>
+__global__ void __launch_bounds__(128) half_gemm_rows_kernel(const __half* __restrict__ W, const __half* __restrict__ x,
+                                                             float* __restrict__ y, int rows, int cols, int batch) {
+    grid_dep_launch();
+    grid_dep_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tig = lane & 3;
+    const int row0 = (blockIdx.x * 4 + warp) * 16;
+    if (row0 >= rows) return;
+    const int ra = row0 + g, rb = row0 + g + 8;
+    const uint4* wa = reinterpret_cast<const uint4*>(W + static_cast<size_t>(min(ra, rows - 1)) * cols) + tig;
+    const uint4* wb = reinterpret_cast<const uint4*>(W + static_cast<size_t>(min(rb, rows - 1)) * cols) + tig;
+    const uint4* xp[NT];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) xp[j] = reinterpret_cast<const uint4*>(x + static_cast<size_t>(min(8 * j + g, batch - 1)) * cols) + tig;
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
+    for (int k = 0; k < cols / 32; ++k) {
+        const uint4 a = ld_stream_v4(reinterpret_cast<const uint32_t*>(wa + 4 * k));
+        const uint4 b = ld_stream_v4(reinterpret_cast<const uint32_t*>(wb + 4 * k));
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            const uint4 v = __ldg(xp[j] + 4 * k);
+            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                         : "+f"(acc[j][0]), "+f"(acc[j][1]), "+f"(acc[j][2]), "+f"(acc[j][3])
+                         : "r"(a.x), "r"(b.x), "r"(a.y), "r"(b.y), "r"(v.x), "r"(v.y));
+            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                         : "+f"(acc[j][0]), "+f"(acc[j][1]), "+f"(acc[j][2]), "+f"(acc[j][3])
+                         : "r"(a.z), "r"(b.z), "r"(a.w), "r"(b.w), "r"(v.z), "r"(v.w));
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        const int n0 = 8 * j + 2 * tig;
+        if (n0 < batch) {
+            if (ra < rows) y[static_cast<size_t>(n0) * rows + ra] = acc[j][0];
+            if (rb < rows) y[static_cast<size_t>(n0) * rows + rb] = acc[j][2];
+        }
+        if (n0 + 1 < batch) {
+            if (ra < rows) y[static_cast<size_t>(n0 + 1) * rows + ra] = acc[j][1];
+            if (rb < rows) y[static_cast<size_t>(n0 + 1) * rows + rb] = acc[j][3];
+        }
+    }
+}
+
+int half_gemm_rows(const __half* W, const __half* x, float* y, int rows, int cols, int batch, void* stream) {
+    if (cols % 32 || (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(x) & 15))
+        return fail(SPB_E_UNSUPPORTED, "batched lm_head: hidden size must be a multiple of 32 and rows 16-byte aligned");
+    const dim3 grid((rows + 63) / 64), block(128);
+    const int nt = (batch + 7) / 8;
+    if (nt <= 1) return launch("half_gemm_rows", half_gemm_rows_kernel<1>, grid, block, 0, stream, W, x, y, rows, cols, batch);
+    if (nt <= 2) return launch("half_gemm_rows", half_gemm_rows_kernel<2>, grid, block, 0, stream, W, x, y, rows, cols, batch);
+    if (nt <= 4) return launch("half_gemm_rows", half_gemm_rows_kernel<4>, grid, block, 0, stream, W, x, y, rows, cols, batch);
+    return launch("half_gemm_rows", half_gemm_rows_kernel<8>, grid, block, 0, stream, W, x, y, rows, cols, batch);
+}
+
+struct Linear {
+    const uint32_t* meta = nullptr;
+    const uint32_t* values = nullptr;
+    float gamma = 0.0f;
+    int rows = 0, cols = 0, ms = 0, vs = 0;
+};
+struct Layer {
+    Linear lin[7];              // q k v o gate up down: this rank's row slices
+    const float* norm[4] = {};  // input_ln, post_attn_ln, attn_sub_norm, ffn_sub_norm (full vectors)
+};
+
+void split_range(int units, int world, int rank, int multiple, int* start, int* stop) {
+    const int n = units / multiple, base = n / world, extra = n % world;
+    const int a = rank * base + std::min(rank, extra);
+    *start = a * multiple;
+    *stop = (a + base + (rank < extra ? 1 : 0)) * multiple;
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+int cuda_fail(const char* what, cudaError_t err) {
+    cudaGetLastError();
+    return fail(SPB_E_CUDA, "%s: %s", what, cudaGetErrorString(err));
+}
+#define SPB_CUDA(call)                                            \
+    do {                                                          \
+        cudaError_t err__ = (call);                               \
+        if (err__ != cudaSuccess) return cuda_fail(#call, err__); \
+    } while (0)
+
+BitLinearGroup make_group(const Linear* const* L, __half* const* out, int n) {
+    BitLinearGroup g{};
+    g.nmat = n;
+    g.cols = L[0]->cols;
+    for (int i = 0; i < n; ++i) {
+        g.meta[i] = L[i]->meta; g.values[i] = L[i]->values; g.out[i] = out[i]; g.gamma[i] = L[i]->gamma;
+        g.rows[i] = L[i]->rows; g.ms[i] = L[i]->ms; g.vs[i] = L[i]->vs;
+    }
+    return g;
+}
+
+}  // namespace
+}  // namespace spb
+
+using namespace spb;
+
+struct spb_shard_engine {
+    spb_model_config cfg{};
+    int rank = 0, world = 1, batch = 1, device = 0;
+    std::vector<Layer> layers;
+    const __half* embed = nullptr;
+    const __half* lm_head_loc = nullptr;  // this rank's vocabulary rows
+    const float* final_norm = nullptr;
+
+    // the split: [start, stop) per rank
+    int kv0[kMaxWorld + 1] = {}, hrow[kMaxWorld + 1] = {}, irow[kMaxWorld + 1] = {}, vrow[kMaxWorld + 1] = {};
+    int group_heads = 1;
+    int nkv_loc = 0, nh_loc = 0, h_loc = 0, i_loc = 0, v_loc = 0;
+
+    cudaStream_t stream = nullptr;
+    uint8_t* pool = nullptr;
+    size_t kv_layer_bytes = 0;  // one layer's K (or V) caches of all sequences
+    size_t seq_stride = 0;      // elements between the caches of two sequences
+    __half *kcache = nullptr, *vcache = nullptr;
+    __half *x = nullptr, *x2 = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr, *o = nullptr;
+    __half *gate = nullptr, *up = nullptr, *down = nullptr, *xfinal = nullptr;
+    int8_t* xq = nullptr;
+    float *absmax = nullptr, *attn_scratch = nullptr, *logits = nullptr, *pairs = nullptr;
+    int32_t* acc = nullptr;  // three int32 workspaces for the SIMT form of the batched product
+    size_t acc_third = 0;
+    int *d_pos = nullptr, *d_next = nullptr, *d_prompt = nullptr, *d_out = nullptr;
+    unsigned* counters = nullptr;  // [X_KINDS][2]: seqno, done
+    int prompt_cap = 0, n_prompt_in_graph = 0, out_cap = 0;
+    bool split_attention = false, fused = false;
+
+    // exchange buffer (exported through CUDA IPC) and the peers' mappings
+    uint8_t* xbuf = nullptr;
+    size_t xbuf_bytes = 0;
+    uint8_t* peer[kMaxWorld] = {};
+    bool peers_set = false;
+    size_t off_flags = 0, off_attn = 0, off_o = 0, off_gate = 0, off_up = 0, off_down = 0, off_amax = 0;
+    int* status = nullptr;  // pinned, mapped
+    unsigned long long timeout_ns = 5000000000ull;
+
+    cudaGraphExec_t graph = nullptr;
+    bool graph_records = false;
+    int seq_len = 0;
+};
+
+namespace {
+
+int exchange(spb_shard_engine* e, int kind, const XSeg* segs, int nseg) {
+    if (e->world == 1) {  // nothing to exchange: the "slice" is the whole vector; copy it into place
+        for (int s = 0; s < nseg; ++s)
+            SPB_CUDA(cudaMemcpy2DAsync(e->xbuf + segs[s].dst_off, segs[s].dst_pitch, segs[s].src, segs[s].len, segs[s].len,
+                                       e->batch, cudaMemcpyDeviceToDevice, e->stream));
+        return SPB_OK;
+    }
+    XArgs a{};
+    for (int p = 0; p < e->world; ++p) a.peer[p] = e->peer[p];
+    bool wide = true;
+    size_t bytes = 0;
+    for (int s = 0; s < nseg; ++s) {
+        a.seg[s] = segs[s];
+        wide = wide && segs[s].len % 16 == 0 && segs[s].dst_off % 16 == 0 && segs[s].dst_pitch % 16 == 0 &&
+               (reinterpret_cast<uintptr_t>(segs[s].src) & 15) == 0;
+        bytes += static_cast<size_t>(segs[s].len) * e->batch;
+    }
+    a.nseg = nseg; a.rows = e->batch; a.world = e->world; a.rank = e->rank;
+    a.flag_off = static_cast<uint32_t>(e->off_flags + kind * kFlagBytesPerKind);
+    a.seqno = e->counters + 2 * kind;
+    a.done = e->counters + 2 * kind + 1;
+    a.status = e->status;
+    a.broken = reinterpret_cast<int*>(e->counters + 2 * X_KINDS);
+    a.timeout_ns = e->timeout_ns;
+    const int blocks = static_cast<int>(std::max<size_t>(1, std::min<size_t>(64, bytes / (16 * 1024))));
+    return wide ? launch("exchange", exchange_kernel<true>, dim3(blocks), dim3(256), 0, e->stream, a)
+                : launch("exchange", exchange_kernel<false>, dim3(blocks), dim3(256), 0, e->stream, a);
+}
+
+XSeg seg_of(const void* src, size_t region, size_t off_bytes, size_t pitch, size_t len) {
+    return XSeg{static_cast<const uint8_t*>(src), static_cast<uint32_t>(region + off_bytes), static_cast<uint32_t>(pitch),
+                static_cast<uint32_t>(len)};
+}
+
+// Enqueues one decode step of all `batch` sequences on e->stream.
+int enqueue_step(spb_shard_engine* e, bool record) {
+    const spb_model_config& c = e->cfg;
+    const int H = c.hidden_size, hd = c.head_dim, inter = c.intermediate_size, B = e->batch, r = e->rank;
+    const int qdim = c.num_attention_heads * hd;
+    void* s = e->stream;
+    int rc;
+    __half* cur = e->x;
+    __half* other = e->x2;
+    __half* attn_full = reinterpret_cast<__half*>(e->xbuf + e->off_attn);
+    __half* o_full = reinterpret_cast<__half*>(e->xbuf + e->off_o);
+    __half* gate_full = reinterpret_cast<__half*>(e->xbuf + e->off_gate);
+    __half* up_full = reinterpret_cast<__half*>(e->xbuf + e->off_up);
+    __half* down_full = reinterpret_cast<__half*>(e->xbuf + e->off_down);
+    float* amax_full = reinterpret_cast<float*>(e->xbuf + e->off_amax);
+    float* am0 = e->absmax;
+    float* am1 = e->absmax + B;
+    if ((rc = launch("shard_embed", shard_embed_kernel, dim3(std::max(1, H / 8 / 256), B), dim3(256), 0, s, e->embed, cur, H,
+                     static_cast<const int*>(e->d_prompt), e->n_prompt_in_graph, static_cast<const int*>(e->d_next),
+                     static_cast<const int*>(e->d_pos), B))) return rc;
+    const float attn_scale = 1.0f / sqrtf(static_cast<float>(hd));
+    auto linear_b = [&](const Linear& L, const float* am, __half* out, int32_t* ws) {
+        return spb_sparse_bitlinear_gemm(L.meta, L.values, e->xq, out, am, L.gamma, ws, L.rows, L.cols, B, L.ms, L.vs, s);
+    };
+    for (int l = 0; l < c.num_hidden_layers; ++l) {
+        const Layer& L = e->layers[l];
+        __half* kc = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(e->kcache) + l * e->kv_layer_bytes);
+        __half* vc = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(e->vcache) + l * e->kv_layer_bytes);
+        const Linear* g3[3] = {&L.lin[0], &L.lin[1], &L.lin[2]};
+        __half* o3[3] = {e->q, e->k, e->v};
+        const Linear* g1o[1] = {&L.lin[3]};
+        __half* o1o[1] = {e->o};
+        const Linear* g2[2] = {&L.lin[4], &L.lin[5]};
+        __half* o2[2] = {e->gate, e->up};
+        const Linear* g1d[1] = {&L.lin[6]};
+        __half* o1d[1] = {e->down};
+        const __half* delta = l == 0 ? nullptr : down_full;
+        // ---- q / k / v on this rank's heads ----
+        if (B == 1 && e->fused) {
+            if ((rc = bitlinear_resnorm_group(make_group(g3, o3, 3), cur, delta, nullptr, L.norm[0], other, c.rms_norm_eps, s))) return rc;
+            std::swap(cur, other);
+        } else {
+            if ((rc = residual_norm_quant(delta, nullptr, cur, L.norm[0], nullptr, e->xq, am0, H, c.rms_norm_eps, s, B))) return rc;
+            if (B == 1) {
+                if ((rc = bitlinear_q8_group(make_group(g3, o3, 3), e->xq, am0, s))) return rc;
+            } else {
+                for (int i = 0; i < 3; ++i)
+                    if ((rc = linear_b(L.lin[i], am0, o3[i], e->acc + i * e->acc_third))) return rc;
+            }
+        }
+        if ((rc = rope_scatter(e->q, e->k, e->v, kc, vc, e->nh_loc, e->nkv_loc, hd, c.max_position_embeddings, c.rope_theta,
+                               e->d_pos, s, B, B > 1 ? e->seq_stride : 0))) return rc;
+        if (B == 1 && e->split_attention) {
+            if ((rc = decode_attention_split(e->q, kc, vc, e->attn, e->nh_loc, e->nkv_loc, hd, c.max_position_embeddings, 0,
+                                             e->d_pos, attn_scale, e->attn_scratch, s))) return rc;
+        } else if ((rc = decode_attention_pos(e->q, kc, vc, e->attn, e->nh_loc, e->nkv_loc, hd, c.max_position_embeddings,
+                                              attn_scale, e->d_pos, s, B, B > 1 ? e->seq_stride : 0))) {
+            return rc;
+        }
+        {
+            const XSeg sg = seg_of(e->attn, e->off_attn, static_cast<size_t>(e->kv0[r]) * e->group_heads * hd * 2,
+                                   static_cast<size_t>(qdim) * 2, static_cast<size_t>(e->nh_loc) * hd * 2);
+            if ((rc = exchange(e, X_ATTN, &sg, 1))) return rc;
+        }
+        // ---- o_proj rows ----
+        if (B == 1 && e->fused) {
+            if ((rc = bitlinear_amax_group(make_group(g1o, o1o, 1), attn_full, s))) return rc;
+        } else {
+            if ((rc = absmax_quantize_rows(attn_full, e->xq, am1, qdim, B, s))) return rc;
+            if (B == 1) {
+                if ((rc = bitlinear_q8_group(make_group(g1o, o1o, 1), e->xq, am1, s))) return rc;
+            } else if ((rc = linear_b(L.lin[3], am1, e->o, e->acc))) {
+                return rc;
+            }
+        }
+        {
+            const XSeg sg = seg_of(e->o, e->off_o, static_cast<size_t>(e->hrow[r]) * 2, static_cast<size_t>(H) * 2,
+                                   static_cast<size_t>(e->h_loc) * 2);
+            if ((rc = exchange(e, X_O, &sg, 1))) return rc;
+        }
+        // ---- gate / up rows ----
+        if (B == 1 && e->fused) {
+            if ((rc = bitlinear_resnorm_group(make_group(g2, o2, 2), cur, o_full, L.norm[2], L.norm[1], other, c.rms_norm_eps, s))) return rc;
+            std::swap(cur, other);
+        } else {
+            if ((rc = residual_norm_quant(o_full, L.norm[2], cur, L.norm[1], nullptr, e->xq, am0, H, c.rms_norm_eps, s, B))) return rc;
+            if (B == 1) {
+                if ((rc = bitlinear_q8_group(make_group(g2, o2, 2), e->xq, am0, s))) return rc;
+            } else {
+                if ((rc = linear_b(L.lin[4], am0, e->gate, e->acc))) return rc;
+                if ((rc = linear_b(L.lin[5], am0, e->up, e->acc + e->acc_third))) return rc;
+            }
+        }
+        {
+            const XSeg sg[2] = {seg_of(e->gate, e->off_gate, static_cast<size_t>(e->irow[r]) * 2, static_cast<size_t>(inter) * 2,
+                                       static_cast<size_t>(e->i_loc) * 2),
+                                seg_of(e->up, e->off_up, static_cast<size_t>(e->irow[r]) * 2, static_cast<size_t>(inter) * 2,
+                                       static_cast<size_t>(e->i_loc) * 2)};
+            if ((rc = exchange(e, X_GU, sg, 2))) return rc;
+        }
+        // ---- down rows: relu2 * up and ffn_sub_norm need the whole vectors ----
+        if (B == 1 && e->fused) {
+            if ((rc = bitlinear_relu2_group(make_group(g1d, o1d, 1), gate_full, up_full, L.norm[3], c.rms_norm_eps, s))) return rc;
+        } else {
+            if ((rc = relu2_norm_quant(gate_full, up_full, L.norm[3], nullptr, e->xq, am1, inter, c.rms_norm_eps, s, B))) return rc;
+            if (B == 1) {
+                if ((rc = bitlinear_q8_group(make_group(g1d, o1d, 1), e->xq, am1, s))) return rc;
+            } else if ((rc = linear_b(L.lin[6], am1, e->down, e->acc))) {
+                return rc;
+            }
+        }
+        {
+            const XSeg sg = seg_of(e->down, e->off_down, static_cast<size_t>(e->hrow[r]) * 2, static_cast<size_t>(H) * 2,
+                                   static_cast<size_t>(e->h_loc) * 2);
+            if ((rc = exchange(e, X_DOWN, &sg, 1))) return rc;
+        }
+    }
+    // last residual add + final norm, LM head on this rank's vocabulary rows, arg-max candidates
+    if ((rc = residual_norm_quant(c.num_hidden_layers ? down_full : nullptr, nullptr, cur, e->final_norm, e->xfinal, e->xq, am0,
+                                  H, c.rms_norm_eps, s, B))) return rc;
+    if (B == 1) {
+        if ((rc = spb_half_gemv(e->lm_head_loc, e->xfinal, e->logits, e->v_loc, H, s))) return rc;
+    } else if ((rc = half_gemm_rows(e->lm_head_loc, e->xfinal, e->logits, e->v_loc, H, B, s))) {
+        return rc;
+    }
+    if ((rc = launch("shard_argmax", shard_argmax_kernel, dim3(B), dim3(1024), 0, s, static_cast<const float*>(e->logits),
+                     e->v_loc, e->vrow[r], e->pairs))) return rc;
+    {
+        const XSeg sg = seg_of(e->pairs, e->off_amax, static_cast<size_t>(r) * 8, static_cast<size_t>(e->world) * 8, 8);
+        if ((rc = exchange(e, X_AMAX, &sg, 1))) return rc;
+    }
+    return launch("shard_pick", shard_pick_kernel, dim3(1), dim3(kMaxBatch), 0, s, static_cast<const float*>(amax_full), e->world,
+                  B, e->d_next, record ? e->d_out : nullptr, e->d_pos);
+}
+
+int check_ready(const spb_shard_engine* e) {
+    if (!e) return fail(SPB_E_INVALID, "sharded engine: null handle");
+    if (!e->embed || !e->final_norm || !e->lm_head_loc) return fail(SPB_E_INVALID, "sharded engine: globals not set");
+    if (e->world > 1 && !e->peers_set) return fail(SPB_E_INVALID, "sharded engine: peers not set");
+    for (const Layer& L : e->layers) {
+        for (int i = 0; i < 7; ++i)
+            if (!L.lin[i].meta) return fail(SPB_E_INVALID, "sharded engine: a linear layer has no weights attached");
+        if (!L.norm[0] || !L.norm[1]) return fail(SPB_E_INVALID, "sharded engine: a layer norm is missing");
+    }
+    return SPB_OK;
+}
+
+void drop_graph(spb_shard_engine* e) {
+    if (e->graph) cudaGraphExecDestroy(e->graph);
+    e->graph = nullptr;
+}
+
+int ensure_graph(spb_shard_engine* e, bool record, int n_prompt) {
+    if (e->graph && e->graph_records == record && e->n_prompt_in_graph == n_prompt) return SPB_OK;
+    drop_graph(e);
+    e->n_prompt_in_graph = n_prompt;
+    e->fused = true;
+    for (const Layer& L : e->layers) {
+        const Linear* all[7] = {&L.lin[0], &L.lin[1], &L.lin[2], &L.lin[3], &L.lin[4], &L.lin[5], &L.lin[6]};
+        __half* none[7] = {};
+        for (int i = 0; i < 7 && e->fused; ++i) e->fused = bitlinear_group_is_fast(make_group(all + i, none + i, 1));
+    }
+    SPB_CUDA(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
+    const int rc = enqueue_step(e, record);
+    cudaGraph_t g = nullptr;
+    const cudaError_t err = cudaStreamEndCapture(e->stream, &g);
+    if (rc) {
+        if (g) cudaGraphDestroy(g);
+        return rc;
+    }
+    if (err != cudaSuccess) return cuda_fail("cudaStreamEndCapture", err);
+    const cudaError_t ierr = cudaGraphInstantiate(&e->graph, g, 0);
+    cudaGraphDestroy(g);
+    if (ierr != cudaSuccess) return cuda_fail("cudaGraphInstantiate", ierr);
+    e->graph_records = record;
+    return SPB_OK;
+}
+
+int check_status(spb_shard_engine* e, const char* where) {
+    if (*static_cast<volatile int*>(e->status) == 0) return SPB_OK;
+    return fail(SPB_E_TIMEOUT, "%s: rank %d waited longer than %.0f ms for a peer in an exchange; the engine's outputs are "
+                "unspecified and it must be recreated", where, e->rank, e->timeout_ns / 1e6);
+}
+
+class DeviceScope {
+public:
+    explicit DeviceScope(int device) {
+        if (cudaGetDevice(&prev_) != cudaSuccess) prev_ = -1;
+        if (prev_ != device) switched_ = cudaSetDevice(device) == cudaSuccess;
+    }
+    ~DeviceScope() {
+        if (switched_ && prev_ >= 0) cudaSetDevice(prev_);
+    }
+
+private:
+    int prev_ = -1;
+    bool switched_ = false;
+};
+
+}  // namespace
+
+extern "C" spb_shard_engine* spb_shard_engine_create(const spb_model_config* cfg, int rank, int world, int batch) {
+    if (!cfg || cfg->hidden_size <= 0 || cfg->num_hidden_layers < 0 || cfg->num_attention_heads <= 0 ||
+        cfg->num_key_value_heads <= 0 || cfg->head_dim <= 0 || cfg->head_dim % 8 || cfg->intermediate_size <= 0 ||
+        cfg->vocab_size <= 0 || cfg->max_position_embeddings <= 0 || cfg->hidden_size % 8 || cfg->intermediate_size % 8 ||
+        cfg->num_attention_heads % cfg->num_key_value_heads) {
+        fail(SPB_E_INVALID, "spb_shard_engine_create: bad config (hidden, intermediate and head_dim must be multiples of 8)");
+        return nullptr;
+    }
+    if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world || batch < 1 || batch > kMaxBatch ||
+        world > cfg->num_key_value_heads || (world > 1 && cfg->num_hidden_layers < 1)) {
+        fail(SPB_E_INVALID, "spb_shard_engine_create: world 1..%d (at most the KV heads; at least one layer when sharded), "
+             "batch 1..%d", kMaxWorld, kMaxBatch);
+        return nullptr;
+    }
+    spb_shard_engine* e = new (std::nothrow) spb_shard_engine();
+    if (!e) return nullptr;
+    prepare_host_state();
+    e->cfg = *cfg; e->rank = rank; e->world = world; e->batch = batch;
+    e->layers.resize(cfg->num_hidden_layers);
+    cudaGetDevice(&e->device);
+    const int H = cfg->hidden_size, hd = cfg->head_dim, inter = cfg->intermediate_size, B = batch;
+    const int qdim = cfg->num_attention_heads * hd;
+    e->group_heads = cfg->num_attention_heads / cfg->num_key_value_heads;
+    for (int p = 0; p < world; ++p) {
+        int a, b;
+        split_range(cfg->num_key_value_heads, world, p, 1, &a, &b);
+        e->kv0[p] = a; e->kv0[p + 1] = b;
+        split_range(H, world, p, 8, &a, &b);
+        e->hrow[p] = a; e->hrow[p + 1] = b;
+        split_range(inter, world, p, 8, &a, &b);
+        e->irow[p] = a; e->irow[p + 1] = b;
+        split_range(cfg->vocab_size, world, p, 1, &a, &b);
+        e->vrow[p] = a; e->vrow[p + 1] = b;
+    }
+    e->nkv_loc = e->kv0[rank + 1] - e->kv0[rank];
+    e->nh_loc = e->nkv_loc * e->group_heads;
+    e->h_loc = e->hrow[rank + 1] - e->hrow[rank];
+    e->i_loc = e->irow[rank + 1] - e->irow[rank];
+    e->v_loc = e->vrow[rank + 1] - e->vrow[rank];
+    e->split_attention = e->group_heads <= 8 && hd <= 256;
+    e->seq_stride = static_cast<size_t>(e->nkv_loc) * cfg->max_position_embeddings * hd;
+    e->kv_layer_bytes = align_up(sizeof(__half) * e->seq_stride * B, 256);
+    const size_t maxdim = std::max(std::max(H, qdim), inter);
+    const size_t max_rows_loc = std::max(std::max(e->nh_loc * hd, e->h_loc), e->i_loc);
+    e->acc_third = static_cast<size_t>(B) * max_rows_loc;
+    e->out_cap = cfg->max_position_embeddings;
+
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return o; };
+    const size_t o_kc = take(e->kv_layer_bytes * cfg->num_hidden_layers), o_vc = take(e->kv_layer_bytes * cfg->num_hidden_layers);
+    const size_t o_x = take(2 * B * H), o_x2 = take(2 * B * H), o_q = take(2 * B * e->nh_loc * hd), o_k = take(2 * B * e->nkv_loc * hd);
+    const size_t o_v = take(2 * B * e->nkv_loc * hd), o_attn = take(2 * B * e->nh_loc * hd), o_o = take(2 * B * e->h_loc);
+    const size_t o_gate = take(2 * B * e->i_loc), o_up = take(2 * B * e->i_loc), o_down = take(2 * B * e->h_loc), o_xf = take(2 * B * H);
+    const size_t o_xq = take(B * maxdim), o_abs = take(4 * 2 * B), o_acc = take(B > 1 ? 3 * 4 * e->acc_third : 16);
+    const size_t o_ascr = take(decode_attention_scratch_bytes(std::max(e->nh_loc, 1), hd, cfg->max_position_embeddings));
+    const size_t o_logits = take(4 * static_cast<size_t>(B) * e->v_loc), o_pairs = take(8 * B), o_ints = take(4 * (1 + B));
+    const size_t o_out = take(4 * static_cast<size_t>(e->out_cap) * B), o_ctr = take(4 * (2 * X_KINDS + 1));
+    const size_t pool_bytes = off;
+    // exchange buffer
+    off = 0;
+    e->off_flags = take(kFlagBytesPerKind * X_KINDS);
+    e->off_attn = take(2 * static_cast<size_t>(B) * qdim);
+    e->off_o = take(2 * static_cast<size_t>(B) * H);
+    e->off_gate = take(2 * static_cast<size_t>(B) * inter);
+    e->off_up = take(2 * static_cast<size_t>(B) * inter);
+    e->off_down = take(2 * static_cast<size_t>(B) * H);
+    e->off_amax = take(8 * static_cast<size_t>(B) * world);
+    e->xbuf_bytes = off;
+    if (cudaMalloc(&e->pool, pool_bytes) != cudaSuccess || cudaMemset(e->pool, 0, pool_bytes) != cudaSuccess ||
+        cudaMalloc(&e->xbuf, e->xbuf_bytes) != cudaSuccess || cudaMemset(e->xbuf, 0, e->xbuf_bytes) != cudaSuccess ||
+        cudaHostAlloc(reinterpret_cast<void**>(&e->status), sizeof(int), cudaHostAllocPortable | cudaHostAllocMapped) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) != cudaSuccess) {
+        cuda_fail("spb_shard_engine_create", cudaGetLastError());
+        if (e->pool) cudaFree(e->pool);
+        if (e->xbuf) cudaFree(e->xbuf);
+        if (e->status) cudaFreeHost(e->status);
+        delete e;
+        return nullptr;
+    }
+    *e->status = 0;
+    cudaDeviceSynchronize();
+    uint8_t* p = e->pool;
+    e->kcache = reinterpret_cast<__half*>(p + o_kc); e->vcache = reinterpret_cast<__half*>(p + o_vc);
+    e->x = reinterpret_cast<__half*>(p + o_x); e->x2 = reinterpret_cast<__half*>(p + o_x2);
+    e->q = reinterpret_cast<__half*>(p + o_q); e->k = reinterpret_cast<__half*>(p + o_k); e->v = reinterpret_cast<__half*>(p + o_v);
+    e->attn = reinterpret_cast<__half*>(p + o_attn); e->o = reinterpret_cast<__half*>(p + o_o);
+    e->gate = reinterpret_cast<__half*>(p + o_gate); e->up = reinterpret_cast<__half*>(p + o_up);
+    e->down = reinterpret_cast<__half*>(p + o_down); e->xfinal = reinterpret_cast<__half*>(p + o_xf);
+    e->xq = reinterpret_cast<int8_t*>(p + o_xq); e->absmax = reinterpret_cast<float*>(p + o_abs);
+    e->acc = reinterpret_cast<int32_t*>(p + o_acc); e->attn_scratch = reinterpret_cast<float*>(p + o_ascr);
+    e->logits = reinterpret_cast<float*>(p + o_logits); e->pairs = reinterpret_cast<float*>(p + o_pairs);
+    e->d_pos = reinterpret_cast<int*>(p + o_ints); e->d_next = e->d_pos + 1;
+    e->d_out = reinterpret_cast<int*>(p + o_out); e->counters = reinterpret_cast<unsigned*>(p + o_ctr);
+    e->peer[rank] = e->xbuf;
+    return e;
+}
+
+extern "C" void spb_shard_engine_destroy(spb_shard_engine* e) {
+    if (!e) return;
+    DeviceScope scope(e->device);
+    cudaStreamSynchronize(e->stream);
+    drop_graph(e);
+    for (int p = 0; p < e->world; ++p)
+        if (p != e->rank && e->peer[p]) cudaIpcCloseMemHandle(e->peer[p]);
+    if (e->d_prompt) cudaFree(e->d_prompt);
+    cudaFree(e->pool);
+    cudaFree(e->xbuf);
+    cudaFreeHost(e->status);
+    cudaStreamDestroy(e->stream);
+    delete e;
+}
+
+extern "C" int spb_shard_engine_row_range(const spb_shard_engine* e, int which, int* start, int* stop) {
+    if (!e || !start || !stop || which < 0 || which > 7) return fail(SPB_E_INVALID, "spb_shard_engine_row_range: bad arguments");
+    const int hd = e->cfg.head_dim, r = e->rank;
+    switch (which) {
+        case 0: *start = e->kv0[r] * e->group_heads * hd; *stop = e->kv0[r + 1] * e->group_heads * hd; break;
+        case 1: case 2: *start = e->kv0[r] * hd; *stop = e->kv0[r + 1] * hd; break;
+        case 3: case 6: *start = e->hrow[r]; *stop = e->hrow[r + 1]; break;
+        case 4: case 5: *start = e->irow[r]; *stop = e->irow[r + 1]; break;
+        default: *start = e->vrow[r]; *stop = e->vrow[r + 1]; break;
+    }
+    return SPB_OK;
+}
+
+extern "C" int spb_shard_engine_ipc_handle(spb_shard_engine* e, void* handle_out) {
+    if (!e || !handle_out) return fail(SPB_E_INVALID, "spb_shard_engine_ipc_handle: null pointer");
+    DeviceScope scope(e->device);
+    cudaIpcMemHandle_t h;
+    SPB_CUDA(cudaIpcGetMemHandle(&h, e->xbuf));
+    static_assert(sizeof(h) == 64, "CUDA IPC handles are 64 bytes");
+    std::memcpy(handle_out, &h, sizeof h);
+    return SPB_OK;
+}
+
+extern "C" int spb_shard_engine_set_peers(spb_shard_engine* e, const void* handles) {
+    if (!e || (e->world > 1 && !handles)) return fail(SPB_E_INVALID, "spb_shard_engine_set_peers: null pointer");
+    if (e->peers_set) return fail(SPB_E_INVALID, "spb_shard_engine_set_peers: peers already set");
+    DeviceScope scope(e->device);
+    for (int p = 0; p < e->world; ++p) {
+        if (p == e->rank) continue;
+        cudaIpcMemHandle_t h;
+        std::memcpy(&h, static_cast<const uint8_t*>(handles) + 64 * p, sizeof h);
+        void* ptr = nullptr;
+        SPB_CUDA(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+        e->peer[p] = static_cast<uint8_t*>(ptr);
+    }
+    e->peers_set = true;
+    drop_graph(e);
+    return SPB_OK;
+}
+
+extern "C" int spb_shard_engine_set_peer_pointers(spb_shard_engine* e, void* const* buffers) {
+    // same-process form (and the failure test's stand-in peer): device pointers that this GPU can already reach
+    if (!e || !buffers) return fail(SPB_E_INVALID, "spb_shard_engine_set_peer_pointers: null pointer");
+    if (e->peers_set) return fail(SPB_E_INVALID, "spb_shard_engine_set_peer_pointers: peers already set");
+    for (int p = 0; p < e->world; ++p)
+        if (p != e->rank) {
+            if (!buffers[p]) return fail(SPB_E_INVALID, "spb_shard_engine_set_peer_pointers: null buffer for rank %d", p);
+            e->peer[p] = static_cast<uint8_t*>(buffers[p]);
+        }
+    e->peers_set = true;
+    drop_graph(e);
+    return SPB_OK;
+}
+
+extern "C" size_t spb_shard_engine_exchange_bytes(const spb_shard_engine* e) { return e ? e->xbuf_bytes : 0; }
+
+extern "C" int spb_shard_engine_set_timeout_ms(spb_shard_engine* e, int ms) {
+    if (!e || ms < 1) return fail(SPB_E_INVALID, "spb_shard_engine_set_timeout_ms: bad arguments");
+    e->timeout_ns = static_cast<unsigned long long>(ms) * 1000000ull;
+    drop_graph(e);
+    return SPB_OK;
+}
+
+extern "C" int spb_shard_engine_set_linear(spb_shard_engine* e, int layer, int which, const uint32_t* d_meta,
+                                           const uint32_t* d_values, float gamma, int rows, int cols, int meta_stride,
+                                           int values_stride) {
+    if (!e || layer < 0 || layer >= static_cast<int>(e->layers.size()) || which < 0 || which > 6)
+        return fail(SPB_E_INVALID, "spb_shard_engine_set_linear: bad layer/which");
+    if (!d_meta || !d_values || rows <= 0 || cols <= 0 || cols % 4) return fail(SPB_E_INVALID, "spb_shard_engine_set_linear: bad tensor");
+    int a = 0, b = 0;
+    spb_shard_engine_row_range(e, which, &a, &b);
+    const spb_model_config& c = e->cfg;
+    const int qdim = c.num_attention_heads * c.head_dim;
+    const int want_cols[7] = {c.hidden_size, c.hidden_size, c.hidden_size, qdim, c.hidden_size, c.hidden_size, c.intermediate_size};
+    if (rows != b - a || cols != want_cols[which])
+        return fail(SPB_E_INVALID, "spb_shard_engine_set_linear: layer %d tensor %d is %dx%d, rank %d of %d owns %dx%d", layer, which,
+                    rows, cols, e->rank, e->world, b - a, want_cols[which]);
+    Linear& L = e->layers[layer].lin[which];
+    L.meta = d_meta; L.values = d_values; L.gamma = gamma; L.rows = rows; L.cols = cols; L.ms = meta_stride; L.vs = values_stride;
+    drop_graph(e);
+    return SPB_OK;
+}
+
+extern "C" int spb_shard_engine_set_norm(spb_shard_engine* e, int layer, int which, const float* d_weight) {
+    if (!e || layer < 0 || layer >= static_cast<int>(e->layers.size()) || which < 0 || which > 3)
+        return fail(SPB_E_INVALID, "spb_shard_engine_set_norm: bad layer/which");
+    e->layers[layer].norm[which] = d_weight;
+    drop_graph(e);
+    return SPB_OK;
+}
+
+extern "C" int spb_shard_engine_set_globals(spb_shard_engine* e, const void* d_embed, const void* d_lm_head_rows,
+                                            const float* d_final_norm) {
+    if (!e || !d_embed || !d_lm_head_rows || !d_final_norm) return fail(SPB_E_INVALID, "spb_shard_engine_set_globals: null pointer");
+    e->embed = static_cast<const __half*>(d_embed);
+    e->lm_head_loc = static_cast<const __half*>(d_lm_head_rows);
+    e->final_norm = d_final_norm;
+    drop_graph(e);
+    return SPB_OK;
+}
+
+extern "C" int spb_shard_engine_reset(spb_shard_engine* e) {
+    if (!e) return fail(SPB_E_INVALID, "spb_shard_engine_reset: null handle");
+    DeviceScope scope(e->device);
+    const size_t kv_total = e->kv_layer_bytes * e->cfg.num_hidden_layers;
+    SPB_CUDA(cudaMemsetAsync(e->kcache, 0, kv_total, e->stream));
+    SPB_CUDA(cudaMemsetAsync(e->vcache, 0, kv_total, e->stream));
+    SPB_CUDA(cudaMemsetAsync(e->d_pos, 0, 4 * (1 + e->batch), e->stream));
+    SPB_CUDA(cudaStreamSynchronize(e->stream));
+    e->seq_len = 0;
+    return SPB_OK;
+}
+
+extern "C" int spb_shard_engine_seq_len(const spb_shard_engine* e) { return e ? e->seq_len : 0; }
+
+extern "C" int spb_shard_engine_step(spb_shard_engine* e, const int* tokens) {
+    int rc = check_ready(e);
+    if (rc) return rc;
+    if (!tokens) return fail(SPB_E_INVALID, "spb_shard_engine_step: null pointer");
+    for (int b = 0; b < e->batch; ++b)
+        if (tokens[b] < 0 || tokens[b] >= e->cfg.vocab_size) return fail(SPB_E_INVALID, "spb_shard_engine_step: token outside the vocabulary");
+    if (e->seq_len >= e->cfg.max_position_embeddings) return fail(SPB_E_INVALID, "spb_shard_engine_step: KV cache full");
+    DeviceScope scope(e->device);
+    if ((rc = ensure_graph(e, false, 0))) return rc;
+    SPB_CUDA(cudaMemcpyAsync(e->d_next, tokens, sizeof(int) * e->batch, cudaMemcpyHostToDevice, e->stream));
+    SPB_CUDA(cudaGraphLaunch(e->graph, e->stream));
+    SPB_CUDA(cudaStreamSynchronize(e->stream));
+    e->seq_len++;
+    return check_status(e, "spb_shard_engine_step");
+}
+
+extern "C" int spb_shard_engine_copy_logits(spb_shard_engine* e, float* h_logits_rows) {
+    if (!e || !h_logits_rows) return fail(SPB_E_INVALID, "spb_shard_engine_copy_logits: null pointer");
+    DeviceScope scope(e->device);
+    SPB_CUDA(cudaMemcpyAsync(h_logits_rows, e->logits, sizeof(float) * e->batch * e->v_loc, cudaMemcpyDeviceToHost, e->stream));
+    SPB_CUDA(cudaStreamSynchronize(e->stream));
+    return check_status(e, "spb_shard_engine_copy_logits");
+}
+
+extern "C" int spb_shard_engine_generate(spb_shard_engine* e, const int* prompt, int n_prompt, int max_tokens, int* out_tokens) {
+    int rc = check_ready(e);
+    if (rc) return rc;
+    if (!prompt || n_prompt < 1 || max_tokens < 0 || (max_tokens > 0 && !out_tokens))
+        return fail(SPB_E_INVALID, "spb_shard_engine_generate: bad arguments");
+    const int B = e->batch, start = e->seq_len, steps = n_prompt - 1 + max_tokens;
+    if (start + steps > e->cfg.max_position_embeddings || start + steps > e->out_cap)
+        return fail(SPB_E_INVALID, "spb_shard_engine_generate: %d positions exceed the KV cache", start + steps);
+    for (int i = 0; i < n_prompt * B; ++i)
+        if (prompt[i] < 0 || prompt[i] >= e->cfg.vocab_size) return fail(SPB_E_INVALID, "spb_shard_engine_generate: token outside the vocabulary");
+    DeviceScope scope(e->device);
+    const int need = start + n_prompt;  // the prompt table is indexed by absolute position
+    if (need > e->prompt_cap) {
+        if (e->d_prompt) cudaFree(e->d_prompt);
+        e->d_prompt = nullptr;
+        const int cap = std::max(need, 1024);
+        SPB_CUDA(cudaMalloc(&e->d_prompt, sizeof(int) * cap * B));
+        e->prompt_cap = cap;
+        drop_graph(e);
+    }
+    SPB_CUDA(cudaMemcpyAsync(e->d_prompt + static_cast<size_t>(start) * B, prompt, sizeof(int) * n_prompt * B, cudaMemcpyHostToDevice, e->stream));
+    if ((rc = ensure_graph(e, true, need))) return rc;
+    for (int s = 0; s < steps; ++s) SPB_CUDA(cudaGraphLaunch(e->graph, e->stream));
+    e->seq_len += steps;
+    if (max_tokens > 0)
+        SPB_CUDA(cudaMemcpyAsync(out_tokens, e->d_out + static_cast<size_t>(start + n_prompt - 1) * B, sizeof(int) * max_tokens * B,
+                                 cudaMemcpyDeviceToHost, e->stream));
+    SPB_CUDA(cudaStreamSynchronize(e->stream));
+    if ((rc = check_status(e, "spb_shard_engine_generate"))) return rc;
+    return max_tokens;
+}

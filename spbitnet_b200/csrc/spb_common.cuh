@@ -29,7 +29,7 @@ int sm_count();
 int ensure_dynamic_smem_impl(const char* name, const void* kernel, size_t bytes);
 template <typename... KArgs>
 int ensure_dynamic_smem(const char* name, void (*kernel)(KArgs...), size_t bytes) {
-    if (bytes <= 48 * 1024) return SPB_OK;
+    // no shortcut for small sizes: the default limit of 48 KB covers static + dynamic shared memory together
     return ensure_dynamic_smem_impl(name, reinterpret_cast<const void*>(kernel), bytes);
 }
 
@@ -40,6 +40,9 @@ int ensure_dynamic_smem(const char* name, void (*kernel)(KArgs...), size_t bytes
 int* timeout_counter();
 // Current value of the counter (0 when it could not be allocated).
 int timeouts_now();
+// Performs every lazy host-side look-up and allocation of the launchers (gemm_tcsp_ws.cu); engines call it at
+// creation, outside any stream capture.
+void prepare_host_state();
 
 // Launches `kernel` on `stream`.  With PDL enabled the launch carries
 // cudaLaunchAttributeProgrammaticStreamSerialization, so the grid may start

@@ -62,6 +62,15 @@ class InferenceEngine:
         check(self._lib.spb_engine_set_globals(self._h, C.c_void_p(model.embed.data_ptr()), head,
                                                C.c_void_p(model.final_norm.data_ptr())))
 
+    @classmethod
+    def from_loaded(cls, loaded):
+        """An engine over a model directory read by the C++ loader (spbitnet_b200.tokenizer.LoadedModel)."""
+        self = cls.__new__(cls)
+        self._lib = load()
+        self.model = loaded
+        self._h = loaded.engine_handle()
+        return self
+
     def forward(self, token_id: int) -> int:
         """One token; returns the device address of the logits (vocab_size float32)."""
         out = C.c_void_p(0)

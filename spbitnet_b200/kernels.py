@@ -42,6 +42,11 @@ def set_gemm_variant(variant: int) -> int:
     return load().spb_set_gemm_variant(int(variant))
 
 
+def set_gemm_row_halves(halves: int) -> int:
+    """0 automatic, 1 / 2 weight-row halves per block of the tcgen05 product; returns the previous setting."""
+    return load().spb_set_gemm_row_halves(int(halves))
+
+
 def gemm_tc_timeouts() -> int:
     return load().spb_gemm_tc_timeouts()
 

@@ -11,7 +11,9 @@ Sources of truth used here:
                                 relu2_mul, half_gemv, InferenceEngine.forward
   * include/spbitnet/sparse_ternary_tensor.h through oracle/_ref/libspb_ref.so
     (pack_from_dense, pack_with_pruning, unpack_to_int8, and the test-style CPU GEMV)
-The tests read only the .npz files written here; nothing at test time touches the reference.
+  * src/tokenizer.cpp through oracle/_ref/libspb_reftok.so (encode / decode on the synthetic tokenizer.json of
+    tests/tokenizer_fixture.py) -> tokenizer_golden.json
+The tests read only the files written here; nothing at test time touches the reference.
 """
 import argparse
 import hashlib
@@ -154,7 +156,22 @@ def main():
         tokens.append(tok)
     np.savez_compressed(HERE / "engine_py.npz", prompt=prompt.astype(np.int32), tokens=np.array(tokens, np.int32),
                         logits=np.stack(logits), seed=np.int32(5))
-    for f in sorted(HERE.glob("*.npz")):
+    # ---- tokenizer: ids and decoded bytes from the reference's own src/tokenizer.cpp ----------------
+    import json
+    import tempfile
+    sys.path.insert(0, str(ROOT / "tests"))
+    import tokenizer_fixture as tf
+    with tempfile.TemporaryDirectory() as d:
+        path = Path(d) / "tokenizer.json"
+        tf.write(path)
+        ref = oracle.RefTokenizer(path)
+        cases = []
+        for text in tf.TEXTS:
+            raw = text.encode("utf-8")
+            ids = ref.encode(raw)
+            cases.append({"text_hex": raw.hex(), "ids": ids, "decoded_hex": ref.decode(ids).hex()})
+        (HERE / "tokenizer_golden.json").write_text(json.dumps({"vocab_size": ref.vocab_size, "cases": cases}, indent=0))
+    for f in sorted(HERE.glob("*.npz")) + [HERE / "tokenizer_golden.json"]:
         print(f.name, f.stat().st_size)
 
 

@@ -25,8 +25,16 @@ def full_case(request):
     return case
 
 
+@pytest.fixture(params=[0, 1, 2], ids=["rows-auto", "rows-128", "rows-256"])
+def row_halves(request):
+    """Weight rows per block of the tcgen05 form: automatic, 128, or 256 (two accumulators on one activation tile)."""
+    old = K.set_gemm_row_halves(request.param)
+    yield request.param
+    K.set_gemm_row_halves(old)
+
+
 @pytest.mark.parametrize("n", [256, 1024])
-def test_gemm_int32_every_element(full_case, n):
+def test_gemm_int32_every_element(full_case, n, row_halves):
     c = full_case
     rows, cols = c["rows"], c["cols"]
     before = K.gemm_tc_timeouts()
@@ -38,8 +46,32 @@ def test_gemm_int32_every_element(full_case, n):
     assert K.gemm_tc_timeouts() == before
 
 
+@pytest.mark.parametrize("rows,cols,n", [(300, 512, 200), (256, 256, 129), (129, 384, 257), (1000, 1024, 300),
+                                          (257, 2560, 240), (512, 128, 241)])
+def test_two_row_halves_on_ragged_shapes(rows, cols, n):
+    # 256-row blocks forced on shapes that do not fill them: row tails in either half, batch tails, one K step
+    case = synth.gemm_case(rows, cols, n, seed=rows + n)
+    want = oracle.sparse_gemm(case["meta"], case["values"], case["X"], rows, cols)
+    before = K.gemm_tc_timeouts()
+    old = K.set_gemm_row_halves(2)
+    try:
+        Y = Guarded(n * rows * 4)
+        K.sparse_ternary_gemm_gpu(dev(case["meta"]), dev(case["values"]), dev(case["X"]), Y.ptr, rows, cols, n,
+                                  case["meta_stride"], case["values_stride"])
+        assert (Y.read(np.int32).reshape(n, rows) == want).all()
+        absmax = case["absmax"]
+        out = Guarded(n * rows * 2)
+        K.sparse_bitlinear_gemm_gpu(dev(case["meta"]), dev(case["values"]), dev(case["X"]), out.ptr, dev(absmax), 0.05,
+                                    rows, cols, n, case["meta_stride"], case["values_stride"])
+        wh = np.stack([oracle.dequantize(want[j], absmax[j], np.float32(0.05)) for j in range(n)])
+        assert (out.read(np.float16).reshape(n, rows).view(np.uint16) == wh.view(np.uint16)).all()
+    finally:
+        K.set_gemm_row_halves(old)
+    assert K.gemm_tc_timeouts() == before
+
+
 @pytest.mark.parametrize("n", [256, 1024])
-def test_bitlinear_gemm_half_every_element(full_case, n):
+def test_bitlinear_gemm_half_every_element(full_case, n, row_halves):
     c = full_case
     rows, cols = c["rows"], c["cols"]
     gamma = np.float32(0.0213)
