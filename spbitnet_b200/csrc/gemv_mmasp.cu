@@ -227,12 +227,155 @@ __global__ void __launch_bounds__(kGmThreads, SPB_GEMV_MMA_MIN_BLOCKS) gemv_mmas
     }
 }
 
+// The same kernel for rows too long to hold whole in shared memory (cols > 16384, e.g. a 28672-column down
+// projection): the K extent is cut into chunks of `csteps` steps whose raw slabs alternate between two buffers,
+// chunk c + 1 being copied while chunk c is multiplied; the accumulators live across chunks, x is staged whole.
+// Inside a chunk the work split is the one above (KS warps per row block, contiguous step ranges).
+struct GmChunkArgs {
+    GmArgs g;
+    int csteps;      // steps per chunk (a multiple of 4 * ks)
+    int nchunks;
+    int slab_bytes;  // one buffer: 16 rb x (mpitch + vpitch) words
+};
+
+__global__ void __launch_bounds__(kGmThreads, 2) gemv_mmasp_chunked_kernel(const GmChunkArgs ca) {
+    const GmArgs& a = ca.g;
+    __shared__ __align__(16) uint32_t sgn_tab[16 * 32];
+    __shared__ int red[kGmWarps * 16];
+    extern __shared__ __align__(16) uint8_t gm_raw[];  // [x, permuted: cols bytes][slab 0][slab 1]
+    const uint32_t tab_s = static_cast<uint32_t>(__cvta_generic_to_shared(sgn_tab));
+    const uint32_t xs_s = static_cast<uint32_t>(__cvta_generic_to_shared(gm_raw));
+    const uint32_t slab0_s = xs_s + static_cast<uint32_t>(a.cols);
+    const int nrows_blk = 16 * a.rb;
+    const uint32_t v_in_slab = static_cast<uint32_t>(nrows_blk * a.mpitch) * 4u;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int row0 = blockIdx.x * nrows_blk;
+    const int valid = min(nrows_blk, a.rows - row0);
+    const int mch = ca.csteps >> 1, vch = ca.csteps >> 2;  // 16-byte pieces of a row's chunk: 8 / 4 bytes per step
+
+    auto issue_chunk = [&](int c) {
+        const int steps_here = min(ca.csteps, a.steps - c * ca.csteps);
+        const int m_here = (steps_here + 1) >> 1, v_here = (steps_here + 3) >> 2, cpr = m_here + v_here;
+        const uint32_t ms_s = slab0_s + static_cast<uint32_t>(c & 1) * ca.slab_bytes, vs_s = ms_s + v_in_slab;
+        const size_t m_col = static_cast<size_t>(c) * mch * 16, v_col = static_cast<size_t>(c) * vch * 16;
+        for (int k = lane; k < cpr; k += 32) {
+            const bool is_m = k < m_here;
+            const uint8_t* src = is_m ? reinterpret_cast<const uint8_t*>(a.meta) + m_col + k * 16
+                                      : reinterpret_cast<const uint8_t*>(a.values) + v_col + (k - m_here) * 16;
+            const size_t src_pitch = static_cast<size_t>(is_m ? a.meta_stride : a.values_stride) * 4u;
+            const uint32_t dst = is_m ? ms_s + static_cast<uint32_t>(k) * 16u : vs_s + static_cast<uint32_t>(k - m_here) * 16u;
+            const uint32_t dst_pitch = static_cast<uint32_t>(is_m ? a.mpitch : a.vpitch) * 4u;
+            src += static_cast<size_t>(row0 + warp) * src_pitch;
+            for (int r = warp; r < valid; r += kGmWarps) {
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + static_cast<uint32_t>(r) * dst_pitch), "l"(src)
+                             : "memory");
+                src += kGmWarps * src_pitch;
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    issue_chunk(0);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const uint32_t i = tid + j * kGmThreads;
+        const uint32_t t = ((i >> 5) * 0x00204081u) & 0x01010101u;
+        sgn_tab[i] = (t * 0xFEu) | 0x01010101u;
+    }
+    const int g = lane >> 2, tig = lane & 3;
+    const int warp_u = __shfl_sync(0xFFFFFFFFu, warp, 0);
+    const int rbi = warp_u >> a.ks_log2, kq = warp_u & (a.ks - 1);
+    const uint32_t lane_or = static_cast<uint32_t>(lane) << 2;
+    const uint32_t rot_lo = (static_cast<uint32_t>(tig) * 4u + 25u) & 31u, rot_hi = (static_cast<uint32_t>(tig) * 4u + 9u) & 31u;
+    const uint32_t v_half = static_cast<uint32_t>(8 * a.vpitch) * 4u;
+
+    grid_dep_wait();
+    grid_dep_launch();
+    for (int q = tid; q < (a.cols >> 4); q += kGmThreads) {
+        const uint4 xv = __ldg(reinterpret_cast<const uint4*>(a.x) + q);
+        const uint32_t st = static_cast<uint32_t>(q) >> 2, j = static_cast<uint32_t>(q) & 3u;
+        const uint32_t d = xs_s + st * 64u + j * 4u;
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(d), "r"(xv.x) : "memory");
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(d + 16u), "r"(xv.y) : "memory");
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(d + 32u), "r"(xv.z) : "memory");
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(d + 48u), "r"(xv.w) : "memory");
+    }
+    int c0 = 0, c1 = 0, c2 = 0, c3 = 0;
+    for (int c = 0; c < ca.nchunks; ++c) {
+        if (c + 1 < ca.nchunks) {
+            issue_chunk(c + 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();  // chunk c has landed for every thread (and, at c == 0, the table and x are visible)
+        const int steps_here = min(ca.csteps, a.steps - c * ca.csteps);
+        const int s_begin = kq * a.spw, s_end = min(steps_here, s_begin + a.spw);  // within the chunk; spw % 4 == 0
+        const uint32_t ms_s = slab0_s + static_cast<uint32_t>(c & 1) * ca.slab_bytes, vs_s = ms_s + v_in_slab;
+        uint32_t me_p = ms_s + static_cast<uint32_t>((rbi * 16 + g + 8 * (tig & 1)) * a.mpitch + (tig >> 1) + 2 * s_begin) * 4u;
+        uint32_t v0_p = vs_s + static_cast<uint32_t>((rbi * 16 + g) * a.vpitch + s_begin) * 4u;
+        uint32_t xq_p = xs_s + static_cast<uint32_t>(tig) * 16u + static_cast<uint32_t>(c * ca.csteps + s_begin) * 64u;
+        auto step = [&](uint32_t w0, uint32_t w1, uint32_t me_off, uint32_t x_off) {
+            const uint32_t e = gm_index_pairs(gm_lds(me_p + me_off));
+            const uint32_t a0 = gm_tab(tab_s, (__funnelshift_r(w0, w0, rot_lo) & 0x780u) | lane_or);
+            const uint32_t a1 = gm_tab(tab_s, (__funnelshift_r(w1, w1, rot_lo) & 0x780u) | lane_or);
+            const uint32_t a2 = gm_tab(tab_s, (__funnelshift_r(w0, w0, rot_hi) & 0x780u) | lane_or);
+            const uint32_t a3 = gm_tab(tab_s, (__funnelshift_r(w1, w1, rot_hi) & 0x780u) | lane_or);
+            uint32_t b0, b1, b2, b3;
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(xq_p + x_off));
+            asm volatile(
+                "mma.sp::ordered_metadata.sync.aligned.m16n8k64.row.col.s32.s8.s8.s32 "
+                "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9, %10, %11}, {%0, %1, %2, %3}, %12, 0x0;"
+                : "+r"(c0), "+r"(c1), "+r"(c2), "+r"(c3)
+                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(b2), "r"(b3), "r"(e));
+        };
+        int st = s_begin;
+        for (; st + 4 <= s_end; st += 4) {
+            uint4 w0, w1;
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w0.x), "=r"(w0.y), "=r"(w0.z), "=r"(w0.w) : "r"(v0_p));
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w1.x), "=r"(w1.y), "=r"(w1.z), "=r"(w1.w) : "r"(v0_p + v_half));
+            step(w0.x, w1.x, 0u, 0u);
+            step(w0.y, w1.y, 8u, 64u);
+            step(w0.z, w1.z, 16u, 128u);
+            step(w0.w, w1.w, 24u, 192u);
+            me_p += 32u; v0_p += 16u; xq_p += 256u;
+        }
+        for (; st < s_end; ++st) {  // a last chunk whose step count is not a multiple of four
+            step(gm_lds(v0_p), gm_lds(v0_p + v_half), 0u, 0u);
+            me_p += 8u; v0_p += 4u; xq_p += 64u;
+        }
+        __syncthreads();  // everybody is done with this buffer before chunk c + 2 is copied into it
+    }
+    if (tig == 0) {
+        red[warp_u * 16 + g] = c0;
+        red[warp_u * 16 + g + 8] = c2;
+    }
+    __syncthreads();
+    if (tid < nrows_blk && tid < valid) {
+        const int rblk = tid >> 4, r = tid & 15;
+        int acc = 0;
+        for (int k = 0; k < a.ks; ++k) acc += red[((rblk << a.ks_log2) + k) * 16 + r];
+        const int row = row0 + tid;
+        if (a.out_mode == GM_OUT_I32) {
+            static_cast<int32_t*>(a.y)[row] = acc;
+        } else {
+            const float f = __fmul_rn(static_cast<float>(acc), dequant_scale(a.gamma, *a.d_absmax));
+            if (a.out_mode == GM_OUT_F32) {
+                static_cast<float*>(a.y)[row] = f;
+                if (a.y_acc) a.y_acc[row] = acc;
+            } else {
+                static_cast<__half*>(a.y)[row] = __float2half_rn(f);
+            }
+        }
+    }
+}
+
 // Whether the layout can take this kernel: whole 16-byte sign rows (cols % 256 == 0), 16-byte aligned
 // rows in both arrays and x, and a slab that fits in shared memory.
 bool gemv_mmasp_supported(const uint32_t* meta, const uint32_t* values, const int8_t* x, int rows, int cols,
                           int meta_stride, int values_stride) {
     auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
-    return rows > 0 && cols > 0 && cols % 256 == 0 && cols <= 16384 && meta_stride % 4 == 0 && values_stride % 4 == 0 &&
+    return rows > 0 && cols > 0 && cols % 256 == 0 && cols <= 65536 && meta_stride % 4 == 0 && values_stride % 4 == 0 &&
            al16(meta) && al16(values) && al16(x);
 }
 
@@ -246,6 +389,21 @@ int gemv_mmasp_launch(const char* name, const uint32_t* meta, const uint32_t* va
     a.meta = meta; a.values = values; a.x = x; a.y = y; a.y_acc = y_acc; a.d_absmax = d_absmax; a.gamma = gamma;
     a.out_mode = out_mode; a.rows = rows; a.cols = cols; a.meta_stride = meta_stride; a.values_stride = values_stride;
     a.steps = cols / 64;
+    if (cols > 16384) {  // rows too long for one slab: chunks of 64 steps (4096 columns), four warps per row block
+        GmChunkArgs ca{};
+        a.ks = 4; a.ks_log2 = 2; a.rb = 2;
+        ca.csteps = 64;
+        a.spw = ca.csteps / a.ks;
+        a.mpitch = pitch(ca.csteps * 2);
+        a.vpitch = pitch(ca.csteps);
+        ca.nchunks = (a.steps + ca.csteps - 1) / ca.csteps;
+        ca.slab_bytes = 16 * a.rb * (a.mpitch + a.vpitch) * 4;
+        ca.g = a;
+        const size_t smem = static_cast<size_t>(cols) + 2 * static_cast<size_t>(ca.slab_bytes);
+        if (int rc = ensure_dynamic_smem(name, gemv_mmasp_chunked_kernel, smem)) return rc;
+        const unsigned blocks = static_cast<unsigned>((rows + 16 * a.rb - 1) / (16 * a.rb));
+        return launch(name, gemv_mmasp_chunked_kernel, dim3(blocks), dim3(kGmThreads), smem, stream, ca);
+    }
     // Warps per row block: long step ranges per warp amortise a warp's fixed cost (measured: about 20 steps
     // per warp is best at 6912 x 2560), but a small matrix still has to give every SM a few warps.
     const int row_blocks = (rows + 15) / 16;

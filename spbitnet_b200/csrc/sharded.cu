@@ -79,15 +79,27 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
 
 template <typename T>
 __device__ __forceinline__ void xcopy(const XArgs& a, int tid_global, int nthreads) {
+    constexpr int kUnroll = 4;  // loads of four pieces in flight per thread before the first store
     for (int s = 0; s < a.nseg; ++s) {
         const XSeg& g = a.seg[s];
         const uint32_t per_row = g.len / sizeof(T);
         const uint32_t total = per_row * static_cast<uint32_t>(a.rows);
-        for (uint32_t i = tid_global; i < total; i += nthreads) {
-            const uint32_t row = i / per_row, c = i - row * per_row;
-            const T v = reinterpret_cast<const T*>(g.src + static_cast<size_t>(row) * g.len)[c];
-            const size_t o = static_cast<size_t>(g.dst_off) + static_cast<size_t>(row) * g.dst_pitch + static_cast<size_t>(c) * sizeof(T);
-            for (int p = 0; p < a.world; ++p) *reinterpret_cast<T*>(a.peer[p] + o) = v;
+        for (uint32_t i0 = tid_global; i0 < total; i0 += kUnroll * nthreads) {
+            T v[kUnroll];
+            size_t o[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const uint32_t i = i0 + u * nthreads;
+                if (i < total) {
+                    const uint32_t row = a.rows == 1 ? 0u : i / per_row, c = i - row * per_row;
+                    v[u] = reinterpret_cast<const T*>(g.src + static_cast<size_t>(row) * g.len)[c];
+                    o[u] = static_cast<size_t>(g.dst_off) + static_cast<size_t>(row) * g.dst_pitch + static_cast<size_t>(c) * sizeof(T);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u)
+                if (i0 + u * nthreads < total)
+                    for (int p = 0; p < a.world; ++p) *reinterpret_cast<T*>(a.peer[p] + o[u]) = v[u];
         }
     }
 }
@@ -101,20 +113,22 @@ __global__ void __launch_bounds__(256) exchange_kernel(const XArgs a) {
     const int tid = blockIdx.x * blockDim.x + threadIdx.x, nthreads = gridDim.x * blockDim.x;
     if (WIDE) xcopy<uint4>(a, tid, nthreads);
     else xcopy<uint32_t>(a, tid, nthreads);
-    __threadfence_system();
+    __threadfence_system();  // every thread's stores are ordered before what follows its barrier arrival
     __syncthreads();
     if (threadIdx.x == 0) {
-        const unsigned ticket = atomicAdd(a.done, 1u);
+        const unsigned ticket = gridDim.x == 1 ? 0u : atomicAdd(a.done, 1u);
         s_last = ticket == gridDim.x - 1 ? 1u : 0u;
         if (s_last) {
-            *a.done = 0;
+            if (gridDim.x > 1) {
+                *a.done = 0;
+                __threadfence();  // the other blocks' stores (ordered before their tickets) before the flags below
+            }
             s_seq = *a.seqno + 1;
             *a.seqno = s_seq;
         }
     }
     __syncthreads();
     if (!s_last) return;
-    __threadfence_system();
     const unsigned seq = s_seq;
     const int p = threadIdx.x;
     if (p < a.world && p != a.rank) {
@@ -150,42 +164,63 @@ __global__ void __launch_bounds__(256) shard_embed_kernel(const __half* __restri
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < hidden / 8; i += gridDim.x * blockDim.x) dst[i] = row[i];
 }
 
-// First maximum of the rank's logits of sequence blockIdx.x (std::max_element order): (value, global index).
-__global__ void __launch_bounds__(1024) shard_argmax_kernel(const float* __restrict__ logits, int n, int index0,
-                                                            float* __restrict__ out_pairs) {
+// First maximum of the rank's logits (std::max_element order), two stages.  Stage 1: block (x, b) scans a strided
+// share of sequence b's row and leaves one candidate (value, local index).  Stage 2: block b folds the candidates of
+// sequence b into (value, global index).
+__device__ __forceinline__ void argmax_take(float& a, int& ai, float b, int bi) {
+    if (bi != 0x7FFFFFFF && (ai == 0x7FFFFFFF || b > a || (b == a && bi < ai))) { a = b; ai = bi; }
+}
+__device__ __forceinline__ void argmax_block_fold(float& best, int& besti, float* sv, int* si) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+        argmax_take(best, besti, __shfl_xor_sync(0xFFFFFFFFu, best, off), __shfl_xor_sync(0xFFFFFFFFu, besti, off));
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    if (lane == 0) { sv[warp] = best; si[warp] = besti; }
+    __syncthreads();
+    if (warp == 0) {
+        best = lane < nw ? sv[lane] : -INFINITY;
+        besti = lane < nw ? si[lane] : 0x7FFFFFFF;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1)
+            argmax_take(best, besti, __shfl_xor_sync(0xFFFFFFFFu, best, off), __shfl_xor_sync(0xFFFFFFFFu, besti, off));
+    }
+}
+__global__ void __launch_bounds__(1024) shard_argmax1_kernel(const float* __restrict__ logits, int n, float* __restrict__ cand) {
     __shared__ float sv[32];
     __shared__ int si[32];
     grid_dep_launch();
     grid_dep_wait();
-    const float* v = logits + static_cast<size_t>(blockIdx.x) * n;
+    const float* v = logits + static_cast<size_t>(blockIdx.y) * n;
     float best = -INFINITY;
     int besti = 0x7FFFFFFF;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         const float x = v[i];
         if (besti == 0x7FFFFFFF || x > best) {  // i grows: a later equal value never replaces an earlier one
             best = x;
             besti = i;
         }
     }
-    auto take = [](float& a, int& ai, float b, int bi) {
-        if (bi != 0x7FFFFFFF && (ai == 0x7FFFFFFF || b > a || (b == a && bi < ai))) { a = b; ai = bi; }
-    };
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1)
-        take(best, besti, __shfl_xor_sync(0xFFFFFFFFu, best, off), __shfl_xor_sync(0xFFFFFFFFu, besti, off));
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (lane == 0) { sv[warp] = best; si[warp] = besti; }
-    __syncthreads();
-    if (warp == 0) {
-        best = sv[lane];
-        besti = si[lane];
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1)
-            take(best, besti, __shfl_xor_sync(0xFFFFFFFFu, best, off), __shfl_xor_sync(0xFFFFFFFFu, besti, off));
-        if (lane == 0) {
-            out_pairs[2 * blockIdx.x] = best;
-            reinterpret_cast<int*>(out_pairs)[2 * blockIdx.x + 1] = besti == 0x7FFFFFFF ? besti : besti + index0;
-        }
+    argmax_block_fold(best, besti, sv, si);
+    if (threadIdx.x == 0) {
+        float* c = cand + 2 * (static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x);
+        c[0] = best;
+        reinterpret_cast<int*>(c)[1] = besti;
+    }
+}
+__global__ void __launch_bounds__(128) shard_argmax2_kernel(const float* __restrict__ cand, int nblocks, int index0,
+                                                            float* __restrict__ out_pairs) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    grid_dep_launch();
+    grid_dep_wait();
+    const float* c = cand + 2 * static_cast<size_t>(blockIdx.x) * nblocks;
+    float best = -INFINITY;
+    int besti = 0x7FFFFFFF;
+    for (int i = threadIdx.x; i < nblocks; i += blockDim.x) argmax_take(best, besti, c[2 * i], reinterpret_cast<const int*>(c)[2 * i + 1]);
+    argmax_block_fold(best, besti, sv, si);
+    if (threadIdx.x == 0) {
+        out_pairs[2 * blockIdx.x] = best;
+        reinterpret_cast<int*>(out_pairs)[2 * blockIdx.x + 1] = besti == 0x7FFFFFFF ? besti : besti + index0;
     }
 }
 
@@ -259,6 +294,231 @@ __global__ void __launch_bounds__(128) half_gemm_rows_kernel(const __half* __res
             if (ra < rows) y[static_cast<size_t>(n0 + 1) * rows + ra] = acc[j][1];
             if (rb < rows) y[static_cast<size_t>(n0 + 1) * rows + rb] = acc[j][3];
         }
+    }
+}
+
+// ---- vector ops for wide models -------------------------------------------------------------------------
+// The same arithmetic as residual_norm_quant / relu2_norm_quant / absmax_quantize_rows (fused_ops.cu, prefill.cu:
+// every rounding point of the reference's op sequence), laid out for vectors of 4096 .. 32768 elements: one block
+// of 1024 threads per vector, every thread keeps its elements (up to four runs of eight) in registers, all loads
+// are issued before the first reduction, so a kernel costs one memory round trip plus two or three block
+// reductions instead of five passes over shared memory.  Only the order in which the squares are summed differs
+// from the narrow kernels (both are fp32 sums of the same terms).
+constexpr int kWideThreads = 1024;
+constexpr int kWideRuns = 4;  // runs of eight elements per thread: vectors of up to 32768
+
+__device__ __forceinline__ float wide_bsum(float v, float* sh) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+    __syncthreads();
+    v = sh[threadIdx.x & 31];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+    return v;
+}
+__device__ __forceinline__ float wide_bmax(float v, float* sh) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, off));
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+    __syncthreads();
+    v = sh[threadIdx.x & 31];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, off));
+    return v;
+}
+__device__ __forceinline__ void unpack8(const uint4& u, float* f) {
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 t = __half22float2(h[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+__device__ __forceinline__ void load8f(const float* p, float* f) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+__device__ __forceinline__ void quantise_store8(const float* v, float qs, int8_t* dst) {
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        lo |= (static_cast<uint32_t>(quantize_one(v[i], qs)) & 0xFFu) << (8 * i);
+        hi |= (static_cast<uint32_t>(quantize_one(v[4 + i], qs)) & 0xFFu) << (8 * i);
+    }
+    *reinterpret_cast<uint2*>(dst) = make_uint2(lo, hi);
+}
+
+// residual_norm_quant for one vector per block (blockIdx.x = vector): x += [rms_norm(sub_w)](delta) in half, then
+// xn = rms_norm(w)(x) in half (to xn_out when given), absmax, int8.  n % 8 == 0, n <= 8192: one run of eight
+// elements per thread, everything in registers.
+__global__ void __launch_bounds__(kWideThreads) wide_residual_norm_quant_kernel(
+    const __half* __restrict__ delta, const float* __restrict__ sub_w, __half* __restrict__ x, const float* __restrict__ w,
+    __half* __restrict__ xn_out, int8_t* __restrict__ xq, float* __restrict__ d_absmax, int n, float eps) {
+    __shared__ float sh[32];
+    grid_dep_launch();
+    grid_dep_wait();
+    const size_t off = static_cast<size_t>(blockIdx.x) * n;
+    const int runs = n >> 3;
+    constexpr int kRuns = 1;
+    float v[kRuns][8], wv[kRuns][8];
+    float s = 0.0f;
+    if (delta) {
+        float d[kRuns][8], sw[kRuns][8];
+#pragma unroll
+        for (int k = 0; k < kRuns; ++k) {
+            const int r = threadIdx.x + k * kWideThreads;
+            if (r < runs) {
+                unpack8(*reinterpret_cast<const uint4*>(delta + off + 8 * r), d[k]);
+                unpack8(*reinterpret_cast<const uint4*>(x + off + 8 * r), v[k]);
+                load8f(w + 8 * r, wv[k]);
+                if (sub_w) load8f(sub_w + 8 * r, sw[k]);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) s += d[k][i] * d[k][i];
+            }
+        }
+        float sub_scale = 1.0f;
+        if (sub_w) sub_scale = rsqrtf(wide_bsum(s, sh) / static_cast<float>(n) + eps);
+        s = 0.0f;
+#pragma unroll
+        for (int k = 0; k < kRuns; ++k) {
+            const int r = threadIdx.x + k * kWideThreads;
+            if (r < runs) {
+                __half2 out[4];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    float dd = d[k][i];
+                    if (sub_w) dd = __half2float(__float2half_rn(__fmul_rn(__fmul_rn(dd, sub_scale), sw[k][i])));
+                    const __half h = __float2half_rn(dd + v[k][i]);
+                    reinterpret_cast<__half*>(out)[i] = h;
+                    v[k][i] = __half2float(h);
+                    s += v[k][i] * v[k][i];
+                }
+                *reinterpret_cast<uint4*>(x + off + 8 * r) = *reinterpret_cast<const uint4*>(out);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < kRuns; ++k) {
+            const int r = threadIdx.x + k * kWideThreads;
+            if (r < runs) {
+                unpack8(*reinterpret_cast<const uint4*>(x + off + 8 * r), v[k]);
+                load8f(w + 8 * r, wv[k]);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) s += v[k][i] * v[k][i];
+            }
+        }
+    }
+    const float scale = rsqrtf(wide_bsum(s, sh) / static_cast<float>(n) + eps);
+    float m = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kRuns; ++k) {
+        const int r = threadIdx.x + k * kWideThreads;
+        if (r < runs) {
+            __half2 out[4];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const __half h = __float2half_rn(__fmul_rn(__fmul_rn(v[k][i], scale), wv[k][i]));
+                reinterpret_cast<__half*>(out)[i] = h;
+                v[k][i] = __half2float(h);
+                m = fmaxf(m, fabsf(v[k][i]));
+            }
+            if (xn_out) *reinterpret_cast<uint4*>(xn_out + off + 8 * r) = *reinterpret_cast<const uint4*>(out);
+        }
+    }
+    const float absmax = wide_bmax(m, sh);
+    if (threadIdx.x == 0) d_absmax[blockIdx.x] = absmax;
+    const float qs = quant_scale(absmax);
+#pragma unroll
+    for (int k = 0; k < kRuns; ++k) {
+        const int r = threadIdx.x + k * kWideThreads;
+        if (r < runs) quantise_store8(v[k], qs, xq + off + 8 * r);
+    }
+}
+
+// relu2_norm_quant for one vector per block: m = relu(gate)^2 * up in fp32, h = half(m * rsqrt(mean m^2 + eps) * sub_w)
+// (or half(m) without sub_w), absmax, int8.
+__global__ void __launch_bounds__(kWideThreads) wide_relu2_norm_quant_kernel(
+    const __half* __restrict__ gate, const __half* __restrict__ up, const float* __restrict__ sub_w, int8_t* __restrict__ hq,
+    float* __restrict__ d_absmax, int n, float eps) {
+    __shared__ float sh[32];
+    grid_dep_launch();
+    grid_dep_wait();
+    const size_t off = static_cast<size_t>(blockIdx.x) * n;
+    const int runs = n >> 3;
+    float v[kWideRuns][8];  // the products stay in registers; sub_w is read when it is needed (cache-resident)
+    float s = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kWideRuns; ++k) {
+        const int r = threadIdx.x + k * kWideThreads;
+        if (r < runs) {
+            float g[8], u[8];
+            unpack8(*reinterpret_cast<const uint4*>(gate + off + 8 * r), g);
+            unpack8(*reinterpret_cast<const uint4*>(up + off + 8 * r), u);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float t = fmaxf(0.0f, g[i]);
+                v[k][i] = __fmul_rn(__fmul_rn(t, t), u[i]);
+                s += v[k][i] * v[k][i];
+            }
+        }
+    }
+    float scale = 1.0f;
+    if (sub_w) scale = rsqrtf(wide_bsum(s, sh) / static_cast<float>(n) + eps);
+    float m = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kWideRuns; ++k) {
+        const int r = threadIdx.x + k * kWideThreads;
+        if (r < runs) {
+            float sw[8];
+            if (sub_w) load8f(sub_w + 8 * r, sw);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const __half h = sub_w ? __float2half_rn(__fmul_rn(__fmul_rn(v[k][i], scale), sw[i])) : __float2half_rn(v[k][i]);
+                v[k][i] = __half2float(h);
+                m = fmaxf(m, fabsf(v[k][i]));
+            }
+        }
+    }
+    const float absmax = wide_bmax(m, sh);
+    if (threadIdx.x == 0) d_absmax[blockIdx.x] = absmax;
+    const float qs = quant_scale(absmax);
+#pragma unroll
+    for (int k = 0; k < kWideRuns; ++k) {
+        const int r = threadIdx.x + k * kWideThreads;
+        if (r < runs) quantise_store8(v[k], qs, hq + off + 8 * r);
+    }
+}
+
+// absmax_quantize_gpu for one vector per block.
+__global__ void __launch_bounds__(kWideThreads) wide_absmax_quantize_kernel(const __half* __restrict__ in, int8_t* __restrict__ out,
+                                                                            float* __restrict__ d_absmax, int n) {
+    __shared__ float sh[32];
+    grid_dep_launch();
+    grid_dep_wait();
+    const size_t off = static_cast<size_t>(blockIdx.x) * n;
+    const int runs = n >> 3;
+    float v[kWideRuns][8];
+    float m = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kWideRuns; ++k) {
+        const int r = threadIdx.x + k * kWideThreads;
+        if (r < runs) {
+            unpack8(*reinterpret_cast<const uint4*>(in + off + 8 * r), v[k]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[k][i]));
+        }
+    }
+    const float absmax = wide_bmax(m, sh);
+    if (threadIdx.x == 0) d_absmax[blockIdx.x] = absmax;
+    const float qs = quant_scale(absmax);
+#pragma unroll
+    for (int k = 0; k < kWideRuns; ++k) {
+        const int r = threadIdx.x + k * kWideThreads;
+        if (r < runs) quantise_store8(v[k], qs, out + off + 8 * r);
     }
 }
 
@@ -340,13 +600,14 @@ struct spb_shard_engine {
     __half *x = nullptr, *x2 = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr, *o = nullptr;
     __half *gate = nullptr, *up = nullptr, *down = nullptr, *xfinal = nullptr;
     int8_t* xq = nullptr;
-    float *absmax = nullptr, *attn_scratch = nullptr, *logits = nullptr, *pairs = nullptr;
+    float *absmax = nullptr, *attn_scratch = nullptr, *logits = nullptr, *pairs = nullptr, *cand = nullptr;
+    int argmax_blocks = 1;
     int32_t* acc = nullptr;  // three int32 workspaces for the SIMT form of the batched product
     size_t acc_third = 0;
     int *d_pos = nullptr, *d_next = nullptr, *d_prompt = nullptr, *d_out = nullptr;
     unsigned* counters = nullptr;  // [X_KINDS][2]: seqno, done
     int prompt_cap = 0, n_prompt_in_graph = 0, out_cap = 0;
-    bool split_attention = false, fused = false;
+    bool split_attention = false, fused = false, wide = false;
 
     // exchange buffer (exported through CUDA IPC) and the peers' mappings
     uint8_t* xbuf = nullptr;
@@ -388,7 +649,7 @@ int exchange(spb_shard_engine* e, int kind, const XSeg* segs, int nseg) {
     a.status = e->status;
     a.broken = reinterpret_cast<int*>(e->counters + 2 * X_KINDS);
     a.timeout_ns = e->timeout_ns;
-    const int blocks = static_cast<int>(std::max<size_t>(1, std::min<size_t>(64, bytes / (16 * 1024))));
+    const int blocks = static_cast<int>(std::max<size_t>(1, std::min<size_t>(64, bytes / (8 * 1024))));
     return wide ? launch("exchange", exchange_kernel<true>, dim3(blocks), dim3(256), 0, e->stream, a)
                 : launch("exchange", exchange_kernel<false>, dim3(blocks), dim3(256), 0, e->stream, a);
 }
@@ -422,6 +683,21 @@ int enqueue_step(spb_shard_engine* e, bool record) {
     auto linear_b = [&](const Linear& L, const float* am, __half* out, int32_t* ws) {
         return spb_sparse_bitlinear_gemm(L.meta, L.values, e->xq, out, am, L.gamma, ws, L.rows, L.cols, B, L.ms, L.vs, s);
     };
+    // one matrix per launch on the quantised vector: takes the tensor-core GEMV wherever the layout allows
+    auto linear_1 = [&](const Linear& L, const float* am, __half* out) {
+        return spb_sparse_bitlinear_q8(L.meta, L.values, e->xq, out, am, L.gamma, L.rows, L.cols, L.ms, L.vs, s);
+    };
+    // Wide models (hidden >= 4096): a matrix is tens of megabytes and its GEMV runs for tens of microseconds, so
+    // throughput decides, not launch latency: the vector op runs once in a kernel of its own and every matrix goes
+    // through the tensor-core GEMV, instead of the SIMT kernels that recompute the vector op in every block.
+    const bool fused1 = e->fused && !e->wide;
+    // vector ops: the register-resident kernels for wide models, the shared ones of the single-GPU engine otherwise
+    auto res_norm_quant = [&](const __half* delta, const float* sub_w, __half* x, const float* w, __half* xn_out, float* am) {
+        if (e->wide)
+            return launch("wide_residual_norm_quant", wide_residual_norm_quant_kernel, dim3(B), dim3(kWideThreads), 0, s, delta, sub_w,
+                          x, w, xn_out, e->xq, am, H, c.rms_norm_eps);
+        return residual_norm_quant(delta, sub_w, x, w, xn_out, e->xq, am, H, c.rms_norm_eps, s, B);
+    };
     for (int l = 0; l < c.num_hidden_layers; ++l) {
         const Layer& L = e->layers[l];
         __half* kc = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(e->kcache) + l * e->kv_layer_bytes);
@@ -436,12 +712,15 @@ int enqueue_step(spb_shard_engine* e, bool record) {
         __half* o1d[1] = {e->down};
         const __half* delta = l == 0 ? nullptr : down_full;
         // ---- q / k / v on this rank's heads ----
-        if (B == 1 && e->fused) {
+        if (B == 1 && fused1) {
             if ((rc = bitlinear_resnorm_group(make_group(g3, o3, 3), cur, delta, nullptr, L.norm[0], other, c.rms_norm_eps, s))) return rc;
             std::swap(cur, other);
         } else {
-            if ((rc = residual_norm_quant(delta, nullptr, cur, L.norm[0], nullptr, e->xq, am0, H, c.rms_norm_eps, s, B))) return rc;
-            if (B == 1) {
+            if ((rc = res_norm_quant(delta, nullptr, cur, L.norm[0], nullptr, am0))) return rc;
+            if (B == 1 && e->wide) {
+                for (int i = 0; i < 3; ++i)
+                    if ((rc = linear_1(L.lin[i], am0, o3[i]))) return rc;
+            } else if (B == 1) {
                 if ((rc = bitlinear_q8_group(make_group(g3, o3, 3), e->xq, am0, s))) return rc;
             } else {
                 for (int i = 0; i < 3; ++i)
@@ -463,12 +742,17 @@ int enqueue_step(spb_shard_engine* e, bool record) {
             if ((rc = exchange(e, X_ATTN, &sg, 1))) return rc;
         }
         // ---- o_proj rows ----
-        if (B == 1 && e->fused) {
+        if (B == 1 && fused1) {
             if ((rc = bitlinear_amax_group(make_group(g1o, o1o, 1), attn_full, s))) return rc;
         } else {
-            if ((rc = absmax_quantize_rows(attn_full, e->xq, am1, qdim, B, s))) return rc;
+            if (e->wide) {
+                if ((rc = launch("wide_absmax_quantize", wide_absmax_quantize_kernel, dim3(B), dim3(kWideThreads), 0, s,
+                                 static_cast<const __half*>(attn_full), e->xq, am1, qdim))) return rc;
+            } else if ((rc = absmax_quantize_rows(attn_full, e->xq, am1, qdim, B, s))) {
+                return rc;
+            }
             if (B == 1) {
-                if ((rc = bitlinear_q8_group(make_group(g1o, o1o, 1), e->xq, am1, s))) return rc;
+                if ((rc = linear_1(L.lin[3], am1, e->o))) return rc;
             } else if ((rc = linear_b(L.lin[3], am1, e->o, e->acc))) {
                 return rc;
             }
@@ -479,12 +763,15 @@ int enqueue_step(spb_shard_engine* e, bool record) {
             if ((rc = exchange(e, X_O, &sg, 1))) return rc;
         }
         // ---- gate / up rows ----
-        if (B == 1 && e->fused) {
+        if (B == 1 && fused1) {
             if ((rc = bitlinear_resnorm_group(make_group(g2, o2, 2), cur, o_full, L.norm[2], L.norm[1], other, c.rms_norm_eps, s))) return rc;
             std::swap(cur, other);
         } else {
-            if ((rc = residual_norm_quant(o_full, L.norm[2], cur, L.norm[1], nullptr, e->xq, am0, H, c.rms_norm_eps, s, B))) return rc;
-            if (B == 1) {
+            if ((rc = res_norm_quant(o_full, L.norm[2], cur, L.norm[1], nullptr, am0))) return rc;
+            if (B == 1 && e->wide) {
+                if ((rc = linear_1(L.lin[4], am0, e->gate))) return rc;
+                if ((rc = linear_1(L.lin[5], am0, e->up))) return rc;
+            } else if (B == 1) {
                 if ((rc = bitlinear_q8_group(make_group(g2, o2, 2), e->xq, am0, s))) return rc;
             } else {
                 if ((rc = linear_b(L.lin[4], am0, e->gate, e->acc))) return rc;
@@ -499,12 +786,18 @@ int enqueue_step(spb_shard_engine* e, bool record) {
             if ((rc = exchange(e, X_GU, sg, 2))) return rc;
         }
         // ---- down rows: relu2 * up and ffn_sub_norm need the whole vectors ----
-        if (B == 1 && e->fused) {
+        if (B == 1 && fused1) {
             if ((rc = bitlinear_relu2_group(make_group(g1d, o1d, 1), gate_full, up_full, L.norm[3], c.rms_norm_eps, s))) return rc;
         } else {
-            if ((rc = relu2_norm_quant(gate_full, up_full, L.norm[3], nullptr, e->xq, am1, inter, c.rms_norm_eps, s, B))) return rc;
+            if (e->wide) {
+                if ((rc = launch("wide_relu2_norm_quant", wide_relu2_norm_quant_kernel, dim3(B), dim3(kWideThreads), 0, s,
+                                 static_cast<const __half*>(gate_full), static_cast<const __half*>(up_full), L.norm[3], e->xq, am1,
+                                 inter, c.rms_norm_eps))) return rc;
+            } else if ((rc = relu2_norm_quant(gate_full, up_full, L.norm[3], nullptr, e->xq, am1, inter, c.rms_norm_eps, s, B))) {
+                return rc;
+            }
             if (B == 1) {
-                if ((rc = bitlinear_q8_group(make_group(g1d, o1d, 1), e->xq, am1, s))) return rc;
+                if ((rc = linear_1(L.lin[6], am1, e->down))) return rc;
             } else if ((rc = linear_b(L.lin[6], am1, e->down, e->acc))) {
                 return rc;
             }
@@ -516,15 +809,16 @@ int enqueue_step(spb_shard_engine* e, bool record) {
         }
     }
     // last residual add + final norm, LM head on this rank's vocabulary rows, arg-max candidates
-    if ((rc = residual_norm_quant(c.num_hidden_layers ? down_full : nullptr, nullptr, cur, e->final_norm, e->xfinal, e->xq, am0,
-                                  H, c.rms_norm_eps, s, B))) return rc;
+    if ((rc = res_norm_quant(c.num_hidden_layers ? down_full : nullptr, nullptr, cur, e->final_norm, e->xfinal, am0))) return rc;
     if (B == 1) {
         if ((rc = spb_half_gemv(e->lm_head_loc, e->xfinal, e->logits, e->v_loc, H, s))) return rc;
     } else if ((rc = half_gemm_rows(e->lm_head_loc, e->xfinal, e->logits, e->v_loc, H, B, s))) {
         return rc;
     }
-    if ((rc = launch("shard_argmax", shard_argmax_kernel, dim3(B), dim3(1024), 0, s, static_cast<const float*>(e->logits),
-                     e->v_loc, e->vrow[r], e->pairs))) return rc;
+    if ((rc = launch("shard_argmax1", shard_argmax1_kernel, dim3(e->argmax_blocks, B), dim3(1024), 0, s,
+                     static_cast<const float*>(e->logits), e->v_loc, e->cand))) return rc;
+    if ((rc = launch("shard_argmax2", shard_argmax2_kernel, dim3(B), dim3(128), 0, s, static_cast<const float*>(e->cand),
+                     e->argmax_blocks, e->vrow[r], e->pairs))) return rc;
     {
         const XSeg sg = seg_of(e->pairs, e->off_amax, static_cast<size_t>(r) * 8, static_cast<size_t>(e->world) * 8, 8);
         if ((rc = exchange(e, X_AMAX, &sg, 1))) return rc;
@@ -639,6 +933,7 @@ extern "C" spb_shard_engine* spb_shard_engine_create(const spb_model_config* cfg
     e->i_loc = e->irow[rank + 1] - e->irow[rank];
     e->v_loc = e->vrow[rank + 1] - e->vrow[rank];
     e->split_attention = e->group_heads <= 8 && hd <= 256;
+    e->wide = H >= 4096 && H <= 8 * kWideThreads && inter <= 8 * kWideThreads * kWideRuns && qdim <= 8 * kWideThreads * kWideRuns;
     e->seq_stride = static_cast<size_t>(e->nkv_loc) * cfg->max_position_embeddings * hd;
     e->kv_layer_bytes = align_up(sizeof(__half) * e->seq_stride * B, 256);
     const size_t maxdim = std::max(std::max(H, qdim), inter);
@@ -654,7 +949,9 @@ extern "C" spb_shard_engine* spb_shard_engine_create(const spb_model_config* cfg
     const size_t o_gate = take(2 * B * e->i_loc), o_up = take(2 * B * e->i_loc), o_down = take(2 * B * e->h_loc), o_xf = take(2 * B * H);
     const size_t o_xq = take(B * maxdim), o_abs = take(4 * 2 * B), o_acc = take(B > 1 ? 3 * 4 * e->acc_third : 16);
     const size_t o_ascr = take(decode_attention_scratch_bytes(std::max(e->nh_loc, 1), hd, cfg->max_position_embeddings));
+    e->argmax_blocks = std::max(1, std::min(128, (e->v_loc + 1023) / 1024));
     const size_t o_logits = take(4 * static_cast<size_t>(B) * e->v_loc), o_pairs = take(8 * B), o_ints = take(4 * (1 + B));
+    const size_t o_cand = take(8 * static_cast<size_t>(B) * e->argmax_blocks);
     const size_t o_out = take(4 * static_cast<size_t>(e->out_cap) * B), o_ctr = take(4 * (2 * X_KINDS + 1));
     const size_t pool_bytes = off;
     // exchange buffer
@@ -690,6 +987,7 @@ extern "C" spb_shard_engine* spb_shard_engine_create(const spb_model_config* cfg
     e->xq = reinterpret_cast<int8_t*>(p + o_xq); e->absmax = reinterpret_cast<float*>(p + o_abs);
     e->acc = reinterpret_cast<int32_t*>(p + o_acc); e->attn_scratch = reinterpret_cast<float*>(p + o_ascr);
     e->logits = reinterpret_cast<float*>(p + o_logits); e->pairs = reinterpret_cast<float*>(p + o_pairs);
+    e->cand = reinterpret_cast<float*>(p + o_cand);
     e->d_pos = reinterpret_cast<int*>(p + o_ints); e->d_next = e->d_pos + 1;
     e->d_out = reinterpret_cast<int*>(p + o_out); e->counters = reinterpret_cast<unsigned*>(p + o_ctr);
     e->peer[rank] = e->xbuf;

@@ -106,6 +106,20 @@ def test_padded_strides_and_unaligned_pointers():
     assert (y.read(np.int32) == want).all()
 
 
+@pytest.mark.parametrize("rows,cols", [(48, 16640), (100, 28672), (17, 32768), (1024, 28672), (33, 20480)])
+def test_rows_longer_than_one_slab(rows, cols):
+    # cols > 16384: the tensor-core kernel walks the row in double-buffered chunks of 4096 columns
+    case = synth.gemv_case(rows, cols, seed=cols)
+    want = oracle.sparse_gemv(case["meta"], case["values"], case["x"], rows, cols, threads=8)
+    assert (run_gemv(case) == want).all()
+    # and the scaled half output of the BitLinear on a quantised vector
+    out = Guarded(rows * 2)
+    K.sparse_bitlinear_q8_gpu(dev(case["meta"]), dev(case["values"]), dev(case["x"]), out.ptr,
+                              dev(np.array([1.7], np.float32)), 0.01, rows, cols, case["meta_stride"], case["values_stride"])
+    wh = oracle.dequantize(want, np.float32(1.7), np.float32(0.01))
+    assert (out.read(np.uint16) == wh.view(np.uint16)).all()
+
+
 def test_invalid_bitmaps_are_memory_safe(gemv_variant):
     # src/kernels/sparse_ternary.cu:34-51 decodes any bitmap without exactly two bits as (0,0) while the
     # reference's CPU unpack yields as many non-zeros as bits: the result is unspecified there.  The kernels

@@ -94,3 +94,22 @@ def test_a_silent_peer_ends_in_a_timeout_not_a_hang():
     assert (ok.generate(np.array([5, 9], np.int32), 4) == want).all()
     # rank 0 pushed its slices into the stand-in peer before it gave up
     assert fake_peer.any().item()
+
+
+@pytest.mark.parametrize("batch", [1, 3])
+def test_wide_model_path(batch):
+    """hidden >= 4096 switches the engine to its throughput form (one vector kernel per activation, every matrix through
+    the tensor-core GEMV, the down projection's 16640-column rows in chunks): against the single-GPU engine, which
+    runs the fused SIMT form."""
+    cfg = dict(hidden_size=4096, num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+               intermediate_size=16640, vocab_size=2048, max_position_embeddings=32, rms_norm_eps=1e-5, rope_theta=500000.0)
+    dm = synth.DeviceRandomModel(cfg, seed=12)
+    wide, ref = ShardEngine(dm, batch=batch), InferenceEngine(dm)
+    prompts = np.random.default_rng(5).integers(0, cfg["vocab_size"], (3, batch)).astype(np.int32)
+    got = wide.generate(prompts, 6)
+    lg = wide.logits()
+    for b in range(batch):
+        ref.reset()
+        want = ref.generate(prompts[:, b], 6)
+        assert (got[:, b] == want).all(), b
+        assert np.abs(lg[b] - ref.logits()).max() < 1e-2
