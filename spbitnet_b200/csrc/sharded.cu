@@ -18,6 +18,9 @@
 //   3. waits until the local flag words of all peers have reached that sequence number, bounded by time:
 //      when the bound runs out the kernel raises a status word that the host reads at its next
 //      synchronisation (SPB_E_TIMEOUT), and every later exchange of the engine skips its wait.
+// Slices of up to 96 KB per sender (every exchange of a batch-1 step) take a second form without the fence round
+// trip: every 4 bytes travel as one 8-byte store {data, sequence number} into a per-sender staging area, the
+// receiver polls each word until it carries the current number and moves the data into place (exchange_ll_kernel).
 // No multicast, no bulk-copy engine, no library kernel ever sees a peer pointer; remote data always lands in
 // the consumer's own memory before anything reads it.  Sequence numbers only grow, so flags are never reset.
 // A buffer is reused once per layer: a rank that writes exchange n into a peer has passed its wait of
@@ -146,6 +149,95 @@ __global__ void __launch_bounds__(256) exchange_kernel(const XArgs a) {
                 }
                 __nanosleep(64);
             }
+        }
+    }
+}
+
+// The small-message form of the exchange.  The fenced form above pays a system-scope fence round trip between
+// the data and the flag; for slices of a few kilobytes that round trip is most of the exchange.  Here every
+// 4 bytes of data travel as ONE 8-byte store {data, sequence number} into a per-sender staging area of the
+// receiver's buffer (8-byte stores arrive whole), so the data is its own flag: the receiver polls each word until
+// it carries the current sequence number and moves the data into the gathered array.  One NVLink crossing, no
+// fence, twice the bytes.  Sequence numbers grow by one per exchange of a kind, so a slot's previous contents
+// (number - 1, or 0 after allocation) never look current.  The poll is bounded by time like the flag wait.
+struct LSeg {
+    const uint8_t* src;       // local compact slice: rows x len[rank] bytes
+    uint32_t dst_region;      // byte offset of the gathered array in the exchange buffer
+    uint32_t dst_pitch;       // bytes between its rows
+    uint32_t off[kMaxWorld];  // byte offset of every rank's slice inside a row
+    uint32_t len[kMaxWorld];  // bytes per row of every rank's slice (multiples of 4)
+    uint32_t ll_off;          // byte offset of this segment's staging area in the exchange buffer
+    uint32_t ll_stride;       // bytes of staging per sending rank
+};
+struct LArgs {
+    uint8_t* peer[kMaxWorld];
+    LSeg seg[2];
+    int nseg, rows, world, rank;
+    unsigned* seqno;
+    unsigned* done;
+    int* status;
+    int* broken;
+    unsigned long long timeout_ns;
+};
+
+__global__ void __launch_bounds__(256) exchange_ll_kernel(const LArgs a) {
+    grid_dep_launch();
+    grid_dep_wait();  // the slice was written by the predecessor
+    const unsigned seq = *reinterpret_cast<volatile unsigned*>(a.seqno) + 1u;
+    const uint32_t tid = blockIdx.x * blockDim.x + threadIdx.x, nthreads = gridDim.x * blockDim.x;
+    // send: this rank's words, to its own gathered array directly and to every peer's staging area with the number
+    for (int s = 0; s < a.nseg; ++s) {
+        const LSeg& g = a.seg[s];
+        const uint32_t wpr = g.len[a.rank] >> 2, words = wpr * static_cast<uint32_t>(a.rows);
+        for (uint32_t j = tid; j < words; j += nthreads) {
+            const uint32_t row = a.rows == 1 ? 0u : j / wpr, c = j - row * wpr;
+            const uint32_t v = reinterpret_cast<const uint32_t*>(g.src)[j];
+            *reinterpret_cast<uint32_t*>(a.peer[a.rank] + g.dst_region + static_cast<size_t>(row) * g.dst_pitch + g.off[a.rank] + 4u * c) = v;
+            const size_t slot = static_cast<size_t>(g.ll_off) + static_cast<size_t>(a.rank) * g.ll_stride + 8u * static_cast<size_t>(j);
+            for (int p = 0; p < a.world; ++p)
+                if (p != a.rank)
+                    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(a.peer[p] + slot), "r"(v), "r"(seq) : "memory");
+        }
+    }
+    // receive: every peer's words out of the local staging area
+    bool alive = *reinterpret_cast<volatile int*>(a.broken) == 0;
+    unsigned long long t0 = 0;
+    for (int s = 0; s < a.nseg && alive; ++s) {
+        const LSeg& g = a.seg[s];
+        for (int p = 0; p < a.world && alive; ++p) {
+            if (p == a.rank) continue;
+            const uint32_t wpr = g.len[p] >> 2, words = wpr * static_cast<uint32_t>(a.rows);
+            const uint8_t* stage = a.peer[a.rank] + g.ll_off + static_cast<size_t>(p) * g.ll_stride;
+            for (uint32_t j = tid; j < words && alive; j += nthreads) {
+                uint32_t v, n;
+                unsigned spins = 0;
+                for (;;) {
+                    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v), "=r"(n) : "l"(stage + 8u * static_cast<size_t>(j)) : "memory");
+                    if (n == seq) break;
+                    if ((++spins & 255u) == 0) {
+                        const unsigned long long now = globaltimer_ns();
+                        if (t0 == 0) t0 = now;
+                        if (now - t0 > a.timeout_ns || *reinterpret_cast<volatile int*>(a.broken) != 0) {
+                            *reinterpret_cast<volatile int*>(a.broken) = 1;
+                            atomicExch_system(a.status, 1);
+                            alive = false;
+                            break;
+                        }
+                    }
+                }
+                if (!alive) break;
+                const uint32_t row = a.rows == 1 ? 0u : j / wpr, c = j - row * wpr;
+                *reinterpret_cast<uint32_t*>(a.peer[a.rank] + g.dst_region + static_cast<size_t>(row) * g.dst_pitch + g.off[p] + 4u * c) = v;
+            }
+        }
+    }
+    // the last block to finish advances the sequence number (every block has read it by then)
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned ticket = gridDim.x == 1 ? 0u : atomicAdd(a.done, 1u);
+        if (ticket == gridDim.x - 1) {
+            if (gridDim.x > 1) *a.done = 0;
+            *a.seqno = seq;
         }
     }
 }
@@ -615,6 +707,9 @@ struct spb_shard_engine {
     uint8_t* peer[kMaxWorld] = {};
     bool peers_set = false;
     size_t off_flags = 0, off_attn = 0, off_o = 0, off_gate = 0, off_up = 0, off_down = 0, off_amax = 0;
+    size_t ll_off[X_KINDS] = {};   // staging areas of the small-message exchange
+    bool ll_ok[X_KINDS] = {};      // the kind's slices are small enough for it
+    int ident[kMaxWorld + 1] = {0, 1, 2, 3, 4, 5, 6, 7, 8};
     int* status = nullptr;  // pinned, mapped
     unsigned long long timeout_ns = 5000000000ull;
 
@@ -625,12 +720,42 @@ struct spb_shard_engine {
 
 namespace {
 
-int exchange(spb_shard_engine* e, int kind, const XSeg* segs, int nseg) {
+// bounds[s]: the split table of segment s (world + 1 entries, in units of unit_bytes[s] bytes per row)
+int exchange(spb_shard_engine* e, int kind, const XSeg* segs, int nseg, const int* const* bounds, const int* unit_bytes) {
     if (e->world == 1) {  // nothing to exchange: the "slice" is the whole vector; copy it into place
         for (int s = 0; s < nseg; ++s)
             SPB_CUDA(cudaMemcpy2DAsync(e->xbuf + segs[s].dst_off, segs[s].dst_pitch, segs[s].src, segs[s].len, segs[s].len,
                                        e->batch, cudaMemcpyDeviceToDevice, e->stream));
         return SPB_OK;
+    }
+    if (e->ll_ok[kind]) {  // small slices: data and sequence number in one store, no fence
+        LArgs l{};
+        for (int p = 0; p < e->world; ++p) l.peer[p] = e->peer[p];
+        size_t words = 0, ll_at = e->ll_off[kind];
+        for (int s = 0; s < nseg; ++s) {
+            LSeg& g = l.seg[s];
+            g.src = segs[s].src;
+            g.dst_pitch = segs[s].dst_pitch;
+            g.dst_region = segs[s].dst_off - static_cast<uint32_t>(bounds[s][e->rank]) * unit_bytes[s];
+            uint32_t maxlen = 0;
+            for (int p = 0; p < e->world; ++p) {
+                g.off[p] = static_cast<uint32_t>(bounds[s][p]) * unit_bytes[s];
+                g.len[p] = static_cast<uint32_t>(bounds[s][p + 1] - bounds[s][p]) * unit_bytes[s];
+                maxlen = std::max(maxlen, g.len[p]);
+                words += static_cast<size_t>(g.len[p] / 4) * e->batch;
+            }
+            g.ll_off = static_cast<uint32_t>(ll_at);
+            g.ll_stride = 2 * maxlen * e->batch;
+            ll_at += static_cast<size_t>(g.ll_stride) * e->world;
+        }
+        l.nseg = nseg; l.rows = e->batch; l.world = e->world; l.rank = e->rank;
+        l.seqno = e->counters + 2 * kind;
+        l.done = e->counters + 2 * kind + 1;
+        l.status = e->status;
+        l.broken = reinterpret_cast<int*>(e->counters + 2 * X_KINDS);
+        l.timeout_ns = e->timeout_ns;
+        const int blocks = static_cast<int>(std::max<size_t>(1, std::min<size_t>(32, words / 1024)));
+        return launch("exchange_ll", exchange_ll_kernel, dim3(blocks), dim3(256), 0, e->stream, l);
     }
     XArgs a{};
     for (int p = 0; p < e->world; ++p) a.peer[p] = e->peer[p];
@@ -739,7 +864,9 @@ int enqueue_step(spb_shard_engine* e, bool record) {
         {
             const XSeg sg = seg_of(e->attn, e->off_attn, static_cast<size_t>(e->kv0[r]) * e->group_heads * hd * 2,
                                    static_cast<size_t>(qdim) * 2, static_cast<size_t>(e->nh_loc) * hd * 2);
-            if ((rc = exchange(e, X_ATTN, &sg, 1))) return rc;
+            const int* bd[1] = {e->kv0};
+            const int ub[1] = {e->group_heads * hd * 2};
+            if ((rc = exchange(e, X_ATTN, &sg, 1, bd, ub))) return rc;
         }
         // ---- o_proj rows ----
         if (B == 1 && fused1) {
@@ -760,7 +887,9 @@ int enqueue_step(spb_shard_engine* e, bool record) {
         {
             const XSeg sg = seg_of(e->o, e->off_o, static_cast<size_t>(e->hrow[r]) * 2, static_cast<size_t>(H) * 2,
                                    static_cast<size_t>(e->h_loc) * 2);
-            if ((rc = exchange(e, X_O, &sg, 1))) return rc;
+            const int* bd[1] = {e->hrow};
+            const int ub[1] = {2};
+            if ((rc = exchange(e, X_O, &sg, 1, bd, ub))) return rc;
         }
         // ---- gate / up rows ----
         if (B == 1 && fused1) {
@@ -783,7 +912,9 @@ int enqueue_step(spb_shard_engine* e, bool record) {
                                        static_cast<size_t>(e->i_loc) * 2),
                                 seg_of(e->up, e->off_up, static_cast<size_t>(e->irow[r]) * 2, static_cast<size_t>(inter) * 2,
                                        static_cast<size_t>(e->i_loc) * 2)};
-            if ((rc = exchange(e, X_GU, sg, 2))) return rc;
+            const int* bd[2] = {e->irow, e->irow};
+            const int ub[2] = {2, 2};
+            if ((rc = exchange(e, X_GU, sg, 2, bd, ub))) return rc;
         }
         // ---- down rows: relu2 * up and ffn_sub_norm need the whole vectors ----
         if (B == 1 && fused1) {
@@ -805,7 +936,9 @@ int enqueue_step(spb_shard_engine* e, bool record) {
         {
             const XSeg sg = seg_of(e->down, e->off_down, static_cast<size_t>(e->hrow[r]) * 2, static_cast<size_t>(H) * 2,
                                    static_cast<size_t>(e->h_loc) * 2);
-            if ((rc = exchange(e, X_DOWN, &sg, 1))) return rc;
+            const int* bd[1] = {e->hrow};
+            const int ub[1] = {2};
+            if ((rc = exchange(e, X_DOWN, &sg, 1, bd, ub))) return rc;
         }
     }
     // last residual add + final norm, LM head on this rank's vocabulary rows, arg-max candidates
@@ -821,7 +954,9 @@ int enqueue_step(spb_shard_engine* e, bool record) {
                      e->argmax_blocks, e->vrow[r], e->pairs))) return rc;
     {
         const XSeg sg = seg_of(e->pairs, e->off_amax, static_cast<size_t>(r) * 8, static_cast<size_t>(e->world) * 8, 8);
-        if ((rc = exchange(e, X_AMAX, &sg, 1))) return rc;
+        const int* bd[1] = {e->ident};
+        const int ub[1] = {8};
+        if ((rc = exchange(e, X_AMAX, &sg, 1, bd, ub))) return rc;
     }
     return launch("shard_pick", shard_pick_kernel, dim3(1), dim3(kMaxBatch), 0, s, static_cast<const float*>(amax_full), e->world,
                   B, e->d_next, record ? e->d_out : nullptr, e->d_pos);
@@ -963,6 +1098,17 @@ extern "C" spb_shard_engine* spb_shard_engine_create(const spb_model_config* cfg
     e->off_up = take(2 * static_cast<size_t>(B) * inter);
     e->off_down = take(2 * static_cast<size_t>(B) * H);
     e->off_amax = take(8 * static_cast<size_t>(B) * world);
+    {   // staging of the small-message exchange: per kind, per segment, per sending rank 2 x (largest slice) x batch
+        auto maxdiff = [&](const int* b) { int m = 0; for (int p = 0; p < world; ++p) m = std::max(m, b[p + 1] - b[p]); return static_cast<size_t>(m); };
+        const size_t slice[X_KINDS] = {maxdiff(e->kv0) * e->group_heads * hd * 2, maxdiff(e->hrow) * 2, maxdiff(e->irow) * 2,
+                                       maxdiff(e->hrow) * 2, 8};
+        const int nseg[X_KINDS] = {1, 1, 2, 1, 1};
+        constexpr size_t kLlMaxSliceBytes = 96 * 1024;  // per segment and sender; larger slices take the fenced form
+        for (int k = 0; k < X_KINDS; ++k) {
+            e->ll_ok[k] = world > 1 && slice[k] * B <= kLlMaxSliceBytes;
+            if (e->ll_ok[k]) e->ll_off[k] = take(2 * slice[k] * B * world * nseg[k]);
+        }
+    }
     e->xbuf_bytes = off;
     if (cudaMalloc(&e->pool, pool_bytes) != cudaSuccess || cudaMemset(e->pool, 0, pool_bytes) != cudaSuccess ||
         cudaMalloc(&e->xbuf, e->xbuf_bytes) != cudaSuccess || cudaMemset(e->xbuf, 0, e->xbuf_bytes) != cudaSuccess ||
