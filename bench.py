@@ -12,7 +12,13 @@ over all ranks.  With N > 1 every rank runs the same per-GPU workload on its own
 data-path collective (weak scaling of independent replicas); time is the max over ranks.
 
 Prints ONE JSON line.  `--impl reference` times the reference's own CPU implementation of
-the same GEMV on the host cores instead.
+the same GEMV on the host cores instead (and imports nothing of the product).
+
+Beside the headline the line carries: `sweep` (all nine shapes, each with the reference's own CUDA kernel
+recompiled for sm_100a in the same graph), `cpu_baseline`, `gemm` (the batched product against cuBLASLt and
+cuSPARSELt, every result checked against the CPU oracle before it is timed), `decode` (2B-4T-shape greedy decode,
+one replica per rank) and `sharded` (the Llama-70B-shaped model row-sharded over the ranks of the run; with more
+than one rank nothing is timed unless the sharded logits equal one rank's bit for bit).
 """
 from __future__ import annotations
 
@@ -677,11 +683,16 @@ def bench_gemm(args, l2_bytes):
     from spbitnet_b200 import kernels as K, synth
     out = {}
     peak_hbm, _ = measured_peaks()
-    sp_peak = sparse_int8_peak()
+    sp_peak = None if args.gemm_shape else sparse_int8_peak()
     out["sparse_int8_peak"] = sp_peak
     peak_tops = (sp_peak or {}).get("dense_equiv_tops") or NOMINAL_SPARSE_INT8_TOPS
     threads = os.cpu_count() or 1
-    for (r, c) in synth.GEMM_SHAPES:
+    shapes = synth.GEMM_SHAPES
+    batches = synth.GEMM_BATCHES
+    if args.gemm_shape:  # one shape, one batch size, no library arms: a small case for a profiler capture
+        r_, c_ = (int(v) for v in args.gemm_shape.lower().split("x"))
+        shapes, batches = [(r_, c_)], [args.gemm_n]
+    for (r, c) in shapes:
         case = synth.gemv_case(r, c, seed=0)
         per = r * 4 * (case["meta_stride"] + case["values_stride"])
         copies = max(4, int(np.ceil(1.5 * l2_bytes / per)))
@@ -691,7 +702,7 @@ def bench_gemm(args, l2_bytes):
         vals = torch.stack([values.roll(i, 0) for i in range(copies)]).contiguous()
         last_meta, last_values = np.roll(case["meta"], copies - 1, 0), np.roll(case["values"], copies - 1, 0)
         Wd = torch.from_numpy(oracle_unpack(case, r, c)).cuda()  # dense int8 copy, what the reference hands to cuSPARSELt
-        for n in synth.GEMM_BATCHES:
+        for n in batches:
             X = torch.randint(-127, 128, (n, c), dtype=torch.int8, device="cuda")
             Y = torch.empty((n, r), dtype=torch.int32, device="cuda")
             Xh = X.cpu().numpy()
@@ -699,6 +710,8 @@ def bench_gemm(args, l2_bytes):
             want = {j: oracle.sparse_gemv(last_meta, last_values, Xh[j], r, c, threads=threads) for j in probe}
             row = {}
             for name, variant in (("auto", 0), ("simt", 1), ("tc_sparse", 3), ("mma_sp", 4)):
+                if args.gemm_shape and variant != 0:
+                    continue
                 if (variant == 1 and n > 64) or (variant == 3 and n < 16) or (variant == 4 and n > 256):
                     continue
                 K.set_gemm_variant(variant)
@@ -729,7 +742,7 @@ def bench_gemm(args, l2_bytes):
                                        "unit": "GB/s" if bound == "hbm" else "TOP/s (dense-equivalent)",
                                        "frac": round((t_hbm if bound == "hbm" else t_tc) / us, 4)}
             K.set_gemm_variant(0)
-            if n >= 16:
+            if n >= 16 and not args.gemm_shape:
                 # the libraries run on copy 0 of the weights
                 w0 = oracle.sparse_gemv(case["meta"], case["values"], Xh[0], r, c, threads=threads)
                 row.update(library_gemm(Wd, X, r, c, n, w0[None, :]))
@@ -852,17 +865,26 @@ def bench_sharded(args, rank, world, dist):
     from spbitnet_b200.shard_engine import ShardEngine
     peak, _ = measured_peaks()
     out = {"world": world}
+    # The ranks' control plane here (barriers, the IPC handles, max over ranks) runs over a gloo group with a short
+    # timeout: should a rank fail, the others get a Python exception within two minutes instead of sitting in a
+    # device-side collective, and the run still prints its line.
+    ctl = None
+    if world > 1:
+        import datetime
+        torch.cuda.synchronize()
+        dist.barrier()  # the ranks arrive here at different times (rank 0 ran the sweep and the batched product)
+        ctl = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=120))
 
     def barrier():
         torch.cuda.synchronize()
         if world > 1:
-            dist.barrier()
+            dist.barrier(group=ctl)
 
     def max_over_ranks(x):
         if world == 1:
             return x
-        t = torch.tensor([x], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        t = torch.tensor([x], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=ctl)
         return float(t.item())
 
     # ---- parity gate -------------------------------------------------------------------------------------
@@ -873,7 +895,7 @@ def bench_sharded(args, rank, world, dist):
         dm = synth.DeviceRandomModel(small, seed=9)
         verdicts = []
         for batch in (1, 5):
-            sharded, one = ShardEngine(dm, rank=rank, world=world, batch=batch), ShardEngine(dm, batch=batch)
+            sharded, one = ShardEngine(dm, rank=rank, world=world, batch=batch, group=ctl), ShardEngine(dm, batch=batch)
             prompts = np.random.default_rng(7).integers(0, small["vocab_size"], (4, batch)).astype(np.int32)
             same = True
             for step in range(4):
@@ -893,8 +915,8 @@ def bench_sharded(args, rank, world, dist):
             barrier()
             sharded.close()
             one.close()
-        flag = torch.tensor([1.0 if all(verdicts) else 0.0], device="cuda")
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        flag = torch.tensor([1.0 if all(verdicts) else 0.0])
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=ctl)
         out["parity"] = "bit-identical" if flag.item() == 1.0 else "MISMATCH"
         out["parity_what"] = ("2-layer model (hidden 1024, 8 KV heads, vocab 4001), batch 1 and 5: logits of 4 steps equal "
                               "bit for bit to the same engine with one rank, 8 greedy tokens equal, batch-1 tokens equal to "
@@ -915,7 +937,7 @@ def bench_sharded(args, rank, world, dist):
     full.layers = [full.layers[0]] * L  # ShardEngine clones the rank's slices layer by layer
     results = {}
     for batch in (1, 64):
-        eng = ShardEngine(full, rank=rank, world=world, batch=batch)
+        eng = ShardEngine(full, rank=rank, world=world, batch=batch, group=ctl)
         rng = np.random.default_rng(11)
         prompts = rng.integers(0, cfg["vocab_size"], (args.shard_prompt, batch)).astype(np.int32)
         warm = eng.generate(prompts[:4], 2)  # graph capture, page-in
@@ -999,6 +1021,8 @@ def main():
     ap.add_argument("--shard-layers", type=int, default=0, help="override the layer count of the sharded model")
     ap.add_argument("--shard-prompt", type=int, default=512)
     ap.add_argument("--shard-tokens", type=int, default=48)
+    ap.add_argument("--gemm-shape", default="", help="with --only-gemm: one ROWSxCOLS shape only, automatic form only")
+    ap.add_argument("--gemm-n", type=int, default=1024, help="batch rows for --gemm-shape")
     ap.add_argument("--only-gemm", action="store_true", help="only the batched-product section (profiling aid)")
     ap.add_argument("--only-decode", action="store_true", help="skip the GEMV sections (profiling aid)")
     ap.add_argument("--only-prefill", action="store_true", help="only the batched-prefill timing (profiling aid)")
