@@ -685,6 +685,8 @@ struct spb_shard_engine {
     int nkv_loc = 0, nh_loc = 0, h_loc = 0, i_loc = 0, v_loc = 0;
 
     cudaStream_t stream = nullptr;
+    cudaStream_t side[2] = {nullptr, nullptr};  // parallel branches of the captured step
+    cudaEvent_t fork = nullptr, join[2] = {nullptr, nullptr};
     uint8_t* pool = nullptr;
     size_t kv_layer_bytes = 0;  // one layer's K (or V) caches of all sequences
     size_t seq_stride = 0;      // elements between the caches of two sequences
@@ -809,8 +811,23 @@ int enqueue_step(spb_shard_engine* e, bool record) {
         return spb_sparse_bitlinear_gemm(L.meta, L.values, e->xq, out, am, L.gamma, ws, L.rows, L.cols, B, L.ms, L.vs, s);
     };
     // one matrix per launch on the quantised vector: takes the tensor-core GEMV wherever the layout allows
-    auto linear_1 = [&](const Linear& L, const float* am, __half* out) {
-        return spb_sparse_bitlinear_q8(L.meta, L.values, e->xq, out, am, L.gamma, L.rows, L.cols, L.ms, L.vs, s);
+    auto linear_1 = [&](const Linear& L, const float* am, __half* out, void* on = nullptr) {
+        return spb_sparse_bitlinear_q8(L.meta, L.values, e->xq, out, am, L.gamma, L.rows, L.cols, L.ms, L.vs, on ? on : s);
+    };
+    // Matrices that read the same quantised vector (q / k / v, gate / up) do not depend on one another: the first
+    // goes on the engine's stream, the others on side streams between a fork and a join event, which the capture
+    // turns into parallel branches of the graph.  k and v are latency bound on their own; side by side they cost
+    // one GEMV's latency, and two large GEMVs in flight get more of the memory system than one.
+    auto linear_side_by_side = [&](const Linear* const* L, __half* const* out, int n, const float* am) -> int {
+        SPB_CUDA(cudaEventRecord(e->fork, e->stream));
+        for (int i = 1; i < n; ++i) {
+            SPB_CUDA(cudaStreamWaitEvent(e->side[i - 1], e->fork, 0));
+            if (int r2 = linear_1(*L[i], am, out[i], e->side[i - 1])) return r2;
+            SPB_CUDA(cudaEventRecord(e->join[i - 1], e->side[i - 1]));
+        }
+        if (int r2 = linear_1(*L[0], am, out[0])) return r2;
+        for (int i = 1; i < n; ++i) SPB_CUDA(cudaStreamWaitEvent(e->stream, e->join[i - 1], 0));
+        return SPB_OK;
     };
     // Wide models (hidden >= 4096): a matrix is tens of megabytes and its GEMV runs for tens of microseconds, so
     // throughput decides, not launch latency: the vector op runs once in a kernel of its own and every matrix goes
@@ -843,8 +860,7 @@ int enqueue_step(spb_shard_engine* e, bool record) {
         } else {
             if ((rc = res_norm_quant(delta, nullptr, cur, L.norm[0], nullptr, am0))) return rc;
             if (B == 1 && e->wide) {
-                for (int i = 0; i < 3; ++i)
-                    if ((rc = linear_1(L.lin[i], am0, o3[i]))) return rc;
+                if ((rc = linear_side_by_side(g3, o3, 3, am0))) return rc;
             } else if (B == 1) {
                 if ((rc = bitlinear_q8_group(make_group(g3, o3, 3), e->xq, am0, s))) return rc;
             } else {
@@ -900,8 +916,7 @@ int enqueue_step(spb_shard_engine* e, bool record) {
         } else {
             if ((rc = res_norm_quant(o_full, L.norm[2], cur, L.norm[1], nullptr, am0))) return rc;
             if (B == 1 && e->wide) {
-                if ((rc = linear_1(L.lin[4], am0, e->gate))) return rc;
-                if ((rc = linear_1(L.lin[5], am0, e->up))) return rc;
+                if ((rc = linear_side_by_side(g2, o2, 2, am0))) return rc;
             } else if (B == 1) {
                 if ((rc = bitlinear_q8_group(make_group(g2, o2, 2), e->xq, am0, s))) return rc;
             } else {
@@ -1124,6 +1139,11 @@ extern "C" spb_shard_engine* spb_shard_engine_create(const spb_model_config* cfg
         return nullptr;
     }
     *e->status = 0;
+    cudaEventCreateWithFlags(&e->fork, cudaEventDisableTiming);
+    for (int i = 0; i < 2; ++i) {
+        cudaStreamCreateWithFlags(&e->side[i], cudaStreamNonBlocking);
+        cudaEventCreateWithFlags(&e->join[i], cudaEventDisableTiming);
+    }
     cudaDeviceSynchronize();
     uint8_t* p = e->pool;
     e->kcache = reinterpret_cast<__half*>(p + o_kc); e->vcache = reinterpret_cast<__half*>(p + o_vc);
@@ -1150,6 +1170,11 @@ extern "C" void spb_shard_engine_destroy(spb_shard_engine* e) {
     for (int p = 0; p < e->world; ++p)
         if (p != e->rank && e->peer[p]) cudaIpcCloseMemHandle(e->peer[p]);
     if (e->d_prompt) cudaFree(e->d_prompt);
+    for (int i = 0; i < 2; ++i) {
+        if (e->side[i]) cudaStreamDestroy(e->side[i]);
+        if (e->join[i]) cudaEventDestroy(e->join[i]);
+    }
+    if (e->fork) cudaEventDestroy(e->fork);
     cudaFree(e->pool);
     cudaFree(e->xbuf);
     cudaFreeHost(e->status);
