@@ -779,6 +779,22 @@ def bench_decode(args, with_reference=True, with_cpu=False):
     dt = time.perf_counter() - t0
     steps = len(prompt) - 1 + n_gen
     weight_bytes = dm.sparse_bytes() + dm.embed.numel() * 2
+    # the same job with the layers of a token as one persistent kernel (opt-in mode of the engine)
+    persistent = None
+    try:
+        eng.reset()
+        eng.set_decode_mode(InferenceEngine.DECODE_PERSISTENT)
+        eng.generate(prompt, 8)
+        eng.reset()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        toks_p = eng.generate(prompt, n_gen)
+        dt_p2 = time.perf_counter() - t0
+        persistent = {"tok_s": steps / dt_p2, "ms_per_token": 1e3 * dt_p2 / steps, "same_tokens": bool((toks_p == toks).all())}
+    except Exception as exc:
+        persistent = {"error": repr(exc)[:160]}
+    eng.reset()
+    eng.set_decode_mode(InferenceEngine.DECODE_AUTO)
     # the same job with the prompt fed as one batch (BitLinear layers as the batched product)
     eng.reset()
     eng.set_prefill_chunk(256)
@@ -800,6 +816,7 @@ def bench_decode(args, with_reference=True, with_cpu=False):
     peak, _ = measured_peaks()
     out = {"tok_s": steps / dt, "batched_prompt": batched, "ms_per_token": 1e3 * dt / steps, "generated": int(len(toks)),
            "prompt": int(len(prompt)), "weight_mb_per_token": round(weight_bytes / 1e6, 1),
+           "step": "chain of five PDL-linked kernels per layer", "persistent_kernel": persistent,
            "hbm_gbs": weight_bytes * steps / dt / 1e9, "hbm_frac_measured": weight_bytes * steps / dt / 1e9 / peak,
            "what": "prefill (token-serial, as the reference) + decode, wall clock around generate() incl. prompt "
                    "H2D and token D2H; random-init 2B-4T shape, every matrix of every layer drawn with its own seed"}

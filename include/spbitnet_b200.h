@@ -328,6 +328,22 @@ int spb_engine_prefill(spb_engine* e, const int* tokens, int n, const float** d_
  * the same chunk when it is set, else 1024).  Returns the previous
  * setting, or a negative status. */
 int spb_engine_set_prefill_chunk(spb_engine* e, int chunk);
+/* How the layers of a decode token are run:
+ *   0 (default) and 1: a chain of five PDL-linked kernels per layer (the vector ops fused into the BitLinear launches,
+ *     RoPE and the KV scatter into the q/k/v launch, the merge of the attention chunks into the attention launch);
+ *   2 the persistent kernel: one cooperative launch per token, a block per SM, grid barriers between the stages of
+ *     a layer, weights prefetched into shared memory; SPB_E_UNSUPPORTED at the next step if the model does not fit.
+ *     Measured slower than the chain so far (see the design notes), hence not the default;
+ *   3 the chain with every vector op group as its own launch (the reference's op order, for testing).
+ * All modes produce the same tokens and logits bit for bit.  A grid-barrier wait of the persistent kernel is
+ * bounded (about a second); when one runs out the step's results are unspecified, the library's timeout counter
+ * moves (SPB_E_TIMEOUT from the engine call that synchronises next) and spb_engine_reset clears the barrier state. */
+int spb_engine_set_decode_mode(spb_engine* e, int mode);
+/* 1 when the last step that was set up runs the persistent kernel. */
+int spb_engine_decode_is_persistent(const spb_engine* e);
+/* Test aid: two blocks at a grid barrier that expects three; both waits run out after limit_cycles (clamped),
+ * the run-out is counted, the kernel returns.  Returns SPB_E_TIMEOUT when that happened as it must. */
+int spb_debug_grid_barrier_selftest(long long limit_cycles, void* stream);
 
 /* ---- model directory loader: include/spbitnet/model.h:88-145, src/model.cu:179-311 ---------------------- */
 

@@ -66,6 +66,7 @@ SIGNATURES = {
     "spb_set_gemm_row_halves": (_i, [_i]),
     "spb_gemm_tc_timeouts": (_i, []),
     "spb_debug_bounded_wait_selftest": (_i, [C.c_longlong, _p]),
+    "spb_debug_grid_barrier_selftest": (_i, [C.c_longlong, _p]),
     "spb_rms_norm": (_i, [_p, _p, _p, _i, _f, _p]),
     "spb_absmax_quantize": (_i, [_p, _p, _p, _i, _p]),
     "spb_absmax_reduce": (_i, [_p, _p, _i, _p]),
@@ -105,6 +106,8 @@ SIGNATURES = {
     "spb_engine_copy_logits": (_i, [_p, _p]),
     "spb_engine_prefill": (_i, [_p, _p, _i, _p]),
     "spb_engine_set_prefill_chunk": (_i, [_p, _i]),
+    "spb_engine_set_decode_mode": (_i, [_p, _i]),
+    "spb_engine_decode_is_persistent": (_i, [_p]),
     "spb_model_load": (_p, [C.c_char_p]),
     "spb_model_destroy": (None, [_p]),
     "spb_model_get_config": (_i, [_p, C.POINTER(ModelConfig), C.POINTER(_i), C.POINTER(_i)]),

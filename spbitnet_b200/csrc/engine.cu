@@ -15,6 +15,7 @@
 #include <new>
 #include <vector>
 
+#include "decode_persistent.cuh"
 #include "fused_ops.cuh"
 
 namespace spb {
@@ -53,6 +54,7 @@ struct spb_engine {
     int8_t* xq = nullptr;   // quantised activation, max(hidden, inter, heads*head_dim)
     float* absmax = nullptr;
     float* attn_scratch = nullptr;  // split-KV partial results
+    unsigned* attn_counters = nullptr;  // per KV head: chunks written so far (zero between launches)
     bool split_attention = false;
     float* logits = nullptr;
     float* bval = nullptr;
@@ -65,7 +67,12 @@ struct spb_engine {
     cudaGraphExec_t graph = nullptr;  // one token, position and token read from device memory
     bool graph_generates = false;     // the captured graph records tokens into d_out
     bool fused = false;               // vector ops run inside the BitLinear launches
-    bool force_unfused = false;
+    bool rope_in_qkv = false;         // ... and rope + KV scatter inside the q/k/v launch
+    int decode_mode = 0;              // spb_engine_set_decode_mode
+    bool persistent = false;          // the layers of a token run as the one persistent kernel (decode_persistent.cu)
+    PdModel pd{};
+    PdLayer* d_pd_layers = nullptr;
+    unsigned* d_pd_sync = nullptr;
     int seq_len = 0;
     int timeouts_seen = 0;  // value of the library's bounded-wait counter when the engine last looked
 
@@ -165,9 +172,16 @@ int enqueue_token(spb_engine* e, bool record_tokens) {
     int rc;
     __half* cur = e->x;
     __half* other = e->x2;
-    if ((rc = embed_token(e->embed, cur, H, e->d_prompt, e->n_prompt_in_graph, e->d_next, e->d_pos, s))) return rc;
     const float attn_scale = 1.0f / sqrtf(static_cast<float>(hd));
-    for (int l = 0; l < c.num_hidden_layers; ++l) {
+    if (e->persistent) {
+        // embedding gather and every layer in one cooperative launch; the residual stream ends up in e->x
+        e->pd.d_prompt = e->d_prompt;
+        e->pd.n_prompt = e->n_prompt_in_graph;
+        if ((rc = decode_persistent_launch(e->pd, 0, s))) return rc;
+    } else if ((rc = embed_token(e->embed, cur, H, e->d_prompt, e->n_prompt_in_graph, e->d_next, e->d_pos, s))) {
+        return rc;
+    }
+    for (int l = 0; l < c.num_hidden_layers && !e->persistent; ++l) {
         const Layer& L = e->layers[l];
         __half* kc = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(e->kcache) + l * e->kv_bytes_per_layer);
         __half* vc = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(e->vcache) + l * e->kv_bytes_per_layer);
@@ -181,19 +195,22 @@ int enqueue_token(spb_engine* e, bool record_tokens) {
         __half* o1d[1] = {e->down};
         if (e->fused) {
             // previous layer's down-projection residual add + input norm + quantise, inside q/k/v
+            // ... and rope(q), rope(k), scatter of k and v into the caches as its epilogue
+            const RopeScatter rs{e->d_pos, c.rope_theta, hd, c.max_position_embeddings, kc, vc};
             if ((rc = bitlinear_resnorm_group(make_group(g3, o3, 3), cur, l == 0 ? nullptr : e->down, nullptr, L.norm[0],
-                                              other, c.rms_norm_eps, s))) return rc;
+                                              other, c.rms_norm_eps, s, e->rope_in_qkv ? &rs : nullptr))) return rc;
             std::swap(cur, other);
         } else {
             if ((rc = residual_norm_quant(l == 0 ? nullptr : e->down, nullptr, cur, L.norm[0], nullptr, e->xq, e->absmax,
                                           H, c.rms_norm_eps, s))) return rc;
             if ((rc = bitlinear_q8_group(make_group(g3, o3, 3), e->xq, e->absmax, s))) return rc;
         }
-        if ((rc = rope_scatter(e->q, e->k, e->v, kc, vc, nh, nkv, hd, c.max_position_embeddings, c.rope_theta,
-                               e->d_pos, s))) return rc;
+        if (!(e->fused && e->rope_in_qkv) &&
+            (rc = rope_scatter(e->q, e->k, e->v, kc, vc, nh, nkv, hd, c.max_position_embeddings, c.rope_theta, e->d_pos, s)))
+            return rc;
         if (e->split_attention) {
             if ((rc = decode_attention_split(e->q, kc, vc, e->attn, nh, nkv, hd, c.max_position_embeddings, 0, e->d_pos,
-                                             attn_scale, e->attn_scratch, s))) return rc;
+                                             attn_scale, e->attn_scratch, s, e->fused ? e->attn_counters : nullptr))) return rc;
         } else if ((rc = decode_attention_pos(e->q, kc, vc, e->attn, nh, nkv, hd, c.max_position_embeddings,
                                               attn_scale, e->d_pos, s))) {
             return rc;
@@ -244,16 +261,74 @@ void drop_graph(spb_engine* e) {
     e->pf_prev_T = 0;
 }
 
+// Decides whether the layers of a token run as the persistent kernel and, if so, hands it the model: the layer
+// table goes to device memory here, outside any stream capture.
+int choose_persistent(spb_engine* e) {
+    e->persistent = false;
+    if (e->decode_mode != 2) return SPB_OK;  // measured slower than the chain of kernels so far: only on request
+    const spb_model_config& c = e->cfg;
+    const int qdim = c.num_attention_heads * c.head_dim, kvdim = c.num_key_value_heads * c.head_dim;
+    PdModel m{};
+    m.nlayers = c.num_hidden_layers;
+    m.H = c.hidden_size; m.inter = c.intermediate_size; m.nh = c.num_attention_heads; m.nkv = c.num_key_value_heads;
+    m.hd = c.head_dim; m.max_seq = c.max_position_embeddings;
+    m.eps = c.rms_norm_eps; m.theta = c.rope_theta; m.attn_scale = 1.0f / sqrtf(static_cast<float>(c.head_dim));
+    m.embed = e->embed;
+    m.d_next = e->d_next; m.d_pos = e->d_pos;
+    m.xa = e->x; m.xb = e->x2; m.q = e->q; m.attn = e->attn; m.o = e->o; m.gate = e->gate; m.up = e->up; m.down = e->down;
+    m.scratch = e->attn_scratch;
+    const char* why = "";
+    std::vector<PdLayer> host(e->layers.size());
+    const int want_rows[7] = {qdim, kvdim, kvdim, c.hidden_size, c.intermediate_size, c.intermediate_size, c.hidden_size};
+    const int want_cols[7] = {c.hidden_size, c.hidden_size, c.hidden_size, qdim, c.hidden_size, c.hidden_size, c.intermediate_size};
+    bool ok = e->split_attention && !e->layers.empty();
+    if (!ok) why = "attention shape";
+    for (size_t l = 0; l < e->layers.size() && ok; ++l) {
+        const Layer& L = e->layers[l];
+        for (int i = 0; i < 7; ++i) {
+            if (L.lin[i].rows != want_rows[i] || L.lin[i].cols != want_cols[i]) {
+                ok = false;
+                why = "a matrix does not have the shape the model config implies";
+            }
+            host[l].lin[i] = PdLinear{L.lin[i].meta, L.lin[i].values, L.lin[i].gamma, L.lin[i].ms, L.lin[i].vs};
+        }
+        for (int i = 0; i < 4; ++i) host[l].norm[i] = L.norm[i];
+        host[l].kc = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(e->kcache) + l * e->kv_bytes_per_layer);
+        host[l].vc = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(e->vcache) + l * e->kv_bytes_per_layer);
+        if (ok && !decode_persistent_supported(m, host[l].lin, &why)) ok = false;
+    }
+    if (!ok) {
+        if (e->decode_mode == 2) return fail(SPB_E_UNSUPPORTED, "engine: the persistent decode step does not take this model: %s", why);
+        return SPB_OK;
+    }
+    // Both transfers go through the engine's own stream (it does not synchronise with the null stream) and are
+    // waited for here: the kernel must not start before its tables are in place.
+    if (!e->d_pd_layers) SPB_CUDA(cudaMalloc(&e->d_pd_layers, sizeof(PdLayer) * host.size()));
+    if (!e->d_pd_sync) {
+        SPB_CUDA(cudaMalloc(&e->d_pd_sync, sizeof(unsigned) * (kPdSyncWords + c.num_key_value_heads)));
+        SPB_CUDA(cudaMemsetAsync(e->d_pd_sync, 0, sizeof(unsigned) * (kPdSyncWords + c.num_key_value_heads), e->stream));
+    }
+    SPB_CUDA(cudaMemcpyAsync(e->d_pd_layers, host.data(), sizeof(PdLayer) * host.size(), cudaMemcpyHostToDevice, e->stream));
+    SPB_CUDA(cudaStreamSynchronize(e->stream));
+    m.layers = e->d_pd_layers;
+    m.sync = e->d_pd_sync;
+    e->pd = m;
+    e->persistent = true;
+    return SPB_OK;
+}
+
 int ensure_graph(spb_engine* e, bool record_tokens, int n_prompt) {
     if (e->graph && e->graph_generates == record_tokens && e->n_prompt_in_graph == n_prompt) return SPB_OK;
     drop_graph(e);
     e->n_prompt_in_graph = n_prompt;
-    e->fused = !e->force_unfused;
+    e->fused = e->decode_mode != 3;
+    if (int rc = choose_persistent(e)) return rc;
     for (const Layer& L : e->layers) {
         const Linear* all[7] = {&L.lin[0], &L.lin[1], &L.lin[2], &L.lin[3], &L.lin[4], &L.lin[5], &L.lin[6]};
         __half* none[7] = {};
         for (int i = 0; i < 7 && e->fused; ++i) e->fused = bitlinear_group_is_fast(make_group(all + i, none + i, 1));
     }
+    e->rope_in_qkv = e->fused && e->cfg.head_dim % 2 == 0;
     SPB_CUDA(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
     int rc = enqueue_token(e, record_tokens);
     cudaGraph_t g = nullptr;
@@ -469,8 +544,6 @@ extern "C" spb_engine* spb_engine_create(const spb_model_config* cfg) {
     if (!e) return nullptr;
     e->cfg = *cfg;
     e->layers.resize(cfg->num_hidden_layers);
-    const char* unf = std::getenv("SPB_ENGINE_UNFUSED");  // testing aid: one launch per vector op group
-    e->force_unfused = unf && unf[0] == '1';
     cudaGetDevice(&e->device);
     const int H = cfg->hidden_size, qdim = cfg->num_attention_heads * cfg->head_dim;
     const int kvdim = cfg->num_key_value_heads * cfg->head_dim, inter = cfg->intermediate_size;
@@ -486,14 +559,15 @@ extern "C" spb_engine* spb_engine_create(const spb_model_config* cfg) {
     const size_t o_attn = take(2 * qdim), o_o = take(2 * H), o_gate = take(2 * inter), o_up = take(2 * inter);
     const size_t o_down = take(2 * H), o_xf = take(2 * H), o_xq = take(maxdim), o_abs = take(16);
     const size_t o_logits = take(4 * static_cast<size_t>(cfg->vocab_size));
-    e->split_attention = cfg->num_attention_heads % cfg->num_key_value_heads == 0 &&
-                         cfg->num_attention_heads / cfg->num_key_value_heads <= 8 && cfg->head_dim <= 256;
+    e->split_attention = decode_attention_split_supported(cfg->num_attention_heads, cfg->num_key_value_heads, cfg->head_dim);
     const size_t o_ascr = take(decode_attention_scratch_bytes(cfg->num_attention_heads, cfg->head_dim,
                                                               cfg->max_position_embeddings));
+    const size_t o_actr = take(4 * static_cast<size_t>(cfg->num_key_value_heads));
     const size_t o_bval = take(4 * 128), o_bidx = take(4 * 128), o_ints = take(16);
     const size_t o_out = take(4 * static_cast<size_t>(kMaxTokensOut));
     e->pool_bytes = off;
     if (cudaMalloc(&e->pool, e->pool_bytes) != cudaSuccess || cudaMemset(e->pool, 0, e->pool_bytes) != cudaSuccess ||
+        cudaDeviceSynchronize() != cudaSuccess ||  // the fill runs on the null stream, the engine on a stream that does not wait for it
         cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) != cudaSuccess) {
         cuda_fail("spb_engine_create", cudaGetLastError());
         if (e->pool) cudaFree(e->pool);
@@ -518,6 +592,7 @@ extern "C" spb_engine* spb_engine_create(const spb_model_config* cfg) {
     e->absmax = reinterpret_cast<float*>(p + o_abs);
     e->logits = reinterpret_cast<float*>(p + o_logits);
     e->attn_scratch = reinterpret_cast<float*>(p + o_ascr);
+    e->attn_counters = reinterpret_cast<unsigned*>(p + o_actr);
     e->bval = reinterpret_cast<float*>(p + o_bval);
     e->bidx = reinterpret_cast<int*>(p + o_bidx);
     e->d_pos = reinterpret_cast<int*>(p + o_ints);
@@ -540,6 +615,8 @@ extern "C" void spb_engine_destroy(spb_engine* e) {
         if (e->pf_join[i]) cudaEventDestroy(e->pf_join[i]);
     }
     if (e->pf_fork) cudaEventDestroy(e->pf_fork);
+    if (e->d_pd_layers) cudaFree(e->d_pd_layers);
+    if (e->d_pd_sync) cudaFree(e->d_pd_sync);
     cudaFree(e->pool);
     cudaStreamDestroy(e->stream);
     delete e;
@@ -636,10 +713,27 @@ extern "C" int spb_engine_reset(spb_engine* e) {
     SPB_CUDA(cudaMemsetAsync(e->kcache, 0, kv_total, e->stream));
     SPB_CUDA(cudaMemsetAsync(e->vcache, 0, kv_total, e->stream));
     SPB_CUDA(cudaMemsetAsync(e->d_pos, 0, 16, e->stream));
+    // barrier words of the persistent step: a launch that gave up at a barrier leaves them marked broken
+    if (e->d_pd_sync)
+        SPB_CUDA(cudaMemsetAsync(e->d_pd_sync, 0, sizeof(unsigned) * (kPdSyncWords + e->cfg.num_key_value_heads), e->stream));
     SPB_CUDA(cudaStreamSynchronize(e->stream));
     e->seq_len = 0;
     return SPB_OK;
 }
+
+extern "C" int spb_engine_set_decode_mode(spb_engine* e, int mode) {
+    if (!e) return fail(SPB_E_INVALID, "spb_engine_set_decode_mode: null handle");
+    if (mode < 0 || mode > 3) return fail(SPB_E_INVALID, "spb_engine_set_decode_mode: mode %d", mode);
+    SPB_ON_ENGINE_DEVICE(e);
+    if (mode != e->decode_mode) {
+        SPB_CUDA(cudaStreamSynchronize(e->stream));
+        drop_graph(e);
+        e->decode_mode = mode;
+    }
+    return SPB_OK;
+}
+
+extern "C" int spb_engine_decode_is_persistent(const spb_engine* e) { return e && e->persistent ? 1 : 0; }
 
 extern "C" int spb_engine_seq_len(const spb_engine* e) { return e ? e->seq_len : 0; }
 

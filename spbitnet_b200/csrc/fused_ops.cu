@@ -168,13 +168,10 @@ __global__ void __launch_bounds__(256) rope_scatter_kernel(__half* __restrict__ 
         const bool is_q = t < q_pairs;
         const int tt = is_q ? t : t - q_pairs;
         const int head = tt / hp, pair = tt % hp;
-        const float freq = 1.0f / powf(theta, static_cast<float>(2 * pair) / static_cast<float>(head_dim));
-        const float angle = static_cast<float>(pos) * freq;
-        const float c = cosf(angle), s = sinf(angle);
         const int idx = head * head_dim + 2 * pair;
         const __half* src = is_q ? q : k;
-        const float x0 = __half2float(src[idx]), x1 = __half2float(src[idx + 1]);
-        const __half y0 = __float2half_rn(x0 * c - x1 * s), y1 = __float2half_rn(x0 * s + x1 * c);
+        __half y0, y1;
+        rope_rotate(__half2float(src[idx]), __half2float(src[idx + 1]), pos, pair, head_dim, theta, y0, y1);
         if (is_q) {
             q[idx] = y0;
             q[idx + 1] = y1;

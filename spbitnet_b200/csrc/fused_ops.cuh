@@ -9,6 +9,26 @@
 
 namespace spb {
 
+// rope_gpu on one (even, odd) pair of a head at position pos (src/kernels/inference_kernels.cu, rope_kernel):
+// angle = pos / theta^(2 pair / head_dim), fp32 rotation, rounded to half.  The fused multiply-adds are written out
+// so that every kernel that rotates (rope_scatter, the persistent decode step) rounds alike.
+__device__ __forceinline__ void rope_angle(int pos, int pair, int head_dim, float theta, float& c, float& s) {
+    const float freq = 1.0f / powf(theta, static_cast<float>(2 * pair) / static_cast<float>(head_dim));
+    const float angle = static_cast<float>(pos) * freq;
+    c = cosf(angle);
+    s = sinf(angle);
+}
+__device__ __forceinline__ void rope_apply(float x0, float x1, float c, float s, __half& y0, __half& y1) {
+    y0 = __float2half_rn(__fmaf_rn(x0, c, -__fmul_rn(x1, s)));
+    y1 = __float2half_rn(__fmaf_rn(x0, s, __fmul_rn(x1, c)));
+}
+__device__ __forceinline__ void rope_rotate(float x0, float x1, int pos, int pair, int head_dim, float theta,
+                                            __half& y0, __half& y1) {
+    float c, s;
+    rope_angle(pos, pair, head_dim, theta, c, s);
+    rope_apply(x0, x1, c, s, y0, y1);
+}
+
 int residual_norm_quant(const void* delta, const float* sub_w, void* x, const float* w, void* xn_out,
                         int8_t* xq, float* d_absmax, int n, float eps, void* stream, int vectors = 1);
 int relu2_norm_quant(const void* gate, const void* up, const float* sub_w, void* h_out, int8_t* hq,
@@ -20,10 +40,14 @@ int decode_attention_pos(const void* Q, const void* K, const void* V, void* out,
                          int num_kv_heads, int head_dim, int max_seq_len, float scale, const int* d_pos,
                          void* stream, int vectors = 1, size_t seq_stride = 0);
 // attention.cu: split-KV decode attention.  seq_len comes from *d_pos + 1 when d_pos is given.
+// `counters` (optional): num_kv_heads zeroed words; with them the merge of a KV head's chunks runs inside the same
+// launch, in the block that finishes last, instead of as a second kernel.  They are left at zero.
 int decode_attention_split(const void* Q, const void* K, const void* V, void* out, int num_heads,
                            int num_kv_heads, int head_dim, int max_seq_len, int seq_len, const int* d_pos,
-                           float scale, float* scratch, void* stream);
+                           float scale, float* scratch, void* stream, unsigned* counters = nullptr);
 size_t decode_attention_scratch_bytes(int num_heads, int head_dim, int max_seq_len);
+// the split kernel takes GQA groups of up to 8 heads and head dims that are multiples of 8 up to 256 (16-byte aligned Q, K, V)
+bool decode_attention_split_supported(int num_heads, int num_kv_heads, int head_dim);
 int embed_token(const void* embed, void* x, int hidden, const int* d_prompt, int n_prompt,
                 const int* d_next, const int* d_pos, void* stream);
 int argmax_advance(const float* logits, int n, float* bval, int* bidx, int nblocks, int* d_next,
@@ -49,9 +73,20 @@ bool bitlinear_group_is_fast(const BitLinearGroup& g);
 int bitlinear_q8_group(const BitLinearGroup& g, const int8_t* xq, const float* d_absmax, void* stream);
 // activation = half vector; absmax formed inside the launch
 int bitlinear_amax_group(const BitLinearGroup& g, const void* x_half, void* stream);
-// activation = quantised rms_norm(w_norm) of x_out = x_in + [rms_norm(w_sub)](delta); block 0 writes x_out
+// What a q/k/v launch does with its rows instead of storing them as they are: matrix 0 (q) is rotated in place of
+// the store (rope_gpu) and goes to out[0]; matrix 1 (k) is rotated and written to row *d_pos of the K cache, matrix 2
+// (v) to row *d_pos of the V cache (scatter_kv_gpu): the launch absorbs the rope_scatter kernel.
+struct RopeScatter {
+    const int* d_pos;
+    float theta;
+    int head_dim, max_seq_len;
+    void* kcache;  // [kv head][max_seq_len][head_dim] half
+    void* vcache;
+};
+// activation = quantised rms_norm(w_norm) of x_out = x_in + [rms_norm(w_sub)](delta); block 0 writes x_out.
+// With `rope` the group must be q, k, v (see RopeScatter).
 int bitlinear_resnorm_group(const BitLinearGroup& g, const void* x_in, const void* delta, const float* w_sub,
-                            const float* w_norm, void* x_out, float eps, void* stream);
+                            const float* w_norm, void* x_out, float eps, void* stream, const RopeScatter* rope = nullptr);
 // activation = quantised [rms_norm(w_sub)](relu(gate)^2 * up)
 int bitlinear_relu2_group(const BitLinearGroup& g, const void* gate, const void* up, const float* w_sub, float eps,
                           void* stream);

@@ -1,0 +1,421 @@
+// The activation producers of the BitLinear launches: how the int8 activation vector of a launch comes to be.
+// Shared by the GEMV kernels (gemv.cu) and the persistent decode-step kernel (decode_persistent.cu), so that
+// both form every sum in the same order and round at the same points.  Activation vectors are read with
+// L2 loads (ld.global.cg): in the persistent kernel they were written by other blocks of the same grid.
+#pragma once
+#include "spb_common.cuh"
+
+namespace spb {
+
+//   IN_I8      : given (absmax_quantize_gpu output)
+//   IN_F16     : half vector quantised with the given *d_absmax (fused_sparse_bitlinear_gpu)
+//   IN_F16_AMAX: half vector; every block forms absmax itself (absmax_reduce_gpu + the above)
+//   IN_RESNORM : x_out = half(x_in + [rms_norm(sub_w)](delta)); xn = half(rms_norm(w)(x_out)); quantise xn
+//                (rms_norm_gpu [sub-norm], residual_add_gpu, rms_norm_gpu, absmax_quantize_gpu)
+//   IN_RELU2   : m = relu2_mul_f32(gate, up); h = sub_w ? rms_norm_f32in(m) : float_to_half(m); quantise h
+// The last three let a BitLinear launch absorb the single-block vector kernels that precede it
+// in a decode step: every block recomputes the (short) vector redundantly, block 0 publishes
+// x_out.  All rounding points of the separate kernels are kept.
+enum { IN_I8 = 0, IN_F16 = 1, IN_F16_AMAX = 2, IN_RESNORM = 3, IN_RELU2 = 4 };
+enum { OUT_I32 = 0, OUT_F32 = 1, OUT_F16 = 2 };
+
+constexpr int kProdThreads = 256;  // block size every producer is written for
+
+// What a producer reads.  (produce_x takes any type with these members.)
+struct ProducerArgs {
+    const void* x;          // int8 (IN_I8), half (IN_F16*), residual x_in (IN_RESNORM), gate (IN_RELU2)
+    const void* x2;         // delta (IN_RESNORM, may be null), up (IN_RELU2)
+    const float* w_sub;     // sub-norm weights (IN_RESNORM on delta, IN_RELU2), may be null; global or shared memory
+    const float* w_norm;    // norm weights (IN_RESNORM); global or shared memory
+    void* x_out;            // updated residual stream (IN_RESNORM)
+    float eps;
+    const float* d_absmax;  // device scalar (IN_I8 with scaled output, IN_F16)
+    int cols;
+};
+
+// ---- activation producers ----------------------------------------------------------------
+// Four norm weights.  A plain (generic) load: the GEMV kernels pass global memory, the persistent decode kernel
+// a copy it keeps in shared memory.
+__device__ __forceinline__ float4 prod_ld_weights(const float* w, int idx) {
+    return *(reinterpret_cast<const float4*>(w) + idx);
+}
+__device__ __forceinline__ float blk_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = (lane < kProdThreads / 32) ? red[lane] : 0.0f;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, off);
+    return t;
+}
+__device__ __forceinline__ float blk_max(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, off));
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = (lane < kProdThreads / 32) ? red[lane] : 0.0f;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) t = fmaxf(t, __shfl_xor_sync(0xFFFFFFFFu, t, off));
+    return t;
+}
+
+// int8 element i of the activation vector lives at byte i of the swizzled chunk array.
+__device__ __forceinline__ int8_t* xs_byte(uint4* xs, int i) {
+    const int q = i >> 4, c = q >> 3, k = q & 7;
+    return reinterpret_cast<int8_t*>(xs + ((c << 3) + (k ^ (c & 7)))) + (i & 15);
+}
+
+// Strided-loop form of the normalising producers, for vectors too long for the register form.
+template <int IN, class Args>
+__device__ __noinline__ float produce_x_loops(const Args& a, uint4* xs, __half* hbuf, float* red,
+                                              bool publisher) {
+    const int tid = threadIdx.x;
+    const int n = a.cols;
+    if (IN == IN_RESNORM) {
+        const __half* x_in = static_cast<const __half*>(a.x);
+        const __half* delta = static_cast<const __half*>(a.x2);
+        __half* x_out = static_cast<__half*>(a.x_out);
+        // 1. residual stream: x_new = half(float(d) + float(x)), d = delta or its sub-norm
+        float s = 0.0f;
+        if (delta) {
+            float sub_scale = 1.0f;
+            if (a.w_sub) {
+                float ss = 0.0f;
+                for (int i = tid; i < n; i += kProdThreads) {
+                    const float v = __half2float(delta[i]);
+                    ss += v * v;
+                }
+                sub_scale = rsqrtf(blk_sum(ss, red) / static_cast<float>(n) + a.eps);
+            }
+            for (int i = tid; i < n; i += kProdThreads) {
+                float d = __half2float(delta[i]);
+                if (a.w_sub) d = __half2float(__float2half_rn(__fmul_rn(__fmul_rn(d, sub_scale), a.w_sub[i])));
+                const __half r = __float2half_rn(d + __half2float(x_in[i]));
+                hbuf[i] = r;
+                if (publisher) x_out[i] = r;
+                const float v = __half2float(r);
+                s += v * v;
+            }
+        } else {
+            for (int i = tid; i < n; i += kProdThreads) {
+                const __half r = x_in[i];
+                hbuf[i] = r;
+                if (publisher && x_out != x_in) x_out[i] = r;
+                const float v = __half2float(r);
+                s += v * v;
+            }
+        }
+        // 2. xn = half(x_new * rsqrt(mean + eps) * w); absmax over the rounded values
+        const float scale = rsqrtf(blk_sum(s, red) / static_cast<float>(n) + a.eps);
+        float mx = 0.0f;
+        for (int i = tid; i < n; i += kProdThreads) {
+            const __half h = __float2half_rn(__fmul_rn(__fmul_rn(__half2float(hbuf[i]), scale), a.w_norm[i]));
+            hbuf[i] = h;
+            mx = fmaxf(mx, fabsf(__half2float(h)));
+        }
+        const float absmax = blk_max(mx, red);
+        const float qs = quant_scale(absmax);
+        for (int i = tid; i < n; i += kProdThreads)
+            *xs_byte(xs, i) = static_cast<int8_t>(quantize_one(__half2float(hbuf[i]), qs));
+        return absmax;
+    }
+    // IN_RELU2
+    {
+        const __half* gate = static_cast<const __half*>(a.x);
+        const __half* up = static_cast<const __half*>(a.x2);
+        float scale = 1.0f;
+        if (a.w_sub) {
+            float s = 0.0f;
+            for (int i = tid; i < n; i += kProdThreads) {
+                const float r = fmaxf(0.0f, __half2float(gate[i]));
+                const float v = __fmul_rn(__fmul_rn(r, r), __half2float(up[i]));
+                s += v * v;
+            }
+            scale = rsqrtf(blk_sum(s, red) / static_cast<float>(n) + a.eps);
+        }
+        float mx = 0.0f;
+        for (int i = tid; i < n; i += kProdThreads) {
+            const float r = fmaxf(0.0f, __half2float(gate[i]));
+            const float v = __fmul_rn(__fmul_rn(r, r), __half2float(up[i]));
+            const __half h = a.w_sub ? __float2half_rn(__fmul_rn(__fmul_rn(v, scale), a.w_sub[i])) : __float2half_rn(v);
+            hbuf[i] = h;
+            mx = fmaxf(mx, fabsf(__half2float(h)));
+        }
+        const float absmax = blk_max(mx, red);
+        const float qs = quant_scale(absmax);
+        for (int i = tid; i < n; i += kProdThreads)
+            *xs_byte(xs, i) = static_cast<int8_t>(quantize_one(__half2float(hbuf[i]), qs));
+        return absmax;
+    }
+}
+
+// Fills xs (swizzled int8) and returns the absmax that belongs to it.  hbuf: cols halfs of
+// scratch (only touched by the normalising producers).
+template <int IN, int OUT, class Args>
+__device__ __forceinline__ float produce_x(const Args& a, uint4* xs, __half* hbuf, float* red,
+                                           bool publisher) {
+    const int tid = threadIdx.x;
+    const int n = a.cols, nchunks = n >> 4;
+    if (IN == IN_I8) {
+        const uint4* xg = static_cast<const uint4*>(a.x);
+        for (int q = tid; q < nchunks; q += kProdThreads) {
+            const int c = q >> 3, i = q & 7;
+            xs[(c << 3) + (i ^ (c & 7))] = __ldcg(xg + q);
+        }
+        return (OUT != OUT_I32) ? *a.d_absmax : 0.0f;
+    }
+    if (IN == IN_F16 || IN == IN_F16_AMAX) {
+        const uint4* xg = static_cast<const uint4*>(a.x);
+        float absmax;
+        if (IN == IN_F16) {
+            absmax = *a.d_absmax;
+        } else {
+            float mx = 0.0f;
+            for (int q = tid; q < 2 * nchunks; q += kProdThreads) {
+                const uint4 t = __ldcg(xg + q);
+                const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const __half2 h2 = *reinterpret_cast<const __half2*>(&w[k]);
+                    mx = fmaxf(mx, fmaxf(fabsf(__low2float(h2)), fabsf(__high2float(h2))));
+                }
+            }
+            absmax = blk_max(mx, red);
+        }
+        const float scale = quant_scale(absmax);
+        for (int q = tid; q < nchunks; q += kProdThreads) {
+            const uint4 lo = __ldcg(xg + 2 * q), hi = __ldcg(xg + 2 * q + 1);
+            const uint32_t hw[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+            uint32_t out[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                uint32_t packed = 0;
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const __half2 h2 = *reinterpret_cast<const __half2*>(&hw[2 * k + e]);
+                    const int q0 = quantize_one(__low2float(h2), scale);
+                    const int q1 = quantize_one(__high2float(h2), scale);
+                    packed |= (static_cast<uint32_t>(q0) & 0xFFu) << (16 * e);
+                    packed |= (static_cast<uint32_t>(q1) & 0xFFu) << (16 * e + 8);
+                }
+                out[k] = packed;
+            }
+            const int c = q >> 3, i = q & 7;
+            xs[(c << 3) + (i ^ (c & 7))] = make_uint4(out[0], out[1], out[2], out[3]);
+        }
+        return absmax;
+    }
+    // The normalising producers.  A thread owns up to kOwn chunks of 8 consecutive elements
+    // (chunk q = tid + k*256); all global loads of a pass are issued before any is consumed, and
+    // the values a later pass needs stay in registers as packed halves.  Vectors longer than
+    // kOwn*8*256 elements take the strided-loop form below.
+    constexpr int kOwn = 4;
+    const int nq = n >> 3;  // n is a multiple of 128
+    if (nq <= kOwn * kProdThreads) {
+        auto h2f2 = [](uint32_t w, float& lo, float& hi) {
+            const __half2 h2 = *reinterpret_cast<const __half2*>(&w);
+            lo = __low2float(h2);
+            hi = __high2float(h2);
+        };
+        auto pack2 = [](__half lo, __half hi) {
+            const __half2 h2 = __halves2half2(lo, hi);
+            return *reinterpret_cast<const uint32_t*>(&h2);
+        };
+        uint32_t hv[kOwn][4];  // the thread's elements as packed halves (x_new, then xn / h)
+        float absmax;
+        if (IN == IN_RESNORM) {
+            const uint4* x_in = static_cast<const uint4*>(a.x);
+            const uint4* delta = static_cast<const uint4*>(a.x2);
+            uint4* x_out = static_cast<uint4*>(a.x_out);
+            uint4 xv[kOwn], dv[kOwn];
+#pragma unroll
+            for (int k = 0; k < kOwn; ++k) {
+                const int q = tid + k * kProdThreads;
+                xv[k] = make_uint4(0, 0, 0, 0);
+                dv[k] = make_uint4(0, 0, 0, 0);
+                if (q < nq) {
+                    xv[k] = __ldcg(x_in + q);
+                    if (delta) dv[k] = __ldcg(delta + q);
+                }
+            }
+            float sub_scale = 1.0f;
+            if (delta && a.w_sub) {
+                float ss = 0.0f;
+#pragma unroll
+                for (int k = 0; k < kOwn; ++k) {
+                    const uint32_t w[4] = {dv[k].x, dv[k].y, dv[k].z, dv[k].w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        float lo, hi;
+                        h2f2(w[e], lo, hi);
+                        ss += lo * lo;
+                        ss += hi * hi;
+                    }
+                }
+                sub_scale = rsqrtf(blk_sum(ss, red) / static_cast<float>(n) + a.eps);
+            }
+            float s = 0.0f;
+#pragma unroll
+            for (int k = 0; k < kOwn; ++k) {
+                const int q = tid + k * kProdThreads;
+                const uint32_t xw[4] = {xv[k].x, xv[k].y, xv[k].z, xv[k].w};
+                const uint32_t dw[4] = {dv[k].x, dv[k].y, dv[k].z, dv[k].w};
+                float ws[8];
+                if (delta && a.w_sub && q < nq) {
+                    const float4 w0 = prod_ld_weights(a.w_sub, 2 * q);
+                    const float4 w1 = prod_ld_weights(a.w_sub, 2 * q + 1);
+                    ws[0] = w0.x; ws[1] = w0.y; ws[2] = w0.z; ws[3] = w0.w;
+                    ws[4] = w1.x; ws[5] = w1.y; ws[6] = w1.z; ws[7] = w1.w;
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) ws[e] = 1.0f;
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float x0, x1, d0, d1;
+                    h2f2(xw[e], x0, x1);
+                    h2f2(dw[e], d0, d1);
+                    __half r0, r1;
+                    if (delta) {
+                        if (a.w_sub) {
+                            d0 = __half2float(__float2half_rn(__fmul_rn(__fmul_rn(d0, sub_scale), ws[2 * e])));
+                            d1 = __half2float(__float2half_rn(__fmul_rn(__fmul_rn(d1, sub_scale), ws[2 * e + 1])));
+                        }
+                        r0 = __float2half_rn(d0 + x0);
+                        r1 = __float2half_rn(d1 + x1);
+                    } else {
+                        r0 = __float2half_rn(x0);
+                        r1 = __float2half_rn(x1);
+                    }
+                    hv[k][e] = pack2(r0, r1);
+                    const float f0 = __half2float(r0), f1 = __half2float(r1);
+                    s += f0 * f0;
+                    s += f1 * f1;
+                }
+                if (publisher && q < nq && (delta || x_out != static_cast<void*>(const_cast<uint4*>(x_in))))
+                    x_out[q] = make_uint4(hv[k][0], hv[k][1], hv[k][2], hv[k][3]);
+            }
+            const float scale = rsqrtf(blk_sum(s, red) / static_cast<float>(n) + a.eps);
+            float mx = 0.0f;
+#pragma unroll
+            for (int k = 0; k < kOwn; ++k) {
+                const int q = tid + k * kProdThreads;
+                float wn[8];
+                if (q < nq) {
+                    const float4 w0 = prod_ld_weights(a.w_norm, 2 * q);
+                    const float4 w1 = prod_ld_weights(a.w_norm, 2 * q + 1);
+                    wn[0] = w0.x; wn[1] = w0.y; wn[2] = w0.z; wn[3] = w0.w;
+                    wn[4] = w1.x; wn[5] = w1.y; wn[6] = w1.z; wn[7] = w1.w;
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) wn[e] = 0.0f;
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float f0, f1;
+                    h2f2(hv[k][e], f0, f1);
+                    const __half h0 = __float2half_rn(__fmul_rn(__fmul_rn(f0, scale), wn[2 * e]));
+                    const __half h1 = __float2half_rn(__fmul_rn(__fmul_rn(f1, scale), wn[2 * e + 1]));
+                    hv[k][e] = pack2(h0, h1);
+                    mx = fmaxf(mx, fmaxf(fabsf(__half2float(h0)), fabsf(__half2float(h1))));
+                }
+            }
+            absmax = blk_max(mx, red);
+        } else {  // IN_RELU2
+            const uint4* gate = static_cast<const uint4*>(a.x);
+            const uint4* up = static_cast<const uint4*>(a.x2);
+            uint4 gv[kOwn], uv[kOwn];
+#pragma unroll
+            for (int k = 0; k < kOwn; ++k) {
+                const int q = tid + k * kProdThreads;
+                gv[k] = make_uint4(0, 0, 0, 0);
+                uv[k] = make_uint4(0, 0, 0, 0);
+                if (q < nq) {
+                    gv[k] = __ldcg(gate + q);
+                    uv[k] = __ldcg(up + q);
+                }
+            }
+            auto relu2 = [](float gq, float uq) {
+                const float r = fmaxf(0.0f, gq);
+                return __fmul_rn(__fmul_rn(r, r), uq);
+            };
+            float scale = 1.0f;
+            if (a.w_sub) {
+                float s = 0.0f;
+#pragma unroll
+                for (int k = 0; k < kOwn; ++k) {
+                    const uint32_t gw[4] = {gv[k].x, gv[k].y, gv[k].z, gv[k].w};
+                    const uint32_t uw[4] = {uv[k].x, uv[k].y, uv[k].z, uv[k].w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        float g0, g1, u0, u1;
+                        h2f2(gw[e], g0, g1);
+                        h2f2(uw[e], u0, u1);
+                        const float m0 = relu2(g0, u0), m1 = relu2(g1, u1);
+                        s += m0 * m0;
+                        s += m1 * m1;
+                    }
+                }
+                scale = rsqrtf(blk_sum(s, red) / static_cast<float>(n) + a.eps);
+            }
+            float mx = 0.0f;
+#pragma unroll
+            for (int k = 0; k < kOwn; ++k) {
+                const int q = tid + k * kProdThreads;
+                const uint32_t gw[4] = {gv[k].x, gv[k].y, gv[k].z, gv[k].w};
+                const uint32_t uw[4] = {uv[k].x, uv[k].y, uv[k].z, uv[k].w};
+                float ws[8];
+                if (a.w_sub && q < nq) {
+                    const float4 w0 = prod_ld_weights(a.w_sub, 2 * q);
+                    const float4 w1 = prod_ld_weights(a.w_sub, 2 * q + 1);
+                    ws[0] = w0.x; ws[1] = w0.y; ws[2] = w0.z; ws[3] = w0.w;
+                    ws[4] = w1.x; ws[5] = w1.y; ws[6] = w1.z; ws[7] = w1.w;
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) ws[e] = 0.0f;
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float g0, g1, u0, u1;
+                    h2f2(gw[e], g0, g1);
+                    h2f2(uw[e], u0, u1);
+                    const float m0 = relu2(g0, u0), m1 = relu2(g1, u1);
+                    const __half h0 = a.w_sub ? __float2half_rn(__fmul_rn(__fmul_rn(m0, scale), ws[2 * e])) : __float2half_rn(m0);
+                    const __half h1 = a.w_sub ? __float2half_rn(__fmul_rn(__fmul_rn(m1, scale), ws[2 * e + 1])) : __float2half_rn(m1);
+                    hv[k][e] = pack2(h0, h1);
+                    if (q < nq) mx = fmaxf(mx, fmaxf(fabsf(__half2float(h0)), fabsf(__half2float(h1))));
+                }
+            }
+            absmax = blk_max(mx, red);
+        }
+        const float qs = quant_scale(absmax);
+#pragma unroll
+        for (int k = 0; k < kOwn; ++k) {
+            const int q = tid + k * kProdThreads;
+            if (q < nq) {
+                uint32_t o[2] = {0, 0};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float f0, f1;
+                    h2f2(hv[k][e], f0, f1);
+                    const uint32_t b0 = static_cast<uint32_t>(quantize_one(f0, qs)) & 0xFFu;
+                    const uint32_t b1 = static_cast<uint32_t>(quantize_one(f1, qs)) & 0xFFu;
+                    o[e >> 1] |= (b0 | (b1 << 8)) << (16 * (e & 1));
+                }
+                // elements 8q..8q+7 are half of the 16-byte chunk q>>1 of the swizzled x array
+                const int q16 = q >> 1, c = q16 >> 3, i = q16 & 7;
+                uint2* dst = reinterpret_cast<uint2*>(xs + ((c << 3) + (i ^ (c & 7)))) + (q & 1);
+                *dst = make_uint2(o[0], o[1]);
+            }
+        }
+        return absmax;
+    }
+    return produce_x_loops<IN, Args>(a, xs, hbuf, red, publisher);
+}
+
+}  // namespace spb

@@ -694,6 +694,7 @@ struct spb_shard_engine {
     __half *x = nullptr, *x2 = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr, *o = nullptr;
     __half *gate = nullptr, *up = nullptr, *down = nullptr, *xfinal = nullptr;
     int8_t* xq = nullptr;
+    unsigned* attn_counters = nullptr;  // per local KV head: attention chunks written so far (zero between launches)
     float *absmax = nullptr, *attn_scratch = nullptr, *logits = nullptr, *pairs = nullptr, *cand = nullptr;
     int argmax_blocks = 1;
     int32_t* acc = nullptr;  // three int32 workspaces for the SIMT form of the batched product
@@ -874,7 +875,7 @@ int enqueue_step(spb_shard_engine* e, bool record) {
             // (a batched form of the split kernel, one block per (KV head, chunk, sequence), was measured slower for
             // 64 sequences than one block per (head, sequence): 54.6 against 51.6 ms per step)
             if ((rc = decode_attention_split(e->q, kc, vc, e->attn, e->nh_loc, e->nkv_loc, hd, c.max_position_embeddings, 0,
-                                             e->d_pos, attn_scale, e->attn_scratch, s))) return rc;
+                                             e->d_pos, attn_scale, e->attn_scratch, s, e->attn_counters))) return rc;
         } else if ((rc = decode_attention_pos(e->q, kc, vc, e->attn, e->nh_loc, e->nkv_loc, hd, c.max_position_embeddings,
                                               attn_scale, e->d_pos, s, B, B > 1 ? e->seq_stride : 0))) {
             return rc;
@@ -1084,7 +1085,7 @@ extern "C" spb_shard_engine* spb_shard_engine_create(const spb_model_config* cfg
     e->h_loc = e->hrow[rank + 1] - e->hrow[rank];
     e->i_loc = e->irow[rank + 1] - e->irow[rank];
     e->v_loc = e->vrow[rank + 1] - e->vrow[rank];
-    e->split_attention = e->group_heads <= 8 && hd <= 256;
+    e->split_attention = e->nkv_loc > 0 && decode_attention_split_supported(e->nh_loc, e->nkv_loc, hd);
     e->wide = H >= 4096 && H <= 8 * kWideThreads && inter <= 8 * kWideThreads * kWideRuns && qdim <= 8 * kWideThreads * kWideRuns;
     e->seq_stride = static_cast<size_t>(e->nkv_loc) * cfg->max_position_embeddings * hd;
     e->kv_layer_bytes = align_up(sizeof(__half) * e->seq_stride * B, 256);
@@ -1101,6 +1102,7 @@ extern "C" spb_shard_engine* spb_shard_engine_create(const spb_model_config* cfg
     const size_t o_gate = take(2 * B * e->i_loc), o_up = take(2 * B * e->i_loc), o_down = take(2 * B * e->h_loc), o_xf = take(2 * B * H);
     const size_t o_xq = take(B * maxdim), o_abs = take(4 * 2 * B), o_acc = take(B > 1 ? 3 * 4 * e->acc_third : 16);
     const size_t o_ascr = take(decode_attention_scratch_bytes(std::max(e->nh_loc, 1), hd, cfg->max_position_embeddings));
+    const size_t o_actr = take(4 * static_cast<size_t>(std::max(e->nkv_loc, 1)));
     e->argmax_blocks = std::max(1, std::min(128, (e->v_loc + 1023) / 1024));
     const size_t o_logits = take(4 * static_cast<size_t>(B) * e->v_loc), o_pairs = take(8 * B), o_ints = take(4 * (1 + B));
     const size_t o_cand = take(8 * static_cast<size_t>(B) * e->argmax_blocks);
@@ -1129,6 +1131,7 @@ extern "C" spb_shard_engine* spb_shard_engine_create(const spb_model_config* cfg
     e->xbuf_bytes = off;
     if (cudaMalloc(&e->pool, pool_bytes) != cudaSuccess || cudaMemset(e->pool, 0, pool_bytes) != cudaSuccess ||
         cudaMalloc(&e->xbuf, e->xbuf_bytes) != cudaSuccess || cudaMemset(e->xbuf, 0, e->xbuf_bytes) != cudaSuccess ||
+        cudaDeviceSynchronize() != cudaSuccess ||  // the fills run on the null stream, the engine on a stream that does not wait for it
         cudaHostAlloc(reinterpret_cast<void**>(&e->status), sizeof(int), cudaHostAllocPortable | cudaHostAllocMapped) != cudaSuccess ||
         cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) != cudaSuccess) {
         cuda_fail("spb_shard_engine_create", cudaGetLastError());
@@ -1154,6 +1157,7 @@ extern "C" spb_shard_engine* spb_shard_engine_create(const spb_model_config* cfg
     e->down = reinterpret_cast<__half*>(p + o_down); e->xfinal = reinterpret_cast<__half*>(p + o_xf);
     e->xq = reinterpret_cast<int8_t*>(p + o_xq); e->absmax = reinterpret_cast<float*>(p + o_abs);
     e->acc = reinterpret_cast<int32_t*>(p + o_acc); e->attn_scratch = reinterpret_cast<float*>(p + o_ascr);
+    e->attn_counters = reinterpret_cast<unsigned*>(p + o_actr);
     e->logits = reinterpret_cast<float*>(p + o_logits); e->pairs = reinterpret_cast<float*>(p + o_pairs);
     e->cand = reinterpret_cast<float*>(p + o_cand);
     e->d_pos = reinterpret_cast<int*>(p + o_ints); e->d_next = e->d_pos + 1;

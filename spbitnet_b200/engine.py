@@ -93,6 +93,18 @@ class InferenceEngine:
             check(prev)
         return prev
 
+    DECODE_AUTO, DECODE_CHAIN, DECODE_PERSISTENT, DECODE_UNFUSED = 0, 1, 2, 3
+
+    def set_decode_mode(self, mode: int) -> None:
+        """How the layers of a decode token run: DECODE_AUTO = DECODE_CHAIN (five PDL-linked kernels per layer),
+        DECODE_PERSISTENT (one cooperative launch per token), DECODE_UNFUSED (one launch per op group).
+        All modes give the same tokens and logits."""
+        check(self._lib.spb_engine_set_decode_mode(self._h, int(mode)))
+
+    @property
+    def decode_is_persistent(self) -> bool:
+        return bool(self._lib.spb_engine_decode_is_persistent(self._h))
+
     def logits(self) -> np.ndarray:
         h = np.empty(self.model.config["vocab_size"], np.float32)
         check(self._lib.spb_engine_copy_logits(self._h, C.c_void_p(h.ctypes.data)))

@@ -57,6 +57,12 @@ def debug_bounded_wait_selftest(limit_cycles: int = 4000, stream=None) -> int:
     return load().spb_debug_bounded_wait_selftest(int(limit_cycles), _stream(stream))
 
 
+def debug_grid_barrier_selftest(limit_cycles: int = 200000, stream=None) -> int:
+    """Two blocks at a grid barrier of the persistent decode step that expects three arrivals: returns
+    SPB_E_TIMEOUT when both bounded waits ran out, were counted and the kernel returned."""
+    return load().spb_debug_grid_barrier_selftest(int(limit_cycles), _stream(stream))
+
+
 # ---- sparse_ternary_kernels.h ---------------------------------------------------------
 
 def sparse_ternary_unpack_gpu(meta, values, out, rows, cols, meta_row_stride, values_row_stride, stream=None):

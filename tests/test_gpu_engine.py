@@ -70,20 +70,22 @@ def test_wide_model_few_layers():
         assert tok == int(want_tokens[step]), step
 
 
-def test_unfused_path_gives_the_same_tokens(monkeypatch):
-    # SPB_ENGINE_UNFUSED=1 runs the vector ops as their own launches; results must not change
+def test_every_decode_mode_gives_the_same_tokens_and_logits():
+    """Chain of fused kernels, one launch per vector-op group, the persistent kernel: the same bits."""
     model = synth.random_model(synth.TINY, seed=7)
     prompt = np.array([1, 2, 3, 400], np.int32)
-    fused = InferenceEngine(DeviceModel(model))
-    a = fused.generate(prompt, 8)
-    la = fused.logits()
-    monkeypatch.setenv("SPB_ENGINE_UNFUSED", "1")
-    unfused = InferenceEngine(DeviceModel(model))
-    b = unfused.generate(prompt, 8)
-    lb = unfused.logits()
-    assert (a == b).all() and (la == lb).all()
+    dm = DeviceModel(model)
+    outs = []
+    for mode in (InferenceEngine.DECODE_CHAIN, InferenceEngine.DECODE_UNFUSED, InferenceEngine.DECODE_PERSISTENT,
+                 InferenceEngine.DECODE_AUTO):
+        eng = InferenceEngine(dm)
+        eng.set_decode_mode(mode)
+        outs.append((eng.generate(prompt, 8), eng.logits()))
+        assert eng.decode_is_persistent == (mode == InferenceEngine.DECODE_PERSISTENT)
+    for tokens, logits in outs[1:]:
+        assert (tokens == outs[0][0]).all() and (logits == outs[0][1]).all()
     want, _ = oracle.Engine(model).generate(prompt, 8)
-    assert (a == want).all()
+    assert (outs[0][0] == want).all()
 
 
 def test_full_2b4t_shape_against_the_reference_cuda_kernels():

@@ -57,7 +57,7 @@ def test_noalloc_matches_caller_scratch_twice_in_a_row():
 
 def test_noalloc_refuses_what_does_not_fit():
     lib = _lib.load()
-    nh, nkv, hd, mx = 64, 8, 128, 16384  # 64 * 256 chunks * 130 floats = 8.5 MB of partial results
+    nh, nkv, hd, mx = 64, 8, 128, 16384  # 64 heads * 512 chunks * 130 floats = 17 MB of partial results
     assert lib.spb_decode_attention_scratch_bytes(nh, hd, mx) > lib.spb_decode_attention_noalloc_capacity()
     dummy = torch.zeros(16, dtype=torch.float16, device="cuda")
     rc = lib.spb_decode_attention_noalloc(_p(dummy), _p(dummy), _p(dummy), _p(dummy), nh, nkv, hd, mx, 1,
