@@ -344,6 +344,13 @@ int spb_engine_decode_is_persistent(const spb_engine* e);
 /* Test aid: two blocks at a grid barrier that expects three; both waits run out after limit_cycles (clamped),
  * the run-out is counted, the kernel returns.  Returns SPB_E_TIMEOUT when that happened as it must. */
 int spb_debug_grid_barrier_selftest(long long limit_cycles, void* stream);
+/* Diagnostic: persistent decode kernels enqueued (or captured) after this call record stage times.  d_trace is device
+ * memory for 2 x 4096 64-bit words, or NULL to switch the recording off: thread 0 of the first block writes words
+ * [0, 4096), thread 0 of the last block [4096, 8192); word 20 * layer + k is the global nanosecond timer at point k of
+ * that layer (0-3 stage 1: weights there, activation produced, rows done, barrier passed; 4-6 stage 2: next slab
+ * issued, attention chunks done, barrier passed; 7-10, 11-14, 15-18 stages 3, 4, 5 as stage 1).  Each token overwrites
+ * the previous one's marks.  python -m spbitnet_b200.decode_trace prints the table. */
+void spb_debug_set_decode_trace(void* d_trace);
 
 /* ---- model directory loader: include/spbitnet/model.h:88-145, src/model.cu:179-311 ---------------------- */
 

@@ -67,6 +67,7 @@ SIGNATURES = {
     "spb_gemm_tc_timeouts": (_i, []),
     "spb_debug_bounded_wait_selftest": (_i, [C.c_longlong, _p]),
     "spb_debug_grid_barrier_selftest": (_i, [C.c_longlong, _p]),
+    "spb_debug_set_decode_trace": (None, [_p]),
     "spb_rms_norm": (_i, [_p, _p, _p, _i, _f, _p]),
     "spb_absmax_quantize": (_i, [_p, _p, _p, _i, _p]),
     "spb_absmax_reduce": (_i, [_p, _p, _i, _p]),

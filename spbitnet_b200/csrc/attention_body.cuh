@@ -157,7 +157,7 @@ __host__ __device__ inline size_t attn_merge_smem_floats(int G, int max_seq_len)
 //   3. thread t takes (head, dim) pairs t, t + 256, ..: sum_s w[s] * o[s][d] with eight loads in flight.
 template <int G>
 __device__ __forceinline__ void attn_merge_group(const float* scratch, __half* out, int kvh, int head_dim,
-                                                 int nsplit_max, int nsplit, float* sm, unsigned long long* TR = nullptr) {
+                                                 int nsplit_max, int nsplit, float* sm) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const size_t hstride = static_cast<size_t>(nsplit_max) * (head_dim + 2);
     const float* base = scratch + static_cast<size_t>(kvh) * G * hstride;
@@ -168,7 +168,6 @@ __device__ __forceinline__ void attn_merge_group(const float* scratch, __half* o
         w[i] = __ldcg(base + g * hstride + static_cast<size_t>(s) * (head_dim + 2));
     }
     __syncthreads();
-    if (TR && tid == 0) { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); TR[0] = t; }
     for (int g = warp; g < G; g += kAttnThreads / 32) {
         float M = -1e30f;
         for (int s = lane; s < nsplit; s += 32) M = fmaxf(M, w[g * nsplit + s]);
@@ -185,7 +184,6 @@ __device__ __forceinline__ void attn_merge_group(const float* scratch, __half* o
         if (lane == 0) inv[g] = 1.0f / L;
     }
     __syncthreads();
-    if (TR && tid == 0) { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); TR[1] = t; }
     // Eight loads in flight per output; a chunk index past the end is clamped (a valid address) and weighted 0.
     for (int t = tid; t < G * head_dim; t += kAttnThreads) {
         const int g = t / head_dim, d = t - g * head_dim;

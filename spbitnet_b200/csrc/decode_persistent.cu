@@ -1,10 +1,9 @@
 // One decode token's layers as ONE persistent kernel (sm_100a): a block per SM, grid-wide barriers between the
 // stages of a layer, every layer's weight slabs prefetched into shared memory several stages ahead.
 //
-// The chain-of-kernels step (engine.cu, enqueue_token) spends most of a layer's 45 us between kernels: six
-// dependent launches, each of which starts by fetching its weights from HBM and its activation vector from L2
-// and ends with a drain.  The work itself is small (13 MB of weights per layer at the 2B-4T shape, 2 us of HBM
-// time).  Here the blocks stay resident for the whole token:
+// The chain-of-kernels step (engine.cu, enqueue_token) runs a layer as five dependent launches, each of which
+// fetches its activation vector from L2, reduces it, multiplies and drains.  The work itself is small (13 MB of
+// weights per layer at the 2B-4T shape, 2 us of HBM time).  Here the blocks stay resident for the whole token:
 //
 //   stage 1  x = quantise(rms_norm(residual + down))            q, k, v rows of this block; RoPE; K, V -> cache
 //   stage 2  split-KV attention, (KV head, chunk of 16 or 32 positions) per block; the last block of a KV head merges
@@ -19,15 +18,23 @@
 // warp-level sparse MMA exactly as in gemv_mmasp.cu (bitmaps -> index pairs, sign nibbles -> +-1 bytes, mma.sp
 // m16n8k64), its K extent split over the warps of the block.
 //
-// Weight slabs never depend on activations, so they are copied (16-byte cp.async) four stages before their
-// use: each of the four kinds of slab (q/k/v, o, gate/up, down) has its own shared-memory region, refilled for
-// the next layer as soon as the stage that read it is over.  Every stage commits exactly one copy group, so
-// "the slab of this stage has landed" is cp.async.wait_group 4 throughout.
+// Weight slabs never depend on activations, so they are copied four stages before their use: each of the four
+// kinds of slab (q/k/v, o, gate/up, down) has its own shared-memory region, refilled for the next layer as soon
+// as the stage that read it is over, by one bulk copy (cp.async.bulk) per row and stream that reports to the
+// kind's mbarrier; the layer's norm weights travel with them when they fit, and the layer table (pointers,
+// strides, scales) of this layer and the next is kept in shared memory too, because every global read after a
+// barrier is a trip to L2 (about 0.8 us) on the block's critical path.
 //
-// The grid barrier is a counter in global memory: arrive = fence + atomic add, wait = acquire loads until the
-// count reaches (generation + k * blocks).  The wait is bounded in time; a block whose wait runs out marks the
-// barrier state broken, bumps the library's timeout counter, waits for its own copies in flight and returns;
-// the other blocks run out of their own bounds.  The kernel is launched cooperatively (all blocks resident).
+// The grid barrier is a counter in global memory: arrive = fence + atomic add; the block whose arrival completes
+// the count publishes the target on a second word, which the others poll.  Every wait (grid barrier, slab
+// mbarrier) is bounded in time; a block whose wait runs out marks the barrier state broken, bumps the library's
+// timeout counter, waits (bounded) for its own copies in flight and returns; the other blocks run out of their
+// own bounds.  The kernel is launched cooperatively (all blocks resident).
+//
+// Where the time goes (2B-4T shape, position ~150, one B200): a layer takes 43 us against 37 us for the chain of
+// five kernels.  A stage is a chain of dependent round trips that the persistent form does not remove: barrier
+// arrival (atomic) -> flag seen by the pollers -> activation vector from L2 -> two or three block-wide reductions ->
+// rows -> stores, 6 - 9 us in all, of which the barrier itself is 1.5 - 3 us.  Hence an opt-in mode.
 #include "decode_persistent.cuh"
 
 #include <algorithm>
@@ -43,6 +50,8 @@ constexpr int kPdThreads = kProdThreads;  // the producers are written for this 
 constexpr int kPdWarps = kPdThreads / 32;
 constexpr long long kPdWaitCycles = 2000000000LL;  // about a second
 constexpr size_t kPdStaticSmem = 5 * 1024;            // the kernel's static shared memory, rounded up
+constexpr int kPdTraceWords = 4096;                   // marks per traced block (spb_debug_set_decode_trace)
+constexpr int kPdMarksPerLayer = 20;
 
 // Shared-memory geometry, worked out on the host.
 struct PdGeom {
@@ -55,7 +64,7 @@ struct PdGeom {
     int norms;             // 1: the norm weights travel with the slabs into shared memory; 0: read from global memory
     long long wait_cycles;
     int* timeouts;
-    unsigned long long* trace;  // TRACE
+    unsigned long long* trace;  // stage timing (spb_debug_set_decode_trace), or null
 };
 
 using PdProd = ProducerArgs;
@@ -373,14 +382,19 @@ __global__ void __launch_bounds__(kPdThreads, 1) decode_persistent_kernel(const 
             asm volatile("st.shared.u32 [%0], %1;" ::"r"(d + 48u), "r"(xv.w) : "memory");
         }
     };
-    int tr_i = 0;  // TRACE
-    auto mark = [&]() {  // TRACE
-        if (geo.trace && (b == 0 || b == 147) && tid == 0) {
+    // Stage timing for spb_debug_set_decode_trace: thread 0 of the first and of the last block write the global
+    // nanosecond timer at up to kPdMarksPerLayer points of every layer, in this order:
+    //   stage 1: slab and norm weights there, x produced, tiles done, barrier passed        (0 .. 3)
+    //   stage 2: next q/k/v slab issued, chunks (and merge) done, barrier passed            (4 .. 6)
+    //   stages 3, 4, 5: as stage 1                                                          (7 .. 10, 11 .. 14, 15 .. 18)
+    int layer_now = 0;
+    auto mark = [&](int k) {
+        const int i = layer_now * kPdMarksPerLayer + k;
+        if (geo.trace && (b == 0 || b == nb - 1) && tid == 0 && i < kPdTraceWords) {
             unsigned long long t;
             asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-            geo.trace[(b ? 4096 : 0) + tr_i] = t;
+            geo.trace[(b ? kPdTraceWords : 0) + i] = t;
         }
-        ++tr_i;
     };
     auto barrier = [&]() {
         ++bar_n;
@@ -401,6 +415,7 @@ __global__ void __launch_bounds__(kPdThreads, 1) decode_persistent_kernel(const 
     for (int l = 0; l < m.nlayers; ++l) {
         if (l >= 1 && l + 1 < m.nlayers && tid < kLayerWords) reinterpret_cast<uint32_t*>(&s_layer[(l + 1) & 1])[tid] = next_word;
         const PdLayer& Ly = s_layer[l & 1];
+        layer_now = l;
         // ---- stage 1: residual + input norm -> q k v, RoPE, cache --------------------------------------------
         issue_rows(l, 6, m.inter, dn_s, geo.t_dn, geo.mp_i, geo.vp_i);
         issued[3] = l;
@@ -415,11 +430,11 @@ __global__ void __launch_bounds__(kPdThreads, 1) decode_persistent_kernel(const 
             pa.cols = m.H;
             if (!slab_ready(0, l)) return leave();
             consumed[0] = l;
-            mark();
+            mark(0);
             const float absmax = produce_x<IN_RESNORM, OUT_F16>(pa, xs_sw, static_cast<__half*>(nullptr), redf, b == 0);
             reorder_x(m.H);
             __syncthreads();
-            mark();
+            mark(1);
             const float dq_q = dequant_scale(Ly.lin[0].gamma, absmax), dq_k = dequant_scale(Ly.lin[1].gamma, absmax);
             const float dq_v = dequant_scale(Ly.lin[2].gamma, absmax);
             pd_tiles(qkv_s, geo.t_qkv, T_qkv, geo.mp_h, geo.vp_h, m.H >> 6, xs_s, tab_s, redi, tid, lane, warp,
@@ -445,19 +460,18 @@ __global__ void __launch_bounds__(kPdThreads, 1) decode_persistent_kernel(const 
                          else Ly.kc[(static_cast<size_t>(head) * m.max_seq + pos) * m.hd + d] = y;
                      });
         }
-        mark();
+        mark(2);
         if (!barrier()) return leave();
-        mark();
+        mark(3);
 
         // ---- stage 2: attention ------------------------------------------------------------------------------
         issue_qkv(l + 1);
         if (l + 1 < m.nlayers) issued[0] = l + 1;
-        mark();
+        mark(4);
         for (int item = b; item < m.nkv * nsplit; item += nb) {
             const int kvh = item / nsplit, split = item - kvh * nsplit;
             attn_chunk_block<G>(m.q, Ly.kc, Ly.vc, m.scratch, kvh, split, m.hd, m.max_seq, nsplit_max, m.attn_scale, seq_len,
                                 attn_sm);
-            mark();
             __syncthreads();
             if (tid == 0) {
                 __threadfence();  // cumulative: the block's partial results, then the count
@@ -468,18 +482,13 @@ __global__ void __launch_bounds__(kPdThreads, 1) decode_persistent_kernel(const 
                 s_flag[1] = last;
             }
             __syncthreads();
-            mark();
-            if (geo.trace && s_flag[1] && kvh == 2 && tid == 0) {  // TRACE
-                unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); geo.trace[6000 + l * 4] = t; geo.trace[6000 + l * 4 + 2] = b; }
             if (s_flag[1])  // every chunk of this KV head is written: merge them for its G query heads
-                attn_merge_group<G>(m.scratch, m.attn, kvh, m.hd, nsplit_max, nsplit, reinterpret_cast<float*>(attn_sm), (geo.trace && kvh == 2) ? geo.trace + 7000 + l * 2 : nullptr);
+                attn_merge_group<G>(m.scratch, m.attn, kvh, m.hd, nsplit_max, nsplit, reinterpret_cast<float*>(attn_sm));
             __syncthreads();
-            if (geo.trace && s_flag[1] && kvh == 2 && tid == 0) {  // TRACE
-                unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); geo.trace[6000 + l * 4 + 1] = t; }
         }
-        mark();
+        mark(5);
         if (!barrier()) return leave();
-        mark();
+        mark(6);
 
         // ---- stage 3: o projection ---------------------------------------------------------------------------
         if (T_h > 0) {
@@ -488,20 +497,20 @@ __global__ void __launch_bounds__(kPdThreads, 1) decode_persistent_kernel(const 
             pa.cols = qdim;
             if (!slab_ready(1, l)) return leave();
             consumed[1] = l;
-            mark();
+            mark(7);
             const float absmax = produce_x<IN_F16_AMAX, OUT_F16>(pa, xs_sw, static_cast<__half*>(nullptr), redf, b == 0);
             reorder_x(qdim);
             __syncthreads();
-            mark();
+            mark(8);
             const float dq = dequant_scale(Ly.lin[3].gamma, absmax);
             pd_tiles(o_s, geo.t_o, T_h, geo.mp_q, geo.vp_q, qdim >> 6, xs_s, tab_s, redi, tid, lane, warp,
                      [&](bool active, int tl, int r, int acc) {
                          if (active) m.o[16 * (b + tl * nb) + r] = __float2half_rn(__fmul_rn(static_cast<float>(acc), dq));
                      });
         }
-        mark();
+        mark(9);
         if (!barrier()) return leave();
-        mark();
+        mark(10);
 
         // ---- stage 4: sub-norm(o) + residual + post-attention norm -> gate, up --------------------------------
         issue_rows(l + 1, 3, qdim, o_s, geo.t_o, geo.mp_q, geo.vp_q);
@@ -517,11 +526,11 @@ __global__ void __launch_bounds__(kPdThreads, 1) decode_persistent_kernel(const 
             pa.cols = m.H;
             if (!slab_ready(2, l)) return leave();
             consumed[2] = l;
-            mark();
+            mark(11);
             const float absmax = produce_x<IN_RESNORM, OUT_F16>(pa, xs_sw, static_cast<__half*>(nullptr), redf, b == 0);
             reorder_x(m.H);
             __syncthreads();
-            mark();
+            mark(12);
             const float dq_g = dequant_scale(Ly.lin[4].gamma, absmax), dq_u = dequant_scale(Ly.lin[5].gamma, absmax);
             pd_tiles(gu_s, geo.t_gu, T_gu, geo.mp_h, geo.vp_h, m.H >> 6, xs_s, tab_s, redi, tid, lane, warp,
                      [&](bool active, int tl, int r, int acc) {
@@ -531,9 +540,9 @@ __global__ void __launch_bounds__(kPdThreads, 1) decode_persistent_kernel(const 
                          else m.gate[row] = __float2half_rn(__fmul_rn(static_cast<float>(acc), dq_g));
                      });
         }
-        mark();
+        mark(13);
         if (!barrier()) return leave();
-        mark();
+        mark(14);
 
         // ---- stage 5: relu(gate)^2 * up, sub-norm -> down -----------------------------------------------------
         if (l + 2 < m.nlayers && tid < kLayerWords)
@@ -549,20 +558,20 @@ __global__ void __launch_bounds__(kPdThreads, 1) decode_persistent_kernel(const 
             pa.cols = m.inter;
             if (!slab_ready(3, l)) return leave();
             consumed[3] = l;
-            mark();
+            mark(15);
             const float absmax = produce_x<IN_RELU2, OUT_F16>(pa, xs_sw, static_cast<__half*>(nullptr), redf, b == 0);
             reorder_x(m.inter);
             __syncthreads();
-            mark();
+            mark(16);
             const float dq = dequant_scale(Ly.lin[6].gamma, absmax);
             pd_tiles(dn_s, geo.t_dn, T_h, geo.mp_i, geo.vp_i, m.inter >> 6, xs_s, tab_s, redi, tid, lane, warp,
                      [&](bool active, int tl, int r, int acc) {
                          if (active) m.down[16 * (b + tl * nb) + r] = __float2half_rn(__fmul_rn(static_cast<float>(acc), dq));
                      });
         }
-        mark();
+        mark(17);
         if (l + 1 < m.nlayers && !barrier()) return leave();
-        mark();
+        mark(18);
     }
     // Arrive only: the kernel boundary orders the rest.  The last block to arrive publishes the count as the
     // next launch's generation.
@@ -627,7 +636,7 @@ size_t make_geom(const PdModel& m, int blocks, PdGeom& g) {
     return off;
 }
 
-unsigned long long* g_pd_trace = nullptr;  // TRACE
+unsigned long long* g_pd_trace = nullptr;  // spb_debug_set_decode_trace
 using PdKernel = void (*)(PdModel, PdGeom);
 PdKernel kernel_for(int G) {
     switch (G) {
@@ -690,7 +699,7 @@ int decode_persistent_launch(const PdModel& m, long long wait_cycles, void* stre
     const size_t smem = make_geom(m, blocks, g);
     g.wait_cycles = wait_cycles > 0 ? wait_cycles : kPdWaitCycles;
     g.timeouts = timeout_counter();
-    g.trace = g_pd_trace;  // TRACE
+    g.trace = g_pd_trace;
     if (int rc = ensure_dynamic_smem(name, kernel, smem)) return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(blocks));
@@ -739,4 +748,4 @@ extern "C" int spb_debug_grid_barrier_selftest(long long limit_cycles, void* str
                 state[kSyncBroken]);
 }
 
-extern "C" void spb_debug_set_decode_trace(void* p) { spb::g_pd_trace = static_cast<unsigned long long*>(p); }  // TRACE
+extern "C" void spb_debug_set_decode_trace(void* d_trace) { spb::g_pd_trace = static_cast<unsigned long long*>(d_trace); }
