@@ -503,6 +503,54 @@ def run_ours(args):
             sweep[f"{r}x{c}"] = row
             del mt, vl, yy, g2
 
+    # ---- the GEMV on prepared weights (the packed format re-laid once, what an engine that owns its weights can
+    #      use) beside the GEMV on the packed format, same graph of launches, on the shapes of the two models ----
+    prepared = None
+    if rank == 0 and not args.no_sweep:
+        prepared = {"what": "us per GEMV / GB/s of algorithmic bytes, graph of launches in %d branches over weight copies "
+                            "larger than L2; 'packed' is spb_sparse_ternary_gemv on the reference format, 'prepared' "
+                            "spb_prepared_gemv on spb_prepare_weights' output (same bytes per weight)" % args.chains}
+        for (r, c) in [(6912, 2560), (8192, 8192), (28672, 8192), (8192, 28672)]:
+            try:
+                meta, values = synth.device_sparse_matrix(r, c, seed=7)
+                pb = synth.gemv_algorithmic_bytes(r, c)
+                cp = min(64, max(8, int(np.ceil(max(2 * l2_bytes, 256 << 20) / pb))))
+                mt = [meta.roll(i, 0) for i in range(cp)]
+                vl = [values.roll(i, 0) for i in range(cp)]
+                pr = [K.prepare_weights(mt[i], vl[i], r, c, c // 32, c // 64) for i in range(cp)]
+                xx = torch.from_numpy(rng.integers(-127, 128, (8, c), dtype=np.int8)).cuda()
+                ya = torch.zeros((cp, r), dtype=torch.int32, device="cuda")
+                yb = torch.zeros((cp, r), dtype=torch.int32, device="cuda")
+                row = {}
+                for name in ("packed", "prepared"):
+                    def one(i, name=name):
+                        if name == "packed":
+                            K.sparse_ternary_gemv_gpu(mt[i], vl[i], xx[i % 8], ya[i], r, c, c // 32, c // 64)
+                        else:
+                            K.prepared_gemv_gpu(pr[i], xx[i % 8], yb[i], r, c)
+                    for i in range(cp):
+                        one(i)
+                    torch.cuda.synchronize()
+                    g4 = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g4):
+                        main = torch.cuda.current_stream()
+                        for st in branch_streams[:args.chains]:
+                            st.wait_stream(main)
+                        for i in range(cp):
+                            with torch.cuda.stream(branch_streams[i % max(args.chains, 1)]):
+                                one(i)
+                        for st in branch_streams[:args.chains]:
+                            main.wait_stream(st)
+                    us = time_graph(g4, 5, cp)
+                    row[name] = {"us_per_gemv": round(us, 3), "gbs": round(pb / (us * 1e-6) / 1e9, 1),
+                                 "frac_measured": round(pb / (us * 1e-6) / 1e9 / peak, 4)}
+                    del g4
+                row["same_result"] = bool((ya == yb).all().item())
+                prepared[f"{r}x{c}"] = row
+                del mt, vl, pr, ya, yb, meta, values
+            except Exception as exc:
+                prepared[f"{r}x{c}"] = {"error": repr(exc)[:160]}
+
     ref_cuda = None
     if refcuda is not None and "6912x2560" in sweep:
         ref_cuda = dict(sweep["6912x2560"].get("reference_kernel", {}),
@@ -578,7 +626,7 @@ def run_ours(args):
             "clocks": clocks,
             "cpu_baseline": cpu,
             "ref_cuda_same_gpu": ref_cuda,
-            "sweep": sweep,
+            "sweep": sweep, "prepared_weights": prepared,
             "gemm": gemm,
             "decode": decode,
             "sharded": sharded,

@@ -273,6 +273,24 @@ int spb_prune_pack_gpu(const float* weights, int rows, int cols, size_t weights_
 
 /* ---- engine: include/spbitnet/inference.h:23-70, src/inference.cu ----------------- */
 
+/* ---- prepared weights: the packed format re-laid once for the warp-level sparse MMA --------------------------------
+ * An owner of weights that uploads them once (an engine) may trade the packed rows for a device-private layout of the
+ * same density (1.5 bits per weight) in which the GEMV finds its tensor-core operands almost ready: per tile of 16
+ * rows and 256 columns, 768 contiguous bytes = the lanes' metadata words (bitmaps already as index pairs) and the
+ * lanes' sign bits in the order a byte permute expands them.  Results are the packed GEMV's, bit for bit.  It pays
+ * for matrices of tens of megabytes (4.9 against 3.2 TB/s at 28672 x 8192); small ones are quicker in the packed form.
+ * cols must be a multiple of 256 (<= 65536); rows beyond a multiple of 16 are padded inside the buffer. */
+/* Bytes of the prepared form (0 for a shape it does not take). */
+size_t spb_prepared_weights_bytes(int rows, int cols);
+/* Packed rows (device, strides in uint32 words as everywhere) -> prepared buffer (device, 16-byte aligned). */
+int spb_prepare_weights(const uint32_t* d_meta, const uint32_t* d_values, int rows, int cols, int meta_row_stride,
+                        int values_row_stride, void* d_prepared, void* stream);
+/* y[r] = sum_c W[r, c] * x[c], int32, as spb_sparse_ternary_gemv.  x 16-byte aligned. */
+int spb_prepared_gemv(const void* d_prepared, const int8_t* d_x, int32_t* d_y, int rows, int cols, void* stream);
+/* As spb_sparse_bitlinear_q8: out[r] = half(float(acc) * gamma * absmax / 127). */
+int spb_prepared_bitlinear_q8(const void* d_prepared, const int8_t* d_xq, void* d_out_half, const float* d_absmax,
+                              float gamma, int rows, int cols, void* stream);
+
 typedef struct spb_engine spb_engine;
 
 typedef struct {
@@ -419,6 +437,12 @@ int spb_shard_engine_set_peer_pointers(spb_shard_engine* e, void* const* buffers
 size_t spb_shard_engine_exchange_bytes(const spb_shard_engine* e);
 /* Bound of every wait for a peer (default 5000 ms). */
 int spb_shard_engine_set_timeout_ms(spb_shard_engine* e, int ms);
+/* Whether the engine keeps a prepared copy (spb_prepare_weights) of the slices set with spb_shard_engine_set_linear
+ * and multiplies on it: 1 (default) for slices of 32 M weights and more, 2 for every slice the layout takes, 0 for
+ * none.  It applies to the single-sequence step of wide models (hidden size >= 4096), which multiplies matrix by
+ * matrix on the quantised vector; elsewhere the setting has no effect.  The copies are the engine's (as large as
+ * the slices); results are the same bit for bit.  May be called before or after the slices are set. */
+int spb_shard_engine_set_prepared_weights(spb_shard_engine* e, int on);
 int spb_shard_engine_reset(spb_shard_engine* e);
 int spb_shard_engine_seq_len(const spb_shard_engine* e);
 /* One decode step: tokens[batch] (HOST) enter at the current position; synchronises.  Afterwards the rank's logits

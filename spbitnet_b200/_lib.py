@@ -65,6 +65,10 @@ SIGNATURES = {
     "spb_set_gemm_variant": (_i, [_i]),
     "spb_set_gemm_row_halves": (_i, [_i]),
     "spb_gemm_tc_timeouts": (_i, []),
+    "spb_prepared_weights_bytes": (C.c_size_t, [_i, _i]),
+    "spb_prepare_weights": (_i, [_p, _p, _i, _i, _i, _i, _p, _p]),
+    "spb_prepared_gemv": (_i, [_p, _p, _p, _i, _i, _p]),
+    "spb_prepared_bitlinear_q8": (_i, [_p, _p, _p, _p, _f, _i, _i, _p]),
     "spb_debug_bounded_wait_selftest": (_i, [C.c_longlong, _p]),
     "spb_debug_grid_barrier_selftest": (_i, [C.c_longlong, _p]),
     "spb_debug_set_decode_trace": (None, [_p]),
@@ -130,6 +134,7 @@ SIGNATURES = {
     "spb_shard_engine_set_peer_pointers": (_i, [_p, _p]),
     "spb_shard_engine_exchange_bytes": (C.c_size_t, [_p]),
     "spb_shard_engine_set_timeout_ms": (_i, [_p, _i]),
+    "spb_shard_engine_set_prepared_weights": (_i, [_p, _i]),
     "spb_shard_engine_reset": (_i, [_p]),
     "spb_shard_engine_seq_len": (_i, [_p]),
     "spb_shard_engine_step": (_i, [_p, _p]),

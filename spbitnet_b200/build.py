@@ -15,7 +15,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libspbitnet_b200.so"
 CLI = HERE / "spbitnet_infer"
-SOURCES = ["core.cu", "gemv.cu", "gemv_batch_mma.cu", "gemv_mmasp.cu", "gemm.cu", "gemm_tcsp_ws.cu", "gemm_mmasp.cu", "unpack.cu",
+SOURCES = ["core.cu", "gemv.cu", "gemv_batch_mma.cu", "gemv_mmasp.cu", "gemv_prepared.cu", "gemm.cu", "gemm_tcsp_ws.cu", "gemm_mmasp.cu", "unpack.cu",
            "decode_ops.cu", "attention.cu", "fused_ops.cu", "prefill.cu", "decode_persistent.cu", "engine.cu", "sharded.cu", "noalloc.cu", "pack.cu", "format_host.cpp",
            "tokenizer.cpp", "model_loader.cpp"]
 COMPILE_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",

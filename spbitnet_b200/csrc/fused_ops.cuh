@@ -59,6 +59,10 @@ int absmax_quantize_rows(const void* in, int8_t* out, float* d_absmax, int n, in
 int dequantize_rows(const int32_t* acc, void* out, const float* d_absmax, float gamma, int rows, int vectors,
                     void* stream);
 
+// gemv_prepared.cu: BitLinear on weights re-laid by spb_prepare_weights; quantised activation, scaled half output
+int prepared_bitlinear_q8(const void* prep, const int8_t* xq, void* out_half, const float* d_absmax, float gamma, int rows,
+                          int cols, void* stream);
+
 // gemv.cu: up to three BitLinear layers that consume the same activation vector, one launch.
 struct BitLinearGroup {
     const uint32_t* meta[3];

@@ -1,0 +1,284 @@
+// Sparse-ternary GEMV on weights re-laid once for the warp-level sparse MMA ("prepared" weights), sm_100a.
+//
+// The GEMV on the packed format (gemv_mmasp.cu) tops out near 3 TB/s whatever the matrix size: per 64-column step
+// of 16 rows a warp issues about 23 instructions and 12 shared-memory wavefronts to turn 192 bytes of bitmaps and
+// sign bits into the operands of one mma.sp.  An engine that owns its weights (it uploads them once) can pay that
+// conversion once instead.  The prepared form keeps 1.5 bits per weight and holds, per tile of 16 rows and "quad"
+// of four steps (256 columns), 768 contiguous bytes in the order the lanes consume them:
+//
+//   [lane 0..31][4 words]   the metadata operand of steps 4q .. 4q+3: the index pairs of bitmap word
+//                           2 s + (tig >> 1) of row 16 t + g + 8 (tig & 1)            (g = lane / 4, tig = lane % 4)
+//   [lane 0..31][64 bits]   the sign bits of the lane's four A registers of those steps, 16 bits a step:
+//                           bit 4 k + r = sign of byte k of register r
+//                           (r = 0: row g, compressed columns 4 tig..; 1: row g + 8, same; 2, 3: columns 16 + 4 tig..)
+//
+// so a warp reads its weights straight from global memory with one 16-byte and one 8-byte load per lane and quad,
+// fully coalesced, and nothing of them passes through shared memory.  A register of four sign bytes comes out of
+// ONE byte permute: the 16-bit field is the selector, and the permute's source is a constant whose byte i is 0xFF
+// when bit r of i is set, so byte k of the result is 0xFF (-1) or 0x00 according to bit r of selector nibble k (the
+// nibble's top bit asks for sign replication, which leaves 0x00 / 0xFF as they are; register 3 takes the selector
+// shifted by one).  With A in {0, -1} the step needs a second MMA with A = 1 on the same metadata and activations:
+//   y = sum over kept x  +  2 * sum of (A * x)   =   S + 2 R.
+// A step is about ten instructions and one shared-memory wavefront (the activation registers; only the four lanes
+// of output column 0 load them).
+//
+// Measured (one B200, graphs of launches over weight copies larger than L2, eight branches): 28672 x 8192 in 9.0 us =
+// 4.9 TB/s against 13.9 us = 3.2 TB/s for the packed-format kernel, 8192 x 28672 9.7 against 15.6 us, 8192 x 8192 3.7
+// against 4.0 us; at the 2B-4T shapes (a few MB per matrix, a handful of quads per warp) the packed-format kernel is
+// the faster one (6912 x 2560: 0.94 against 1.22 us), so this form is meant for matrices of tens of megabytes.
+// A form that cut the work by bytes instead of by row tiles (equal contiguous runs of quads per block, partial tiles
+// summed through atomics) balanced the SMs exactly and was slower everywhere (28672 x 8192: 17.1 against 14.7 us as a
+// chain of launches): the block-wide reduction per piece cost more than the idle tail it removed.
+#include "spb_common.cuh"
+
+namespace spb {
+
+constexpr int kGpThreads = 256;
+constexpr int kGpWarps = kGpThreads / 32;
+constexpr int kGpQuadBytes = 768;
+
+enum { GP_OUT_I32 = 0, GP_OUT_F32 = 1, GP_OUT_F16 = 2 };
+
+struct GpArgs {
+    const uint8_t* prep;
+    const int8_t* x;
+    void* y;
+    int32_t* y_acc;
+    const float* d_absmax;
+    float gamma;
+    int out_mode;
+    int rows, cols;
+    int ntiles, nquads;
+    int ks, ks_log2;  // warps per tile (power of two <= 8); a block holds 8 / ks tiles
+    int qpw;          // quads per warp
+};
+
+// Eight bitmaps (two of four bits set each) -> eight index pairs {low index | high index << 2}.
+__device__ __forceinline__ uint32_t gp_index_pairs(uint32_t m) {
+    const uint32_t mr = m >> 1, ml = m << 1;
+    const uint32_t t1 = (0x11111111u & (~m & mr)) | (~0x11111111u & (mr | ~m));
+    const uint32_t t2 = (0x22222222u & (~ml & ~m)) | (~0x22222222u & (m | ml));
+    return (t1 & 0x55555555u) | (t2 & 0xAAAAAAAAu);
+}
+
+// One thread per (tile, quad, lane): reads the packed rows, writes the lane's 24 bytes of the prepared block.
+__global__ void __launch_bounds__(256) gemv_prepare_kernel(const uint32_t* __restrict__ meta, const uint32_t* __restrict__ values,
+                                                           int rows, int cols, int meta_stride, int values_stride, int ntiles,
+                                                           int nquads, uint8_t* __restrict__ prep) {
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= static_cast<long long>(ntiles) * nquads * 32) return;
+    const int lane = static_cast<int>(i & 31);
+    const long long tq = i >> 5;
+    const int q = static_cast<int>(tq % nquads), t = static_cast<int>(tq / nquads);
+    const int g = lane >> 2, tig = lane & 3;
+    const int mrow = 16 * t + g + 8 * (tig & 1);
+    uint32_t mw[4];
+    unsigned long long sg = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int s = 4 * q + j;
+        mw[j] = mrow < rows ? gp_index_pairs(meta[static_cast<size_t>(mrow) * meta_stride + 2 * s + (tig >> 1)]) : 0x44444444u;
+        const int r0 = 16 * t + g, r1 = r0 + 8;
+        const uint32_t w0 = r0 < rows ? values[static_cast<size_t>(r0) * values_stride + s] : 0u;
+        const uint32_t w1 = r1 < rows ? values[static_cast<size_t>(r1) * values_stride + s] : 0u;
+        const uint32_t nib[4] = {(w0 >> (4 * tig)) & 15u, (w1 >> (4 * tig)) & 15u, (w0 >> (16 + 4 * tig)) & 15u,
+                                 (w1 >> (16 + 4 * tig)) & 15u};
+        uint32_t field = 0;
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) field |= ((nib[r] >> k) & 1u) << (4 * k + r);
+        sg |= static_cast<unsigned long long>(field) << (16 * j);
+    }
+    uint8_t* blk = prep + static_cast<size_t>(tq) * kGpQuadBytes;
+    reinterpret_cast<uint4*>(blk)[lane] = make_uint4(mw[0], mw[1], mw[2], mw[3]);
+    reinterpret_cast<uint2*>(blk + 512)[lane] = make_uint2(static_cast<uint32_t>(sg), static_cast<uint32_t>(sg >> 32));
+}
+
+// Streaming loads of one quad of a tile: the lane's four metadata words and its 64 sign bits.
+__device__ __forceinline__ void gp_load_quad(const uint8_t* tile_base, int q, int lane, uint4& m, uint2& s) {
+    const uint8_t* blk = tile_base + static_cast<size_t>(q) * kGpQuadBytes;
+    m = ld_stream_v4(reinterpret_cast<const uint32_t*>(blk) + 4 * lane);
+    s = ld_stream_v2(reinterpret_cast<const uint32_t*>(blk + 512) + 2 * lane);
+}
+
+// Quads [q_begin, q_end) of one tile times the staged activation vector; the first three quads are already in
+// (m0, s0), (m1, s1), (m2, s2) (zeros past q_end).  Returns S + 2 R of output column 0 for rows g (c_lo) and g + 8
+// (c_hi), meaningful in the lanes with tig == 0.
+__device__ __forceinline__ void gp_run_quads(const uint8_t* tile_base, int q_begin, int q_end, uint4 m0, uint2 s0, uint4 m1,
+                                             uint2 s1, uint4 m2, uint2 s2, uint32_t xs_s, int lane, int& c_lo, int& c_hi) {
+    const int g = lane >> 2, tig = lane & 3;
+    // R: A in {0, -1} from the sign bits; S: A = 1.  Two sets of each on alternate steps.
+    int r0 = 0, r1 = 0, r2 = 0, r3 = 0, t0 = 0, t1 = 0, t2 = 0, t3 = 0;
+    int u0 = 0, u1 = 0, u2 = 0, u3 = 0, v0 = 0, v1 = 0, v2 = 0, v3 = 0;
+    const bool bcol = g == 0;  // the lanes that hold output column 0 of the activation operand
+    uint32_t xq_p = xs_s + static_cast<uint32_t>(tig) * 16u + static_cast<uint32_t>(q_begin) * 256u;
+    auto step = [&](int& c0, int& c1, int& c2, int& c3, int& d0, int& d1, int& d2, int& d3, uint32_t e, uint32_t sel, uint32_t x_off) {
+        const uint32_t a0 = __byte_perm(0xFF00FF00u, 0xFF00FF00u, sel);
+        const uint32_t a1 = __byte_perm(0xFFFF0000u, 0xFFFF0000u, sel);
+        const uint32_t a2 = __byte_perm(0x00000000u, 0xFFFFFFFFu, sel);
+        const uint32_t a3 = __byte_perm(0x00000000u, 0xFFFFFFFFu, sel >> 1);
+        uint32_t b0 = 0, b1 = 0, b2 = 0, b3 = 0;
+        if (bcol) asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(xq_p + x_off));
+        asm volatile(
+            "mma.sp::ordered_metadata.sync.aligned.m16n8k64.row.col.s32.s8.s8.s32 "
+            "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9, %10, %11}, {%0, %1, %2, %3}, %12, 0x0;"
+            : "+r"(c0), "+r"(c1), "+r"(c2), "+r"(c3)
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(b2), "r"(b3), "r"(e));
+        asm volatile(
+            "mma.sp::ordered_metadata.sync.aligned.m16n8k64.row.col.s32.s8.s8.s32 "
+            "{%0, %1, %2, %3}, {%4, %4, %4, %4}, {%5, %6, %7, %8}, {%0, %1, %2, %3}, %9, 0x0;"
+            : "+r"(d0), "+r"(d1), "+r"(d2), "+r"(d3)
+            : "r"(0x01010101u), "r"(b0), "r"(b1), "r"(b2), "r"(b3), "r"(e));
+    };
+    for (int q = q_begin; q < q_end; ++q) {
+        uint4 mn = make_uint4(0, 0, 0, 0);
+        uint2 sn = make_uint2(0, 0);
+        if (q + 3 < q_end) gp_load_quad(tile_base, q + 3, lane, mn, sn);
+        step(r0, r1, r2, r3, u0, u1, u2, u3, m0.x, s0.x, 0u);
+        step(t0, t1, t2, t3, v0, v1, v2, v3, m0.y, s0.x >> 16, 64u);
+        step(r0, r1, r2, r3, u0, u1, u2, u3, m0.z, s0.y, 128u);
+        step(t0, t1, t2, t3, v0, v1, v2, v3, m0.w, s0.y >> 16, 192u);
+        xq_p += 256u;
+        m0 = m1; s0 = s1;
+        m1 = m2; s1 = s2;
+        m2 = mn; s2 = sn;
+    }
+    c_lo = (u0 + v0) + 2 * (r0 + t0);
+    c_hi = (u2 + v2) + 2 * (r2 + t2);
+}
+
+__global__ void __launch_bounds__(kGpThreads, 3) gemv_prepared_kernel(const GpArgs a) {
+    __shared__ int red[kGpWarps * 16];
+    extern __shared__ __align__(16) uint8_t gp_raw[];  // x in B-register order: xs[step][tig][j][0..3] = x[64 step + 16 j + 4 tig ..+3]
+    const uint32_t xs_s = static_cast<uint32_t>(__cvta_generic_to_shared(gp_raw));
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xFFFFFFFFu, tid >> 5, 0);
+    const int tiles_blk = kGpWarps >> a.ks_log2;
+    const int tile = blockIdx.x * tiles_blk + (warp >> a.ks_log2), kq = warp & (a.ks - 1);
+    const bool live = tile < a.ntiles;
+    const int q_begin = live ? min(a.nquads, kq * a.qpw) : 0, q_end = live ? min(a.nquads, q_begin + a.qpw) : 0;
+    const int g = lane >> 2, tig = lane & 3;
+
+    const uint8_t* tp = a.prep + (static_cast<size_t>(live ? tile : 0) * a.nquads) * kGpQuadBytes;
+    auto load_quad = [&](int q, uint4& m, uint2& s) {
+        if (q < q_end) gp_load_quad(tp, q, lane, m, s);
+    };
+    // weights never depend on a predecessor: the first quads are requested before the dependency wait
+    uint4 m0 = make_uint4(0, 0, 0, 0), m1 = m0, m2 = m0;
+    uint2 s0 = make_uint2(0, 0), s1 = s0, s2 = s0;
+    load_quad(q_begin, m0, s0);
+    load_quad(q_begin + 1, m1, s1);
+    load_quad(q_begin + 2, m2, s2);
+
+    grid_dep_wait();
+    grid_dep_launch();
+    for (int q = tid; q < (a.cols >> 4); q += kGpThreads) {
+        const uint4 xv = __ldg(reinterpret_cast<const uint4*>(a.x) + q);
+        const uint32_t d = xs_s + (static_cast<uint32_t>(q) >> 2) * 64u + (static_cast<uint32_t>(q) & 3u) * 4u;
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(d), "r"(xv.x) : "memory");
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(d + 16u), "r"(xv.y) : "memory");
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(d + 32u), "r"(xv.z) : "memory");
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(d + 48u), "r"(xv.w) : "memory");
+    }
+    __syncthreads();
+
+    int c_lo = 0, c_hi = 0;
+    gp_run_quads(tp, q_begin, q_end, m0, s0, m1, s1, m2, s2, xs_s, lane, c_lo, c_hi);
+    // column 0 of the tile: lanes with tig == 0 hold rows g (register 0) and g + 8 (register 2)
+    if (tig == 0) {
+        red[warp * 16 + g] = c_lo;
+        red[warp * 16 + g + 8] = c_hi;
+    }
+    __syncthreads();
+    if (tid < 16 * tiles_blk) {
+        const int tl = tid >> 4, r = tid & 15;
+        const int row = (blockIdx.x * tiles_blk + tl) * 16 + r;
+        if (row < a.rows) {
+            int acc = 0;
+            for (int k = 0; k < a.ks; ++k) acc += red[((tl << a.ks_log2) + k) * 16 + r];
+            if (a.out_mode == GP_OUT_I32) {
+                static_cast<int32_t*>(a.y)[row] = acc;
+            } else {
+                const float f = __fmul_rn(static_cast<float>(acc), dequant_scale(a.gamma, *a.d_absmax));
+                if (a.out_mode == GP_OUT_F32) {
+                    static_cast<float*>(a.y)[row] = f;
+                    if (a.y_acc) a.y_acc[row] = acc;
+                } else {
+                    static_cast<__half*>(a.y)[row] = __float2half_rn(f);
+                }
+            }
+        }
+    }
+}
+
+static bool gp_shape_ok(int rows, int cols) { return rows > 0 && cols > 0 && cols % 256 == 0 && cols <= 65536; }
+static size_t gp_weight_bytes(int rows, int cols) { return static_cast<size_t>((rows + 15) / 16) * (cols / 256) * kGpQuadBytes; }
+
+static int gp_launch(const char* name, const void* prep, const int8_t* x, void* y, int32_t* y_acc, const float* d_absmax,
+                     float gamma, int out_mode, int rows, int cols, void* stream) {
+    if (rows < 0 || cols < 0) return fail(SPB_E_INVALID, "%s: negative size", name);
+    if (rows == 0 || cols == 0) return SPB_OK;
+    if (!prep || !x || !y) return fail(SPB_E_INVALID, "%s: null pointer", name);
+    if (out_mode != GP_OUT_I32 && !d_absmax) return fail(SPB_E_INVALID, "%s: d_absmax is null", name);
+    if (!gp_shape_ok(rows, cols)) return fail(SPB_E_UNSUPPORTED, "%s: cols=%d is not a multiple of 256 up to 65536", name, cols);
+    if ((reinterpret_cast<uintptr_t>(prep) | reinterpret_cast<uintptr_t>(x)) & 15u)
+        return fail(SPB_E_INVALID, "%s: prepared weights and x must be 16-byte aligned", name);
+    GpArgs a{};
+    a.prep = static_cast<const uint8_t*>(prep);
+    a.x = x; a.y = y; a.y_acc = y_acc; a.d_absmax = d_absmax; a.gamma = gamma; a.out_mode = out_mode;
+    a.rows = rows; a.cols = cols;
+    a.ntiles = (rows + 15) / 16;
+    a.nquads = cols / 256;
+    // Warps per tile: a warp wants a run of quads (its fixed cost is the three-quad prefetch and the final
+    // reduction), but the matrix has to give every SM its three blocks.
+    a.ks = 1;
+    while (a.ks < 8 && a.ntiles * a.ks < 24 * sm_count() && a.nquads / (2 * a.ks) >= 2) a.ks <<= 1;
+    a.ks_log2 = a.ks == 8 ? 3 : a.ks == 4 ? 2 : a.ks == 2 ? 1 : 0;
+    a.qpw = (a.nquads + a.ks - 1) / a.ks;
+    const int tiles_blk = kGpWarps / a.ks;
+    const unsigned blocks = static_cast<unsigned>((a.ntiles + tiles_blk - 1) / tiles_blk);
+    const size_t smem = static_cast<size_t>(cols);
+    if (int rc = ensure_dynamic_smem(name, gemv_prepared_kernel, smem)) return rc;
+    return launch(name, gemv_prepared_kernel, dim3(blocks), dim3(kGpThreads), smem, stream, a);
+}
+
+// engine-internal: BitLinear on prepared weights, quantised activation, scaled half output
+int prepared_bitlinear_q8(const void* prep, const int8_t* xq, void* out_half, const float* d_absmax, float gamma, int rows,
+                          int cols, void* stream) {
+    return gp_launch("prepared_bitlinear_q8", prep, xq, out_half, nullptr, d_absmax, gamma, GP_OUT_F16, rows, cols, stream);
+}
+
+}  // namespace spb
+
+using namespace spb;
+
+extern "C" size_t spb_prepared_weights_bytes(int rows, int cols) {
+    if (!gp_shape_ok(rows, cols)) return 0;
+    return gp_weight_bytes(rows, cols);
+}
+
+extern "C" int spb_prepare_weights(const uint32_t* d_meta, const uint32_t* d_values, int rows, int cols, int meta_row_stride,
+                                   int values_row_stride, void* d_prepared, void* stream) {
+    const char* name = "spb_prepare_weights";
+    if (rows < 0 || cols < 0) return fail(SPB_E_INVALID, "%s: negative size", name);
+    if (rows == 0 || cols == 0) return SPB_OK;
+    if (!d_meta || !d_values || !d_prepared) return fail(SPB_E_INVALID, "%s: null pointer", name);
+    if (!gp_shape_ok(rows, cols)) return fail(SPB_E_UNSUPPORTED, "%s: cols=%d is not a multiple of 256 up to 65536", name, cols);
+    if (meta_row_stride < cols / 32 || values_row_stride < cols / 64) return fail(SPB_E_INVALID, "%s: row stride shorter than a row", name);
+    if (reinterpret_cast<uintptr_t>(d_prepared) & 15u) return fail(SPB_E_INVALID, "%s: the prepared buffer must be 16-byte aligned", name);
+    const int ntiles = (rows + 15) / 16, nquads = cols / 256;
+    const long long threads = static_cast<long long>(ntiles) * nquads * 32;
+    const unsigned blocks = static_cast<unsigned>((threads + 255) / 256);
+    return launch(name, gemv_prepare_kernel, dim3(blocks), dim3(256), 0, stream, d_meta, d_values, rows, cols, meta_row_stride,
+                  values_row_stride, ntiles, nquads, static_cast<uint8_t*>(d_prepared));
+}
+
+extern "C" int spb_prepared_gemv(const void* d_prepared, const int8_t* d_x, int32_t* d_y, int rows, int cols, void* stream) {
+    return gp_launch("spb_prepared_gemv", d_prepared, d_x, d_y, nullptr, nullptr, 0.0f, GP_OUT_I32, rows, cols, stream);
+}
+
+extern "C" int spb_prepared_bitlinear_q8(const void* d_prepared, const int8_t* d_xq, void* d_out_half, const float* d_absmax,
+                                         float gamma, int rows, int cols, void* stream) {
+    return prepared_bitlinear_q8(d_prepared, d_xq, d_out_half, d_absmax, gamma, rows, cols, stream);
+}

@@ -630,6 +630,7 @@ struct Linear {
     const uint32_t* values = nullptr;
     float gamma = 0.0f;
     int rows = 0, cols = 0, ms = 0, vs = 0;
+    void* prep = nullptr;  // the slice re-laid for the tensor-core GEMV (gemv_prepared.cu), owned by the engine; or null
 };
 struct Layer {
     Linear lin[7];              // q k v o gate up down: this rank's row slices
@@ -703,6 +704,7 @@ struct spb_shard_engine {
     unsigned* counters = nullptr;  // [X_KINDS][2]: seqno, done
     int prompt_cap = 0, n_prompt_in_graph = 0, out_cap = 0;
     bool split_attention = false, fused = false, wide = false;
+    int use_prepared = 1;  // wide form, one sequence: GEMVs on weights re-laid at set_linear (1 large slices, 2 every slice, 0 none)
 
     // exchange buffer (exported through CUDA IPC) and the peers' mappings
     uint8_t* xbuf = nullptr;
@@ -813,6 +815,7 @@ int enqueue_step(spb_shard_engine* e, bool record) {
     };
     // one matrix per launch on the quantised vector: takes the tensor-core GEMV wherever the layout allows
     auto linear_1 = [&](const Linear& L, const float* am, __half* out, void* on = nullptr) {
+        if (L.prep) return prepared_bitlinear_q8(L.prep, e->xq, out, am, L.gamma, L.rows, L.cols, on ? on : s);
         return spb_sparse_bitlinear_q8(L.meta, L.values, e->xq, out, am, L.gamma, L.rows, L.cols, L.ms, L.vs, on ? on : s);
     };
     // Matrices that read the same quantised vector (q / k / v, gate / up) do not depend on one another: the first
@@ -1166,6 +1169,23 @@ extern "C" spb_shard_engine* spb_shard_engine_create(const spb_model_config* cfg
     return e;
 }
 
+// (Re)builds or drops the prepared form of a slice according to the engine's setting.  Only the wide single-sequence
+// step multiplies matrix by matrix on the quantised vector, which is where the prepared GEMV applies.
+static int prepare_linear(spb_shard_engine* e, Linear& L) {
+    if (L.prep) {
+        SPB_CUDA(cudaStreamSynchronize(e->stream));
+        cudaFree(L.prep);
+        L.prep = nullptr;
+    }
+    const size_t bytes = spb_prepared_weights_bytes(L.rows, L.cols);
+    // (measured: the prepared form wins from some tens of millions of weights per matrix on, 8192 x 8192 is about even,
+    // 1024 x 8192 is quicker in the packed form)
+    const bool large = e->use_prepared == 2 || static_cast<long long>(L.rows) * L.cols >= 32LL * 1024 * 1024;
+    if (!e->use_prepared || !e->wide || e->batch != 1 || !large || bytes == 0 || L.ms < L.cols / 32 || L.vs < L.cols / 64) return SPB_OK;
+    SPB_CUDA(cudaMalloc(&L.prep, bytes));
+    return spb_prepare_weights(L.meta, L.values, L.rows, L.cols, L.ms, L.vs, L.prep, e->stream);
+}
+
 extern "C" void spb_shard_engine_destroy(spb_shard_engine* e) {
     if (!e) return;
     DeviceScope scope(e->device);
@@ -1179,6 +1199,9 @@ extern "C" void spb_shard_engine_destroy(spb_shard_engine* e) {
         if (e->join[i]) cudaEventDestroy(e->join[i]);
     }
     if (e->fork) cudaEventDestroy(e->fork);
+    for (Layer& Ly : e->layers)
+        for (Linear& L : Ly.lin)
+            if (L.prep) cudaFree(L.prep);
     cudaFree(e->pool);
     cudaFree(e->xbuf);
     cudaFreeHost(e->status);
@@ -1266,6 +1289,20 @@ extern "C" int spb_shard_engine_set_linear(spb_shard_engine* e, int layer, int w
     Linear& L = e->layers[layer].lin[which];
     L.meta = d_meta; L.values = d_values; L.gamma = gamma; L.rows = rows; L.cols = cols; L.ms = meta_stride; L.vs = values_stride;
     drop_graph(e);
+    DeviceScope scope(e->device);
+    return prepare_linear(e, L);
+}
+
+extern "C" int spb_shard_engine_set_prepared_weights(spb_shard_engine* e, int on) {
+    if (!e) return fail(SPB_E_INVALID, "spb_shard_engine_set_prepared_weights: null handle");
+    DeviceScope scope(e->device);
+    SPB_CUDA(cudaStreamSynchronize(e->stream));
+    drop_graph(e);
+    e->use_prepared = on < 0 ? 0 : on > 2 ? 2 : on;
+    for (Layer& Ly : e->layers)
+        for (Linear& L : Ly.lin)
+            if (L.meta)
+                if (int rc = prepare_linear(e, L)) return rc;
     return SPB_OK;
 }
 

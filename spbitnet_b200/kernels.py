@@ -75,6 +75,30 @@ def sparse_ternary_gemv_gpu(meta, values, x, y, rows, cols, meta_row_stride, val
                                          values_row_stride, _stream(stream)))
 
 
+def prepared_weights_bytes(rows, cols) -> int:
+    return int(load().spb_prepared_weights_bytes(rows, cols))
+
+
+def prepare_weights(meta, values, rows, cols, meta_row_stride, values_row_stride, stream=None):
+    """Packed rows on the device -> the prepared form (a uint8 CUDA tensor) that prepared_gemv_gpu takes."""
+    nbytes = prepared_weights_bytes(rows, cols)
+    if nbytes == 0:
+        raise ValueError(f"prepared weights: shape {rows}x{cols} not taken (cols must be a multiple of 256)")
+    out = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    check(load().spb_prepare_weights(_p(meta), _p(values), rows, cols, meta_row_stride, values_row_stride, _p(out),
+                                     _stream(stream)))
+    return out
+
+
+def prepared_gemv_gpu(prepared, x, y, rows, cols, stream=None):
+    check(load().spb_prepared_gemv(_p(prepared), _p(x), _p(y), rows, cols, _stream(stream)))
+
+
+def prepared_bitlinear_q8_gpu(prepared, xq, out_half, d_absmax, gamma, rows, cols, stream=None):
+    check(load().spb_prepared_bitlinear_q8(_p(prepared), _p(xq), _p(out_half), _p(d_absmax), float(gamma), rows, cols,
+                                           _stream(stream)))
+
+
 class GemvWorkList:
     """A device-resident list of GEMVs for sparse_ternary_gemv_batch_gpu.  items: iterable of
     (meta, values, x, y, rows, cols, meta_row_stride, values_row_stride) with CUDA tensors (or

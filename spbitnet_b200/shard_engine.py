@@ -130,6 +130,11 @@ class ShardEngine:
         arr = (C.c_void_p * self.world)(*[C.c_void_p(p) for p in pointers])
         check(self._lib.spb_shard_engine_set_peer_pointers(self._h, arr))
 
+    def set_prepared_weights(self, level: int) -> None:
+        """Whether the engine multiplies on prepared copies of its slices (kernels.prepare_weights): 1 (default) the
+        large ones, 2 every slice the layout takes, 0 none.  Wide models, one sequence; same results either way."""
+        check(self._lib.spb_shard_engine_set_prepared_weights(self._h, int(level)))
+
     def weight_bytes(self) -> int:
         """Bytes of weights this rank streams per decode step (its row slices + its LM head rows)."""
         n = sum(t.numel() * t.element_size() for t in self._keep if t.dtype == torch.int32)

@@ -113,3 +113,29 @@ def test_wide_model_path(batch):
         want = ref.generate(prompts[:, b], 6)
         assert (got[:, b] == want).all(), b
         assert np.abs(lg[b] - ref.logits()).max() < 1e-2
+
+
+def test_prepared_weights_do_not_change_a_bit():
+    """The wide single-sequence step on prepared copies of the slices (the large ones by default, all, none): the
+    same tokens and the same logits bit for bit."""
+    cfg = dict(hidden_size=4096, num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+               intermediate_size=16640, vocab_size=2048, max_position_embeddings=32, rms_norm_eps=1e-5, rope_theta=500000.0)
+    dm = synth.DeviceRandomModel(cfg, seed=21)
+    prompt = np.random.default_rng(6).integers(0, cfg["vocab_size"], (4, 1)).astype(np.int32)
+    outs = []
+    for level in (1, 0, 2, 1):
+        eng = ShardEngine(dm, batch=1)
+        eng.set_prepared_weights(level)
+        outs.append((eng.generate(prompt, 8), eng.logits()))
+        eng.close()
+    for tokens, logits in outs[1:]:
+        assert (tokens == outs[0][0]).all() and (logits == outs[0][1]).all()
+    # switching on a live engine
+    eng = ShardEngine(dm, batch=1)
+    a = eng.generate(prompt, 8)
+    eng.set_prepared_weights(0)
+    eng.reset()
+    assert (eng.generate(prompt, 8) == a).all()
+    eng.set_prepared_weights(2)
+    eng.reset()
+    assert (eng.generate(prompt, 8) == a).all() and (a == outs[0][0]).all()
