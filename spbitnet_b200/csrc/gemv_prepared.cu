@@ -26,9 +26,11 @@
 // 4.9 TB/s against 13.9 us = 3.2 TB/s for the packed-format kernel, 8192 x 28672 9.7 against 15.6 us, 8192 x 8192 3.7
 // against 4.0 us; at the 2B-4T shapes (a few MB per matrix, a handful of quads per warp) the packed-format kernel is
 // the faster one (6912 x 2560: 0.94 against 1.22 us), so this form is meant for matrices of tens of megabytes.
-// A form that cut the work by bytes instead of by row tiles (equal contiguous runs of quads per block, partial tiles
-// summed through atomics) balanced the SMs exactly and was slower everywhere (28672 x 8192: 17.1 against 14.7 us as a
-// chain of launches): the block-wide reduction per piece cost more than the idle tail it removed.
+// Two forms that cut the work by bytes instead of by row tiles (equal contiguous runs of quads, partial tiles summed
+// through atomics into a workspace and finished by whoever completes a tile's count) balanced the SMs exactly and
+// were slower everywhere: per block with a block-wide reduction per piece, 17.1 against 14.7 us at 28672 x 8192 as a
+// chain of launches; per warp with no block-wide step, 16.5 against 14.6 us (14.0 against 8.9 us in the graph of eight
+// branches): the fence and the round trip of the counting atomic drain the warp's prefetch at every hand-over.
 #include "spb_common.cuh"
 
 namespace spb {
