@@ -822,9 +822,12 @@ def bench_decode(args, with_reference=True, with_cpu=False):
     eng.generate(prompt, 8)  # warm-up: graph capture, page-in
     eng.reset()
     torch.cuda.synchronize()
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
     t0 = time.perf_counter()
     toks = eng.generate(prompt, n_gen)
     dt = time.perf_counter() - t0
+    decode_clocks = sampler.stop()
     steps = len(prompt) - 1 + n_gen
     weight_bytes = dm.sparse_bytes() + dm.embed.numel() * 2
     # the same job with the layers of a token as one persistent kernel (opt-in mode of the engine)
@@ -864,7 +867,7 @@ def bench_decode(args, with_reference=True, with_cpu=False):
     peak, _ = measured_peaks()
     out = {"tok_s": steps / dt, "batched_prompt": batched, "ms_per_token": 1e3 * dt / steps, "generated": int(len(toks)),
            "prompt": int(len(prompt)), "weight_mb_per_token": round(weight_bytes / 1e6, 1),
-           "step": "chain of five PDL-linked kernels per layer", "persistent_kernel": persistent,
+           "step": "chain of five PDL-linked kernels per layer", "persistent_kernel": persistent, "clocks": decode_clocks,
            "hbm_gbs": weight_bytes * steps / dt / 1e9, "hbm_frac_measured": weight_bytes * steps / dt / 1e9 / peak,
            "what": "prefill (token-serial, as the reference) + decode, wall clock around generate() incl. prompt "
                    "H2D and token D2H; random-init 2B-4T shape, every matrix of every layer drawn with its own seed"}

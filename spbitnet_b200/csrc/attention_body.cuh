@@ -154,7 +154,7 @@ __host__ __device__ inline size_t attn_merge_smem_floats(int G, int max_seq_len)
 // the whole block of kAttnThreads threads works on it.  sm: attn_merge_smem_floats() floats.
 //   1. the chunk maxima of every head into shared memory (one round of loads);
 //   2. warp g takes head g: M = max, w[s] = exp(m[s] - M) into shared memory, L = sum l[s] * w[s];
-//   3. thread t takes (head, dim) pairs t, t + 256, ..: sum_s w[s] * o[s][d], about 32 loads in flight per thread.
+//   3. thread t takes (head, dim) pairs t, t + 256, ..: sum_s w[s] * o[s][d] with eight loads in flight.
 template <int G>
 __device__ __forceinline__ void attn_merge_group(const float* scratch, __half* out, int kvh, int head_dim,
                                                  int nsplit_max, int nsplit, float* sm) {
@@ -184,42 +184,22 @@ __device__ __forceinline__ void attn_merge_group(const float* scratch, __half* o
         if (lane == 0) inv[g] = 1.0f / L;
     }
     __syncthreads();
-    // Thread t takes the (head, dim) pairs t, t + 256, .. (at most G of them); the partial rows of kB chunks are
-    // requested for all of them at once (about 32 loads in flight), then added chunk by chunk in order.  A chunk
-    // index past the end is clamped (a valid address) and weighted 0.
-    constexpr int kB = (32 / G) < 4 ? 4 : 32 / G;
-    float o[G];
+    // Eight loads in flight per output; a chunk index past the end is clamped (a valid address) and weighted 0.
+    // (Requesting the partial rows of all of a thread's outputs at once, 32 loads in flight, was measured no faster:
+    // 750 against 761 tok/s on the 2B-4T decode.)
+    for (int t = tid; t < G * head_dim; t += kAttnThreads) {
+        const int g = t / head_dim, d = t - g * head_dim;
+        const float* ob = base + g * hstride + 2 + d;
+        const float* wg = w + g * nsplit;
+        float o = 0.0f;
+        for (int s = 0; s < nsplit; s += 8) {
+            float v[8];
 #pragma unroll
-    for (int j = 0; j < G; ++j) o[j] = 0.0f;
-    for (int s = 0; s < nsplit; s += kB) {
-        float v[G][kB];
+            for (int k = 0; k < 8; ++k) v[k] = __ldcg(ob + static_cast<size_t>(min(s + k, nsplit - 1)) * (head_dim + 2));
 #pragma unroll
-        for (int j = 0; j < G; ++j) {
-            const int t = tid + j * kAttnThreads;
-            if (t < G * head_dim) {
-                const int g = t / head_dim, d = t - g * head_dim;
-                const float* ob = base + g * hstride + 2 + d;
-#pragma unroll
-                for (int k = 0; k < kB; ++k) v[j][k] = __ldcg(ob + static_cast<size_t>(min(s + k, nsplit - 1)) * (head_dim + 2));
-            }
+            for (int k = 0; k < 8; ++k) o = fmaf(v[k], s + k < nsplit ? wg[s + k] : 0.0f, o);
         }
-#pragma unroll
-        for (int j = 0; j < G; ++j) {
-            const int t = tid + j * kAttnThreads;
-            if (t < G * head_dim) {
-                const float* wg = w + (t / head_dim) * nsplit;
-#pragma unroll
-                for (int k = 0; k < kB; ++k) o[j] = fmaf(v[j][k], s + k < nsplit ? wg[s + k] : 0.0f, o[j]);
-            }
-        }
-    }
-#pragma unroll
-    for (int j = 0; j < G; ++j) {
-        const int t = tid + j * kAttnThreads;
-        if (t < G * head_dim) {
-            const int g = t / head_dim, d = t - g * head_dim;
-            out[(static_cast<size_t>(kvh) * G + g) * head_dim + d] = __float2half_rn(__fmul_rn(o[j], inv[g]));
-        }
+        out[(static_cast<size_t>(kvh) * G + g) * head_dim + d] = __float2half_rn(__fmul_rn(o, inv[g]));
     }
 }
 

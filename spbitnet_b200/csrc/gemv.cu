@@ -146,7 +146,7 @@ template <int IN, int OUT>
 __global__ void __launch_bounds__(kThreads, (IN >= IN_RESNORM) ? 2 : 4) gemv_pairs_kernel(const GemvArgs a) {
     extern __shared__ __align__(128) uint8_t psmem[];
     // [sel 15360][sgn 2048][red 64 floats][partials upr*pitch ints (16-aligned)][x cols bytes]
-    // [half scratch 2*cols bytes, only for the producers that normalise]
+    // [half scratch 2*cols bytes, only for the producers that normalise][their norm weights: cols floats each]
     const uint32_t win_s = smem_u32(psmem);
     uint8_t* win = psmem;
     const int pitch = a.rpc | 1;
@@ -164,6 +164,27 @@ __global__ void __launch_bounds__(kThreads, (IN >= IN_RESNORM) ? 2 : 4) gemv_pai
     const int nunits = nrows * a.upr;
 
     grid_dep_launch();
+
+    // The norm weights of the normalising producers are constants: they start towards shared memory now, so that
+    // the producer does not go to L2 for them between its reductions.
+    ProducerArgs pa{a.x, a.x2, a.w_sub, a.w_norm, a.x_out, a.eps, a.d_absmax, a.cols};
+    if (IN >= IN_RESNORM) {
+        float* wbuf = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(xs) + 3 * a.cols);
+        auto stage = [&](const float* src, float* dst) {
+            for (int q = tid; q < (a.cols >> 2); q += kThreads)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst + 4 * q)), "l"(src + 4 * q) : "memory");
+        };
+        if (IN == IN_RESNORM) {
+            stage(a.w_norm, wbuf);
+            pa.w_norm = wbuf;
+            wbuf += a.cols;
+        }
+        if (a.w_sub) {
+            stage(a.w_sub, wbuf);
+            pa.w_sub = wbuf;
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
 
     // ---- phase A: weights of the first pass, tables, expansion to selectors and signs ---------
     const int npass = (nunits + kThreads - 1) / kThreads;
@@ -205,7 +226,12 @@ __global__ void __launch_bounds__(kThreads, (IN >= IN_RESNORM) ? 2 : 4) gemv_pai
 
     // ---- phase B: activations (only now may a predecessor's output be read) ------------------
     grid_dep_wait();
-    const float absmax = produce_x<IN, OUT>(a, xs, reinterpret_cast<__half*>(xs) + (a.cols >> 1), red,
+    // the position of the fused rotation is asked for now, not in the epilogue where it would be a trip to L2 on the
+    // critical path (volatile: the load stays here)
+    int rope_pos = 0;
+    if (OUT == OUT_F16 && a.rope.d_pos) asm volatile("ld.global.s32 %0, [%1];" : "=r"(rope_pos) : "l"(a.rope.d_pos));
+    if (IN >= IN_RESNORM) asm volatile("cp.async.wait_group 0;" ::: "memory");  // (each weight is first read after a block-wide reduction)
+    const float absmax = produce_x<IN, OUT>(pa, xs, reinterpret_cast<__half*>(xs) + (a.cols >> 1), red,
                                              blockIdx.x == 0);
     __syncthreads();
 
@@ -237,7 +263,7 @@ __global__ void __launch_bounds__(kThreads, (IN >= IN_RESNORM) ? 2 : 4) gemv_pai
     const float dq = (OUT != OUT_I32) ? dequant_scale(M.gamma, absmax) : 0.0f;
     if (OUT == OUT_F16 && a.rope.d_pos) {
         // q, k, v: a thread takes the two rows of a rotation pair (blocks start on even rows and hold an even number)
-        const int pos = *a.rope.d_pos, hd = a.rope.head_dim;
+        const int pos = rope_pos, hd = a.rope.head_dim;
         for (int pr = tid; 2 * pr < nrows; pr += kThreads) {
             int s0 = 0, s1 = 0;
             for (int c = 0; c < a.upr; ++c) {
@@ -632,7 +658,7 @@ static int run_gemv(const char* name, const MatDesc* mats, int nmat, const XDesc
         if (!fast) return launch(name, gemv_generic_kernel<IN, OUT>, dim3(blocks), dim3(kThreads), 0, stream, a);
     }
     const size_t smem = kSelBytes + kSgnBytes + 256 + ((a.upr * (a.rpc | 1) * 4 + 15) & ~15) +
-                        static_cast<size_t>(cols) * (IN >= IN_RESNORM ? 3 : 1);
+                        static_cast<size_t>(cols) * (IN == IN_RESNORM ? 3 + 8 : IN == IN_RELU2 ? 3 + 4 : 1);
     if ((rc = ensure_smem(gemv_pairs_kernel<IN, OUT>, smem))) return rc;
     return launch(name, gemv_pairs_kernel<IN, OUT>, dim3(blocks), dim3(kThreads), smem, stream, a);
 }
