@@ -71,6 +71,7 @@ int decode_attention_split(const void* Q, const void* K, const void* V, void* ou
     if (!decode_attention_split_supported(num_heads, num_kv_heads, head_dim) ||
         ((reinterpret_cast<uintptr_t>(Q) | reinterpret_cast<uintptr_t>(K) | reinterpret_cast<uintptr_t>(V)) & 15u))
         return fail(SPB_E_UNSUPPORTED, "%s: group %d / head_dim %d / alignment outside the kernel's range", name, G, head_dim);
+    if (reinterpret_cast<uintptr_t>(scratch) & 7u) return fail(SPB_E_INVALID, "%s: the scratch buffer must be 8-byte aligned", name);
     const int nsplit_max = attn_nsplit_max(max_seq_len);
     const int nsplit = d_pos ? nsplit_max : attn_nsplit(seq_len);
     const size_t msmem = sizeof(float) * attn_merge_smem_floats(G, max_seq_len);

@@ -145,14 +145,14 @@ __device__ __forceinline__ void attn_chunk_block(const __half* Q, const __half* 
     }
 }
 
-// floats of shared memory attn_merge_group needs: the weights of every (head, chunk) and 1 / sum of every head
+// floats of shared memory attn_merge_group needs: the weight and the sum of every (head, chunk), 1 / sum of every head
 __host__ __device__ inline size_t attn_merge_smem_floats(int G, int max_seq_len) {
-    return static_cast<size_t>(G) * attn_nsplit_max(max_seq_len) + G;
+    return static_cast<size_t>(2 * G) * attn_nsplit_max(max_seq_len) + G;
 }
 
 // Merges the chunks of the G query heads of KV head `kvh` with the usual log-sum-exp weights and rounds to half;
 // the whole block of kAttnThreads threads works on it.  sm: attn_merge_smem_floats() floats.
-//   1. the chunk maxima of every head into shared memory (one round of loads);
+//   1. the chunk maxima and sums of every head into shared memory (one round of loads);
 //   2. warp g takes head g: M = max, w[s] = exp(m[s] - M) into shared memory, L = sum l[s] * w[s];
 //   3. thread t takes (head, dim) pairs t, t + 256, ..: sum_s w[s] * o[s][d] with eight loads in flight.
 template <int G>
@@ -162,10 +162,13 @@ __device__ __forceinline__ void attn_merge_group(const float* scratch, __half* o
     const size_t hstride = static_cast<size_t>(nsplit_max) * (head_dim + 2);
     const float* base = scratch + static_cast<size_t>(kvh) * G * hstride;
     float* w = sm;
-    float* inv = sm + G * nsplit;
+    float* lsum = sm + G * nsplit;
+    float* inv = sm + 2 * G * nsplit;
     for (int i = tid; i < G * nsplit; i += kAttnThreads) {
         const int g = i / nsplit, s = i - g * nsplit;
-        w[i] = __ldcg(base + g * hstride + static_cast<size_t>(s) * (head_dim + 2));
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(base + g * hstride + static_cast<size_t>(s) * (head_dim + 2)));
+        w[i] = ml.x;
+        lsum[i] = ml.y;
     }
     __syncthreads();
     for (int g = warp; g < G; g += kAttnThreads / 32) {
@@ -177,7 +180,7 @@ __device__ __forceinline__ void attn_merge_group(const float* scratch, __half* o
         for (int s = lane; s < nsplit; s += 32) {
             const float e = expf(w[g * nsplit + s] - M);
             w[g * nsplit + s] = e;
-            L = fmaf(__ldcg(base + g * hstride + static_cast<size_t>(s) * (head_dim + 2) + 1), e, L);
+            L = fmaf(lsum[g * nsplit + s], e, L);
         }
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) L += __shfl_xor_sync(0xFFFFFFFFu, L, off);

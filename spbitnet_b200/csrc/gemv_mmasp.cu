@@ -146,6 +146,10 @@ __global__ void __launch_bounds__(kGmThreads, SPB_GEMV_MMA_MIN_BLOCKS) gemv_mmas
     // ---- after the dependency: x, permuted so that a lane's four B registers of a step are 16 contiguous bytes:
     //      xs[step][tig][j][0..3] = x[64 step + 16 j + 4 tig + 0..3] -------------------------------------------
     grid_dep_wait();
+    // the activation scale of the scaled outputs is asked for now, not in the epilogue where the load would be a trip
+    // to L2 on the critical path (volatile: it stays here)
+    float absmax_early = 0.0f;
+    if (a.out_mode != GM_OUT_I32) asm volatile("ld.global.f32 %0, [%1];" : "=f"(absmax_early) : "l"(a.d_absmax));
     // The successor on the stream is let in only now: it then loads and waits while this grid computes, and
     // no deeper queue of waiting grids builds up (measured: a deep queue slows a long chain of launches).
     grid_dep_launch();
@@ -216,7 +220,7 @@ __global__ void __launch_bounds__(kGmThreads, SPB_GEMV_MMA_MIN_BLOCKS) gemv_mmas
         if (a.out_mode == GM_OUT_I32) {
             static_cast<int32_t*>(a.y)[row] = acc;
         } else {
-            const float f = __fmul_rn(static_cast<float>(acc), dequant_scale(a.gamma, *a.d_absmax));
+            const float f = __fmul_rn(static_cast<float>(acc), dequant_scale(a.gamma, absmax_early));
             if (a.out_mode == GM_OUT_F32) {
                 static_cast<float*>(a.y)[row] = f;
                 if (a.y_acc) a.y_acc[row] = acc;
@@ -290,6 +294,10 @@ __global__ void __launch_bounds__(kGmThreads, 2) gemv_mmasp_chunked_kernel(const
     const uint32_t v_half = static_cast<uint32_t>(8 * a.vpitch) * 4u;
 
     grid_dep_wait();
+    // the activation scale of the scaled outputs is asked for now, not in the epilogue where the load would be a trip
+    // to L2 on the critical path (volatile: it stays here)
+    float absmax_early = 0.0f;
+    if (a.out_mode != GM_OUT_I32) asm volatile("ld.global.f32 %0, [%1];" : "=f"(absmax_early) : "l"(a.d_absmax));
     grid_dep_launch();
     for (int q = tid; q < (a.cols >> 4); q += kGmThreads) {
         const uint4 xv = __ldg(reinterpret_cast<const uint4*>(a.x) + q);
@@ -359,7 +367,7 @@ __global__ void __launch_bounds__(kGmThreads, 2) gemv_mmasp_chunked_kernel(const
         if (a.out_mode == GM_OUT_I32) {
             static_cast<int32_t*>(a.y)[row] = acc;
         } else {
-            const float f = __fmul_rn(static_cast<float>(acc), dequant_scale(a.gamma, *a.d_absmax));
+            const float f = __fmul_rn(static_cast<float>(acc), dequant_scale(a.gamma, absmax_early));
             if (a.out_mode == GM_OUT_F32) {
                 static_cast<float*>(a.y)[row] = f;
                 if (a.y_acc) a.y_acc[row] = acc;

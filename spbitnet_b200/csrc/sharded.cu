@@ -538,10 +538,18 @@ __global__ void __launch_bounds__(kWideThreads) wide_relu2_norm_quant_kernel(
     float* __restrict__ d_absmax, int n, float eps) {
     __shared__ float sh[32];
     grid_dep_launch();
+    const int runs = n >> 3;
+    // sub_w is read after the reduction, when it is needed (no registers to hold it until then); it is constant, so its
+    // lines are brought into L1 before the dependency wait and the later read does not go to L2
+    if (sub_w)
+#pragma unroll
+        for (int k = 0; k < kWideRuns; ++k) {
+            const int r = threadIdx.x + k * kWideThreads;
+            if (r < runs) asm volatile("prefetch.global.L1 [%0];" ::"l"(sub_w + 8 * r));
+        }
     grid_dep_wait();
     const size_t off = static_cast<size_t>(blockIdx.x) * n;
-    const int runs = n >> 3;
-    float v[kWideRuns][8];  // the products stay in registers; sub_w is read when it is needed (cache-resident)
+    float v[kWideRuns][8];  // the products stay in registers
     float s = 0.0f;
 #pragma unroll
     for (int k = 0; k < kWideRuns; ++k) {
