@@ -20,7 +20,8 @@
 // shifted by one).  With A in {0, -1} the step needs a second MMA with A = 1 on the same metadata and activations:
 //   y = sum over kept x  +  2 * sum of (A * x)   =   S + 2 R.
 // A step is about ten instructions and one shared-memory wavefront (the activation registers; only the four lanes
-// of output column 0 load them).
+// of output column 0 load them).  (Turning 0x00 / 0xFF into +1 / -1 with an "or" per register and issuing a single MMA
+// was measured slower, 9.5 against 8.9 us at 28672 x 8192: the four extra logic instructions cost more than the MMA.)
 //
 // Measured (one B200, graphs of launches over weight copies larger than L2, eight branches): 28672 x 8192 in 9.0 us =
 // 4.9 TB/s against 13.9 us = 3.2 TB/s for the packed-format kernel, 8192 x 28672 9.7 against 15.6 us, 8192 x 8192 3.7
