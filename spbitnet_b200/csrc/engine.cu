@@ -162,8 +162,10 @@ BitLinearGroup make_group(const Linear* const* L, __half* const* out, int n) {
 
 // Enqueues one token's worth of kernels on e->stream.  The first kernel reads the token
 // (prompt[pos] while pos < n_prompt, else the previous arg-max) and the last advances pos.
-// With layouts the fused-producer GEMV kernels take (every benchmark model), a layer is six
-// launches: the vector ops between the BitLinears run inside the consuming launch.
+// With layouts the fused-producer GEMV kernels take (every benchmark model), a layer is five
+// launches: the vector ops between the BitLinears run inside the consuming launch, RoPE and the
+// KV scatter inside the q/k/v launch, the merge of the attention chunks inside the attention
+// launch.  In the persistent mode the layers of a token are one cooperative launch.
 int enqueue_token(spb_engine* e, bool record_tokens) {
     const spb_model_config& c = e->cfg;
     const int H = c.hidden_size, hd = c.head_dim, nh = c.num_attention_heads, nkv = c.num_key_value_heads;
