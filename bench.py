@@ -844,6 +844,20 @@ def bench_decode(args, with_reference=True, with_cpu=False):
         persistent = {"tok_s": steps / dt_p2, "ms_per_token": 1e3 * dt_p2 / steps, "same_tokens": bool((toks_p == toks).all())}
     except Exception as exc:
         persistent = {"error": repr(exc)[:160]}
+    # ... and without grid barriers (stage outputs as tagged words)
+    tagged = None
+    try:
+        eng.reset()
+        eng.set_decode_mode(InferenceEngine.DECODE_PERSISTENT_TAGGED)
+        eng.generate(prompt, 8)
+        eng.reset()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        toks_p = eng.generate(prompt, n_gen)
+        dt_p3 = time.perf_counter() - t0
+        tagged = {"tok_s": steps / dt_p3, "ms_per_token": 1e3 * dt_p3 / steps, "same_tokens": bool((toks_p == toks).all())}
+    except Exception as exc:
+        tagged = {"error": repr(exc)[:160]}
     eng.reset()
     eng.set_decode_mode(InferenceEngine.DECODE_AUTO)
     # the same job with the prompt fed as one batch (BitLinear layers as the batched product)
@@ -868,7 +882,7 @@ def bench_decode(args, with_reference=True, with_cpu=False):
     peak, _ = measured_peaks()
     out = {"tok_s": steps / dt, "batched_prompt": batched, "ms_per_token": 1e3 * dt / steps, "generated": int(len(toks)),
            "prompt": int(len(prompt)), "weight_mb_per_token": round(weight_bytes / 1e6, 1),
-           "step": "chain of five PDL-linked kernels per layer", "persistent_kernel": persistent, "clocks": decode_clocks,
+           "step": "chain of five PDL-linked kernels per layer", "persistent_kernel": persistent, "persistent_kernel_tagged_words": tagged, "clocks": decode_clocks,
            "hbm_gbs": weight_bytes * steps / dt / 1e9, "hbm_frac_measured": weight_bytes * steps / dt / 1e9 / peak,
            "what": "prefill (token-serial, as the reference) + decode, wall clock around generate() incl. prompt "
                    "H2D and token D2H; random-init 2B-4T shape, every matrix of every layer drawn with its own seed"}
@@ -1005,8 +1019,11 @@ def bench_sharded(args, rank, world, dist):
     full.config = cfg
     full.layers = [full.layers[0]] * L  # ShardEngine clones the rank's slices layer by layer
     results = {}
-    for batch in (1, 64):
+    runs = [(1, True), (64, True)] + ([(1, False)] if world > 1 else [])
+    for batch, fold in runs:
         eng = ShardEngine(full, rank=rank, world=world, batch=batch, group=ctl)
+        if not fold:  # the exchanges as launches of their own instead of inside the kernels that consume the vectors
+            eng.set_exchange_fold(False)
         rng = np.random.default_rng(11)
         prompts = rng.integers(0, cfg["vocab_size"], (args.shard_prompt, batch)).astype(np.int32)
         warm = eng.generate(prompts[:4], 2)  # graph capture, page-in
@@ -1023,7 +1040,7 @@ def bench_sharded(args, rank, world, dist):
         kv_bytes = 2 * L * batch * (cfg["num_key_value_heads"] // world if world <= cfg["num_key_value_heads"] else 1) * \
             (args.shard_prompt + args.shard_tokens // 2) * cfg["head_dim"] * 2
         my_bytes = eng.weight_bytes() + kv_bytes
-        results[f"batch{batch}"] = {
+        results[f"batch{batch}" if fold else f"batch{batch}_exchange_as_launch"] = {
             "tok_s": batch * args.shard_tokens / dt, "ms_per_step": 1e3 * step_s,
             "prompt_s": t_prompt, "prompt_tok_s": batch * (args.shard_prompt - 1) / t_prompt,
             "per_gpu_bytes_per_step": int(my_bytes), "per_gpu_hbm_gbs": my_bytes / step_s / 1e9,

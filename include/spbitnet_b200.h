@@ -352,10 +352,15 @@ int spb_engine_set_prefill_chunk(spb_engine* e, int chunk);
  *   2 the persistent kernel: one cooperative launch per token, a block per SM, grid barriers between the stages of
  *     a layer, weights prefetched into shared memory; SPB_E_UNSUPPORTED at the next step if the model does not fit.
  *     Measured slower than the chain so far (see the design notes), hence not the default;
- *   3 the chain with every vector op group as its own launch (the reference's op order, for testing).
- * All modes produce the same tokens and logits bit for bit.  A grid-barrier wait of the persistent kernel is
- * bounded (about a second); when one runs out the step's results are unspecified, the library's timeout counter
- * moves (SPB_E_TIMEOUT from the engine call that synchronises next) and spb_engine_reset clears the barrier state. */
+ *   3 the chain with every vector op group as its own launch (the reference's op order, for testing);
+ *   4 the persistent kernel without grid barriers: every stage writes its output vector as 8-byte words {two
+ *     halves, tag} (tag = launch count and layer), the consumers poll the words they need until the tag is there,
+ *     and every block keeps the residual stream in its shared memory.  Needs at least as many 16-row tiles as SMs
+ *     in every projection (hidden size >= 16 x SMs), else SPB_E_UNSUPPORTED at the next step.
+ * All modes produce the same tokens and logits bit for bit.  Every wait of the persistent kernel (grid barrier,
+ * tagged word, weight copy) is bounded (about a second); when one runs out the step's results are unspecified, the
+ * library's timeout counter moves (SPB_E_TIMEOUT from the engine call that synchronises next) and spb_engine_reset
+ * clears the barrier state and the tagged words. */
 int spb_engine_set_decode_mode(spb_engine* e, int mode);
 /* 1 when the last step that was set up runs the persistent kernel. */
 int spb_engine_decode_is_persistent(const spb_engine* e);
@@ -438,11 +443,15 @@ size_t spb_shard_engine_exchange_bytes(const spb_shard_engine* e);
 /* Bound of every wait for a peer (default 5000 ms). */
 int spb_shard_engine_set_timeout_ms(spb_shard_engine* e, int ms);
 /* Whether the engine keeps a prepared copy (spb_prepare_weights) of the slices set with spb_shard_engine_set_linear
- * and multiplies on it: 1 (default) for slices of 32 M weights and more, 2 for every slice the layout takes, 0 for
+ * and multiplies on it: 1 (default) for slices of 32 M weights and more (k and v go with q), 2 for every slice the layout takes, 0 for
  * none.  It applies to the single-sequence step of wide models (hidden size >= 4096), which multiplies matrix by
  * matrix on the quantised vector; elsewhere the setting has no effect.  The copies are the engine's (as large as
  * the slices); results are the same bit for bit.  May be called before or after the slices are set. */
 int spb_shard_engine_set_prepared_weights(spb_shard_engine* e, int on);
+/* Single-sequence step of wide models on several ranks: 1 (default) the kernel that consumes a gathered vector (one
+ * block) sends this rank's slice and collects the peers' itself, as {data, sequence number} words; 0 a launch of its
+ * own does (the form every other step uses).  Same results bit for bit; the waits are bounded the same way. */
+int spb_shard_engine_set_exchange_fold(spb_shard_engine* e, int on);
 int spb_shard_engine_reset(spb_shard_engine* e);
 int spb_shard_engine_seq_len(const spb_shard_engine* e);
 /* One decode step: tokens[batch] (HOST) enter at the current position; synchronises.  Afterwards the rank's logits

@@ -135,6 +135,7 @@ SIGNATURES = {
     "spb_shard_engine_exchange_bytes": (C.c_size_t, [_p]),
     "spb_shard_engine_set_timeout_ms": (_i, [_p, _i]),
     "spb_shard_engine_set_prepared_weights": (_i, [_p, _i]),
+    "spb_shard_engine_set_exchange_fold": (_i, [_p, _i]),
     "spb_shard_engine_reset": (_i, [_p]),
     "spb_shard_engine_seq_len": (_i, [_p]),
     "spb_shard_engine_step": (_i, [_p, _p]),

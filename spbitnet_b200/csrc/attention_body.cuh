@@ -40,13 +40,57 @@ __host__ __device__ inline size_t attn_smem_bytes(int G, int head_dim) {
     return static_cast<size_t>(2 * kAttnMaxChunk + G) * head_dim * 2 + static_cast<size_t>(G) * kAttnMaxChunk * 4;
 }
 
+// Vectors that blocks of the same grid publish element by element (the persistent decode kernel without grid
+// barriers): every 64-bit word holds two halves and the tag of the step that wrote it, stored with one 8-byte store,
+// so a reader that sees the tag it expects has the data.  ll_read polls (bounded) until `n` consecutive words carry
+// `tag` and returns their data words; on a run-out it sets *fail and returns what it has.
+struct LlSource {
+    const uint2* q;      // the query vectors: heads * head_dim / 2 words
+    const uint2* k;      // the new K row of every KV head: kv heads * head_dim / 2 words
+    const uint2* v;
+    unsigned tag;
+    int pos;             // the position the new rows belong to
+    long long limit;     // cycles
+    int* fail;           // shared-memory flag
+};
+__device__ __forceinline__ uint32_t ll_read1(const uint2* p, unsigned tag, long long limit, int* fail) {
+    uint32_t d, t;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(d), "=r"(t) : "l"(p));
+    if (t == tag) return d;
+    const long long t0 = clock64();
+    for (;;) {
+        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(d), "=r"(t) : "l"(p));
+        if (t == tag) return d;
+        if (clock64() - t0 > limit) *fail = 1;
+        if (*reinterpret_cast<volatile int*>(fail)) return d;  // this wait or another one of the block ran out
+    }
+}
+// four consecutive words = eight halves
+__device__ __forceinline__ uint4 ll_read4(const uint2* p, unsigned tag, long long limit, int* fail) {
+    uint32_t d[4], t[4];
+    long long t0 = 0;
+    for (int spin = 0;; ++spin) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(d[i]), "=r"(t[i]) : "l"(p + i));
+        if (t[0] == tag && t[1] == tag && t[2] == tag && t[3] == tag) break;
+        if (spin == 0) t0 = clock64();
+        else if (clock64() - t0 > limit) *fail = 1;
+        if (*reinterpret_cast<volatile int*>(fail)) break;  // this wait or another one of the block ran out
+    }
+    return make_uint4(d[0], d[1], d[2], d[3]);
+}
+__device__ __forceinline__ void ll_write(uint2* p, uint32_t data, unsigned tag) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(data), "r"(tag) : "memory");
+}
+
 // Work of one block on chunk `split` of KV head `kvh` (split * attn_chunk(seq_len) < seq_len).  head_dim is a
 // multiple of 8 and at most 256; Q, K, V are 16-byte aligned.  They and the scratch are accessed with L2 loads
 // and plain stores: in the persistent decode kernel other blocks of the same grid wrote them.
+// With `ll` the query vectors and the K, V rows of position ll->pos come from tagged words instead of Q and the caches.
 template <int G>
 __device__ __forceinline__ void attn_chunk_block(const __half* Q, const __half* K, const __half* V, float* scratch,
                                                  int kvh, int split, int head_dim, int max_seq_len, int nsplit_max,
-                                                 float scale, int seq_len, uint8_t* smem) {
+                                                 float scale, int seq_len, uint8_t* smem, const LlSource* ll = nullptr) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int C = attn_chunk(seq_len);
     const int p0 = split * C;
@@ -74,7 +118,7 @@ __device__ __forceinline__ void attn_chunk_block(const __half* Q, const __half* 
                 vr[i] = __ldcg(vg + idx);
             }
         }
-        if (tid < nq4) qr = __ldcg(qg + tid);
+        if (tid < nq4 && !ll) qr = __ldcg(qg + tid);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int idx = tid + i * kAttnThreads;
@@ -83,9 +127,22 @@ __device__ __forceinline__ void attn_chunk_block(const __half* Q, const __half* 
                 reinterpret_cast<uint4*>(Vs)[idx] = vr[i];
             }
         }
-        if (tid < nq4) reinterpret_cast<uint4*>(Qs)[tid] = qr;
+        if (tid < nq4 && !ll) reinterpret_cast<uint4*>(Qs)[tid] = qr;
     }
     __syncthreads();
+    if (ll) {
+        const int hw = head_dim >> 1;  // words per vector
+        uint32_t* Qw = reinterpret_cast<uint32_t*>(Qs);
+        for (int i = tid; i < G * hw; i += kAttnThreads) Qw[i] = ll_read1(ll->q + static_cast<size_t>(kvh) * G * hw + i, ll->tag, ll->limit, ll->fail);
+        const int j = ll->pos - p0;  // the new position's row, if this chunk holds it
+        if (j >= 0 && j < np) {
+            if (tid < hw)
+                reinterpret_cast<uint32_t*>(Ks + j * head_dim)[tid] = ll_read1(ll->k + static_cast<size_t>(kvh) * hw + tid, ll->tag, ll->limit, ll->fail);
+            else if (tid < 2 * hw)
+                reinterpret_cast<uint32_t*>(Vs + j * head_dim)[tid - hw] = ll_read1(ll->v + static_cast<size_t>(kvh) * hw + tid - hw, ll->tag, ll->limit, ll->fail);
+        }
+        __syncthreads();
+    }
 
     // ---- scores ------------------------------------------------------------------------------------------
     {
@@ -155,9 +212,11 @@ __host__ __device__ inline size_t attn_merge_smem_floats(int G, int max_seq_len)
 //   1. the chunk maxima and sums of every head into shared memory (one round of loads);
 //   2. warp g takes head g: M = max, w[s] = exp(m[s] - M) into shared memory, L = sum l[s] * w[s];
 //   3. thread t takes (head, dim) pairs t, t + 256, ..: sum_s w[s] * o[s][d] with eight loads in flight.
+// With ll_out the result goes out as tagged words (two halves each) instead of to `out`.
 template <int G>
 __device__ __forceinline__ void attn_merge_group(const float* scratch, __half* out, int kvh, int head_dim,
-                                                 int nsplit_max, int nsplit, float* sm) {
+                                                 int nsplit_max, int nsplit, float* sm, uint2* ll_out = nullptr,
+                                                 unsigned ll_tag = 0) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const size_t hstride = static_cast<size_t>(nsplit_max) * (head_dim + 2);
     const float* base = scratch + static_cast<size_t>(kvh) * G * hstride;
@@ -202,7 +261,14 @@ __device__ __forceinline__ void attn_merge_group(const float* scratch, __half* o
 #pragma unroll
             for (int k = 0; k < 8; ++k) o = fmaf(v[k], s + k < nsplit ? wg[s + k] : 0.0f, o);
         }
-        out[(static_cast<size_t>(kvh) * G + g) * head_dim + d] = __float2half_rn(__fmul_rn(o, inv[g]));
+        const __half h = __float2half_rn(__fmul_rn(o, inv[g]));
+        if (!ll_out) {
+            out[(static_cast<size_t>(kvh) * G + g) * head_dim + d] = h;
+        } else {  // the even dim of a pair stores both (G * head_dim is a multiple of 16: a pair is active together)
+            const uint32_t mine = __half_as_ushort(h);
+            const uint32_t next = __shfl_down_sync(__activemask(), mine, 1);
+            if ((d & 1) == 0) ll_write(ll_out + (((static_cast<size_t>(kvh) * G + g) * head_dim + d) >> 1), mine | (next << 16), ll_tag);
+        }
     }
 }
 

@@ -60,6 +60,7 @@ struct PdGeom {
     int mp_i, vp_i;  // cols = intermediate size (down)
     int t_qkv, t_o, t_gu, t_dn;  // tile slots per block and kind
     uint32_t off_sw, off_x, off_qkv, off_o, off_gu, off_dn, off_attn;  // byte offsets in dynamic shared memory
+    uint32_t off_res;      // barrier-free form: the block's copy of the residual stream (H halves)
     uint32_t off_norm[4];  // the layer's norm weights (input_ln, post_attn_ln, attn_sub_norm, ffn_sub_norm), if staged
     int norms;             // 1: the norm weights travel with the slabs into shared memory; 0: read from global memory
     long long wait_cycles;
@@ -68,6 +69,35 @@ struct PdGeom {
 };
 
 using PdProd = ProducerArgs;
+
+// Producer operands of the barrier-free form: vectors that other blocks publish as tagged words (attention_body.cuh).
+struct PdProdLl : ProducerArgs {
+    const uint2* ll_x;   // tagged words behind x (attention output; gate and up)
+    const uint2* ll_x2;  // tagged words behind x2 (the delta of a residual add)
+    unsigned tag;
+    long long limit;
+    int* fail;
+};
+// x = the block's own copy of the residual stream (shared memory), x2 = delta as tagged words
+struct LoadsResidualLl {
+    static __device__ __forceinline__ uint4 x(const PdProdLl& a, int q) { return *(static_cast<const uint4*>(a.x) + q); }
+    static __device__ __forceinline__ uint4 x2(const PdProdLl& a, int q) { return ll_read4(a.ll_x2 + 4 * q, a.tag, a.limit, a.fail); }
+};
+// x = a half vector as tagged words
+struct LoadsVectorLl {
+    static __device__ __forceinline__ uint4 x(const PdProdLl& a, int q) { return ll_read4(a.ll_x + 4 * q, a.tag, a.limit, a.fail); }
+    static __device__ __forceinline__ uint4 x2(const PdProdLl& a, int q) { return x(a, q); }
+};
+// x = gate, x2 = up: word i holds gate[i] in its low and up[i] in its high half
+struct LoadsGateUpLl {
+    static __device__ __forceinline__ uint4 pick(const PdProdLl& a, int q, uint32_t sel) {
+        const uint4 lo = ll_read4(a.ll_x + 8 * q, a.tag, a.limit, a.fail), hi = ll_read4(a.ll_x + 8 * q + 4, a.tag, a.limit, a.fail);
+        return make_uint4(__byte_perm(lo.x, lo.y, sel), __byte_perm(lo.z, lo.w, sel), __byte_perm(hi.x, hi.y, sel),
+                          __byte_perm(hi.z, hi.w, sel));
+    }
+    static __device__ __forceinline__ uint4 x(const PdProdLl& a, int q) { return pick(a, q, 0x5410u); }
+    static __device__ __forceinline__ uint4 x2(const PdProdLl& a, int q) { return pick(a, q, 0x7632u); }
+};
 
 __device__ __forceinline__ uint32_t pd_smem(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ uint32_t pd_lds(uint32_t addr) {
@@ -92,6 +122,8 @@ __device__ __forceinline__ unsigned pd_ld_acquire(const unsigned* p) {
 constexpr int kSyncCount = 0;    // arrivals at grid barriers, ever
 constexpr int kSyncGen = 1;      // the count when the previous launch ended
 constexpr int kSyncBroken = 2;   // a wait ran out: the counters no longer mean anything
+constexpr int kSyncEpoch = 3;    // barrier-free form: launches so far (the tags of a launch's words derive from it)
+constexpr int kSyncDone = 4;     // barrier-free form: blocks of the current launch that have finished
 constexpr int kSyncFlag = 32;    // the last barrier every block has arrived at (its target count)
 constexpr int kSyncKv = 64;      // per KV head: chunks of the current attention stage that are written
 
@@ -235,7 +267,7 @@ __device__ __forceinline__ void pd_tiles(uint32_t ms_s, int tcap, int T, int mp,
     epi(active, tid >> 4, tid & 15, acc);
 }
 
-template <int G>
+template <int G, bool LL>
 __global__ void __launch_bounds__(kPdThreads, 1) decode_persistent_kernel(const PdModel m, const PdGeom geo) {
     __shared__ __align__(16) uint32_t sgn_tab[16 * 32];  // entry (nibble n, lane l) at word n * 32 + l
     __shared__ int redi[kPdWarps * 16];
@@ -254,6 +286,9 @@ __global__ void __launch_bounds__(kPdThreads, 1) decode_persistent_kernel(const 
     if (vsync[kSyncBroken] != 0u) return;  // an earlier launch gave up at a barrier: the counters no longer mean anything
     const unsigned bar_base = vsync[kSyncGen];
     unsigned bar_n = 0;  // barriers passed so far
+    // barrier-free form: the words of layer l of this launch carry tag_base + l (never 0, which is what the buffer
+    // is cleared to); the regions of the stage outputs follow one another in m.ll
+    const unsigned tag_base = LL ? vsync[kSyncEpoch] * static_cast<unsigned>(m.nlayers + 1) + 1u : 0u;
 
     if (tid < 2) s_flag[tid] = 0;
     if (tid == 0) {
@@ -287,6 +322,14 @@ __global__ void __launch_bounds__(kPdThreads, 1) decode_persistent_kernel(const 
     const uint32_t xs_s = raw_s + geo.off_x;
     const uint32_t qkv_s = raw_s + geo.off_qkv, o_s = raw_s + geo.off_o, gu_s = raw_s + geo.off_gu, dn_s = raw_s + geo.off_dn;
     uint8_t* attn_sm = pd_raw + geo.off_attn;
+    __half* res_sm = reinterpret_cast<__half*>(pd_raw + geo.off_res);
+    uint2* const ll_q = m.ll;
+    uint2* const ll_k = ll_q + (qdim >> 1);
+    uint2* const ll_v = ll_k + (kvdim >> 1);
+    uint2* const ll_a = ll_v + (kvdim >> 1);
+    uint2* const ll_o = ll_a + (qdim >> 1);
+    uint2* const ll_gu = ll_o + (m.H >> 1);
+    uint2* const ll_d = ll_gu + m.inter;
 
     // ---- slab copies -------------------------------------------------------------------------------------------
     // One bulk copy per row and stream (bitmaps, signs), spread over the threads; thread 0 announces the byte count.
@@ -396,11 +439,29 @@ __global__ void __launch_bounds__(kPdThreads, 1) decode_persistent_kernel(const 
             geo.trace[(b ? kPdTraceWords : 0) + i] = t;
         }
     };
+    // Between two stages: the grid barrier, or (barrier-free form) a block barrier that also collects a poll that
+    // ran out somewhere in the block.
     auto barrier = [&]() {
+        if (LL) {
+            if (__syncthreads_or(s_flag[0])) {
+                if (tid == 0 && atomicExch(m.sync + kSyncBroken, 1u) == 0u && geo.timeouts) atomicAdd_system(geo.timeouts, 1);
+                return false;
+            }
+            return true;
+        }
         ++bar_n;
         return pd_barrier(m.sync, bar_base + bar_n * static_cast<unsigned>(nb), geo.wait_cycles, geo.timeouts, &s_flag[0]);
     };
+    // two halves that neighbouring lanes hold -> one tagged word, stored by the even lane
+    auto ll_pair = [&](uint2* dst, int index, __half mine, bool writer, unsigned tag) {
+        const uint32_t lo = __half_as_ushort(mine);
+        const uint32_t hi = __shfl_down_sync(0xFFFFFFFFu, lo, 1);
+        if (writer) ll_write(dst + (index >> 1), lo | (hi << 16), tag);
+    };
 
+    if (LL)  // every block keeps its own copy of the residual stream; it starts as the token's embedding row
+        for (int q = tid; q < (m.H >> 3); q += kPdThreads)
+            reinterpret_cast<uint4*>(res_sm)[q] = __ldg(reinterpret_cast<const uint4*>(m.embed + static_cast<size_t>(token) * m.H) + q);
     __syncthreads();  // the table, the flags, the copy barriers
     issue_qkv(0);
     issue_rows(0, 3, qdim, o_s, geo.t_o, geo.mp_q, geo.vp_q);
@@ -419,8 +480,9 @@ __global__ void __launch_bounds__(kPdThreads, 1) decode_persistent_kernel(const 
         // ---- stage 1: residual + input norm -> q k v, RoPE, cache --------------------------------------------
         issue_rows(l, 6, m.inter, dn_s, geo.t_dn, geo.mp_i, geo.vp_i);
         issued[3] = l;
+        const unsigned tag = tag_base + static_cast<unsigned>(l);
         if (T_qkv > 0) {
-            PdProd pa{};
+            PdProdLl pa{};
             pa.x = l == 0 ? static_cast<const void*>(m.embed + static_cast<size_t>(token) * m.H) : static_cast<const void*>(m.xa);
             pa.x2 = l == 0 ? nullptr : m.down;
             pa.w_sub = nullptr;
@@ -428,10 +490,19 @@ __global__ void __launch_bounds__(kPdThreads, 1) decode_persistent_kernel(const 
             pa.x_out = m.xb;
             pa.eps = m.eps;
             pa.cols = m.H;
+            if (LL) {  // residual: the block's copy, updated in place; delta: the previous layer's down projection
+                pa.x = res_sm;
+                pa.x_out = res_sm;
+                pa.ll_x2 = ll_d;
+                pa.tag = tag - 1u;
+                pa.limit = geo.wait_cycles;
+                pa.fail = &s_flag[0];
+            }
             if (!slab_ready(0, l)) return leave();
             consumed[0] = l;
             mark(0);
-            const float absmax = produce_x<IN_RESNORM, OUT_F16>(pa, xs_sw, static_cast<__half*>(nullptr), redf, b == 0);
+            const float absmax = LL ? produce_x<IN_RESNORM, OUT_F16, PdProdLl, LoadsResidualLl>(pa, xs_sw, static_cast<__half*>(nullptr), redf, true)
+                                    : produce_x<IN_RESNORM, OUT_F16>(pa, xs_sw, static_cast<__half*>(nullptr), redf, b == 0);
             reorder_x(m.H);
             __syncthreads();
             mark(1);
@@ -446,18 +517,21 @@ __global__ void __launch_bounds__(kPdThreads, 1) decode_persistent_kernel(const 
                          const __half hv = __float2half_rn(__fmul_rn(static_cast<float>(acc), dq));
                          const float v = __half2float(hv);
                          const float p = __shfl_xor_sync(0xFFFFFFFFu, v, 1);  // the other element of the RoPE pair
-                         if (!active) return;
                          const int head = row / m.hd, d = row - head * m.hd;
-                         if (mi == 2) {
-                             Ly.vc[(static_cast<size_t>(head) * m.max_seq + pos) * m.hd + d] = hv;
-                             return;
+                         __half y = hv;
+                         if (mi != 2) {
+                             __half y0, y1;
+                             const float2 cs = rope_cs[(d >> 1) & 127];
+                             rope_apply((r & 1) ? p : v, (r & 1) ? v : p, cs.x, cs.y, y0, y1);
+                             y = (r & 1) ? y1 : y0;
                          }
-                         __half y0, y1;
-                         const float2 cs = rope_cs[d >> 1];
-                         rope_apply((r & 1) ? p : v, (r & 1) ? v : p, cs.x, cs.y, y0, y1);
-                         const __half y = (r & 1) ? y1 : y0;
-                         if (mi == 0) m.q[row] = y;
-                         else Ly.kc[(static_cast<size_t>(head) * m.max_seq + pos) * m.hd + d] = y;
+                         if (LL) ll_pair(mi == 0 ? ll_q : mi == 1 ? ll_k : ll_v, row, y, active && (r & 1) == 0, tag);
+                         if (!active) return;
+                         if (mi == 0) {
+                             if (!LL) m.q[row] = y;
+                         } else {
+                             (mi == 1 ? Ly.kc : Ly.vc)[(static_cast<size_t>(head) * m.max_seq + pos) * m.hd + d] = y;
+                         }
                      });
         }
         mark(2);
@@ -470,8 +544,9 @@ __global__ void __launch_bounds__(kPdThreads, 1) decode_persistent_kernel(const 
         mark(4);
         for (int item = b; item < m.nkv * nsplit; item += nb) {
             const int kvh = item / nsplit, split = item - kvh * nsplit;
+            const LlSource lls{ll_q, ll_k, ll_v, tag, pos, geo.wait_cycles, &s_flag[0]};
             attn_chunk_block<G>(m.q, Ly.kc, Ly.vc, m.scratch, kvh, split, m.hd, m.max_seq, nsplit_max, m.attn_scale, seq_len,
-                                attn_sm);
+                                attn_sm, LL ? &lls : nullptr);
             __syncthreads();
             if (tid == 0) {
                 __threadfence();  // cumulative: the block's partial results, then the count
@@ -483,7 +558,8 @@ __global__ void __launch_bounds__(kPdThreads, 1) decode_persistent_kernel(const 
             }
             __syncthreads();
             if (s_flag[1])  // every chunk of this KV head is written: merge them for its G query heads
-                attn_merge_group<G>(m.scratch, m.attn, kvh, m.hd, nsplit_max, nsplit, reinterpret_cast<float*>(attn_sm));
+                attn_merge_group<G>(m.scratch, m.attn, kvh, m.hd, nsplit_max, nsplit, reinterpret_cast<float*>(attn_sm),
+                                    LL ? ll_a : nullptr, tag);
             __syncthreads();
         }
         mark(5);
@@ -492,20 +568,28 @@ __global__ void __launch_bounds__(kPdThreads, 1) decode_persistent_kernel(const 
 
         // ---- stage 3: o projection ---------------------------------------------------------------------------
         if (T_h > 0) {
-            PdProd pa{};
+            PdProdLl pa{};
             pa.x = m.attn;
             pa.cols = qdim;
+            pa.ll_x = ll_a;
+            pa.tag = tag;
+            pa.limit = geo.wait_cycles;
+            pa.fail = &s_flag[0];
             if (!slab_ready(1, l)) return leave();
             consumed[1] = l;
             mark(7);
-            const float absmax = produce_x<IN_F16_AMAX, OUT_F16>(pa, xs_sw, static_cast<__half*>(nullptr), redf, b == 0);
+            const float absmax = LL ? produce_x<IN_F16_AMAX, OUT_F16, PdProdLl, LoadsVectorLl>(pa, xs_sw, static_cast<__half*>(nullptr), redf, true)
+                                    : produce_x<IN_F16_AMAX, OUT_F16>(pa, xs_sw, static_cast<__half*>(nullptr), redf, b == 0);
             reorder_x(qdim);
             __syncthreads();
             mark(8);
             const float dq = dequant_scale(Ly.lin[3].gamma, absmax);
             pd_tiles(o_s, geo.t_o, T_h, geo.mp_q, geo.vp_q, qdim >> 6, xs_s, tab_s, redi, tid, lane, warp,
                      [&](bool active, int tl, int r, int acc) {
-                         if (active) m.o[16 * (b + tl * nb) + r] = __float2half_rn(__fmul_rn(static_cast<float>(acc), dq));
+                         const int row = 16 * (b + tl * nb) + r;
+                         const __half hv = __float2half_rn(__fmul_rn(static_cast<float>(acc), dq));
+                         if (LL) ll_pair(ll_o, row, hv, active && (r & 1) == 0, tag);
+                         else if (active) m.o[row] = hv;
                      });
         }
         mark(9);
@@ -516,7 +600,7 @@ __global__ void __launch_bounds__(kPdThreads, 1) decode_persistent_kernel(const 
         issue_rows(l + 1, 3, qdim, o_s, geo.t_o, geo.mp_q, geo.vp_q);
         if (l + 1 < m.nlayers) issued[1] = l + 1;
         if (T_gu > 0) {
-            PdProd pa{};
+            PdProdLl pa{};
             pa.x = m.xb;
             pa.x2 = m.o;
             pa.w_sub = norm_ptr(Ly.norm[2], 2);
@@ -524,20 +608,36 @@ __global__ void __launch_bounds__(kPdThreads, 1) decode_persistent_kernel(const 
             pa.x_out = m.xa;
             pa.eps = m.eps;
             pa.cols = m.H;
+            if (LL) {
+                pa.x = res_sm;
+                pa.x_out = res_sm;
+                pa.ll_x2 = ll_o;
+                pa.tag = tag;
+                pa.limit = geo.wait_cycles;
+                pa.fail = &s_flag[0];
+            }
             if (!slab_ready(2, l)) return leave();
             consumed[2] = l;
             mark(11);
-            const float absmax = produce_x<IN_RESNORM, OUT_F16>(pa, xs_sw, static_cast<__half*>(nullptr), redf, b == 0);
+            const float absmax = LL ? produce_x<IN_RESNORM, OUT_F16, PdProdLl, LoadsResidualLl>(pa, xs_sw, static_cast<__half*>(nullptr), redf, true)
+                                    : produce_x<IN_RESNORM, OUT_F16>(pa, xs_sw, static_cast<__half*>(nullptr), redf, b == 0);
             reorder_x(m.H);
             __syncthreads();
             mark(12);
             const float dq_g = dequant_scale(Ly.lin[4].gamma, absmax), dq_u = dequant_scale(Ly.lin[5].gamma, absmax);
             pd_tiles(gu_s, geo.t_gu, T_gu, geo.mp_h, geo.vp_h, m.H >> 6, xs_s, tab_s, redi, tid, lane, warp,
                      [&](bool active, int tl, int r, int acc) {
-                         if (!active) return;
                          const int row = 16 * (b + (tl >> 1) * nb) + r;
-                         if (tl & 1) m.up[row] = __float2half_rn(__fmul_rn(static_cast<float>(acc), dq_u));
-                         else m.gate[row] = __float2half_rn(__fmul_rn(static_cast<float>(acc), dq_g));
+                         const __half hv = __float2half_rn(__fmul_rn(static_cast<float>(acc), (tl & 1) ? dq_u : dq_g));
+                         if (LL) {  // a gate row's thread and its up row's thread are 16 lanes apart: one word for both
+                             const uint32_t lo = __half_as_ushort(hv);
+                             const uint32_t hi = __shfl_down_sync(0xFFFFFFFFu, lo, 16);
+                             if (active && !(tl & 1)) ll_write(ll_gu + row, lo | (hi << 16), tag);
+                             return;
+                         }
+                         if (!active) return;
+                         if (tl & 1) m.up[row] = hv;
+                         else m.gate[row] = hv;
                      });
         }
         mark(13);
@@ -550,28 +650,48 @@ __global__ void __launch_bounds__(kPdThreads, 1) decode_persistent_kernel(const 
         issue_gu(l + 1);
         if (l + 1 < m.nlayers) issued[2] = l + 1;
         if (T_h > 0) {
-            PdProd pa{};
+            PdProdLl pa{};
             pa.x = m.gate;
             pa.x2 = m.up;
             pa.w_sub = norm_ptr(Ly.norm[3], 3);
             pa.eps = m.eps;
             pa.cols = m.inter;
+            pa.ll_x = ll_gu;
+            pa.tag = tag;
+            pa.limit = geo.wait_cycles;
+            pa.fail = &s_flag[0];
             if (!slab_ready(3, l)) return leave();
             consumed[3] = l;
             mark(15);
-            const float absmax = produce_x<IN_RELU2, OUT_F16>(pa, xs_sw, static_cast<__half*>(nullptr), redf, b == 0);
+            const float absmax = LL ? produce_x<IN_RELU2, OUT_F16, PdProdLl, LoadsGateUpLl>(pa, xs_sw, static_cast<__half*>(nullptr), redf, true)
+                                    : produce_x<IN_RELU2, OUT_F16>(pa, xs_sw, static_cast<__half*>(nullptr), redf, b == 0);
             reorder_x(m.inter);
             __syncthreads();
             mark(16);
             const float dq = dequant_scale(Ly.lin[6].gamma, absmax);
             pd_tiles(dn_s, geo.t_dn, T_h, geo.mp_i, geo.vp_i, m.inter >> 6, xs_s, tab_s, redi, tid, lane, warp,
                      [&](bool active, int tl, int r, int acc) {
-                         if (active) m.down[16 * (b + tl * nb) + r] = __float2half_rn(__fmul_rn(static_cast<float>(acc), dq));
+                         const int row = 16 * (b + tl * nb) + r;
+                         const __half hv = __float2half_rn(__fmul_rn(static_cast<float>(acc), dq));
+                         if (LL) ll_pair(ll_d, row, hv, active && (r & 1) == 0, tag);
+                         if (active && (!LL || l + 1 == m.nlayers)) m.down[row] = hv;  // the last layer's goes to the kernels that follow
                      });
         }
         mark(17);
         if (l + 1 < m.nlayers && !barrier()) return leave();
         mark(18);
+    }
+    if (LL) {
+        // the residual stream goes back to global memory for the kernels that follow; the last block to finish
+        // opens the next launch's range of tags
+        if (b == 0)
+            for (int q = tid; q < (m.H >> 3); q += kPdThreads) reinterpret_cast<uint4*>(m.xa)[q] = reinterpret_cast<const uint4*>(res_sm)[q];
+        __syncthreads();
+        if (tid == 0 && atomicAdd(m.sync + kSyncDone, 1u) + 1u == static_cast<unsigned>(nb)) {
+            atomicExch(m.sync + kSyncDone, 0u);
+            atomicAdd(m.sync + kSyncEpoch, 1u);
+        }
+        return;
     }
     // Arrive only: the kernel boundary orders the rest.  The last block to arrive publishes the count as the
     // next launch's generation.
@@ -623,6 +743,7 @@ size_t make_geom(const PdModel& m, int blocks, PdGeom& g) {
     g.off_dn = take(static_cast<size_t>(16) * g.t_dn * (g.mp_i + g.vp_i) * 4);
     const int G = m.nh / m.nkv;
     g.off_attn = take(std::max(attn_smem_bytes(G, m.hd), sizeof(float) * attn_merge_smem_floats(G, m.max_seq)));
+    g.off_res = take(sizeof(__half) * m.H);
     // The norm weights of a layer beside its slabs, if there is room: a producer then finds them without another
     // round trip to L2 after its reduction.
     int dev = 0, max_optin = 0;
@@ -638,12 +759,12 @@ size_t make_geom(const PdModel& m, int blocks, PdGeom& g) {
 
 unsigned long long* g_pd_trace = nullptr;  // spb_debug_set_decode_trace
 using PdKernel = void (*)(PdModel, PdGeom);
-PdKernel kernel_for(int G) {
+PdKernel kernel_for(int G, bool ll = false) {
     switch (G) {
-        case 1: return decode_persistent_kernel<1>;
-        case 2: return decode_persistent_kernel<2>;
-        case 4: return decode_persistent_kernel<4>;
-        case 8: return decode_persistent_kernel<8>;
+        case 1: return ll ? decode_persistent_kernel<1, true> : decode_persistent_kernel<1, false>;
+        case 2: return ll ? decode_persistent_kernel<2, true> : decode_persistent_kernel<2, false>;
+        case 4: return ll ? decode_persistent_kernel<4, true> : decode_persistent_kernel<4, false>;
+        case 8: return ll ? decode_persistent_kernel<8, true> : decode_persistent_kernel<8, false>;
         default: return nullptr;
     }
 }
@@ -687,12 +808,24 @@ bool decode_persistent_supported(const PdModel& m, const PdLinear* lin, const ch
     cudaDeviceGetAttribute(&max_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
     if (g.t_qkv > 8 || g.t_o > 8 || g.t_gu > 8 || g.t_dn > 8) return no("more than eight tiles per block and stage");
     if (smem + kPdStaticSmem > static_cast<size_t>(max_optin)) return no("weight slabs of a layer do not fit in shared memory");
+    if (m.barrier_free) {
+        // every block keeps the residual stream itself, so every block must own rows of every projection
+        const int nb = sm_count();
+        if ((qdim + 2 * kvdim) / 16 < nb || m.H / 16 < nb || m.inter / 16 < nb)
+            return no("barrier-free form: fewer row tiles than blocks in a projection");
+        if (!m.ll) return no("barrier-free form: no buffer of tagged words");
+    }
     return true;
+}
+
+size_t decode_persistent_ll_words(int H, int inter, int nh, int nkv, int hd) {
+    // q, k, v, attention output, o, gate|up, down: two halves per word (gate and up of a row share one)
+    return static_cast<size_t>(nh) * hd + static_cast<size_t>(nkv) * hd + static_cast<size_t>(H) + static_cast<size_t>(inter);
 }
 
 int decode_persistent_launch(const PdModel& m, long long wait_cycles, void* stream) {
     const char* name = "decode step (persistent)";
-    PdKernel kernel = kernel_for(m.nh / m.nkv);
+    PdKernel kernel = kernel_for(m.nh / m.nkv, m.barrier_free != 0);
     if (!kernel) return fail(SPB_E_UNSUPPORTED, "%s: group size", name);
     PdGeom g{};
     const int blocks = sm_count();

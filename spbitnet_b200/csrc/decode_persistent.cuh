@@ -34,9 +34,14 @@ struct PdModel {
     __half *q, *attn, *o, *gate, *up, *down;
     float* scratch;     // split-attention partials, attn_scratch_floats() floats
     unsigned* sync;     // kPdSyncWords + nkv words, zeroed once (barrier words and the per-KV-head chunk counts)
+    uint2* ll;          // decode_persistent_ll_words() tagged words, zeroed once: the stage outputs of the barrier-free form
+    int barrier_free;   // 1: stages hand their outputs over as tagged words that the consumers poll; 0: grid barriers
 };
 
 constexpr int kPdSyncWords = 64;  // words of PdModel::sync ahead of the per-KV-head counts
+
+// 64-bit words of PdModel::ll: q, new K row, new V row, attention output, o, (gate, up), down of one layer.
+size_t decode_persistent_ll_words(int H, int inter, int nh, int nkv, int hd);
 
 // Whether the kernel takes this shape on the current device (layout rules, shared memory, cooperative launch).
 // `why` receives a short reason when it does not.

@@ -73,6 +73,8 @@ struct spb_engine {
     PdModel pd{};
     PdLayer* d_pd_layers = nullptr;
     unsigned* d_pd_sync = nullptr;
+    uint2* d_pd_ll = nullptr;         // tagged words of the barrier-free form (decode mode 4)
+    size_t pd_ll_words = 0;
     int seq_len = 0;
     int timeouts_seen = 0;  // value of the library's bounded-wait counter when the engine last looked
 
@@ -267,7 +269,7 @@ void drop_graph(spb_engine* e) {
 // table goes to device memory here, outside any stream capture.
 int choose_persistent(spb_engine* e) {
     e->persistent = false;
-    if (e->decode_mode != 2) return SPB_OK;  // measured slower than the chain of kernels so far: only on request
+    if (e->decode_mode != 2 && e->decode_mode != 4) return SPB_OK;  // only on request
     const spb_model_config& c = e->cfg;
     const int qdim = c.num_attention_heads * c.head_dim, kvdim = c.num_key_value_heads * c.head_dim;
     PdModel m{};
@@ -279,6 +281,15 @@ int choose_persistent(spb_engine* e) {
     m.d_next = e->d_next; m.d_pos = e->d_pos;
     m.xa = e->x; m.xb = e->x2; m.q = e->q; m.attn = e->attn; m.o = e->o; m.gate = e->gate; m.up = e->up; m.down = e->down;
     m.scratch = e->attn_scratch;
+    m.barrier_free = e->decode_mode == 4 ? 1 : 0;
+    if (m.barrier_free) {
+        if (!e->d_pd_ll) {
+            e->pd_ll_words = decode_persistent_ll_words(m.H, m.inter, m.nh, m.nkv, m.hd);
+            SPB_CUDA(cudaMalloc(&e->d_pd_ll, sizeof(uint2) * e->pd_ll_words));
+            SPB_CUDA(cudaMemsetAsync(e->d_pd_ll, 0, sizeof(uint2) * e->pd_ll_words, e->stream));
+        }
+        m.ll = e->d_pd_ll;
+    }
     const char* why = "";
     std::vector<PdLayer> host(e->layers.size());
     const int want_rows[7] = {qdim, kvdim, kvdim, c.hidden_size, c.intermediate_size, c.intermediate_size, c.hidden_size};
@@ -300,8 +311,7 @@ int choose_persistent(spb_engine* e) {
         if (ok && !decode_persistent_supported(m, host[l].lin, &why)) ok = false;
     }
     if (!ok) {
-        if (e->decode_mode == 2) return fail(SPB_E_UNSUPPORTED, "engine: the persistent decode step does not take this model: %s", why);
-        return SPB_OK;
+        return fail(SPB_E_UNSUPPORTED, "engine: the persistent decode step does not take this model: %s", why);
     }
     // Both transfers go through the engine's own stream (it does not synchronise with the null stream) and are
     // waited for here: the kernel must not start before its tables are in place.
@@ -619,6 +629,7 @@ extern "C" void spb_engine_destroy(spb_engine* e) {
     if (e->pf_fork) cudaEventDestroy(e->pf_fork);
     if (e->d_pd_layers) cudaFree(e->d_pd_layers);
     if (e->d_pd_sync) cudaFree(e->d_pd_sync);
+    if (e->d_pd_ll) cudaFree(e->d_pd_ll);
     cudaFree(e->pool);
     cudaStreamDestroy(e->stream);
     delete e;
@@ -718,6 +729,8 @@ extern "C" int spb_engine_reset(spb_engine* e) {
     // barrier words of the persistent step: a launch that gave up at a barrier leaves them marked broken
     if (e->d_pd_sync)
         SPB_CUDA(cudaMemsetAsync(e->d_pd_sync, 0, sizeof(unsigned) * (kPdSyncWords + e->cfg.num_key_value_heads), e->stream));
+    // the tags of the barrier-free form start over with the launch count: no word of an earlier run may stay
+    if (e->d_pd_ll) SPB_CUDA(cudaMemsetAsync(e->d_pd_ll, 0, sizeof(uint2) * e->pd_ll_words, e->stream));
     SPB_CUDA(cudaStreamSynchronize(e->stream));
     e->seq_len = 0;
     return SPB_OK;
@@ -725,7 +738,7 @@ extern "C" int spb_engine_reset(spb_engine* e) {
 
 extern "C" int spb_engine_set_decode_mode(spb_engine* e, int mode) {
     if (!e) return fail(SPB_E_INVALID, "spb_engine_set_decode_mode: null handle");
-    if (mode < 0 || mode > 3) return fail(SPB_E_INVALID, "spb_engine_set_decode_mode: mode %d", mode);
+    if (mode < 0 || mode > 4) return fail(SPB_E_INVALID, "spb_engine_set_decode_mode: mode %d", mode);
     SPB_ON_ENGINE_DEVICE(e);
     if (mode != e->decode_mode) {
         SPB_CUDA(cudaStreamSynchronize(e->stream));

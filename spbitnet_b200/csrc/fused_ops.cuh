@@ -87,6 +87,11 @@ struct RopeScatter {
     void* kcache;  // [kv head][max_seq_len][head_dim] half
     void* vcache;
 };
+// Up to three BitLinears of the same width on prepared weights and one quantised activation, one launch
+// (gemv_prepared.cu).  With `rope` they are q, k, v: q and k rows are rotated for the position in *rope->d_pos, k and
+// v rows go to the cache rows of that position (out_half[1], out_half[2] are then not written).
+int prepared_bitlinear_q8_group(const void* const* prep, void* const* out_half, const float* gamma, const int* rows, int n,
+                                const int8_t* xq, const float* d_absmax, int cols, const RopeScatter* rope, void* stream);
 // activation = quantised rms_norm(w_norm) of x_out = x_in + [rms_norm(w_sub)](delta); block 0 writes x_out.
 // With `rope` the group must be q, k, v (see RopeScatter).
 int bitlinear_resnorm_group(const BitLinearGroup& g, const void* x_in, const void* delta, const float* w_sub,

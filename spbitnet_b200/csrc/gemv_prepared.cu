@@ -32,6 +32,7 @@
 // were slower everywhere: per block with a block-wide reduction per piece, 17.1 against 14.7 us at 28672 x 8192 as a
 // chain of launches; per warp with no block-wide step, 16.5 against 14.6 us (14.0 against 8.9 us in the graph of eight
 // branches): the fence and the round trip of the counting atomic drain the warp's prefetch at every hand-over.
+#include "fused_ops.cuh"
 #include "spb_common.cuh"
 
 namespace spb {
@@ -42,18 +43,28 @@ constexpr int kGpQuadBytes = 768;
 
 enum { GP_OUT_I32 = 0, GP_OUT_F32 = 1, GP_OUT_F16 = 2 };
 
-struct GpArgs {
+// One launch multiplies up to three matrices of the same width on one activation vector (q, k, v or gate, up): the
+// tiles of the matrices are numbered through.
+constexpr int kGpMaxMats = 3;
+struct GpMat {
     const uint8_t* prep;
-    const int8_t* x;
     void* y;
+    float gamma;
+    int rows;
+    int tile0;  // the matrix's first tile in the launch's numbering
+};
+struct GpArgs {
+    GpMat mat[kGpMaxMats];
+    int nmat;
+    const int8_t* x;
     int32_t* y_acc;
     const float* d_absmax;
-    float gamma;
     int out_mode;
-    int rows, cols;
-    int ntiles, nquads;
-    int ks, ks_log2;  // warps per tile (power of two <= 8); a block holds 8 / ks tiles
-    int qpw;          // quads per warp
+    int cols;
+    int ntiles, nquads;  // tiles of all matrices
+    int ks, ks_log2;     // warps per tile (power of two <= 8); a block holds 8 / ks tiles
+    int qpw;             // quads per warp
+    RopeScatter rope;    // d_pos set: the matrices are q, k, v; q and k rows are rotated, k and v rows go to the cache
 };
 
 // Eight bitmaps (two of four bits set each) -> eight index pairs {low index | high index << 2}.
@@ -163,7 +174,12 @@ __global__ void __launch_bounds__(kGpThreads, 3) gemv_prepared_kernel(const GpAr
     const int q_begin = live ? min(a.nquads, kq * a.qpw) : 0, q_end = live ? min(a.nquads, q_begin + a.qpw) : 0;
     const int g = lane >> 2, tig = lane & 3;
 
-    const uint8_t* tp = a.prep + (static_cast<size_t>(live ? tile : 0) * a.nquads) * kGpQuadBytes;
+    // which matrix a tile belongs to (selects, not an indexed read of the parameter array)
+    auto mat_of = [&](int t) { return (a.nmat > 2 && t >= a.mat[2].tile0) ? 2 : (a.nmat > 1 && t >= a.mat[1].tile0) ? 1 : 0; };
+    const int wm = mat_of(live ? tile : 0);
+    const uint8_t* wprep = wm == 2 ? a.mat[2].prep : wm == 1 ? a.mat[1].prep : a.mat[0].prep;
+    const int wtile0 = wm == 2 ? a.mat[2].tile0 : wm == 1 ? a.mat[1].tile0 : 0;
+    const uint8_t* tp = wprep + (static_cast<size_t>(live ? tile - wtile0 : 0) * a.nquads) * kGpQuadBytes;
     auto load_quad = [&](int q, uint4& m, uint2& s) {
         if (q < q_end) gp_load_quad(tp, q, lane, m, s);
     };
@@ -176,7 +192,9 @@ __global__ void __launch_bounds__(kGpThreads, 3) gemv_prepared_kernel(const GpAr
 
     grid_dep_wait();
     float absmax_early = 0.0f;  // asked for now: in the epilogue the load would be a trip to L2 on the critical path
+    int rope_pos = 0;
     if (a.out_mode != GP_OUT_I32) asm volatile("ld.global.f32 %0, [%1];" : "=f"(absmax_early) : "l"(a.d_absmax));
+    if (a.rope.d_pos) asm volatile("ld.global.s32 %0, [%1];" : "=r"(rope_pos) : "l"(a.rope.d_pos));
     grid_dep_launch();
     for (int q = tid; q < (a.cols >> 4); q += kGpThreads) {
         const uint4 xv = __ldg(reinterpret_cast<const uint4*>(a.x) + q);
@@ -196,21 +214,50 @@ __global__ void __launch_bounds__(kGpThreads, 3) gemv_prepared_kernel(const GpAr
         red[warp * 16 + g + 8] = c_hi;
     }
     __syncthreads();
-    if (tid < 16 * tiles_blk) {
+    // one thread per row of the block's tiles; whole warps take part (the rotation exchanges values between lanes)
+    if (tid < ((16 * tiles_blk + 31) & ~31)) {
         const int tl = tid >> 4, r = tid & 15;
-        const int row = (blockIdx.x * tiles_blk + tl) * 16 + r;
-        if (row < a.rows) {
-            int acc = 0;
+        const int t = blockIdx.x * tiles_blk + tl;
+        const bool in_tile = tl < tiles_blk && t < a.ntiles;
+        const int mi = mat_of(in_tile ? t : 0);
+        const int row = ((in_tile ? t : 0) - (mi == 2 ? a.mat[2].tile0 : mi == 1 ? a.mat[1].tile0 : 0)) * 16 + r;
+        const int mrows = mi == 2 ? a.mat[2].rows : mi == 1 ? a.mat[1].rows : a.mat[0].rows;
+        const bool valid = in_tile && row < mrows;
+        void* y = mi == 2 ? a.mat[2].y : mi == 1 ? a.mat[1].y : a.mat[0].y;
+        int acc = 0;
+        if (in_tile)
             for (int k = 0; k < a.ks; ++k) acc += red[((tl << a.ks_log2) + k) * 16 + r];
-            if (a.out_mode == GP_OUT_I32) {
-                static_cast<int32_t*>(a.y)[row] = acc;
-            } else {
-                const float f = __fmul_rn(static_cast<float>(acc), dequant_scale(a.gamma, absmax_early));
-                if (a.out_mode == GP_OUT_F32) {
-                    static_cast<float*>(a.y)[row] = f;
+        if (a.out_mode == GP_OUT_I32) {
+            if (valid) static_cast<int32_t*>(y)[row] = acc;
+        } else {
+            const float gamma = mi == 2 ? a.mat[2].gamma : mi == 1 ? a.mat[1].gamma : a.mat[0].gamma;
+            const float f = __fmul_rn(static_cast<float>(acc), dequant_scale(gamma, absmax_early));
+            if (a.out_mode == GP_OUT_F32) {
+                if (valid) {
+                    static_cast<float*>(y)[row] = f;
                     if (a.y_acc) a.y_acc[row] = acc;
-                } else {
-                    static_cast<__half*>(a.y)[row] = __float2half_rn(f);
+                }
+            } else if (!a.rope.d_pos) {
+                if (valid) static_cast<__half*>(y)[row] = __float2half_rn(f);
+            } else {
+                // rows 2 i, 2 i + 1 of a head are a rotation pair and neighbours in the warp (head_dim is even, tiles
+                // start at multiples of 16 rows)
+                const __half hv = __float2half_rn(f);
+                const float v = __half2float(hv);
+                const float pv = __shfl_xor_sync(0xFFFFFFFFu, v, 1);
+                const int hd = a.rope.head_dim;
+                const int head = row / hd, d = row - head * hd;
+                __half out = hv;
+                if (mi != 2) {
+                    __half y0, y1;
+                    rope_rotate((r & 1) ? pv : v, (r & 1) ? v : pv, rope_pos, d >> 1, hd, a.rope.theta, y0, y1);
+                    out = (r & 1) ? y1 : y0;
+                }
+                if (valid) {
+                    if (mi == 0)
+                        static_cast<__half*>(y)[row] = out;
+                    else
+                        static_cast<__half*>(mi == 1 ? a.rope.kcache : a.rope.vcache)[(static_cast<size_t>(head) * a.rope.max_seq_len + rope_pos) * hd + d] = out;
                 }
             }
         }
@@ -220,23 +267,47 @@ __global__ void __launch_bounds__(kGpThreads, 3) gemv_prepared_kernel(const GpAr
 static bool gp_shape_ok(int rows, int cols) { return rows > 0 && cols > 0 && cols % 256 == 0 && cols <= 65536; }
 static size_t gp_weight_bytes(int rows, int cols) { return static_cast<size_t>((rows + 15) / 16) * (cols / 256) * kGpQuadBytes; }
 
-static int gp_launch(const char* name, const void* prep, const int8_t* x, void* y, int32_t* y_acc, const float* d_absmax,
-                     float gamma, int out_mode, int rows, int cols, void* stream) {
-    if (rows < 0 || cols < 0) return fail(SPB_E_INVALID, "%s: negative size", name);
-    if (rows == 0 || cols == 0) return SPB_OK;
-    if (!prep || !x || !y) return fail(SPB_E_INVALID, "%s: null pointer", name);
-    if (out_mode != GP_OUT_I32 && !d_absmax) return fail(SPB_E_INVALID, "%s: d_absmax is null", name);
-    if (!gp_shape_ok(rows, cols)) return fail(SPB_E_UNSUPPORTED, "%s: cols=%d is not a multiple of 256 up to 65536", name, cols);
-    if ((reinterpret_cast<uintptr_t>(prep) | reinterpret_cast<uintptr_t>(x)) & 15u)
-        return fail(SPB_E_INVALID, "%s: prepared weights and x must be 16-byte aligned", name);
+struct GpMatDesc {
+    const void* prep;
+    void* y;
+    float gamma;
+    int rows;
+};
+
+static int gp_launch(const char* name, const GpMatDesc* mats, int nmat, const int8_t* x, int32_t* y_acc, const float* d_absmax,
+                     int out_mode, int cols, const RopeScatter* rope, void* stream) {
+    if (nmat < 1 || nmat > kGpMaxMats) return fail(SPB_E_INVALID, "%s: %d matrices", name, nmat);
+    if (cols < 0) return fail(SPB_E_INVALID, "%s: negative size", name);
     GpArgs a{};
-    a.prep = static_cast<const uint8_t*>(prep);
-    a.x = x; a.y = y; a.y_acc = y_acc; a.d_absmax = d_absmax; a.gamma = gamma; a.out_mode = out_mode;
-    a.rows = rows; a.cols = cols;
-    a.ntiles = (rows + 15) / 16;
+    int tiles = 0;
+    for (int i = 0; i < nmat; ++i) {
+        if (mats[i].rows < 0) return fail(SPB_E_INVALID, "%s: negative size", name);
+        if (mats[i].rows == 0 || cols == 0) {
+            if (nmat == 1) return SPB_OK;
+            return fail(SPB_E_INVALID, "%s: an empty matrix in a group", name);
+        }
+        if (!mats[i].prep || !mats[i].y) return fail(SPB_E_INVALID, "%s: null pointer", name);
+        if (reinterpret_cast<uintptr_t>(mats[i].prep) & 15u) return fail(SPB_E_INVALID, "%s: prepared weights must be 16-byte aligned", name);
+        a.mat[i] = GpMat{static_cast<const uint8_t*>(mats[i].prep), mats[i].y, mats[i].gamma, mats[i].rows, tiles};
+        tiles += (mats[i].rows + 15) / 16;
+    }
+    if (!x) return fail(SPB_E_INVALID, "%s: null pointer", name);
+    if (out_mode != GP_OUT_I32 && !d_absmax) return fail(SPB_E_INVALID, "%s: d_absmax is null", name);
+    if (!gp_shape_ok(mats[0].rows, cols)) return fail(SPB_E_UNSUPPORTED, "%s: cols=%d is not a multiple of 256 up to 65536", name, cols);
+    if (reinterpret_cast<uintptr_t>(x) & 15u) return fail(SPB_E_INVALID, "%s: x must be 16-byte aligned", name);
+    if (rope) {
+        if (nmat != 3 || out_mode != GP_OUT_F16 || rope->head_dim < 2 || rope->head_dim % 2 || mats[0].rows % rope->head_dim ||
+            mats[1].rows % rope->head_dim || mats[1].rows != mats[2].rows || !rope->d_pos || !rope->kcache || !rope->vcache)
+            return fail(SPB_E_INVALID, "%s: rotation wants q, k, v with whole heads and half outputs", name);
+        a.rope = *rope;
+    }
+    a.nmat = nmat;
+    a.x = x; a.y_acc = y_acc; a.d_absmax = d_absmax; a.out_mode = out_mode;
+    a.cols = cols;
+    a.ntiles = tiles;
     a.nquads = cols / 256;
     // Warps per tile: a warp wants a run of quads (its fixed cost is the three-quad prefetch and the final
-    // reduction), but the matrix has to give every SM its three blocks.
+    // reduction), but the launch has to give every SM its three blocks.
     a.ks = 1;
     while (a.ks < 8 && a.ntiles * a.ks < 24 * sm_count() && a.nquads / (2 * a.ks) >= 2) a.ks <<= 1;
     a.ks_log2 = a.ks == 8 ? 3 : a.ks == 4 ? 2 : a.ks == 2 ? 1 : 0;
@@ -248,10 +319,30 @@ static int gp_launch(const char* name, const void* prep, const int8_t* x, void* 
     return launch(name, gemv_prepared_kernel, dim3(blocks), dim3(kGpThreads), smem, stream, a);
 }
 
+static int gp_launch(const char* name, const void* prep, const int8_t* x, void* y, int32_t* y_acc, const float* d_absmax,
+                     float gamma, int out_mode, int rows, int cols, void* stream) {
+    if (rows < 0 || cols < 0) return fail(SPB_E_INVALID, "%s: negative size", name);
+    if (rows == 0 || cols == 0) return SPB_OK;
+    if (!prep || !x || !y) return fail(SPB_E_INVALID, "%s: null pointer", name);
+    const GpMatDesc m{prep, y, gamma, rows};
+    return gp_launch(name, &m, 1, x, y_acc, d_absmax, out_mode, cols, nullptr, stream);
+}
+
 // engine-internal: BitLinear on prepared weights, quantised activation, scaled half output
 int prepared_bitlinear_q8(const void* prep, const int8_t* xq, void* out_half, const float* d_absmax, float gamma, int rows,
                           int cols, void* stream) {
     return gp_launch("prepared_bitlinear_q8", prep, xq, out_half, nullptr, d_absmax, gamma, GP_OUT_F16, rows, cols, stream);
+}
+
+// engine-internal: up to three BitLinears of the same width on one quantised activation in one launch; with `rope`
+// they are q, k, v: q and k rows are rotated for the position in *rope->d_pos, k and v rows go to the cache rows of
+// that position (out[1], out[2] are not written)
+int prepared_bitlinear_q8_group(const void* const* prep, void* const* out_half, const float* gamma, const int* rows, int n,
+                                const int8_t* xq, const float* d_absmax, int cols, const RopeScatter* rope, void* stream) {
+    GpMatDesc m[kGpMaxMats];
+    if (n < 1 || n > kGpMaxMats) return fail(SPB_E_INVALID, "prepared_bitlinear_q8_group: %d matrices", n);
+    for (int i = 0; i < n; ++i) m[i] = GpMatDesc{prep[i], out_half[i], gamma[i], rows[i]};
+    return gp_launch("prepared_bitlinear_q8_group", m, n, xq, nullptr, d_absmax, GP_OUT_F16, cols, rope, stream);
 }
 
 }  // namespace spb

@@ -33,6 +33,16 @@ struct ProducerArgs {
     int cols;
 };
 
+// Where a normalising producer gets its activation chunks (eight halves, chunk q of the vector) from.  The GEMV
+// kernels read plain vectors in global memory with L2 loads; the persistent decode kernel supplies its own policy
+// (vectors that other blocks of the same grid publish element by element).
+struct GlobalLoads {
+    template <class Args>
+    static __device__ __forceinline__ uint4 x(const Args& a, int q) { return __ldcg(static_cast<const uint4*>(a.x) + q); }
+    template <class Args>
+    static __device__ __forceinline__ uint4 x2(const Args& a, int q) { return __ldcg(static_cast<const uint4*>(a.x2) + q); }
+};
+
 // ---- activation producers ----------------------------------------------------------------
 // Four norm weights.  A plain (generic) load: the GEMV kernels pass global memory, the persistent decode kernel
 // a copy it keeps in shared memory.
@@ -156,7 +166,7 @@ __device__ __noinline__ float produce_x_loops(const Args& a, uint4* xs, __half* 
 
 // Fills xs (swizzled int8) and returns the absmax that belongs to it.  hbuf: cols halfs of
 // scratch (only touched by the normalising producers).
-template <int IN, int OUT, class Args>
+template <int IN, int OUT, class Args, class Loads = GlobalLoads>
 __device__ __forceinline__ float produce_x(const Args& a, uint4* xs, __half* hbuf, float* red,
                                            bool publisher) {
     const int tid = threadIdx.x;
@@ -177,7 +187,7 @@ __device__ __forceinline__ float produce_x(const Args& a, uint4* xs, __half* hbu
         } else {
             float mx = 0.0f;
             for (int q = tid; q < 2 * nchunks; q += kProdThreads) {
-                const uint4 t = __ldcg(xg + q);
+                const uint4 t = Loads::x(a, q);
                 const uint32_t w[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
@@ -189,7 +199,7 @@ __device__ __forceinline__ float produce_x(const Args& a, uint4* xs, __half* hbu
         }
         const float scale = quant_scale(absmax);
         for (int q = tid; q < nchunks; q += kProdThreads) {
-            const uint4 lo = __ldcg(xg + 2 * q), hi = __ldcg(xg + 2 * q + 1);
+            const uint4 lo = Loads::x(a, 2 * q), hi = Loads::x(a, 2 * q + 1);
             const uint32_t hw[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
             uint32_t out[4];
 #pragma unroll
@@ -239,8 +249,8 @@ __device__ __forceinline__ float produce_x(const Args& a, uint4* xs, __half* hbu
                 xv[k] = make_uint4(0, 0, 0, 0);
                 dv[k] = make_uint4(0, 0, 0, 0);
                 if (q < nq) {
-                    xv[k] = __ldcg(x_in + q);
-                    if (delta) dv[k] = __ldcg(delta + q);
+                    xv[k] = Loads::x(a, q);
+                    if (delta) dv[k] = Loads::x2(a, q);
                 }
             }
             float sub_scale = 1.0f;
@@ -336,8 +346,8 @@ __device__ __forceinline__ float produce_x(const Args& a, uint4* xs, __half* hbu
                 gv[k] = make_uint4(0, 0, 0, 0);
                 uv[k] = make_uint4(0, 0, 0, 0);
                 if (q < nq) {
-                    gv[k] = __ldcg(gate + q);
-                    uv[k] = __ldcg(up + q);
+                    gv[k] = Loads::x(a, q);
+                    uv[k] = Loads::x2(a, q);
                 }
             }
             auto relu2 = [](float gq, float uq) {

@@ -180,23 +180,32 @@ struct LArgs {
     unsigned long long timeout_ns;
 };
 
-__global__ void __launch_bounds__(256) exchange_ll_kernel(const LArgs a) {
-    grid_dep_launch();
-    grid_dep_wait();  // the slice was written by the predecessor
-    const unsigned seq = *reinterpret_cast<volatile unsigned*>(a.seqno) + 1u;
-    const uint32_t tid = blockIdx.x * blockDim.x + threadIdx.x, nthreads = gridDim.x * blockDim.x;
+// Send and receive of one small-message exchange by `nthreads` threads (this one is number `tid`).  A thread keeps
+// eight words in flight, both ways: one word at a time, every poll would be a dependent trip to L2.
+__device__ __forceinline__ void exchange_ll_run(const LArgs& a, uint32_t tid, uint32_t nthreads, unsigned seq) {
+    constexpr int kU = 8;
     // send: this rank's words, to its own gathered array directly and to every peer's staging area with the number
     for (int s = 0; s < a.nseg; ++s) {
         const LSeg& g = a.seg[s];
         const uint32_t wpr = g.len[a.rank] >> 2, words = wpr * static_cast<uint32_t>(a.rows);
-        for (uint32_t j = tid; j < words; j += nthreads) {
-            const uint32_t row = a.rows == 1 ? 0u : j / wpr, c = j - row * wpr;
-            const uint32_t v = reinterpret_cast<const uint32_t*>(g.src)[j];
-            *reinterpret_cast<uint32_t*>(a.peer[a.rank] + g.dst_region + static_cast<size_t>(row) * g.dst_pitch + g.off[a.rank] + 4u * c) = v;
-            const size_t slot = static_cast<size_t>(g.ll_off) + static_cast<size_t>(a.rank) * g.ll_stride + 8u * static_cast<size_t>(j);
-            for (int p = 0; p < a.world; ++p)
-                if (p != a.rank)
-                    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(a.peer[p] + slot), "r"(v), "r"(seq) : "memory");
+        for (uint32_t j0 = tid; j0 < words; j0 += kU * nthreads) {
+            uint32_t v[kU];
+#pragma unroll
+            for (int u = 0; u < kU; ++u) {
+                const uint32_t j = j0 + u * nthreads;
+                v[u] = j < words ? reinterpret_cast<const uint32_t*>(g.src)[j] : 0u;
+            }
+#pragma unroll
+            for (int u = 0; u < kU; ++u) {
+                const uint32_t j = j0 + u * nthreads;
+                if (j >= words) continue;
+                const uint32_t row = a.rows == 1 ? 0u : j / wpr, c = j - row * wpr;
+                *reinterpret_cast<uint32_t*>(a.peer[a.rank] + g.dst_region + static_cast<size_t>(row) * g.dst_pitch + g.off[a.rank] + 4u * c) = v[u];
+                const size_t slot = static_cast<size_t>(g.ll_off) + static_cast<size_t>(a.rank) * g.ll_stride + 8u * static_cast<size_t>(j);
+                for (int p = 0; p < a.world; ++p)
+                    if (p != a.rank)
+                        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(a.peer[p] + slot), "r"(v[u]), "r"(seq) : "memory");
+            }
         }
     }
     // receive: every peer's words out of the local staging area
@@ -208,13 +217,27 @@ __global__ void __launch_bounds__(256) exchange_ll_kernel(const LArgs a) {
             if (p == a.rank) continue;
             const uint32_t wpr = g.len[p] >> 2, words = wpr * static_cast<uint32_t>(a.rows);
             const uint8_t* stage = a.peer[a.rank] + g.ll_off + static_cast<size_t>(p) * g.ll_stride;
-            for (uint32_t j = tid; j < words && alive; j += nthreads) {
-                uint32_t v, n;
+            for (uint32_t j0 = tid; j0 < words && alive; j0 += kU * nthreads) {
+                unsigned pending = 0;
+#pragma unroll
+                for (int u = 0; u < kU; ++u)
+                    if (j0 + u * nthreads < words) pending |= 1u << u;
                 unsigned spins = 0;
-                for (;;) {
-                    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v), "=r"(n) : "l"(stage + 8u * static_cast<size_t>(j)) : "memory");
-                    if (n == seq) break;
-                    if ((++spins & 255u) == 0) {
+                while (pending) {
+                    uint32_t v[kU], n[kU];
+#pragma unroll
+                    for (int u = 0; u < kU; ++u)
+                        if ((pending >> u) & 1u)
+                            asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v[u]), "=r"(n[u]) : "l"(stage + 8u * static_cast<size_t>(j0 + u * nthreads)) : "memory");
+#pragma unroll
+                    for (int u = 0; u < kU; ++u)
+                        if (((pending >> u) & 1u) && n[u] == seq) {
+                            const uint32_t j = j0 + u * nthreads;
+                            const uint32_t row = a.rows == 1 ? 0u : j / wpr, c = j - row * wpr;
+                            *reinterpret_cast<uint32_t*>(a.peer[a.rank] + g.dst_region + static_cast<size_t>(row) * g.dst_pitch + g.off[p] + 4u * c) = v[u];
+                            pending &= ~(1u << u);
+                        }
+                    if (pending && (++spins & 255u) == 0) {
                         const unsigned long long now = globaltimer_ns();
                         if (t0 == 0) t0 = now;
                         if (now - t0 > a.timeout_ns || *reinterpret_cast<volatile int*>(a.broken) != 0) {
@@ -225,12 +248,16 @@ __global__ void __launch_bounds__(256) exchange_ll_kernel(const LArgs a) {
                         }
                     }
                 }
-                if (!alive) break;
-                const uint32_t row = a.rows == 1 ? 0u : j / wpr, c = j - row * wpr;
-                *reinterpret_cast<uint32_t*>(a.peer[a.rank] + g.dst_region + static_cast<size_t>(row) * g.dst_pitch + g.off[p] + 4u * c) = v;
             }
         }
     }
+}
+
+__global__ void __launch_bounds__(256) exchange_ll_kernel(const LArgs a) {
+    grid_dep_launch();
+    grid_dep_wait();  // the slice was written by the predecessor
+    const unsigned seq = *reinterpret_cast<volatile unsigned*>(a.seqno) + 1u;
+    exchange_ll_run(a, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x, seq);
     // the last block to finish advances the sequence number (every block has read it by then)
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -240,6 +267,17 @@ __global__ void __launch_bounds__(256) exchange_ll_kernel(const LArgs a) {
             *a.seqno = seq;
         }
     }
+}
+
+// The same exchange as the first thing a single-block consumer kernel does (a.world > 1): the launch of its own
+// disappears, and so does the kernel boundary between the arrival of the data and its use.  The gathered vector is
+// in local memory, written by this block, when the function returns.
+__device__ __forceinline__ void exchange_ll_in_block(const LArgs& a) {
+    if (a.world <= 1) return;
+    const unsigned seq = *reinterpret_cast<volatile unsigned*>(a.seqno) + 1u;
+    exchange_ll_run(a, threadIdx.x, blockDim.x, seq);
+    __syncthreads();
+    if (threadIdx.x == 0) *a.seqno = seq;
 }
 
 // token of sequence b: prompt[pos * batch + b] while pos < n_prompt, else next[b]; row copy of the embedding
@@ -448,11 +486,12 @@ __device__ __forceinline__ void quantise_store8(const float* v, float qs, int8_t
 // xn = rms_norm(w)(x) in half (to xn_out when given), absmax, int8.  n % 8 == 0, n <= 8192: one run of eight
 // elements per thread, everything in registers.
 __global__ void __launch_bounds__(kWideThreads) wide_residual_norm_quant_kernel(
-    const __half* __restrict__ delta, const float* __restrict__ sub_w, __half* __restrict__ x, const float* __restrict__ w,
-    __half* __restrict__ xn_out, int8_t* __restrict__ xq, float* __restrict__ d_absmax, int n, float eps) {
+    const __half* delta, const float* __restrict__ sub_w, __half* __restrict__ x, const float* __restrict__ w,
+    __half* __restrict__ xn_out, int8_t* __restrict__ xq, float* __restrict__ d_absmax, int n, float eps, const LArgs xin) {
     __shared__ float sh[32];
     grid_dep_launch();
     grid_dep_wait();
+    exchange_ll_in_block(xin);  // delta, gathered from the ranks' slices
     const size_t off = static_cast<size_t>(blockIdx.x) * n;
     const int runs = n >> 3;
     constexpr int kRuns = 1;
@@ -534,8 +573,8 @@ __global__ void __launch_bounds__(kWideThreads) wide_residual_norm_quant_kernel(
 // relu2_norm_quant for one vector per block: m = relu(gate)^2 * up in fp32, h = half(m * rsqrt(mean m^2 + eps) * sub_w)
 // (or half(m) without sub_w), absmax, int8.
 __global__ void __launch_bounds__(kWideThreads) wide_relu2_norm_quant_kernel(
-    const __half* __restrict__ gate, const __half* __restrict__ up, const float* __restrict__ sub_w, int8_t* __restrict__ hq,
-    float* __restrict__ d_absmax, int n, float eps) {
+    const __half* gate, const __half* up, const float* __restrict__ sub_w, int8_t* __restrict__ hq,
+    float* __restrict__ d_absmax, int n, float eps, const LArgs xin) {
     __shared__ float sh[32];
     grid_dep_launch();
     const int runs = n >> 3;
@@ -548,6 +587,7 @@ __global__ void __launch_bounds__(kWideThreads) wide_relu2_norm_quant_kernel(
             if (r < runs) asm volatile("prefetch.global.L1 [%0];" ::"l"(sub_w + 8 * r));
         }
     grid_dep_wait();
+    exchange_ll_in_block(xin);  // gate and up, gathered from the ranks' slices
     const size_t off = static_cast<size_t>(blockIdx.x) * n;
     float v[kWideRuns][8];  // the products stay in registers
     float s = 0.0f;
@@ -594,11 +634,12 @@ __global__ void __launch_bounds__(kWideThreads) wide_relu2_norm_quant_kernel(
 }
 
 // absmax_quantize_gpu for one vector per block.
-__global__ void __launch_bounds__(kWideThreads) wide_absmax_quantize_kernel(const __half* __restrict__ in, int8_t* __restrict__ out,
-                                                                            float* __restrict__ d_absmax, int n) {
+__global__ void __launch_bounds__(kWideThreads) wide_absmax_quantize_kernel(const __half* in, int8_t* __restrict__ out,
+                                                                            float* __restrict__ d_absmax, int n, const LArgs xin) {
     __shared__ float sh[32];
     grid_dep_launch();
     grid_dep_wait();
+    exchange_ll_in_block(xin);
     const size_t off = static_cast<size_t>(blockIdx.x) * n;
     const int runs = n >> 3;
     float v[kWideRuns][8];
@@ -722,6 +763,7 @@ struct spb_shard_engine {
     size_t off_flags = 0, off_attn = 0, off_o = 0, off_gate = 0, off_up = 0, off_down = 0, off_amax = 0;
     size_t ll_off[X_KINDS] = {};   // staging areas of the small-message exchange
     bool ll_ok[X_KINDS] = {};      // the kind's slices are small enough for it
+    bool fold_exchange = true;     // wide single-sequence step: the consumer kernel of a vector performs its exchange
     int ident[kMaxWorld + 1] = {0, 1, 2, 3, 4, 5, 6, 7, 8};
     int* status = nullptr;  // pinned, mapped
     unsigned long long timeout_ns = 5000000000ull;
@@ -734,6 +776,36 @@ struct spb_shard_engine {
 namespace {
 
 // bounds[s]: the split table of segment s (world + 1 entries, in units of unit_bytes[s] bytes per row)
+// Arguments of the small-message exchange of `kind` (e->ll_ok[kind]).
+void make_ll_args(spb_shard_engine* e, int kind, const XSeg* segs, int nseg, const int* const* bounds, const int* unit_bytes,
+                  LArgs& l, size_t* words_out) {
+    for (int p = 0; p < e->world; ++p) l.peer[p] = e->peer[p];
+    size_t words = 0, ll_at = e->ll_off[kind];
+    for (int s = 0; s < nseg; ++s) {
+        LSeg& g = l.seg[s];
+        g.src = segs[s].src;
+        g.dst_pitch = segs[s].dst_pitch;
+        g.dst_region = segs[s].dst_off - static_cast<uint32_t>(bounds[s][e->rank]) * unit_bytes[s];
+        uint32_t maxlen = 0;
+        for (int p = 0; p < e->world; ++p) {
+            g.off[p] = static_cast<uint32_t>(bounds[s][p]) * unit_bytes[s];
+            g.len[p] = static_cast<uint32_t>(bounds[s][p + 1] - bounds[s][p]) * unit_bytes[s];
+            maxlen = std::max(maxlen, g.len[p]);
+            words += static_cast<size_t>(g.len[p] / 4) * e->batch;
+        }
+        g.ll_off = static_cast<uint32_t>(ll_at);
+        g.ll_stride = 2 * maxlen * e->batch;
+        ll_at += static_cast<size_t>(g.ll_stride) * e->world;
+    }
+    l.nseg = nseg; l.rows = e->batch; l.world = e->world; l.rank = e->rank;
+    l.seqno = e->counters + 2 * kind;
+    l.done = e->counters + 2 * kind + 1;
+    l.status = e->status;
+    l.broken = reinterpret_cast<int*>(e->counters + 2 * X_KINDS);
+    l.timeout_ns = e->timeout_ns;
+    if (words_out) *words_out = words;
+}
+
 int exchange(spb_shard_engine* e, int kind, const XSeg* segs, int nseg, const int* const* bounds, const int* unit_bytes) {
     if (e->world == 1) {  // nothing to exchange: the "slice" is the whole vector; copy it into place
         for (int s = 0; s < nseg; ++s)
@@ -743,30 +815,8 @@ int exchange(spb_shard_engine* e, int kind, const XSeg* segs, int nseg, const in
     }
     if (e->ll_ok[kind]) {  // small slices: data and sequence number in one store, no fence
         LArgs l{};
-        for (int p = 0; p < e->world; ++p) l.peer[p] = e->peer[p];
-        size_t words = 0, ll_at = e->ll_off[kind];
-        for (int s = 0; s < nseg; ++s) {
-            LSeg& g = l.seg[s];
-            g.src = segs[s].src;
-            g.dst_pitch = segs[s].dst_pitch;
-            g.dst_region = segs[s].dst_off - static_cast<uint32_t>(bounds[s][e->rank]) * unit_bytes[s];
-            uint32_t maxlen = 0;
-            for (int p = 0; p < e->world; ++p) {
-                g.off[p] = static_cast<uint32_t>(bounds[s][p]) * unit_bytes[s];
-                g.len[p] = static_cast<uint32_t>(bounds[s][p + 1] - bounds[s][p]) * unit_bytes[s];
-                maxlen = std::max(maxlen, g.len[p]);
-                words += static_cast<size_t>(g.len[p] / 4) * e->batch;
-            }
-            g.ll_off = static_cast<uint32_t>(ll_at);
-            g.ll_stride = 2 * maxlen * e->batch;
-            ll_at += static_cast<size_t>(g.ll_stride) * e->world;
-        }
-        l.nseg = nseg; l.rows = e->batch; l.world = e->world; l.rank = e->rank;
-        l.seqno = e->counters + 2 * kind;
-        l.done = e->counters + 2 * kind + 1;
-        l.status = e->status;
-        l.broken = reinterpret_cast<int*>(e->counters + 2 * X_KINDS);
-        l.timeout_ns = e->timeout_ns;
+        size_t words = 0;
+        make_ll_args(e, kind, segs, nseg, bounds, unit_bytes, l, &words);
         const int blocks = static_cast<int>(std::max<size_t>(1, std::min<size_t>(32, words / 1024)));
         return launch("exchange_ll", exchange_ll_kernel, dim3(blocks), dim3(256), 0, e->stream, l);
     }
@@ -814,6 +864,29 @@ int enqueue_step(spb_shard_engine* e, bool record) {
     float* amax_full = reinterpret_cast<float*>(e->xbuf + e->off_amax);
     float* am0 = e->absmax;
     float* am1 = e->absmax + B;
+    // One rank: a "slice" is the whole vector, so the producing kernels write where the consumers read and there
+    // is nothing to exchange.
+    const bool alone = e->world == 1;
+    // Several ranks, wide single-sequence step: every gathered vector has one consumer, a single-block vector kernel;
+    // it sends this rank's slice and collects the peers' itself (small-message form) instead of a launch doing that.
+    LArgs pend{};  // the exchange the next vector kernel performs (world == 0: none)
+    auto exchange_or_defer = [&](int kind, const XSeg* sg, int nseg, const int* const* bd, const int* ub) -> int {
+        if (e->fold_exchange && e->wide && B == 1 && e->ll_ok[kind]) {
+            make_ll_args(e, kind, sg, nseg, bd, ub, pend, nullptr);
+            return SPB_OK;
+        }
+        return exchange(e, kind, sg, nseg, bd, ub);
+    };
+    auto take_pending = [&]() {
+        const LArgs x = pend;
+        pend = LArgs{};
+        return x;
+    };
+    __half* attn_out = alone ? attn_full : e->attn;
+    __half* o_out = alone ? o_full : e->o;
+    __half* gate_out = alone ? gate_full : e->gate;
+    __half* up_out = alone ? up_full : e->up;
+    __half* down_out = alone ? down_full : e->down;
     if ((rc = launch("shard_embed", shard_embed_kernel, dim3(std::max(1, H / 8 / 256), B), dim3(256), 0, s, e->embed, cur, H,
                      static_cast<const int*>(e->d_prompt), e->n_prompt_in_graph, static_cast<const int*>(e->d_next),
                      static_cast<const int*>(e->d_pos), B))) return rc;
@@ -841,6 +914,24 @@ int enqueue_step(spb_shard_engine* e, bool record) {
         for (int i = 1; i < n; ++i) SPB_CUDA(cudaStreamWaitEvent(e->stream, e->join[i - 1], 0));
         return SPB_OK;
     };
+    // ... unless every matrix of the group has a prepared copy: then the group is one launch (no fork and join, whose
+    // graph edges are full dependencies where a stream-ordered launch overlaps its predecessor's tail), and q, k, v
+    // rotate and scatter their rows in its epilogue.
+    auto all_prepared = [&](const Linear* const* L, int n) {
+        for (int i = 0; i < n; ++i)
+            if (!L[i]->prep) return false;
+        return true;
+    };
+    auto linear_group_prepared = [&](const Linear* const* L, __half* const* out, int n, const float* am, const RopeScatter* rope) {
+        const void* prep[3];
+        void* outs[3];
+        float gamma[3];
+        int rows[3];
+        for (int i = 0; i < n; ++i) {
+            prep[i] = L[i]->prep; outs[i] = out[i]; gamma[i] = L[i]->gamma; rows[i] = L[i]->rows;
+        }
+        return prepared_bitlinear_q8_group(prep, outs, gamma, rows, n, e->xq, am, L[0]->cols, rope, s);
+    };
     // Wide models (hidden >= 4096): a matrix is tens of megabytes and its GEMV runs for tens of microseconds, so
     // throughput decides, not launch latency: the vector op runs once in a kernel of its own and every matrix goes
     // through the tensor-core GEMV, instead of the SIMT kernels that recompute the vector op in every block.
@@ -849,7 +940,7 @@ int enqueue_step(spb_shard_engine* e, bool record) {
     auto res_norm_quant = [&](const __half* delta, const float* sub_w, __half* x, const float* w, __half* xn_out, float* am) {
         if (e->wide)
             return launch("wide_residual_norm_quant", wide_residual_norm_quant_kernel, dim3(B), dim3(kWideThreads), 0, s, delta, sub_w,
-                          x, w, xn_out, e->xq, am, H, c.rms_norm_eps);
+                          x, w, xn_out, e->xq, am, H, c.rms_norm_eps, take_pending());
         return residual_norm_quant(delta, sub_w, x, w, xn_out, e->xq, am, H, c.rms_norm_eps, s, B);
     };
     for (int l = 0; l < c.num_hidden_layers; ++l) {
@@ -859,12 +950,13 @@ int enqueue_step(spb_shard_engine* e, bool record) {
         const Linear* g3[3] = {&L.lin[0], &L.lin[1], &L.lin[2]};
         __half* o3[3] = {e->q, e->k, e->v};
         const Linear* g1o[1] = {&L.lin[3]};
-        __half* o1o[1] = {e->o};
+        __half* o1o[1] = {o_out};
         const Linear* g2[2] = {&L.lin[4], &L.lin[5]};
-        __half* o2[2] = {e->gate, e->up};
+        __half* o2[2] = {gate_out, up_out};
         const Linear* g1d[1] = {&L.lin[6]};
-        __half* o1d[1] = {e->down};
+        __half* o1d[1] = {down_out};
         const __half* delta = l == 0 ? nullptr : down_full;
+        bool rope_done = false;  // q, k, v rotated and scattered by the launch that computed them
         // ---- q / k / v on this rank's heads ----
         if (B == 1 && fused1) {
             if ((rc = bitlinear_resnorm_group(make_group(g3, o3, 3), cur, delta, nullptr, L.norm[0], other, c.rms_norm_eps, s))) return rc;
@@ -872,7 +964,13 @@ int enqueue_step(spb_shard_engine* e, bool record) {
         } else {
             if ((rc = res_norm_quant(delta, nullptr, cur, L.norm[0], nullptr, am0))) return rc;
             if (B == 1 && e->wide) {
-                if ((rc = linear_side_by_side(g3, o3, 3, am0))) return rc;
+                if (all_prepared(g3, 3)) {
+                    const RopeScatter rs{e->d_pos, c.rope_theta, hd, c.max_position_embeddings, kc, vc};
+                    if ((rc = linear_group_prepared(g3, o3, 3, am0, &rs))) return rc;
+                    rope_done = true;
+                } else if ((rc = linear_side_by_side(g3, o3, 3, am0))) {
+                    return rc;
+                }
             } else if (B == 1) {
                 if ((rc = bitlinear_q8_group(make_group(g3, o3, 3), e->xq, am0, s))) return rc;
             } else {
@@ -880,23 +978,23 @@ int enqueue_step(spb_shard_engine* e, bool record) {
                     if ((rc = linear_b(L.lin[i], am0, o3[i], e->acc + i * e->acc_third))) return rc;
             }
         }
-        if ((rc = rope_scatter(e->q, e->k, e->v, kc, vc, e->nh_loc, e->nkv_loc, hd, c.max_position_embeddings, c.rope_theta,
+        if (!rope_done && (rc = rope_scatter(e->q, e->k, e->v, kc, vc, e->nh_loc, e->nkv_loc, hd, c.max_position_embeddings, c.rope_theta,
                                e->d_pos, s, B, B > 1 ? e->seq_stride : 0))) return rc;
         if (B == 1 && e->split_attention) {
             // (a batched form of the split kernel, one block per (KV head, chunk, sequence), was measured slower for
             // 64 sequences than one block per (head, sequence): 54.6 against 51.6 ms per step)
-            if ((rc = decode_attention_split(e->q, kc, vc, e->attn, e->nh_loc, e->nkv_loc, hd, c.max_position_embeddings, 0,
+            if ((rc = decode_attention_split(e->q, kc, vc, attn_out, e->nh_loc, e->nkv_loc, hd, c.max_position_embeddings, 0,
                                              e->d_pos, attn_scale, e->attn_scratch, s, e->attn_counters))) return rc;
-        } else if ((rc = decode_attention_pos(e->q, kc, vc, e->attn, e->nh_loc, e->nkv_loc, hd, c.max_position_embeddings,
+        } else if ((rc = decode_attention_pos(e->q, kc, vc, attn_out, e->nh_loc, e->nkv_loc, hd, c.max_position_embeddings,
                                               attn_scale, e->d_pos, s, B, B > 1 ? e->seq_stride : 0))) {
             return rc;
         }
-        {
+        if (!alone) {
             const XSeg sg = seg_of(e->attn, e->off_attn, static_cast<size_t>(e->kv0[r]) * e->group_heads * hd * 2,
                                    static_cast<size_t>(qdim) * 2, static_cast<size_t>(e->nh_loc) * hd * 2);
             const int* bd[1] = {e->kv0};
             const int ub[1] = {e->group_heads * hd * 2};
-            if ((rc = exchange(e, X_ATTN, &sg, 1, bd, ub))) return rc;
+            if ((rc = exchange_or_defer(X_ATTN, &sg, 1, bd, ub))) return rc;
         }
         // ---- o_proj rows ----
         if (B == 1 && fused1) {
@@ -904,22 +1002,22 @@ int enqueue_step(spb_shard_engine* e, bool record) {
         } else {
             if (e->wide) {
                 if ((rc = launch("wide_absmax_quantize", wide_absmax_quantize_kernel, dim3(B), dim3(kWideThreads), 0, s,
-                                 static_cast<const __half*>(attn_full), e->xq, am1, qdim))) return rc;
+                                 static_cast<const __half*>(attn_full), e->xq, am1, qdim, take_pending()))) return rc;
             } else if ((rc = absmax_quantize_rows(attn_full, e->xq, am1, qdim, B, s))) {
                 return rc;
             }
             if (B == 1) {
-                if ((rc = linear_1(L.lin[3], am1, e->o))) return rc;
-            } else if ((rc = linear_b(L.lin[3], am1, e->o, e->acc))) {
+                if ((rc = linear_1(L.lin[3], am1, o_out))) return rc;
+            } else if ((rc = linear_b(L.lin[3], am1, o_out, e->acc))) {
                 return rc;
             }
         }
-        {
+        if (!alone) {
             const XSeg sg = seg_of(e->o, e->off_o, static_cast<size_t>(e->hrow[r]) * 2, static_cast<size_t>(H) * 2,
                                    static_cast<size_t>(e->h_loc) * 2);
             const int* bd[1] = {e->hrow};
             const int ub[1] = {2};
-            if ((rc = exchange(e, X_O, &sg, 1, bd, ub))) return rc;
+            if ((rc = exchange_or_defer(X_O, &sg, 1, bd, ub))) return rc;
         }
         // ---- gate / up rows ----
         if (B == 1 && fused1) {
@@ -928,22 +1026,26 @@ int enqueue_step(spb_shard_engine* e, bool record) {
         } else {
             if ((rc = res_norm_quant(o_full, L.norm[2], cur, L.norm[1], nullptr, am0))) return rc;
             if (B == 1 && e->wide) {
-                if ((rc = linear_side_by_side(g2, o2, 2, am0))) return rc;
+                if (all_prepared(g2, 2)) {
+                    if ((rc = linear_group_prepared(g2, o2, 2, am0, nullptr))) return rc;
+                } else if ((rc = linear_side_by_side(g2, o2, 2, am0))) {
+                    return rc;
+                }
             } else if (B == 1) {
                 if ((rc = bitlinear_q8_group(make_group(g2, o2, 2), e->xq, am0, s))) return rc;
             } else {
-                if ((rc = linear_b(L.lin[4], am0, e->gate, e->acc))) return rc;
-                if ((rc = linear_b(L.lin[5], am0, e->up, e->acc + e->acc_third))) return rc;
+                if ((rc = linear_b(L.lin[4], am0, gate_out, e->acc))) return rc;
+                if ((rc = linear_b(L.lin[5], am0, up_out, e->acc + e->acc_third))) return rc;
             }
         }
-        {
+        if (!alone) {
             const XSeg sg[2] = {seg_of(e->gate, e->off_gate, static_cast<size_t>(e->irow[r]) * 2, static_cast<size_t>(inter) * 2,
                                        static_cast<size_t>(e->i_loc) * 2),
                                 seg_of(e->up, e->off_up, static_cast<size_t>(e->irow[r]) * 2, static_cast<size_t>(inter) * 2,
                                        static_cast<size_t>(e->i_loc) * 2)};
             const int* bd[2] = {e->irow, e->irow};
             const int ub[2] = {2, 2};
-            if ((rc = exchange(e, X_GU, sg, 2, bd, ub))) return rc;
+            if ((rc = exchange_or_defer(X_GU, sg, 2, bd, ub))) return rc;
         }
         // ---- down rows: relu2 * up and ffn_sub_norm need the whole vectors ----
         if (B == 1 && fused1) {
@@ -952,22 +1054,22 @@ int enqueue_step(spb_shard_engine* e, bool record) {
             if (e->wide) {
                 if ((rc = launch("wide_relu2_norm_quant", wide_relu2_norm_quant_kernel, dim3(B), dim3(kWideThreads), 0, s,
                                  static_cast<const __half*>(gate_full), static_cast<const __half*>(up_full), L.norm[3], e->xq, am1,
-                                 inter, c.rms_norm_eps))) return rc;
+                                 inter, c.rms_norm_eps, take_pending()))) return rc;
             } else if ((rc = relu2_norm_quant(gate_full, up_full, L.norm[3], nullptr, e->xq, am1, inter, c.rms_norm_eps, s, B))) {
                 return rc;
             }
             if (B == 1) {
-                if ((rc = linear_1(L.lin[6], am1, e->down))) return rc;
-            } else if ((rc = linear_b(L.lin[6], am1, e->down, e->acc))) {
+                if ((rc = linear_1(L.lin[6], am1, down_out))) return rc;
+            } else if ((rc = linear_b(L.lin[6], am1, down_out, e->acc))) {
                 return rc;
             }
         }
-        {
+        if (!alone) {
             const XSeg sg = seg_of(e->down, e->off_down, static_cast<size_t>(e->hrow[r]) * 2, static_cast<size_t>(H) * 2,
                                    static_cast<size_t>(e->h_loc) * 2);
             const int* bd[1] = {e->hrow};
             const int ub[1] = {2};
-            if ((rc = exchange(e, X_DOWN, &sg, 1, bd, ub))) return rc;
+            if ((rc = exchange_or_defer(X_DOWN, &sg, 1, bd, ub))) return rc;
         }
     }
     // last residual add + final norm, LM head on this rank's vocabulary rows, arg-max candidates
@@ -1179,7 +1281,7 @@ extern "C" spb_shard_engine* spb_shard_engine_create(const spb_model_config* cfg
 
 // (Re)builds or drops the prepared form of a slice according to the engine's setting.  Only the wide single-sequence
 // step multiplies matrix by matrix on the quantised vector, which is where the prepared GEMV applies.
-static int prepare_linear(spb_shard_engine* e, Linear& L) {
+static int prepare_linear(spb_shard_engine* e, Linear& L, int which) {
     if (L.prep) {
         SPB_CUDA(cudaStreamSynchronize(e->stream));
         cudaFree(L.prep);
@@ -1188,7 +1290,10 @@ static int prepare_linear(spb_shard_engine* e, Linear& L) {
     const size_t bytes = spb_prepared_weights_bytes(L.rows, L.cols);
     // (measured: the prepared form wins from some tens of millions of weights per matrix on, 8192 x 8192 is about even,
     // 1024 x 8192 is quicker in the packed form)
-    const bool large = e->use_prepared == 2 || static_cast<long long>(L.rows) * L.cols >= 32LL * 1024 * 1024;
+    // k and v go with q: with prepared copies of all three the group is one launch
+    long long weights = static_cast<long long>(L.rows) * L.cols;
+    if (which == 1 || which == 2) weights *= e->group_heads;
+    const bool large = e->use_prepared == 2 || weights >= 32LL * 1024 * 1024;
     if (!e->use_prepared || !e->wide || e->batch != 1 || !large || bytes == 0 || L.ms < L.cols / 32 || L.vs < L.cols / 64) return SPB_OK;
     SPB_CUDA(cudaMalloc(&L.prep, bytes));
     return spb_prepare_weights(L.meta, L.values, L.rows, L.cols, L.ms, L.vs, L.prep, e->stream);
@@ -1298,7 +1403,16 @@ extern "C" int spb_shard_engine_set_linear(spb_shard_engine* e, int layer, int w
     L.meta = d_meta; L.values = d_values; L.gamma = gamma; L.rows = rows; L.cols = cols; L.ms = meta_stride; L.vs = values_stride;
     drop_graph(e);
     DeviceScope scope(e->device);
-    return prepare_linear(e, L);
+    return prepare_linear(e, L, which);
+}
+
+extern "C" int spb_shard_engine_set_exchange_fold(spb_shard_engine* e, int on) {
+    if (!e) return fail(SPB_E_INVALID, "spb_shard_engine_set_exchange_fold: null handle");
+    DeviceScope scope(e->device);
+    SPB_CUDA(cudaStreamSynchronize(e->stream));
+    drop_graph(e);
+    e->fold_exchange = on != 0;
+    return SPB_OK;
 }
 
 extern "C" int spb_shard_engine_set_prepared_weights(spb_shard_engine* e, int on) {
@@ -1308,9 +1422,9 @@ extern "C" int spb_shard_engine_set_prepared_weights(spb_shard_engine* e, int on
     drop_graph(e);
     e->use_prepared = on < 0 ? 0 : on > 2 ? 2 : on;
     for (Layer& Ly : e->layers)
-        for (Linear& L : Ly.lin)
-            if (L.meta)
-                if (int rc = prepare_linear(e, L)) return rc;
+        for (int which = 0; which < 7; ++which)
+            if (Ly.lin[which].meta)
+                if (int rc = prepare_linear(e, Ly.lin[which], which)) return rc;
     return SPB_OK;
 }
 

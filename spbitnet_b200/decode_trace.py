@@ -29,6 +29,7 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=30)
     ap.add_argument("--prompt", type=int, default=128)
     ap.add_argument("--tokens", type=int, default=40)
+    ap.add_argument("--tagged", action="store_true", help="the barrier-free form (stage outputs as tagged words)")
     args = ap.parse_args()
     cfg = dict(synth.BITNET_2B, num_hidden_layers=args.layers)
     lib = _lib.load()
@@ -37,7 +38,7 @@ def main() -> None:
     lib.spb_debug_set_decode_trace(C.c_void_p(trace.data_ptr()))
     try:
         eng = InferenceEngine(dm)
-        eng.set_decode_mode(InferenceEngine.DECODE_PERSISTENT)
+        eng.set_decode_mode(InferenceEngine.DECODE_PERSISTENT_TAGGED if args.tagged else InferenceEngine.DECODE_PERSISTENT)
         prompt = np.random.default_rng(0).integers(0, cfg["vocab_size"], args.prompt).astype(np.int32)
         eng.generate(prompt, args.tokens)
         torch.cuda.synchronize()

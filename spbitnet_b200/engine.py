@@ -93,11 +93,13 @@ class InferenceEngine:
             check(prev)
         return prev
 
-    DECODE_AUTO, DECODE_CHAIN, DECODE_PERSISTENT, DECODE_UNFUSED = 0, 1, 2, 3
+    DECODE_AUTO, DECODE_CHAIN, DECODE_PERSISTENT, DECODE_UNFUSED, DECODE_PERSISTENT_TAGGED = 0, 1, 2, 3, 4
 
     def set_decode_mode(self, mode: int) -> None:
         """How the layers of a decode token run: DECODE_AUTO = DECODE_CHAIN (five PDL-linked kernels per layer),
-        DECODE_PERSISTENT (one cooperative launch per token), DECODE_UNFUSED (one launch per op group).
+        DECODE_PERSISTENT (one cooperative launch per token, grid barriers between the stages),
+        DECODE_PERSISTENT_TAGGED (the same launch without grid barriers: stage outputs travel as tagged words that
+        their consumers poll), DECODE_UNFUSED (one launch per op group).
         All modes give the same tokens and logits."""
         check(self._lib.spb_engine_set_decode_mode(self._h, int(mode)))
 

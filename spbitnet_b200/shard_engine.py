@@ -135,6 +135,11 @@ class ShardEngine:
         large ones, 2 every slice the layout takes, 0 none.  Wide models, one sequence; same results either way."""
         check(self._lib.spb_shard_engine_set_prepared_weights(self._h, int(level)))
 
+    def set_exchange_fold(self, on: bool) -> None:
+        """Wide models, one sequence, several ranks: whether the kernel that consumes a gathered vector performs the
+        exchange itself (default) or a launch of its own does.  Same results either way."""
+        check(self._lib.spb_shard_engine_set_exchange_fold(self._h, int(bool(on))))
+
     def weight_bytes(self) -> int:
         """Bytes of weights this rank streams per decode step (its row slices + its LM head rows)."""
         n = sum(t.numel() * t.element_size() for t in self._keep if t.dtype == torch.int32)

@@ -11,12 +11,13 @@ from spbitnet_b200.engine import DeviceModel, InferenceEngine
 pytestmark = pytest.mark.gpu
 
 CHAIN, PERSISTENT = InferenceEngine.DECODE_CHAIN, InferenceEngine.DECODE_PERSISTENT
+TAGGED = InferenceEngine.DECODE_PERSISTENT_TAGGED
 
 
-def both_modes(dm, prompt, n_new, check_every=1):
+def both_modes(dm, prompt, n_new, check_every=1, persistent_mode=PERSISTENT):
     """Runs the same greedy generation in both modes, comparing the logits of every check_every-th step."""
     engines = []
-    for mode in (CHAIN, PERSISTENT):
+    for mode in (CHAIN, persistent_mode):
         eng = InferenceEngine(dm)
         eng.set_decode_mode(mode)
         engines.append(eng)
@@ -59,6 +60,41 @@ def test_2b4t_width_two_layers():
     dm = synth.DeviceRandomModel(cfg, seed=5)
     prompt = np.random.default_rng(2).integers(0, cfg["vocab_size"], 8).astype(np.int32)
     both_modes(dm, prompt, 72, check_every=9)
+
+
+@pytest.mark.parametrize("cfg_over", [
+    dict(num_hidden_layers=3),                                                       # the 2B-4T layer shape
+    dict(num_hidden_layers=2, num_attention_heads=20, num_key_value_heads=20, intermediate_size=4096),  # no grouping
+    dict(num_hidden_layers=2, hidden_size=3072, num_attention_heads=16, num_key_value_heads=2, head_dim=128,
+         intermediate_size=8192),                                                    # groups of eight, long vectors
+])
+def test_barrier_free_form_matches_the_chain(cfg_over):
+    """Stage outputs as tagged words, the residual stream in every block's shared memory: same logits, bit for bit,
+    across chunk boundaries of the attention, after a reset, and with the graph replayed per token."""
+    cfg = dict(synth.BITNET_2B, vocab_size=4096, max_position_embeddings=256, **cfg_over)
+    dm = synth.DeviceRandomModel(cfg, seed=21)
+    prompt = np.random.default_rng(7).integers(0, cfg["vocab_size"], 9).astype(np.int32)
+    tokens, chain, tagged = both_modes(dm, prompt, 60, check_every=6, persistent_mode=TAGGED)
+    before = K.gemm_tc_timeouts()
+    for eng in (chain, tagged):
+        eng.reset()
+    want = chain.generate(prompt, 48)
+    assert (tagged.generate(prompt, 48) == want).all()
+    tagged.reset()
+    assert (tagged.generate(prompt, 48) == want).all()
+    assert (want == tokens[:48]).all()
+    assert K.gemm_tc_timeouts() == before
+
+
+def test_barrier_free_form_refuses_narrow_models():
+    dm = DeviceModel(synth.random_model(synth.TINY, seed=3))  # fewer row tiles than blocks
+    eng = InferenceEngine(dm)
+    eng.set_decode_mode(TAGGED)
+    with pytest.raises(_lib.SpbError) as err:
+        eng.generate(np.array([1, 2, 3], np.int32), 4)
+    assert err.value.code == _lib.SPB_E_UNSUPPORTED
+    eng.set_decode_mode(PERSISTENT)
+    assert len(eng.generate(np.array([1, 2, 3], np.int32), 4)) == 4
 
 
 def test_more_tiles_than_blocks_and_fewer():

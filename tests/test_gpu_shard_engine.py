@@ -75,12 +75,18 @@ def test_batched_decode_at_the_2b4t_width():
         assert np.abs(lg[b] - alone.logits()).max() < 1e-2
 
 
-def test_a_silent_peer_ends_in_a_timeout_not_a_hang():
+WIDE = dict(hidden_size=4096, num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+            intermediate_size=16640, vocab_size=2048, max_position_embeddings=32, rms_norm_eps=1e-5, rope_theta=500000.0)
+
+
+@pytest.mark.parametrize("wide", [False, True], ids=["narrow", "wide"])
+def test_a_silent_peer_ends_in_a_timeout_not_a_hang(wide):
     """Rank 0 of a two-rank group whose "peer" is a zero-filled buffer that nobody writes: every exchange stores
     the rank's slices there, the first wait for the peer's flag runs out after the (short) bound, the kernel raises
-    the status word and returns, later exchanges skip their waits, and the host call answers SPB_E_TIMEOUT."""
+    the status word and returns, later exchanges skip their waits, and the host call answers SPB_E_TIMEOUT.
+    (wide: the exchanges are performed by the kernels that consume the gathered vectors.)"""
     model = synth.random_model(synth.TINY, seed=44)
-    dm = DeviceModel(model)
+    dm = synth.DeviceRandomModel(WIDE, seed=44) if wide else DeviceModel(model)
     eng = ShardEngine(dm, rank=0, world=2, timeout_ms=20, connect=False)
     fake_peer = torch.zeros(eng.exchange_bytes, dtype=torch.uint8, device="cuda")
     eng.set_peer_pointers([0, fake_peer.data_ptr()])
@@ -89,7 +95,7 @@ def test_a_silent_peer_ends_in_a_timeout_not_a_hang():
     assert err.value.code == _lib.SPB_E_TIMEOUT
     torch.cuda.synchronize()
     # the context is healthy: an ordinary engine on the same device still decodes correctly
-    ok = InferenceEngine(dm)
+    ok = InferenceEngine(DeviceModel(model))
     want, _ = oracle.Engine(model).generate(np.array([5, 9], np.int32), 4)
     assert (ok.generate(np.array([5, 9], np.int32), 4) == want).all()
     # rank 0 pushed its slices into the stand-in peer before it gave up
