@@ -1019,11 +1019,11 @@ def bench_sharded(args, rank, world, dist):
     full.config = cfg
     full.layers = [full.layers[0]] * L  # ShardEngine clones the rank's slices layer by layer
     results = {}
-    runs = [(1, True), (64, True)] + ([(1, False)] if world > 1 else [])
+    runs = [(1, False), (64, False)] + ([(1, True)] if world > 1 else [])
     for batch, fold in runs:
         eng = ShardEngine(full, rank=rank, world=world, batch=batch, group=ctl)
-        if not fold:  # the exchanges as launches of their own instead of inside the kernels that consume the vectors
-            eng.set_exchange_fold(False)
+        if fold:  # the exchanges inside the kernels that consume the gathered vectors instead of launches of their own
+            eng.set_exchange_fold(True)
         rng = np.random.default_rng(11)
         prompts = rng.integers(0, cfg["vocab_size"], (args.shard_prompt, batch)).astype(np.int32)
         warm = eng.generate(prompts[:4], 2)  # graph capture, page-in
@@ -1040,7 +1040,7 @@ def bench_sharded(args, rank, world, dist):
         kv_bytes = 2 * L * batch * (cfg["num_key_value_heads"] // world if world <= cfg["num_key_value_heads"] else 1) * \
             (args.shard_prompt + args.shard_tokens // 2) * cfg["head_dim"] * 2
         my_bytes = eng.weight_bytes() + kv_bytes
-        results[f"batch{batch}" if fold else f"batch{batch}_exchange_as_launch"] = {
+        results[f"batch{batch}_exchange_in_consumer" if fold else f"batch{batch}"] = {
             "tok_s": batch * args.shard_tokens / dt, "ms_per_step": 1e3 * step_s,
             "prompt_s": t_prompt, "prompt_tok_s": batch * (args.shard_prompt - 1) / t_prompt,
             "per_gpu_bytes_per_step": int(my_bytes), "per_gpu_hbm_gbs": my_bytes / step_s / 1e9,

@@ -32,6 +32,8 @@
 // were slower everywhere: per block with a block-wide reduction per piece, 17.1 against 14.7 us at 28672 x 8192 as a
 // chain of launches; per warp with no block-wide step, 16.5 against 14.6 us (14.0 against 8.9 us in the graph of eight
 // branches): the fence and the round trip of the counting atomic drain the warp's prefetch at every hand-over.
+// Also measured and dropped: asking L2 for the rest of a warp's run of quads before the dependency wait (one bulk
+// prefetch per warp, or a prefetch per 128 bytes): the 70B-shape decode step got 3 - 4 % slower both ways.
 #include "fused_ops.cuh"
 #include "spb_common.cuh"
 
@@ -40,6 +42,7 @@ namespace spb {
 constexpr int kGpThreads = 256;
 constexpr int kGpWarps = kGpThreads / 32;
 constexpr int kGpQuadBytes = 768;
+constexpr int kGpBlocksPerSm = 4;  // 64 registers a thread
 
 enum { GP_OUT_I32 = 0, GP_OUT_F32 = 1, GP_OUT_F16 = 2 };
 
@@ -162,7 +165,7 @@ __device__ __forceinline__ void gp_run_quads(const uint8_t* tile_base, int q_beg
     c_hi = (u2 + v2) + 2 * (r2 + t2);
 }
 
-__global__ void __launch_bounds__(kGpThreads, 3) gemv_prepared_kernel(const GpArgs a) {
+__global__ void __launch_bounds__(kGpThreads, kGpBlocksPerSm) gemv_prepared_kernel(const GpArgs a) {
     __shared__ int red[kGpWarps * 16];
     extern __shared__ __align__(16) uint8_t gp_raw[];  // x in B-register order: xs[step][tig][j][0..3] = x[64 step + 16 j + 4 tig ..+3]
     const uint32_t xs_s = static_cast<uint32_t>(__cvta_generic_to_shared(gp_raw));
@@ -306,10 +309,24 @@ static int gp_launch(const char* name, const GpMatDesc* mats, int nmat, const in
     a.cols = cols;
     a.ntiles = tiles;
     a.nquads = cols / 256;
-    // Warps per tile: a warp wants a run of quads (its fixed cost is the three-quad prefetch and the final
-    // reduction), but the launch has to give every SM its three blocks.
+    // Warps per tile (1, 2, 4 or 8; a block is 8 warps).  A launch runs in waves of sm_count x 4 blocks, and a wave
+    // lasts as long as a warp's run of quads plus a fixed part (start, activation vector into shared memory, the
+    // sum over the tile's warps: about three quads' worth), so the choice minimises waves x (quads per warp + 3):
+    // 512 tiles of 112 quads (8192 x 28672) run as one wave of 512 blocks with 14 quads per warp, where a rule that
+    // only filled the SMs ran the same blocks in two waves.  Ties go to the longer runs.
+    const int slots = sm_count() * kGpBlocksPerSm;
+    long long best = 0;
     a.ks = 1;
-    while (a.ks < 8 && a.ntiles * a.ks < 24 * sm_count() && a.nquads / (2 * a.ks) >= 2) a.ks <<= 1;
+    for (int ks = 1; ks <= 8; ks <<= 1) {
+        const int qpw = (a.nquads + ks - 1) / ks;
+        if (ks > 1 && qpw < 2) break;
+        const int nblocks = (a.ntiles + kGpWarps / ks - 1) / (kGpWarps / ks);
+        const long long cost = static_cast<long long>((nblocks + slots - 1) / slots) * (qpw + 3);
+        if (ks == 1 || cost < best) {
+            best = cost;
+            a.ks = ks;
+        }
+    }
     a.ks_log2 = a.ks == 8 ? 3 : a.ks == 4 ? 2 : a.ks == 2 ? 1 : 0;
     a.qpw = (a.nquads + a.ks - 1) / a.ks;
     const int tiles_blk = kGpWarps / a.ks;

@@ -437,23 +437,57 @@ __global__ void __launch_bounds__(128) half_gemm_rows_kernel(const __half* __res
 constexpr int kWideThreads = 1024;
 constexpr int kWideRuns = 4;  // runs of eight elements per thread: vectors of up to 32768
 
+// Block-wide sum / maximum over 1024 threads.  The 1024 threads are either one block (CL = 1) or a cluster of CL
+// blocks of 1024 / CL threads, in which a thread's number is rank * (1024 / CL) + threadIdx.x; the arithmetic is the
+// same in both forms (warp tree, then a tree over the 32 warp results in warp order), so the results are too.  In the
+// cluster form every warp stores its result into slot (its number among the 32 warps) of `sh` in EVERY block of the
+// cluster (distributed shared memory) and a cluster barrier stands where the block barrier stood.  `sh` is used once
+// per kernel: nothing is overwritten while a slower block still reads.
+__device__ __forceinline__ uint32_t wide_cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+template <int CL>
+__device__ __forceinline__ int wide_tid() {
+    return CL == 1 ? static_cast<int>(threadIdx.x) : static_cast<int>(wide_cluster_rank() * (kWideThreads / CL) + threadIdx.x);
+}
+template <int CL>
+__device__ __forceinline__ void wide_share(float v, float* sh) {
+    if (CL == 1) {
+        __syncthreads();
+        if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+        __syncthreads();
+    } else {
+        if ((threadIdx.x & 31) == 0) {
+            const uint32_t slot = wide_cluster_rank() * (kWideThreads / CL / 32) + (threadIdx.x >> 5);
+            const uint32_t local = static_cast<uint32_t>(__cvta_generic_to_shared(sh + slot));
+#pragma unroll
+            for (int c = 0; c < CL; ++c) {
+                uint32_t remote;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(c));
+                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+            }
+        }
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
+}
+template <int CL>
 __device__ __forceinline__ float wide_bsum(float v, float* sh) {
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
-    __syncthreads();
-    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
-    __syncthreads();
+    wide_share<CL>(v, sh);
     v = sh[threadIdx.x & 31];
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
     return v;
 }
+template <int CL>
 __device__ __forceinline__ float wide_bmax(float v, float* sh) {
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, off));
-    __syncthreads();
-    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
-    __syncthreads();
+    wide_share<CL>(v, sh);
     v = sh[threadIdx.x & 31];
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, off));
@@ -485,14 +519,16 @@ __device__ __forceinline__ void quantise_store8(const float* v, float qs, int8_t
 // residual_norm_quant for one vector per block (blockIdx.x = vector): x += [rms_norm(sub_w)](delta) in half, then
 // xn = rms_norm(w)(x) in half (to xn_out when given), absmax, int8.  n % 8 == 0, n <= 8192: one run of eight
 // elements per thread, everything in registers.
-__global__ void __launch_bounds__(kWideThreads) wide_residual_norm_quant_kernel(
+template <int CL>
+__global__ void __launch_bounds__(kWideThreads / CL) wide_residual_norm_quant_kernel(
     const __half* delta, const float* __restrict__ sub_w, __half* __restrict__ x, const float* __restrict__ w,
     __half* __restrict__ xn_out, int8_t* __restrict__ xq, float* __restrict__ d_absmax, int n, float eps, const LArgs xin) {
-    __shared__ float sh[32];
+    __shared__ float sh[3][32];
+    const int vt = wide_tid<CL>(), vec = blockIdx.x / CL;
     grid_dep_launch();
     grid_dep_wait();
     exchange_ll_in_block(xin);  // delta, gathered from the ranks' slices
-    const size_t off = static_cast<size_t>(blockIdx.x) * n;
+    const size_t off = static_cast<size_t>(vec) * n;
     const int runs = n >> 3;
     constexpr int kRuns = 1;
     float v[kRuns][8], wv[kRuns][8];
@@ -501,7 +537,7 @@ __global__ void __launch_bounds__(kWideThreads) wide_residual_norm_quant_kernel(
         float d[kRuns][8], sw[kRuns][8];
 #pragma unroll
         for (int k = 0; k < kRuns; ++k) {
-            const int r = threadIdx.x + k * kWideThreads;
+            const int r = vt + k * kWideThreads;
             if (r < runs) {
                 unpack8(*reinterpret_cast<const uint4*>(delta + off + 8 * r), d[k]);
                 unpack8(*reinterpret_cast<const uint4*>(x + off + 8 * r), v[k]);
@@ -512,11 +548,11 @@ __global__ void __launch_bounds__(kWideThreads) wide_residual_norm_quant_kernel(
             }
         }
         float sub_scale = 1.0f;
-        if (sub_w) sub_scale = rsqrtf(wide_bsum(s, sh) / static_cast<float>(n) + eps);
+        if (sub_w) sub_scale = rsqrtf(wide_bsum<CL>(s, sh[0]) / static_cast<float>(n) + eps);
         s = 0.0f;
 #pragma unroll
         for (int k = 0; k < kRuns; ++k) {
-            const int r = threadIdx.x + k * kWideThreads;
+            const int r = vt + k * kWideThreads;
             if (r < runs) {
                 __half2 out[4];
 #pragma unroll
@@ -534,7 +570,7 @@ __global__ void __launch_bounds__(kWideThreads) wide_residual_norm_quant_kernel(
     } else {
 #pragma unroll
         for (int k = 0; k < kRuns; ++k) {
-            const int r = threadIdx.x + k * kWideThreads;
+            const int r = vt + k * kWideThreads;
             if (r < runs) {
                 unpack8(*reinterpret_cast<const uint4*>(x + off + 8 * r), v[k]);
                 load8f(w + 8 * r, wv[k]);
@@ -543,11 +579,11 @@ __global__ void __launch_bounds__(kWideThreads) wide_residual_norm_quant_kernel(
             }
         }
     }
-    const float scale = rsqrtf(wide_bsum(s, sh) / static_cast<float>(n) + eps);
+    const float scale = rsqrtf(wide_bsum<CL>(s, sh[1]) / static_cast<float>(n) + eps);
     float m = 0.0f;
 #pragma unroll
     for (int k = 0; k < kRuns; ++k) {
-        const int r = threadIdx.x + k * kWideThreads;
+        const int r = vt + k * kWideThreads;
         if (r < runs) {
             __half2 out[4];
 #pragma unroll
@@ -560,22 +596,24 @@ __global__ void __launch_bounds__(kWideThreads) wide_residual_norm_quant_kernel(
             if (xn_out) *reinterpret_cast<uint4*>(xn_out + off + 8 * r) = *reinterpret_cast<const uint4*>(out);
         }
     }
-    const float absmax = wide_bmax(m, sh);
-    if (threadIdx.x == 0) d_absmax[blockIdx.x] = absmax;
+    const float absmax = wide_bmax<CL>(m, sh[2]);
+    if (vt == 0) d_absmax[vec] = absmax;
     const float qs = quant_scale(absmax);
 #pragma unroll
     for (int k = 0; k < kRuns; ++k) {
-        const int r = threadIdx.x + k * kWideThreads;
+        const int r = vt + k * kWideThreads;
         if (r < runs) quantise_store8(v[k], qs, xq + off + 8 * r);
     }
 }
 
 // relu2_norm_quant for one vector per block: m = relu(gate)^2 * up in fp32, h = half(m * rsqrt(mean m^2 + eps) * sub_w)
 // (or half(m) without sub_w), absmax, int8.
-__global__ void __launch_bounds__(kWideThreads) wide_relu2_norm_quant_kernel(
+template <int CL>
+__global__ void __launch_bounds__(kWideThreads / CL) wide_relu2_norm_quant_kernel(
     const __half* gate, const __half* up, const float* __restrict__ sub_w, int8_t* __restrict__ hq,
     float* __restrict__ d_absmax, int n, float eps, const LArgs xin) {
-    __shared__ float sh[32];
+    __shared__ float sh[2][32];
+    const int vt = wide_tid<CL>(), vec = blockIdx.x / CL;
     grid_dep_launch();
     const int runs = n >> 3;
     // sub_w is read after the reduction, when it is needed (no registers to hold it until then); it is constant, so its
@@ -583,17 +621,17 @@ __global__ void __launch_bounds__(kWideThreads) wide_relu2_norm_quant_kernel(
     if (sub_w)
 #pragma unroll
         for (int k = 0; k < kWideRuns; ++k) {
-            const int r = threadIdx.x + k * kWideThreads;
+            const int r = vt + k * kWideThreads;
             if (r < runs) asm volatile("prefetch.global.L1 [%0];" ::"l"(sub_w + 8 * r));
         }
     grid_dep_wait();
     exchange_ll_in_block(xin);  // gate and up, gathered from the ranks' slices
-    const size_t off = static_cast<size_t>(blockIdx.x) * n;
+    const size_t off = static_cast<size_t>(vec) * n;
     float v[kWideRuns][8];  // the products stay in registers
     float s = 0.0f;
 #pragma unroll
     for (int k = 0; k < kWideRuns; ++k) {
-        const int r = threadIdx.x + k * kWideThreads;
+        const int r = vt + k * kWideThreads;
         if (r < runs) {
             float g[8], u[8];
             unpack8(*reinterpret_cast<const uint4*>(gate + off + 8 * r), g);
@@ -607,11 +645,11 @@ __global__ void __launch_bounds__(kWideThreads) wide_relu2_norm_quant_kernel(
         }
     }
     float scale = 1.0f;
-    if (sub_w) scale = rsqrtf(wide_bsum(s, sh) / static_cast<float>(n) + eps);
+    if (sub_w) scale = rsqrtf(wide_bsum<CL>(s, sh[0]) / static_cast<float>(n) + eps);
     float m = 0.0f;
 #pragma unroll
     for (int k = 0; k < kWideRuns; ++k) {
-        const int r = threadIdx.x + k * kWideThreads;
+        const int r = vt + k * kWideThreads;
         if (r < runs) {
             float sw[8];
             if (sub_w) load8f(sub_w + 8 * r, sw);
@@ -623,45 +661,72 @@ __global__ void __launch_bounds__(kWideThreads) wide_relu2_norm_quant_kernel(
             }
         }
     }
-    const float absmax = wide_bmax(m, sh);
-    if (threadIdx.x == 0) d_absmax[blockIdx.x] = absmax;
+    const float absmax = wide_bmax<CL>(m, sh[1]);
+    if (vt == 0) d_absmax[vec] = absmax;
     const float qs = quant_scale(absmax);
 #pragma unroll
     for (int k = 0; k < kWideRuns; ++k) {
-        const int r = threadIdx.x + k * kWideThreads;
+        const int r = vt + k * kWideThreads;
         if (r < runs) quantise_store8(v[k], qs, hq + off + 8 * r);
     }
 }
 
 // absmax_quantize_gpu for one vector per block.
-__global__ void __launch_bounds__(kWideThreads) wide_absmax_quantize_kernel(const __half* in, int8_t* __restrict__ out,
+template <int CL>
+__global__ void __launch_bounds__(kWideThreads / CL) wide_absmax_quantize_kernel(const __half* in, int8_t* __restrict__ out,
                                                                             float* __restrict__ d_absmax, int n, const LArgs xin) {
     __shared__ float sh[32];
+    const int vt = wide_tid<CL>(), vec = blockIdx.x / CL;
     grid_dep_launch();
     grid_dep_wait();
     exchange_ll_in_block(xin);
-    const size_t off = static_cast<size_t>(blockIdx.x) * n;
+    const size_t off = static_cast<size_t>(vec) * n;
     const int runs = n >> 3;
     float v[kWideRuns][8];
     float m = 0.0f;
 #pragma unroll
     for (int k = 0; k < kWideRuns; ++k) {
-        const int r = threadIdx.x + k * kWideThreads;
+        const int r = vt + k * kWideThreads;
         if (r < runs) {
             unpack8(*reinterpret_cast<const uint4*>(in + off + 8 * r), v[k]);
 #pragma unroll
             for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[k][i]));
         }
     }
-    const float absmax = wide_bmax(m, sh);
-    if (threadIdx.x == 0) d_absmax[blockIdx.x] = absmax;
+    const float absmax = wide_bmax<CL>(m, sh);
+    if (vt == 0) d_absmax[vec] = absmax;
     const float qs = quant_scale(absmax);
 #pragma unroll
     for (int k = 0; k < kWideRuns; ++k) {
-        const int r = threadIdx.x + k * kWideThreads;
+        const int r = vt + k * kWideThreads;
         if (r < runs) quantise_store8(v[k], qs, out + off + 8 * r);
     }
 }
+
+// launch() with thread-block clusters of `cluster` blocks along x (and programmatic dependent launch as usual)
+template <typename... KArgs, typename... Args>
+int launch_clustered(const char* name, void (*kernel)(KArgs...), dim3 grid, dim3 block, unsigned cluster, void* stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return fail(SPB_E_CUDA, "%s: launch failed: %s", name, cudaGetErrorString(err));
+    }
+    return SPB_OK;
+}
+constexpr int kWideCluster = 8;  // blocks that share one vector of the single-sequence step
 
 int half_gemm_rows(const __half* W, const __half* x, float* y, int rows, int cols, int batch, void* stream) {
     if (cols % 32 || (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(x) & 15))
@@ -763,7 +828,7 @@ struct spb_shard_engine {
     size_t off_flags = 0, off_attn = 0, off_o = 0, off_gate = 0, off_up = 0, off_down = 0, off_amax = 0;
     size_t ll_off[X_KINDS] = {};   // staging areas of the small-message exchange
     bool ll_ok[X_KINDS] = {};      // the kind's slices are small enough for it
-    bool fold_exchange = true;     // wide single-sequence step: the consumer kernel of a vector performs its exchange
+    bool fold_exchange = false;    // wide single-sequence step: the consumer kernel of a vector performs its exchange
     int ident[kMaxWorld + 1] = {0, 1, 2, 3, 4, 5, 6, 7, 8};
     int* status = nullptr;  // pinned, mapped
     unsigned long long timeout_ns = 5000000000ull;
@@ -882,6 +947,9 @@ int enqueue_step(spb_shard_engine* e, bool record) {
         pend = LArgs{};
         return x;
     };
+    // One sequence and no exchange to perform inside: the vector kernels run as a cluster of eight blocks (eight SMs
+    // pull the vector and its norm weights instead of one; same arithmetic, same results).
+    auto clustered = [&]() { return B == 1 && pend.world == 0; };
     __half* attn_out = alone ? attn_full : e->attn;
     __half* o_out = alone ? o_full : e->o;
     __half* gate_out = alone ? gate_full : e->gate;
@@ -938,9 +1006,14 @@ int enqueue_step(spb_shard_engine* e, bool record) {
     const bool fused1 = e->fused && !e->wide;
     // vector ops: the register-resident kernels for wide models, the shared ones of the single-GPU engine otherwise
     auto res_norm_quant = [&](const __half* delta, const float* sub_w, __half* x, const float* w, __half* xn_out, float* am) {
-        if (e->wide)
-            return launch("wide_residual_norm_quant", wide_residual_norm_quant_kernel, dim3(B), dim3(kWideThreads), 0, s, delta, sub_w,
+        if (e->wide) {
+            if (clustered())
+                return launch_clustered("wide_residual_norm_quant", wide_residual_norm_quant_kernel<kWideCluster>, dim3(kWideCluster),
+                                        dim3(kWideThreads / kWideCluster), kWideCluster, s, delta, sub_w, x, w, xn_out, e->xq, am, H,
+                                        c.rms_norm_eps, LArgs{});
+            return launch("wide_residual_norm_quant", wide_residual_norm_quant_kernel<1>, dim3(B), dim3(kWideThreads), 0, s, delta, sub_w,
                           x, w, xn_out, e->xq, am, H, c.rms_norm_eps, take_pending());
+        }
         return residual_norm_quant(delta, sub_w, x, w, xn_out, e->xq, am, H, c.rms_norm_eps, s, B);
     };
     for (int l = 0; l < c.num_hidden_layers; ++l) {
@@ -1001,8 +1074,14 @@ int enqueue_step(spb_shard_engine* e, bool record) {
             if ((rc = bitlinear_amax_group(make_group(g1o, o1o, 1), attn_full, s))) return rc;
         } else {
             if (e->wide) {
-                if ((rc = launch("wide_absmax_quantize", wide_absmax_quantize_kernel, dim3(B), dim3(kWideThreads), 0, s,
-                                 static_cast<const __half*>(attn_full), e->xq, am1, qdim, take_pending()))) return rc;
+                if (clustered()) {
+                    if ((rc = launch_clustered("wide_absmax_quantize", wide_absmax_quantize_kernel<kWideCluster>, dim3(kWideCluster),
+                                               dim3(kWideThreads / kWideCluster), kWideCluster, s, static_cast<const __half*>(attn_full),
+                                               e->xq, am1, qdim, LArgs{}))) return rc;
+                } else if ((rc = launch("wide_absmax_quantize", wide_absmax_quantize_kernel<1>, dim3(B), dim3(kWideThreads), 0, s,
+                                        static_cast<const __half*>(attn_full), e->xq, am1, qdim, take_pending()))) {
+                    return rc;
+                }
             } else if ((rc = absmax_quantize_rows(attn_full, e->xq, am1, qdim, B, s))) {
                 return rc;
             }
@@ -1052,9 +1131,16 @@ int enqueue_step(spb_shard_engine* e, bool record) {
             if ((rc = bitlinear_relu2_group(make_group(g1d, o1d, 1), gate_full, up_full, L.norm[3], c.rms_norm_eps, s))) return rc;
         } else {
             if (e->wide) {
-                if ((rc = launch("wide_relu2_norm_quant", wide_relu2_norm_quant_kernel, dim3(B), dim3(kWideThreads), 0, s,
-                                 static_cast<const __half*>(gate_full), static_cast<const __half*>(up_full), L.norm[3], e->xq, am1,
-                                 inter, c.rms_norm_eps, take_pending()))) return rc;
+                if (clustered()) {
+                    if ((rc = launch_clustered("wide_relu2_norm_quant", wide_relu2_norm_quant_kernel<kWideCluster>, dim3(kWideCluster),
+                                               dim3(kWideThreads / kWideCluster), kWideCluster, s, static_cast<const __half*>(gate_full),
+                                               static_cast<const __half*>(up_full), L.norm[3], e->xq, am1, inter, c.rms_norm_eps,
+                                               LArgs{}))) return rc;
+                } else if ((rc = launch("wide_relu2_norm_quant", wide_relu2_norm_quant_kernel<1>, dim3(B), dim3(kWideThreads), 0, s,
+                                        static_cast<const __half*>(gate_full), static_cast<const __half*>(up_full), L.norm[3], e->xq,
+                                        am1, inter, c.rms_norm_eps, take_pending()))) {
+                    return rc;
+                }
             } else if ((rc = relu2_norm_quant(gate_full, up_full, L.norm[3], nullptr, e->xq, am1, inter, c.rms_norm_eps, s, B))) {
                 return rc;
             }
@@ -1288,12 +1374,14 @@ static int prepare_linear(spb_shard_engine* e, Linear& L, int which) {
         L.prep = nullptr;
     }
     const size_t bytes = spb_prepared_weights_bytes(L.rows, L.cols);
-    // (measured: the prepared form wins from some tens of millions of weights per matrix on, 8192 x 8192 is about even,
-    // 1024 x 8192 is quicker in the packed form)
-    // k and v go with q: with prepared copies of all three the group is one launch
+    // (measured on the per-rank shapes of the 70B model, one step of eight layers: at 4 ranks 0.72 ms with every slice
+    // prepared against 0.79 with only those of 32 M weights and more, at 8 ranks 0.67 against 0.80: with prepared
+    // copies q / k / v and gate / up are one launch each and rotate and scatter in the epilogue, which the packed
+    // form's launch per matrix does not make up for even where its kernel is the quicker one.)
+    // k and v go with q: the group is one launch only with prepared copies of all three
     long long weights = static_cast<long long>(L.rows) * L.cols;
     if (which == 1 || which == 2) weights *= e->group_heads;
-    const bool large = e->use_prepared == 2 || weights >= 32LL * 1024 * 1024;
+    const bool large = e->use_prepared == 2 || weights >= 4LL * 1024 * 1024;
     if (!e->use_prepared || !e->wide || e->batch != 1 || !large || bytes == 0 || L.ms < L.cols / 32 || L.vs < L.cols / 64) return SPB_OK;
     SPB_CUDA(cudaMalloc(&L.prep, bytes));
     return spb_prepare_weights(L.meta, L.values, L.rows, L.cols, L.ms, L.vs, L.prep, e->stream);

@@ -131,13 +131,13 @@ class ShardEngine:
         check(self._lib.spb_shard_engine_set_peer_pointers(self._h, arr))
 
     def set_prepared_weights(self, level: int) -> None:
-        """Whether the engine multiplies on prepared copies of its slices (kernels.prepare_weights): 1 (default) the
-        large ones, 2 every slice the layout takes, 0 none.  Wide models, one sequence; same results either way."""
+        """Whether the engine multiplies on prepared copies of its slices (kernels.prepare_weights): 1 (default) those
+        of 4 M weights and more, 2 every slice the layout takes, 0 none.  Wide models, one sequence; same results either way."""
         check(self._lib.spb_shard_engine_set_prepared_weights(self._h, int(level)))
 
     def set_exchange_fold(self, on: bool) -> None:
         """Wide models, one sequence, several ranks: whether the kernel that consumes a gathered vector performs the
-        exchange itself (default) or a launch of its own does.  Same results either way."""
+        exchange itself or a launch of its own does (default).  Same results either way."""
         check(self._lib.spb_shard_engine_set_exchange_fold(self._h, int(bool(on))))
 
     def weight_bytes(self) -> int:

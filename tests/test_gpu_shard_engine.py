@@ -88,6 +88,7 @@ def test_a_silent_peer_ends_in_a_timeout_not_a_hang(wide):
     model = synth.random_model(synth.TINY, seed=44)
     dm = synth.DeviceRandomModel(WIDE, seed=44) if wide else DeviceModel(model)
     eng = ShardEngine(dm, rank=0, world=2, timeout_ms=20, connect=False)
+    eng.set_exchange_fold(wide)
     fake_peer = torch.zeros(eng.exchange_bytes, dtype=torch.uint8, device="cuda")
     eng.set_peer_pointers([0, fake_peer.data_ptr()])
     with pytest.raises(_lib.SpbError) as err:
