@@ -1019,11 +1019,11 @@ def bench_sharded(args, rank, world, dist):
     full.config = cfg
     full.layers = [full.layers[0]] * L  # ShardEngine clones the rank's slices layer by layer
     results = {}
-    runs = [(1, False), (64, False)] + ([(1, True)] if world > 1 else [])
+    runs = [(1, 2), (64, 2)] + ([(1, 0)] if world > 1 else [])
     for batch, fold in runs:
         eng = ShardEngine(full, rank=rank, world=world, batch=batch, group=ctl)
-        if fold:  # the exchanges inside the kernels that consume the gathered vectors instead of launches of their own
-            eng.set_exchange_fold(True)
+        if fold != 2:  # the exchanges as launches of their own instead of in the producers' epilogues
+            eng.set_exchange_fold(fold)
         rng = np.random.default_rng(11)
         prompts = rng.integers(0, cfg["vocab_size"], (args.shard_prompt, batch)).astype(np.int32)
         warm = eng.generate(prompts[:4], 2)  # graph capture, page-in
@@ -1040,7 +1040,7 @@ def bench_sharded(args, rank, world, dist):
         kv_bytes = 2 * L * batch * (cfg["num_key_value_heads"] // world if world <= cfg["num_key_value_heads"] else 1) * \
             (args.shard_prompt + args.shard_tokens // 2) * cfg["head_dim"] * 2
         my_bytes = eng.weight_bytes() + kv_bytes
-        results[f"batch{batch}_exchange_in_consumer" if fold else f"batch{batch}"] = {
+        results[f"batch{batch}" if fold == 2 else f"batch{batch}_exchange_as_launch"] = {
             "tok_s": batch * args.shard_tokens / dt, "ms_per_step": 1e3 * step_s,
             "prompt_s": t_prompt, "prompt_tok_s": batch * (args.shard_prompt - 1) / t_prompt,
             "per_gpu_bytes_per_step": int(my_bytes), "per_gpu_hbm_gbs": my_bytes / step_s / 1e9,
@@ -1056,7 +1056,9 @@ def bench_sharded(args, rank, world, dist):
                     "weights": "one layer drawn at random, uploaded as a separate copy per layer (the HBM traffic is that "
                                "of distinct layers)"}
     out["what"] = ("row-sharded decode: every ternary matrix and the LM head split by output rows over the ranks, slices "
-                   "exchanged inside the captured step by a kernel that stores them into every peer's buffer over NVLink "
+                   "exchanged inside the captured step over NVLink: the single-sequence step stores a slice from the epilogue "
+                   "of the kernel that computes it, as tagged words, into every rank's staging area, where the consuming "
+                   "kernel polls it (bounded); the batched step by a kernel that stores the slices into every peer's buffer "
                    "and waits (bounded) for the peers' flags; wall clock around generate(), max over ranks")
     return out
 

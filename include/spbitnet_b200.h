@@ -448,11 +448,15 @@ int spb_shard_engine_set_timeout_ms(spb_shard_engine* e, int ms);
  * matrix on the quantised vector; elsewhere the setting has no effect.  The copies are the engine's (as large as
  * the slices); results are the same bit for bit.  May be called before or after the slices are set. */
 int spb_shard_engine_set_prepared_weights(spb_shard_engine* e, int on);
-/* Single-sequence step of wide models on several ranks: 1 the kernel that consumes a gathered vector (one block)
- * sends this rank's slice and collects the peers' itself, as {data, sequence number} words; 0 (default) a launch of
- * its own does (the form every other step uses; measured quicker on two GPUs, 1.58 against 1.62 ms per step of 16
- * layers).  Same results bit for bit; the waits are bounded the same way. */
-int spb_shard_engine_set_exchange_fold(spb_shard_engine* e, int on);
+/* How the single-sequence step of a wide model exchanges slices between the ranks:
+ *   2 (default) the kernel that computes a slice (attention merge, prepared GEMV) stores it from its epilogue, as
+ *     {two halves, sequence number} words, straight into every rank's staging area over NVLink, and the kernel that
+ *     consumes the gathered vector polls its local staging area: no exchange launch and no gathered copy (a slice
+ *     whose matrix has no prepared copy falls back to form 0);
+ *   1 the consuming kernel (one block) sends this rank's slice and collects the peers' itself;
+ *   0 a launch of its own does both (the form every other step uses).
+ * Same results bit for bit; the waits are bounded the same way in every form. */
+int spb_shard_engine_set_exchange_fold(spb_shard_engine* e, int form);
 int spb_shard_engine_reset(spb_shard_engine* e);
 int spb_shard_engine_seq_len(const spb_shard_engine* e);
 /* One decode step: tokens[batch] (HOST) enter at the current position; synchronises.  Afterwards the rank's logits

@@ -23,12 +23,13 @@ template <int G>
 __global__ void __launch_bounds__(kAttnThreads) attn_split_kernel(
     const __half* __restrict__ Q, const __half* __restrict__ K, const __half* __restrict__ V,
     float* __restrict__ scratch, int num_kv_heads, int head_dim, int max_seq_len, int nsplit_max,
-    float scale, int seq_len_arg, const int* __restrict__ d_pos, unsigned* counters, __half* out) {
+    float scale, int seq_len_arg, const int* __restrict__ d_pos, unsigned* counters, __half* out, const LlFan fan) {
     extern __shared__ __align__(16) uint8_t attn_sm[];
     __shared__ int s_last;
     grid_dep_launch();
     grid_dep_wait();
     const int seq_len = d_pos ? (*d_pos + 1) : seq_len_arg;
+    const unsigned fan_tag = fan.ndst ? *reinterpret_cast<const volatile unsigned*>(fan.seq) + 1u : 0u;
     const int kvh = blockIdx.x, split = blockIdx.y;
     if (split * attn_chunk(seq_len) >= seq_len) return;
     attn_chunk_block<G>(Q, K, V, scratch, kvh, split, head_dim, max_seq_len, nsplit_max, scale, seq_len, attn_sm);
@@ -46,7 +47,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_split_kernel(
     }
     __syncthreads();
     if (s_last)
-        attn_merge_group<G>(scratch, out, kvh, head_dim, nsplit_max, attn_nsplit(seq_len), reinterpret_cast<float*>(attn_sm));
+        attn_merge_group<G>(scratch, out, kvh, head_dim, nsplit_max, attn_nsplit(seq_len), reinterpret_cast<float*>(attn_sm),
+                            fan.ndst ? &fan : nullptr, fan_tag);
 }
 
 template <int G>
@@ -64,8 +66,10 @@ __global__ void __launch_bounds__(kAttnThreads) attn_combine_kernel(const float*
 // seq_len is taken from *d_pos + 1 when d_pos is given (graph replay), else from seq_len.
 int decode_attention_split(const void* Q, const void* K, const void* V, void* out, int num_heads,
                            int num_kv_heads, int head_dim, int max_seq_len, int seq_len, const int* d_pos,
-                           float scale, float* scratch, void* stream, unsigned* counters) {
+                           float scale, float* scratch, void* stream, unsigned* counters, const LlFan* fan) {
     const char* name = "decode_attention_split";
+    if (fan && (!counters || (num_heads * head_dim) % 2)) return fail(SPB_E_INVALID, "%s: a fan-out wants the merge in the launch", name);
+    const LlFan fanv = fan ? *fan : LlFan{};
     if (num_heads % num_kv_heads) return fail(SPB_E_UNSUPPORTED, "%s: %d heads over %d KV heads", name, num_heads, num_kv_heads);
     const int G = num_heads / num_kv_heads;
     if (!decode_attention_split_supported(num_heads, num_kv_heads, head_dim) ||
@@ -87,7 +91,7 @@ int decode_attention_split(const void* Q, const void* K, const void* V, void* ou
         if ((rc = ensure_dynamic_smem(name, attn_combine_kernel<GG>, msmem))) return rc;                   \
         rc = launch(name, attn_split_kernel<GG>, grid, dim3(kAttnThreads), smem, stream, q, k, v, scratch, \
                     num_kv_heads, head_dim, max_seq_len, nsplit_max, scale, seq_len, d_pos, counters,      \
-                    static_cast<__half*>(out));                                                            \
+                    static_cast<__half*>(out), fanv);                                                      \
         if (rc || counters) return rc;                                                                     \
         return launch("attn_combine", attn_combine_kernel<GG>, dim3(num_kv_heads), dim3(kAttnThreads), msmem, stream, \
                       static_cast<const float*>(scratch), static_cast<__half*>(out), head_dim, nsplit_max, seq_len, d_pos);

@@ -12,6 +12,7 @@
 // and writes the un-normalised partial result {max, sum, sum(e * V)} of every head to the scratch buffer.  The
 // chunks of a head are merged with the usual log-sum-exp weights (attn_merge_group).
 #pragma once
+#include "ll_words.cuh"
 #include "spb_common.cuh"
 
 namespace spb {
@@ -53,36 +54,6 @@ struct LlSource {
     long long limit;     // cycles
     int* fail;           // shared-memory flag
 };
-__device__ __forceinline__ uint32_t ll_read1(const uint2* p, unsigned tag, long long limit, int* fail) {
-    uint32_t d, t;
-    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(d), "=r"(t) : "l"(p));
-    if (t == tag) return d;
-    const long long t0 = clock64();
-    for (;;) {
-        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(d), "=r"(t) : "l"(p));
-        if (t == tag) return d;
-        if (clock64() - t0 > limit) *fail = 1;
-        if (*reinterpret_cast<volatile int*>(fail)) return d;  // this wait or another one of the block ran out
-    }
-}
-// four consecutive words = eight halves
-__device__ __forceinline__ uint4 ll_read4(const uint2* p, unsigned tag, long long limit, int* fail) {
-    uint32_t d[4], t[4];
-    long long t0 = 0;
-    for (int spin = 0;; ++spin) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(d[i]), "=r"(t[i]) : "l"(p + i));
-        if (t[0] == tag && t[1] == tag && t[2] == tag && t[3] == tag) break;
-        if (spin == 0) t0 = clock64();
-        else if (clock64() - t0 > limit) *fail = 1;
-        if (*reinterpret_cast<volatile int*>(fail)) break;  // this wait or another one of the block ran out
-    }
-    return make_uint4(d[0], d[1], d[2], d[3]);
-}
-__device__ __forceinline__ void ll_write(uint2* p, uint32_t data, unsigned tag) {
-    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(data), "r"(tag) : "memory");
-}
-
 // Work of one block on chunk `split` of KV head `kvh` (split * attn_chunk(seq_len) < seq_len).  head_dim is a
 // multiple of 8 and at most 256; Q, K, V are 16-byte aligned.  They and the scratch are accessed with L2 loads
 // and plain stores: in the persistent decode kernel other blocks of the same grid wrote them.
@@ -212,10 +183,11 @@ __host__ __device__ inline size_t attn_merge_smem_floats(int G, int max_seq_len)
 //   1. the chunk maxima and sums of every head into shared memory (one round of loads);
 //   2. warp g takes head g: M = max, w[s] = exp(m[s] - M) into shared memory, L = sum l[s] * w[s];
 //   3. thread t takes (head, dim) pairs t, t + 256, ..: sum_s w[s] * o[s][d] with eight loads in flight.
-// With ll_out the result goes out as tagged words (two halves each) instead of to `out`.
+// With `fan` the result goes out as tagged words (two halves each) to every destination of the fan instead of to
+// `out`; word i of a destination holds elements 2 i, 2 i + 1 of the launch's output vector.
 template <int G>
 __device__ __forceinline__ void attn_merge_group(const float* scratch, __half* out, int kvh, int head_dim,
-                                                 int nsplit_max, int nsplit, float* sm, uint2* ll_out = nullptr,
+                                                 int nsplit_max, int nsplit, float* sm, const LlFan* fan = nullptr,
                                                  unsigned ll_tag = 0) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const size_t hstride = static_cast<size_t>(nsplit_max) * (head_dim + 2);
@@ -262,12 +234,12 @@ __device__ __forceinline__ void attn_merge_group(const float* scratch, __half* o
             for (int k = 0; k < 8; ++k) o = fmaf(v[k], s + k < nsplit ? wg[s + k] : 0.0f, o);
         }
         const __half h = __float2half_rn(__fmul_rn(o, inv[g]));
-        if (!ll_out) {
+        if (!fan) {
             out[(static_cast<size_t>(kvh) * G + g) * head_dim + d] = h;
         } else {  // the even dim of a pair stores both (G * head_dim is a multiple of 16: a pair is active together)
             const uint32_t mine = __half_as_ushort(h);
             const uint32_t next = __shfl_down_sync(__activemask(), mine, 1);
-            if ((d & 1) == 0) ll_write(ll_out + (((static_cast<size_t>(kvh) * G + g) * head_dim + d) >> 1), mine | (next << 16), ll_tag);
+            if ((d & 1) == 0) ll_fan_write(*fan, ((static_cast<size_t>(kvh) * G + g) * head_dim + d) >> 1, mine | (next << 16), ll_tag);
         }
     }
 }

@@ -557,9 +557,13 @@ __global__ void __launch_bounds__(kPdThreads, 1) decode_persistent_kernel(const 
                 s_flag[1] = last;
             }
             __syncthreads();
-            if (s_flag[1])  // every chunk of this KV head is written: merge them for its G query heads
+            if (s_flag[1]) {  // every chunk of this KV head is written: merge them for its G query heads
+                LlFan fan{};
+                fan.dst[0] = ll_a;
+                fan.ndst = 1;
                 attn_merge_group<G>(m.scratch, m.attn, kvh, m.hd, nsplit_max, nsplit, reinterpret_cast<float*>(attn_sm),
-                                    LL ? ll_a : nullptr, tag);
+                                    LL ? &fan : nullptr, tag);
+            }
             __syncthreads();
         }
         mark(5);

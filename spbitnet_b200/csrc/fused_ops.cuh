@@ -5,6 +5,7 @@
 // sequences instead (batched decode): all at position *d_pos, sequence b's K and V caches b * seq_stride elements
 // after the first sequence's.
 #pragma once
+#include "ll_words.cuh"
 #include "spb_common.cuh"
 
 namespace spb {
@@ -42,9 +43,11 @@ int decode_attention_pos(const void* Q, const void* K, const void* V, void* out,
 // attention.cu: split-KV decode attention.  seq_len comes from *d_pos + 1 when d_pos is given.
 // `counters` (optional): num_kv_heads zeroed words; with them the merge of a KV head's chunks runs inside the same
 // launch, in the block that finishes last, instead of as a second kernel.  They are left at zero.
+// `fan` (with counters): the output goes out as tagged words to every destination of the fan instead of to `out`.
 int decode_attention_split(const void* Q, const void* K, const void* V, void* out, int num_heads,
                            int num_kv_heads, int head_dim, int max_seq_len, int seq_len, const int* d_pos,
-                           float scale, float* scratch, void* stream, unsigned* counters = nullptr);
+                           float scale, float* scratch, void* stream, unsigned* counters = nullptr,
+                           const LlFan* fan = nullptr);
 size_t decode_attention_scratch_bytes(int num_heads, int head_dim, int max_seq_len);
 // the split kernel takes GQA groups of up to 8 heads and head dims that are multiples of 8 up to 256 (16-byte aligned Q, K, V)
 bool decode_attention_split_supported(int num_heads, int num_kv_heads, int head_dim);
@@ -90,8 +93,11 @@ struct RopeScatter {
 // Up to three BitLinears of the same width on prepared weights and one quantised activation, one launch
 // (gemv_prepared.cu).  With `rope` they are q, k, v: q and k rows are rotated for the position in *rope->d_pos, k and
 // v rows go to the cache rows of that position (out_half[1], out_half[2] are then not written).
+// With `fans` (one per matrix, at most two matrices, even row counts) the rows go out as tagged words to every
+// destination of the matrix's fan instead of to out_half.
 int prepared_bitlinear_q8_group(const void* const* prep, void* const* out_half, const float* gamma, const int* rows, int n,
-                                const int8_t* xq, const float* d_absmax, int cols, const RopeScatter* rope, void* stream);
+                                const int8_t* xq, const float* d_absmax, int cols, const RopeScatter* rope, void* stream,
+                                const LlFan* fans = nullptr);
 // activation = quantised rms_norm(w_norm) of x_out = x_in + [rms_norm(w_sub)](delta); block 0 writes x_out.
 // With `rope` the group must be q, k, v (see RopeScatter).
 int bitlinear_resnorm_group(const BitLinearGroup& g, const void* x_in, const void* delta, const float* w_sub,

@@ -68,6 +68,7 @@ struct GpArgs {
     int ks, ks_log2;     // warps per tile (power of two <= 8); a block holds 8 / ks tiles
     int qpw;             // quads per warp
     RopeScatter rope;    // d_pos set: the matrices are q, k, v; q and k rows are rotated, k and v rows go to the cache
+    LlFan fan[2];        // ndst > 0: the rows of matrix 0 / 1 go out as tagged words (half outputs, no rotation)
 };
 
 // Eight bitmaps (two of four bits set each) -> eight index pairs {low index | high index << 2}.
@@ -198,6 +199,9 @@ __global__ void __launch_bounds__(kGpThreads, kGpBlocksPerSm) gemv_prepared_kern
     int rope_pos = 0;
     if (a.out_mode != GP_OUT_I32) asm volatile("ld.global.f32 %0, [%1];" : "=f"(absmax_early) : "l"(a.d_absmax));
     if (a.rope.d_pos) asm volatile("ld.global.s32 %0, [%1];" : "=r"(rope_pos) : "l"(a.rope.d_pos));
+    unsigned fan_tag = 0;  // both matrices of a launch belong to the same exchange
+    if (a.fan[0].ndst) asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(fan_tag) : "l"(a.fan[0].seq));
+    fan_tag += 1u;
     grid_dep_launch();
     for (int q = tid; q < (a.cols >> 4); q += kGpThreads) {
         const uint4 xv = __ldg(reinterpret_cast<const uint4*>(a.x) + q);
@@ -240,6 +244,12 @@ __global__ void __launch_bounds__(kGpThreads, kGpBlocksPerSm) gemv_prepared_kern
                     static_cast<float*>(y)[row] = f;
                     if (a.y_acc) a.y_acc[row] = acc;
                 }
+            } else if (a.fan[0].ndst) {
+                // rows 2 i, 2 i + 1 are neighbours in the warp: the even one stores both halves and the tag, once per
+                // destination (the peers' staging areas over NVLink, this GPU's own among them)
+                const uint32_t lo = __half_as_ushort(__float2half_rn(f));
+                const uint32_t hi = __shfl_down_sync(0xFFFFFFFFu, lo, 1);
+                if (valid && !(r & 1)) ll_fan_write(mi == 1 ? a.fan[1] : a.fan[0], static_cast<size_t>(row >> 1), lo | (hi << 16), fan_tag);
             } else if (!a.rope.d_pos) {
                 if (valid) static_cast<__half*>(y)[row] = __float2half_rn(f);
             } else {
@@ -278,7 +288,7 @@ struct GpMatDesc {
 };
 
 static int gp_launch(const char* name, const GpMatDesc* mats, int nmat, const int8_t* x, int32_t* y_acc, const float* d_absmax,
-                     int out_mode, int cols, const RopeScatter* rope, void* stream) {
+                     int out_mode, int cols, const RopeScatter* rope, void* stream, const LlFan* fans = nullptr) {
     if (nmat < 1 || nmat > kGpMaxMats) return fail(SPB_E_INVALID, "%s: %d matrices", name, nmat);
     if (cols < 0) return fail(SPB_E_INVALID, "%s: negative size", name);
     GpArgs a{};
@@ -303,6 +313,14 @@ static int gp_launch(const char* name, const GpMatDesc* mats, int nmat, const in
             mats[1].rows % rope->head_dim || mats[1].rows != mats[2].rows || !rope->d_pos || !rope->kcache || !rope->vcache)
             return fail(SPB_E_INVALID, "%s: rotation wants q, k, v with whole heads and half outputs", name);
         a.rope = *rope;
+    }
+    if (fans) {
+        if (nmat > 2 || rope || out_mode != GP_OUT_F16) return fail(SPB_E_INVALID, "%s: a fan-out wants one or two matrices with half outputs", name);
+        for (int i = 0; i < nmat; ++i) {
+            if (mats[i].rows % 2 || fans[i].ndst < 1 || fans[i].ndst > kLlMaxDest || !fans[i].seq || fans[i].seq != fans[0].seq)
+                return fail(SPB_E_INVALID, "%s: bad fan-out", name);
+            a.fan[i] = fans[i];
+        }
     }
     a.nmat = nmat;
     a.x = x; a.y_acc = y_acc; a.d_absmax = d_absmax; a.out_mode = out_mode;
@@ -355,11 +373,12 @@ int prepared_bitlinear_q8(const void* prep, const int8_t* xq, void* out_half, co
 // they are q, k, v: q and k rows are rotated for the position in *rope->d_pos, k and v rows go to the cache rows of
 // that position (out[1], out[2] are not written)
 int prepared_bitlinear_q8_group(const void* const* prep, void* const* out_half, const float* gamma, const int* rows, int n,
-                                const int8_t* xq, const float* d_absmax, int cols, const RopeScatter* rope, void* stream) {
+                                const int8_t* xq, const float* d_absmax, int cols, const RopeScatter* rope, void* stream,
+                                const LlFan* fans) {
     GpMatDesc m[kGpMaxMats];
     if (n < 1 || n > kGpMaxMats) return fail(SPB_E_INVALID, "prepared_bitlinear_q8_group: %d matrices", n);
     for (int i = 0; i < n; ++i) m[i] = GpMatDesc{prep[i], out_half[i], gamma[i], rows[i]};
-    return gp_launch("prepared_bitlinear_q8_group", m, n, xq, nullptr, d_absmax, GP_OUT_F16, cols, rope, stream);
+    return gp_launch("prepared_bitlinear_q8_group", m, n, xq, nullptr, d_absmax, GP_OUT_F16, cols, rope, stream, fans);
 }
 
 }  // namespace spb

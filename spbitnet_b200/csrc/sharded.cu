@@ -173,6 +173,9 @@ struct LArgs {
     uint8_t* peer[kMaxWorld];
     LSeg seg[2];
     int nseg, rows, world, rank;
+    int direct;                     // the producers already stored the words into the staging areas (their epilogues):
+                                    // the consumer reads its vector from there (ll_gather8), nothing is sent or copied
+    const uint8_t* self;            // this rank's exchange buffer (peer[rank])
     unsigned* seqno;
     unsigned* done;
     int* status;
@@ -269,15 +272,53 @@ __global__ void __launch_bounds__(256) exchange_ll_kernel(const LArgs a) {
     }
 }
 
-// The same exchange as the first thing a single-block consumer kernel does (a.world > 1): the launch of its own
-// disappears, and so does the kernel boundary between the arrival of the data and its use.  The gathered vector is
-// in local memory, written by this block, when the function returns.
-__device__ __forceinline__ void exchange_ll_in_block(const LArgs& a) {
-    if (a.world <= 1) return;
+// Direct form (a.direct): elements 8 run .. 8 run + 7 of gathered vector `seg`, read as four tagged words from the
+// staging area of the rank that owns them (slices are multiples of 8 elements, so a run has one owner).  The poll is
+// bounded like every wait for a peer; when it runs out the status is raised and the data is whatever was there.
+__device__ __forceinline__ uint4 ll_gather8(const LArgs& a, int seg, int run, unsigned seq, bool& alive) {
+    const LSeg& g = a.seg[seg];
+    const uint32_t byte = 16u * static_cast<uint32_t>(run);
+    uint32_t owner = 0, first = 0;
+#pragma unroll
+    for (int p = 0; p < kMaxWorld; ++p)
+        if (p < a.world && byte >= g.off[p] && byte < g.off[p] + g.len[p]) {
+            owner = p;
+            first = g.off[p];
+        }
+    const uint8_t* src = a.self + g.ll_off + static_cast<size_t>(owner) * g.ll_stride + 2u * static_cast<size_t>(byte - first);
+    uint32_t d0, t0, d1, t1, d2, t2, d3, t3;
+    unsigned spins = 0;
+    unsigned long long started = 0;
+    for (;;) {
+        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(d0), "=r"(t0), "=r"(d1), "=r"(t1) : "l"(src) : "memory");
+        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(d2), "=r"(t2), "=r"(d3), "=r"(t3) : "l"(src + 16) : "memory");
+        if ((t0 == seq && t1 == seq && t2 == seq && t3 == seq) || !alive) break;
+        if ((++spins & 255u) == 0) {
+            const unsigned long long now = globaltimer_ns();
+            if (started == 0) started = now;
+            if (now - started > a.timeout_ns || *reinterpret_cast<volatile int*>(a.broken) != 0) {
+                *reinterpret_cast<volatile int*>(a.broken) = 1;
+                atomicExch_system(a.status, 1);
+                alive = false;
+            }
+        }
+    }
+    return make_uint4(d0, d1, d2, d3);
+}
+// What a kernel that consumes gathered vectors does first: nothing (one rank, or an exchange launch ran before it),
+// the whole exchange (a.world > 1, single block), or only the bookkeeping of the direct form.  Returns the sequence
+// number of the exchange.
+__device__ __forceinline__ unsigned consumer_exchange_begin(const LArgs& a, bool& alive) {
+    if (a.world <= 1) return 0u;
     const unsigned seq = *reinterpret_cast<volatile unsigned*>(a.seqno) + 1u;
+    if (a.direct) {
+        alive = *reinterpret_cast<volatile int*>(a.broken) == 0;
+        return seq;
+    }
     exchange_ll_run(a, threadIdx.x, blockDim.x, seq);
     __syncthreads();
     if (threadIdx.x == 0) *a.seqno = seq;
+    return seq;
 }
 
 // token of sequence b: prompt[pos * batch + b] while pos < n_prompt, else next[b]; row copy of the embedding
@@ -527,7 +568,9 @@ __global__ void __launch_bounds__(kWideThreads / CL) wide_residual_norm_quant_ke
     const int vt = wide_tid<CL>(), vec = blockIdx.x / CL;
     grid_dep_launch();
     grid_dep_wait();
-    exchange_ll_in_block(xin);  // delta, gathered from the ranks' slices
+    bool alive = true;
+    const unsigned xseq = consumer_exchange_begin(xin, alive);  // delta is gathered from the ranks' slices
+    const bool direct = xin.world > 1 && xin.direct;
     const size_t off = static_cast<size_t>(vec) * n;
     const int runs = n >> 3;
     constexpr int kRuns = 1;
@@ -539,7 +582,7 @@ __global__ void __launch_bounds__(kWideThreads / CL) wide_residual_norm_quant_ke
         for (int k = 0; k < kRuns; ++k) {
             const int r = vt + k * kWideThreads;
             if (r < runs) {
-                unpack8(*reinterpret_cast<const uint4*>(delta + off + 8 * r), d[k]);
+                unpack8(direct ? ll_gather8(xin, 0, r, xseq, alive) : *reinterpret_cast<const uint4*>(delta + off + 8 * r), d[k]);
                 unpack8(*reinterpret_cast<const uint4*>(x + off + 8 * r), v[k]);
                 load8f(w + 8 * r, wv[k]);
                 if (sub_w) load8f(sub_w + 8 * r, sw[k]);
@@ -598,6 +641,7 @@ __global__ void __launch_bounds__(kWideThreads / CL) wide_residual_norm_quant_ke
     }
     const float absmax = wide_bmax<CL>(m, sh[2]);
     if (vt == 0) d_absmax[vec] = absmax;
+    if (direct && vt == 0) *xin.seqno = xseq;  // every thread read the number before the reduction above
     const float qs = quant_scale(absmax);
 #pragma unroll
     for (int k = 0; k < kRuns; ++k) {
@@ -625,7 +669,9 @@ __global__ void __launch_bounds__(kWideThreads / CL) wide_relu2_norm_quant_kerne
             if (r < runs) asm volatile("prefetch.global.L1 [%0];" ::"l"(sub_w + 8 * r));
         }
     grid_dep_wait();
-    exchange_ll_in_block(xin);  // gate and up, gathered from the ranks' slices
+    bool alive = true;
+    const unsigned xseq = consumer_exchange_begin(xin, alive);  // gate and up are gathered from the ranks' slices
+    const bool direct = xin.world > 1 && xin.direct;
     const size_t off = static_cast<size_t>(vec) * n;
     float v[kWideRuns][8];  // the products stay in registers
     float s = 0.0f;
@@ -634,8 +680,8 @@ __global__ void __launch_bounds__(kWideThreads / CL) wide_relu2_norm_quant_kerne
         const int r = vt + k * kWideThreads;
         if (r < runs) {
             float g[8], u[8];
-            unpack8(*reinterpret_cast<const uint4*>(gate + off + 8 * r), g);
-            unpack8(*reinterpret_cast<const uint4*>(up + off + 8 * r), u);
+            unpack8(direct ? ll_gather8(xin, 0, r, xseq, alive) : *reinterpret_cast<const uint4*>(gate + off + 8 * r), g);
+            unpack8(direct ? ll_gather8(xin, 1, r, xseq, alive) : *reinterpret_cast<const uint4*>(up + off + 8 * r), u);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const float t = fmaxf(0.0f, g[i]);
@@ -663,6 +709,7 @@ __global__ void __launch_bounds__(kWideThreads / CL) wide_relu2_norm_quant_kerne
     }
     const float absmax = wide_bmax<CL>(m, sh[1]);
     if (vt == 0) d_absmax[vec] = absmax;
+    if (direct && vt == 0) *xin.seqno = xseq;  // every thread read the number before the reduction above
     const float qs = quant_scale(absmax);
 #pragma unroll
     for (int k = 0; k < kWideRuns; ++k) {
@@ -679,7 +726,9 @@ __global__ void __launch_bounds__(kWideThreads / CL) wide_absmax_quantize_kernel
     const int vt = wide_tid<CL>(), vec = blockIdx.x / CL;
     grid_dep_launch();
     grid_dep_wait();
-    exchange_ll_in_block(xin);
+    bool alive = true;
+    const unsigned xseq = consumer_exchange_begin(xin, alive);
+    const bool direct = xin.world > 1 && xin.direct;
     const size_t off = static_cast<size_t>(vec) * n;
     const int runs = n >> 3;
     float v[kWideRuns][8];
@@ -688,13 +737,14 @@ __global__ void __launch_bounds__(kWideThreads / CL) wide_absmax_quantize_kernel
     for (int k = 0; k < kWideRuns; ++k) {
         const int r = vt + k * kWideThreads;
         if (r < runs) {
-            unpack8(*reinterpret_cast<const uint4*>(in + off + 8 * r), v[k]);
+            unpack8(direct ? ll_gather8(xin, 0, r, xseq, alive) : *reinterpret_cast<const uint4*>(in + off + 8 * r), v[k]);
 #pragma unroll
             for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[k][i]));
         }
     }
     const float absmax = wide_bmax<CL>(m, sh);
     if (vt == 0) d_absmax[vec] = absmax;
+    if (direct && vt == 0) *xin.seqno = xseq;  // every thread read the number before the reduction above
     const float qs = quant_scale(absmax);
 #pragma unroll
     for (int k = 0; k < kWideRuns; ++k) {
@@ -828,7 +878,8 @@ struct spb_shard_engine {
     size_t off_flags = 0, off_attn = 0, off_o = 0, off_gate = 0, off_up = 0, off_down = 0, off_amax = 0;
     size_t ll_off[X_KINDS] = {};   // staging areas of the small-message exchange
     bool ll_ok[X_KINDS] = {};      // the kind's slices are small enough for it
-    bool fold_exchange = false;    // wide single-sequence step: the consumer kernel of a vector performs its exchange
+    int fold_exchange = 2;         // wide single-sequence step: 0 exchanges are launches, 1 the consumer kernel of a vector
+                                   // performs its exchange, 2 the producer's epilogue sends and the consumer receives
     int ident[kMaxWorld + 1] = {0, 1, 2, 3, 4, 5, 6, 7, 8};
     int* status = nullptr;  // pinned, mapped
     unsigned long long timeout_ns = 5000000000ull;
@@ -863,6 +914,8 @@ void make_ll_args(spb_shard_engine* e, int kind, const XSeg* segs, int nseg, con
         ll_at += static_cast<size_t>(g.ll_stride) * e->world;
     }
     l.nseg = nseg; l.rows = e->batch; l.world = e->world; l.rank = e->rank;
+    l.direct = 0;
+    l.self = e->peer[e->rank];
     l.seqno = e->counters + 2 * kind;
     l.done = e->counters + 2 * kind + 1;
     l.status = e->status;
@@ -936,7 +989,7 @@ int enqueue_step(spb_shard_engine* e, bool record) {
     // it sends this rank's slice and collects the peers' itself (small-message form) instead of a launch doing that.
     LArgs pend{};  // the exchange the next vector kernel performs (world == 0: none)
     auto exchange_or_defer = [&](int kind, const XSeg* sg, int nseg, const int* const* bd, const int* ub) -> int {
-        if (e->fold_exchange && e->wide && B == 1 && e->ll_ok[kind]) {
+        if (e->fold_exchange == 1 && e->wide && B == 1 && e->ll_ok[kind]) {
             make_ll_args(e, kind, sg, nseg, bd, ub, pend, nullptr);
             return SPB_OK;
         }
@@ -949,7 +1002,25 @@ int enqueue_step(spb_shard_engine* e, bool record) {
     };
     // One sequence and no exchange to perform inside: the vector kernels run as a cluster of eight blocks (eight SMs
     // pull the vector and its norm weights instead of one; same arithmetic, same results).
-    auto clustered = [&]() { return B == 1 && pend.world == 0; };
+    auto clustered = [&]() { return B == 1 && (pend.world == 0 || pend.direct); };
+    // Form 2: the kernel that computes this rank's slice stores it, as tagged words, straight into every rank's staging
+    // area (this rank's own included) from its epilogue, and the consumer reads its vector from the local staging
+    // area: no exchange launch, no gathered copy, and the NVLink crossing overlaps the producer's tail.  plan_direct
+    // prepares both sides of exchange `kind` when the form applies; the producer must then be one that takes a fan.
+    auto plan_direct = [&](int kind, const XSeg* sg, int nseg, const int* const* bd, const int* ub, LArgs& x, LlFan* fans) {
+        if (e->fold_exchange != 2 || !e->wide || B != 1 || alone || !e->ll_ok[kind]) return false;
+        x = LArgs{};
+        make_ll_args(e, kind, sg, nseg, bd, ub, x, nullptr);
+        x.direct = 1;
+        for (int i = 0; i < nseg; ++i) {
+            fans[i] = LlFan{};
+            for (int q = 0; q < e->world; ++q)
+                fans[i].dst[q] = reinterpret_cast<uint2*>(e->peer[q] + x.seg[i].ll_off + static_cast<size_t>(e->rank) * x.seg[i].ll_stride);
+            fans[i].ndst = e->world;
+            fans[i].seq = x.seqno;
+        }
+        return true;
+    };
     __half* attn_out = alone ? attn_full : e->attn;
     __half* o_out = alone ? o_full : e->o;
     __half* gate_out = alone ? gate_full : e->gate;
@@ -990,7 +1061,8 @@ int enqueue_step(spb_shard_engine* e, bool record) {
             if (!L[i]->prep) return false;
         return true;
     };
-    auto linear_group_prepared = [&](const Linear* const* L, __half* const* out, int n, const float* am, const RopeScatter* rope) {
+    auto linear_group_prepared = [&](const Linear* const* L, __half* const* out, int n, const float* am, const RopeScatter* rope,
+                                     const LlFan* fans = nullptr) {
         const void* prep[3];
         void* outs[3];
         float gamma[3];
@@ -998,7 +1070,7 @@ int enqueue_step(spb_shard_engine* e, bool record) {
         for (int i = 0; i < n; ++i) {
             prep[i] = L[i]->prep; outs[i] = out[i]; gamma[i] = L[i]->gamma; rows[i] = L[i]->rows;
         }
-        return prepared_bitlinear_q8_group(prep, outs, gamma, rows, n, e->xq, am, L[0]->cols, rope, s);
+        return prepared_bitlinear_q8_group(prep, outs, gamma, rows, n, e->xq, am, L[0]->cols, rope, s, fans);
     };
     // Wide models (hidden >= 4096): a matrix is tens of megabytes and its GEMV runs for tens of microseconds, so
     // throughput decides, not launch latency: the vector op runs once in a kernel of its own and every matrix goes
@@ -1010,7 +1082,7 @@ int enqueue_step(spb_shard_engine* e, bool record) {
             if (clustered())
                 return launch_clustered("wide_residual_norm_quant", wide_residual_norm_quant_kernel<kWideCluster>, dim3(kWideCluster),
                                         dim3(kWideThreads / kWideCluster), kWideCluster, s, delta, sub_w, x, w, xn_out, e->xq, am, H,
-                                        c.rms_norm_eps, LArgs{});
+                                        c.rms_norm_eps, take_pending());
             return launch("wide_residual_norm_quant", wide_residual_norm_quant_kernel<1>, dim3(B), dim3(kWideThreads), 0, s, delta, sub_w,
                           x, w, xn_out, e->xq, am, H, c.rms_norm_eps, take_pending());
         }
@@ -1053,23 +1125,31 @@ int enqueue_step(spb_shard_engine* e, bool record) {
         }
         if (!rope_done && (rc = rope_scatter(e->q, e->k, e->v, kc, vc, e->nh_loc, e->nkv_loc, hd, c.max_position_embeddings, c.rope_theta,
                                e->d_pos, s, B, B > 1 ? e->seq_stride : 0))) return rc;
+        const XSeg sg_attn = seg_of(e->attn, e->off_attn, static_cast<size_t>(e->kv0[r]) * e->group_heads * hd * 2,
+                                    static_cast<size_t>(qdim) * 2, static_cast<size_t>(e->nh_loc) * hd * 2);
+        const int* bd_attn[1] = {e->kv0};
+        const int ub_attn[1] = {e->group_heads * hd * 2};
+        LArgs xd{};
+        LlFan fan[2];
+        bool sent = false;  // the producer's epilogue sent the slice (form 2)
         if (B == 1 && e->split_attention) {
             // (a batched form of the split kernel, one block per (KV head, chunk, sequence), was measured slower for
             // 64 sequences than one block per (head, sequence): 54.6 against 51.6 ms per step)
+            sent = plan_direct(X_ATTN, &sg_attn, 1, bd_attn, ub_attn, xd, fan);
             if ((rc = decode_attention_split(e->q, kc, vc, attn_out, e->nh_loc, e->nkv_loc, hd, c.max_position_embeddings, 0,
-                                             e->d_pos, attn_scale, e->attn_scratch, s, e->attn_counters))) return rc;
+                                             e->d_pos, attn_scale, e->attn_scratch, s, e->attn_counters, sent ? fan : nullptr))) return rc;
         } else if ((rc = decode_attention_pos(e->q, kc, vc, attn_out, e->nh_loc, e->nkv_loc, hd, c.max_position_embeddings,
                                               attn_scale, e->d_pos, s, B, B > 1 ? e->seq_stride : 0))) {
             return rc;
         }
-        if (!alone) {
-            const XSeg sg = seg_of(e->attn, e->off_attn, static_cast<size_t>(e->kv0[r]) * e->group_heads * hd * 2,
-                                   static_cast<size_t>(qdim) * 2, static_cast<size_t>(e->nh_loc) * hd * 2);
-            const int* bd[1] = {e->kv0};
-            const int ub[1] = {e->group_heads * hd * 2};
-            if ((rc = exchange_or_defer(X_ATTN, &sg, 1, bd, ub))) return rc;
-        }
+        if (sent) pend = xd;
+        else if (!alone && (rc = exchange_or_defer(X_ATTN, &sg_attn, 1, bd_attn, ub_attn))) return rc;
         // ---- o_proj rows ----
+        const XSeg sg_o = seg_of(e->o, e->off_o, static_cast<size_t>(e->hrow[r]) * 2, static_cast<size_t>(H) * 2,
+                                 static_cast<size_t>(e->h_loc) * 2);
+        const int* bd_h[1] = {e->hrow};
+        const int ub_h[1] = {2};
+        sent = false;
         if (B == 1 && fused1) {
             if ((rc = bitlinear_amax_group(make_group(g1o, o1o, 1), attn_full, s))) return rc;
         } else {
@@ -1077,7 +1157,7 @@ int enqueue_step(spb_shard_engine* e, bool record) {
                 if (clustered()) {
                     if ((rc = launch_clustered("wide_absmax_quantize", wide_absmax_quantize_kernel<kWideCluster>, dim3(kWideCluster),
                                                dim3(kWideThreads / kWideCluster), kWideCluster, s, static_cast<const __half*>(attn_full),
-                                               e->xq, am1, qdim, LArgs{}))) return rc;
+                                               e->xq, am1, qdim, take_pending()))) return rc;
                 } else if ((rc = launch("wide_absmax_quantize", wide_absmax_quantize_kernel<1>, dim3(B), dim3(kWideThreads), 0, s,
                                         static_cast<const __half*>(attn_full), e->xq, am1, qdim, take_pending()))) {
                     return rc;
@@ -1086,19 +1166,26 @@ int enqueue_step(spb_shard_engine* e, bool record) {
                 return rc;
             }
             if (B == 1) {
-                if ((rc = linear_1(L.lin[3], am1, o_out))) return rc;
+                sent = L.lin[3].prep && plan_direct(X_O, &sg_o, 1, bd_h, ub_h, xd, fan);
+                if (sent) {
+                    if ((rc = linear_group_prepared(g1o, o1o, 1, am1, nullptr, fan))) return rc;
+                } else if ((rc = linear_1(L.lin[3], am1, o_out))) {
+                    return rc;
+                }
             } else if ((rc = linear_b(L.lin[3], am1, o_out, e->acc))) {
                 return rc;
             }
         }
-        if (!alone) {
-            const XSeg sg = seg_of(e->o, e->off_o, static_cast<size_t>(e->hrow[r]) * 2, static_cast<size_t>(H) * 2,
-                                   static_cast<size_t>(e->h_loc) * 2);
-            const int* bd[1] = {e->hrow};
-            const int ub[1] = {2};
-            if ((rc = exchange_or_defer(X_O, &sg, 1, bd, ub))) return rc;
-        }
+        if (sent) pend = xd;
+        else if (!alone && (rc = exchange_or_defer(X_O, &sg_o, 1, bd_h, ub_h))) return rc;
         // ---- gate / up rows ----
+        const XSeg sg_gu[2] = {seg_of(e->gate, e->off_gate, static_cast<size_t>(e->irow[r]) * 2, static_cast<size_t>(inter) * 2,
+                                      static_cast<size_t>(e->i_loc) * 2),
+                               seg_of(e->up, e->off_up, static_cast<size_t>(e->irow[r]) * 2, static_cast<size_t>(inter) * 2,
+                                      static_cast<size_t>(e->i_loc) * 2)};
+        const int* bd_gu[2] = {e->irow, e->irow};
+        const int ub_gu[2] = {2, 2};
+        sent = false;
         if (B == 1 && fused1) {
             if ((rc = bitlinear_resnorm_group(make_group(g2, o2, 2), cur, o_full, L.norm[2], L.norm[1], other, c.rms_norm_eps, s))) return rc;
             std::swap(cur, other);
@@ -1106,7 +1193,8 @@ int enqueue_step(spb_shard_engine* e, bool record) {
             if ((rc = res_norm_quant(o_full, L.norm[2], cur, L.norm[1], nullptr, am0))) return rc;
             if (B == 1 && e->wide) {
                 if (all_prepared(g2, 2)) {
-                    if ((rc = linear_group_prepared(g2, o2, 2, am0, nullptr))) return rc;
+                    sent = plan_direct(X_GU, sg_gu, 2, bd_gu, ub_gu, xd, fan);
+                    if ((rc = linear_group_prepared(g2, o2, 2, am0, nullptr, sent ? fan : nullptr))) return rc;
                 } else if ((rc = linear_side_by_side(g2, o2, 2, am0))) {
                     return rc;
                 }
@@ -1117,16 +1205,12 @@ int enqueue_step(spb_shard_engine* e, bool record) {
                 if ((rc = linear_b(L.lin[5], am0, up_out, e->acc + e->acc_third))) return rc;
             }
         }
-        if (!alone) {
-            const XSeg sg[2] = {seg_of(e->gate, e->off_gate, static_cast<size_t>(e->irow[r]) * 2, static_cast<size_t>(inter) * 2,
-                                       static_cast<size_t>(e->i_loc) * 2),
-                                seg_of(e->up, e->off_up, static_cast<size_t>(e->irow[r]) * 2, static_cast<size_t>(inter) * 2,
-                                       static_cast<size_t>(e->i_loc) * 2)};
-            const int* bd[2] = {e->irow, e->irow};
-            const int ub[2] = {2, 2};
-            if ((rc = exchange_or_defer(X_GU, sg, 2, bd, ub))) return rc;
-        }
+        if (sent) pend = xd;
+        else if (!alone && (rc = exchange_or_defer(X_GU, sg_gu, 2, bd_gu, ub_gu))) return rc;
         // ---- down rows: relu2 * up and ffn_sub_norm need the whole vectors ----
+        const XSeg sg_down = seg_of(e->down, e->off_down, static_cast<size_t>(e->hrow[r]) * 2, static_cast<size_t>(H) * 2,
+                                    static_cast<size_t>(e->h_loc) * 2);
+        sent = false;
         if (B == 1 && fused1) {
             if ((rc = bitlinear_relu2_group(make_group(g1d, o1d, 1), gate_full, up_full, L.norm[3], c.rms_norm_eps, s))) return rc;
         } else {
@@ -1135,7 +1219,7 @@ int enqueue_step(spb_shard_engine* e, bool record) {
                     if ((rc = launch_clustered("wide_relu2_norm_quant", wide_relu2_norm_quant_kernel<kWideCluster>, dim3(kWideCluster),
                                                dim3(kWideThreads / kWideCluster), kWideCluster, s, static_cast<const __half*>(gate_full),
                                                static_cast<const __half*>(up_full), L.norm[3], e->xq, am1, inter, c.rms_norm_eps,
-                                               LArgs{}))) return rc;
+                                               take_pending()))) return rc;
                 } else if ((rc = launch("wide_relu2_norm_quant", wide_relu2_norm_quant_kernel<1>, dim3(B), dim3(kWideThreads), 0, s,
                                         static_cast<const __half*>(gate_full), static_cast<const __half*>(up_full), L.norm[3], e->xq,
                                         am1, inter, c.rms_norm_eps, take_pending()))) {
@@ -1145,18 +1229,18 @@ int enqueue_step(spb_shard_engine* e, bool record) {
                 return rc;
             }
             if (B == 1) {
-                if ((rc = linear_1(L.lin[6], am1, down_out))) return rc;
+                sent = L.lin[6].prep && plan_direct(X_DOWN, &sg_down, 1, bd_h, ub_h, xd, fan);
+                if (sent) {
+                    if ((rc = linear_group_prepared(g1d, o1d, 1, am1, nullptr, fan))) return rc;
+                } else if ((rc = linear_1(L.lin[6], am1, down_out))) {
+                    return rc;
+                }
             } else if ((rc = linear_b(L.lin[6], am1, down_out, e->acc))) {
                 return rc;
             }
         }
-        if (!alone) {
-            const XSeg sg = seg_of(e->down, e->off_down, static_cast<size_t>(e->hrow[r]) * 2, static_cast<size_t>(H) * 2,
-                                   static_cast<size_t>(e->h_loc) * 2);
-            const int* bd[1] = {e->hrow};
-            const int ub[1] = {2};
-            if ((rc = exchange_or_defer(X_DOWN, &sg, 1, bd, ub))) return rc;
-        }
+        if (sent) pend = xd;
+        else if (!alone && (rc = exchange_or_defer(X_DOWN, &sg_down, 1, bd_h, ub_h))) return rc;
     }
     // last residual add + final norm, LM head on this rank's vocabulary rows, arg-max candidates
     if ((rc = res_norm_quant(c.num_hidden_layers ? down_full : nullptr, nullptr, cur, e->final_norm, e->xfinal, am0))) return rc;
@@ -1499,7 +1583,7 @@ extern "C" int spb_shard_engine_set_exchange_fold(spb_shard_engine* e, int on) {
     DeviceScope scope(e->device);
     SPB_CUDA(cudaStreamSynchronize(e->stream));
     drop_graph(e);
-    e->fold_exchange = on != 0;
+    e->fold_exchange = on < 0 ? 0 : on > 2 ? 2 : on;
     return SPB_OK;
 }
 

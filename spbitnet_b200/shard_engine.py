@@ -135,10 +135,11 @@ class ShardEngine:
         of 4 M weights and more, 2 every slice the layout takes, 0 none.  Wide models, one sequence; same results either way."""
         check(self._lib.spb_shard_engine_set_prepared_weights(self._h, int(level)))
 
-    def set_exchange_fold(self, on: bool) -> None:
-        """Wide models, one sequence, several ranks: whether the kernel that consumes a gathered vector performs the
-        exchange itself or a launch of its own does (default).  Same results either way."""
-        check(self._lib.spb_shard_engine_set_exchange_fold(self._h, int(bool(on))))
+    def set_exchange_fold(self, form: int) -> None:
+        """Wide models, one sequence, several ranks: 2 (default) the producing kernels store their slices into every
+        rank's staging area from their epilogues and the consuming kernels poll it, 1 the consuming kernel performs
+        the exchange, 0 a launch of its own does.  Same results every way."""
+        check(self._lib.spb_shard_engine_set_exchange_fold(self._h, int(form)))
 
     def weight_bytes(self) -> int:
         """Bytes of weights this rank streams per decode step (its row slices + its LM head rows)."""

@@ -79,16 +79,17 @@ WIDE = dict(hidden_size=4096, num_hidden_layers=2, num_attention_heads=32, num_k
             intermediate_size=16640, vocab_size=2048, max_position_embeddings=32, rms_norm_eps=1e-5, rope_theta=500000.0)
 
 
-@pytest.mark.parametrize("wide", [False, True], ids=["narrow", "wide"])
-def test_a_silent_peer_ends_in_a_timeout_not_a_hang(wide):
+@pytest.mark.parametrize("wide,form", [(False, 0), (True, 0), (True, 1), (True, 2)],
+                         ids=["narrow", "wide-launch", "wide-consumer", "wide-direct"])
+def test_a_silent_peer_ends_in_a_timeout_not_a_hang(wide, form):
     """Rank 0 of a two-rank group whose "peer" is a zero-filled buffer that nobody writes: every exchange stores
     the rank's slices there, the first wait for the peer's flag runs out after the (short) bound, the kernel raises
     the status word and returns, later exchanges skip their waits, and the host call answers SPB_E_TIMEOUT.
-    (wide: the exchanges are performed by the kernels that consume the gathered vectors.)"""
+    (wide: the three forms of the exchange of the single-sequence step of a wide model.)"""
     model = synth.random_model(synth.TINY, seed=44)
     dm = synth.DeviceRandomModel(WIDE, seed=44) if wide else DeviceModel(model)
     eng = ShardEngine(dm, rank=0, world=2, timeout_ms=20, connect=False)
-    eng.set_exchange_fold(wide)
+    eng.set_exchange_fold(form)
     fake_peer = torch.zeros(eng.exchange_bytes, dtype=torch.uint8, device="cuda")
     eng.set_peer_pointers([0, fake_peer.data_ptr()])
     with pytest.raises(_lib.SpbError) as err:

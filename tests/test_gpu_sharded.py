@@ -188,11 +188,12 @@ def _shard_engine_worker(rank, world, port, out_q):
             (dict(hidden_size=4096, num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
                   intermediate_size=16640, vocab_size=2048, max_position_embeddings=32, rms_norm_eps=1e-5,
                   rope_theta=500000.0), 1),
-            "folded",  # the same model with the exchanges inside the kernels that consume the gathered vectors
+            1,  # the same model with the exchanges inside the kernels that consume the gathered vectors
+            0,  # ... and as launches of their own
         ]
         for ci, entry in enumerate(configs):
-            folded = entry == "folded"
-            cfg, batch = configs[ci - 1] if folded else entry
+            form = entry if isinstance(entry, int) else None  # None: the default (slices sent by the producers' epilogues)
+            cfg, batch = configs[3] if form is not None else entry
             wide = cfg["hidden_size"] >= 4096
             if wide:
                 model, dm = None, synth.DeviceRandomModel(cfg, seed=61)
@@ -200,8 +201,8 @@ def _shard_engine_worker(rank, world, port, out_q):
                 model = synth.random_model(cfg, seed=61 + ci)
                 dm = DeviceModel(model)
             sharded = ShardEngine(dm, rank=rank, world=world, batch=batch)
-            if folded:
-                sharded.set_exchange_fold(True)
+            if form is not None:
+                sharded.set_exchange_fold(form)
             one = ShardEngine(dm, batch=batch)  # the same step with every matrix whole, on this rank's GPU
             prompts = np.random.default_rng(ci).integers(0, cfg["vocab_size"], (5, batch)).astype(np.int32)
             for step in range(5):
