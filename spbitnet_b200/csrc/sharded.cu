@@ -21,13 +21,20 @@
 // Slices of up to 96 KB per sender (every exchange of a batch-1 step) take a second form without the fence round
 // trip: every 4 bytes travel as one 8-byte store {data, sequence number} into a per-sender staging area, the
 // receiver polls each word until it carries the current number and moves the data into place (exchange_ll_kernel).
+// In the single-sequence step of a wide model (hidden >= 4096) that second form needs no kernel of its own: the
+// kernel that computes a slice (attention merge, prepared GEMV) stores the tagged words from its epilogue into every
+// rank's staging area, its own included, and the kernel that consumes the gathered vector polls its local staging
+// area as it loads (ll_gather8), so compute and exchange are one kernel on each side and the NVLink crossing
+// overlaps the producer's tail (spb_shard_engine_set_exchange_fold; form 1 lets the consumer do the whole exchange).
 // No multicast, no bulk-copy engine, no library kernel ever sees a peer pointer; remote data always lands in
 // the consumer's own memory before anything reads it.  Sequence numbers only grow, so flags are never reset.
 // A buffer is reused once per layer: a rank that writes exchange n into a peer has passed its wait of
 // exchange n - 1, so that peer has issued everything up to exchange n - 1, which comes after its last read
 // of this buffer's previous contents (four exchanges earlier).
 //
-// batch = 1 runs the fused GEMV launches of the single-GPU engine on the row slices; batch > 1 decodes that
+// batch = 1 runs the fused GEMV launches of the single-GPU engine on the row slices (wide models: one vector kernel
+// per activation, a cluster of eight blocks, and every matrix through the tensor-core GEMV, q / k / v and gate / up
+// as one launch each on prepared copies of the slices); batch > 1 decodes that
 // many independent sequences in lock step (same position, own KV caches) with the batched product
 // (spb_sparse_bitlinear_gemm) and the row-batched vector kernels.
 #include <algorithm>
