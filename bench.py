@@ -844,6 +844,22 @@ def bench_decode(args, with_reference=True, with_cpu=False):
         persistent = {"tok_s": steps / dt_p2, "ms_per_token": 1e3 * dt_p2 / steps, "same_tokens": bool((toks_p == toks).all())}
     except Exception as exc:
         persistent = {"error": repr(exc)[:160]}
+    # the default chain on the packed format (no prepared copies of the matrices)
+    packed_chain = None
+    try:
+        eng.reset()
+        eng.set_decode_mode(InferenceEngine.DECODE_AUTO)
+        eng.set_prepared_weights(False)
+        eng.generate(prompt, 8)
+        eng.reset()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        toks_p = eng.generate(prompt, n_gen)
+        dt_p4 = time.perf_counter() - t0
+        packed_chain = {"tok_s": steps / dt_p4, "ms_per_token": 1e3 * dt_p4 / steps, "same_tokens": bool((toks_p == toks).all())}
+    except Exception as exc:
+        packed_chain = {"error": repr(exc)[:160]}
+    eng.set_prepared_weights(True)
     # ... and without grid barriers (stage outputs as tagged words)
     tagged = None
     try:
@@ -882,7 +898,7 @@ def bench_decode(args, with_reference=True, with_cpu=False):
     peak, _ = measured_peaks()
     out = {"tok_s": steps / dt, "batched_prompt": batched, "ms_per_token": 1e3 * dt / steps, "generated": int(len(toks)),
            "prompt": int(len(prompt)), "weight_mb_per_token": round(weight_bytes / 1e6, 1),
-           "step": "chain of five PDL-linked kernels per layer", "persistent_kernel": persistent, "persistent_kernel_tagged_words": tagged, "clocks": decode_clocks,
+           "step": "chain of five PDL-linked kernels per layer on prepared copies of the matrices", "chain_on_packed_weights": packed_chain, "persistent_kernel": persistent, "persistent_kernel_tagged_words": tagged, "clocks": decode_clocks,
            "hbm_gbs": weight_bytes * steps / dt / 1e9, "hbm_frac_measured": weight_bytes * steps / dt / 1e9 / peak,
            "what": "prefill (token-serial, as the reference) + decode, wall clock around generate() incl. prompt "
                    "H2D and token D2H; random-init 2B-4T shape, every matrix of every layer drawn with its own seed"}

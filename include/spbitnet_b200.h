@@ -362,6 +362,12 @@ int spb_engine_set_prefill_chunk(spb_engine* e, int chunk);
  * library's timeout counter moves (SPB_E_TIMEOUT from the engine call that synchronises next) and spb_engine_reset
  * clears the barrier state and the tagged words. */
 int spb_engine_set_decode_mode(spb_engine* e, int mode);
+/* Whether the chain of fused launches (decode modes 0 and 1) multiplies on prepared copies of the matrices
+ * (spb_prepare_weights; the engine builds and owns them, as large as the packed tensors, when the next step is set
+ * up): 1 (default) yes, for every group of matrices that fits the one-wave form of that kernel, 0 no (the
+ * packed-format kernels).  With the copies a warp holds all its weights in registers before its launch's dependency
+ * resolves.  Same tokens and logits bit for bit. */
+int spb_engine_set_prepared_weights(spb_engine* e, int on);
 /* 1 when the last step that was set up runs the persistent kernel. */
 int spb_engine_decode_is_persistent(const spb_engine* e);
 /* Test aid: two blocks at a grid barrier that expects three; both waits run out after limit_cycles (clamped),

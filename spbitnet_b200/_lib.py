@@ -112,6 +112,7 @@ SIGNATURES = {
     "spb_engine_prefill": (_i, [_p, _p, _i, _p]),
     "spb_engine_set_prefill_chunk": (_i, [_p, _i]),
     "spb_engine_set_decode_mode": (_i, [_p, _i]),
+    "spb_engine_set_prepared_weights": (_i, [_p, _i]),
     "spb_engine_decode_is_persistent": (_i, [_p]),
     "spb_model_load": (_p, [C.c_char_p]),
     "spb_model_destroy": (None, [_p]),

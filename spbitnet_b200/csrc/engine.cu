@@ -25,6 +25,7 @@ struct Linear {
     const uint32_t* values = nullptr;
     float gamma = 0.0f;
     int rows = 0, cols = 0, ms = 0, vs = 0;
+    void* prep = nullptr;  // the engine's prepared copy (spb_prepare_weights), when it keeps one
 };
 
 struct Layer {
@@ -68,6 +69,7 @@ struct spb_engine {
     bool graph_generates = false;     // the captured graph records tokens into d_out
     bool fused = false;               // vector ops run inside the BitLinear launches
     bool rope_in_qkv = false;         // ... and rope + KV scatter inside the q/k/v launch
+    int use_prepared = 1;             // spb_engine_set_prepared_weights
     int decode_mode = 0;              // spb_engine_set_decode_mode
     bool persistent = false;          // the layers of a token run as the one persistent kernel (decode_persistent.cu)
     PdModel pd{};
@@ -158,6 +160,7 @@ BitLinearGroup make_group(const Linear* const* L, __half* const* out, int n) {
     for (int i = 0; i < n; ++i) {
         g.meta[i] = L[i]->meta; g.values[i] = L[i]->values; g.out[i] = out[i]; g.gamma[i] = L[i]->gamma;
         g.rows[i] = L[i]->rows; g.ms[i] = L[i]->ms; g.vs[i] = L[i]->vs;
+        g.prep[i] = L[i]->prep;
     }
     return g;
 }
@@ -329,6 +332,28 @@ int choose_persistent(spb_engine* e) {
     return SPB_OK;
 }
 
+// The engine's prepared copies of the matrices (the chain of fused launches multiplies on them, gemv_prepared.cu):
+// built here, outside any capture, for every matrix the layout takes; dropped when the setting or the mode says so.
+int sync_prepared(spb_engine* e, bool want) {
+    bool waited = false;
+    for (Layer& Ly : e->layers)
+        for (Linear& L : Ly.lin) {
+            const size_t bytes = want && L.meta ? spb_prepared_weights_bytes(L.rows, L.cols) : 0;
+            const bool can = bytes > 0 && L.ms >= L.cols / 32 && L.vs >= L.cols / 64;
+            if (L.prep && !can) {
+                if (!waited) SPB_CUDA(cudaStreamSynchronize(e->stream));
+                waited = true;
+                cudaFree(L.prep);
+                L.prep = nullptr;
+            } else if (!L.prep && can) {
+                SPB_CUDA(cudaMalloc(&L.prep, bytes));
+                if (int rc = spb_prepare_weights(L.meta, L.values, L.rows, L.cols, L.ms, L.vs, L.prep, e->stream)) return rc;
+            }
+        }
+    SPB_CUDA(cudaStreamSynchronize(e->stream));
+    return SPB_OK;
+}
+
 int ensure_graph(spb_engine* e, bool record_tokens, int n_prompt) {
     if (e->graph && e->graph_generates == record_tokens && e->n_prompt_in_graph == n_prompt) return SPB_OK;
     drop_graph(e);
@@ -340,6 +365,7 @@ int ensure_graph(spb_engine* e, bool record_tokens, int n_prompt) {
         __half* none[7] = {};
         for (int i = 0; i < 7 && e->fused; ++i) e->fused = bitlinear_group_is_fast(make_group(all + i, none + i, 1));
     }
+    if (int rc = sync_prepared(e, e->use_prepared && e->fused && !e->persistent)) return rc;
     e->rope_in_qkv = e->fused && e->cfg.head_dim % 2 == 0;
     SPB_CUDA(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
     int rc = enqueue_token(e, record_tokens);
@@ -630,6 +656,9 @@ extern "C" void spb_engine_destroy(spb_engine* e) {
     if (e->d_pd_layers) cudaFree(e->d_pd_layers);
     if (e->d_pd_sync) cudaFree(e->d_pd_sync);
     if (e->d_pd_ll) cudaFree(e->d_pd_ll);
+    for (Layer& Ly : e->layers)
+        for (Linear& L : Ly.lin)
+            if (L.prep) cudaFree(L.prep);
     cudaFree(e->pool);
     cudaStreamDestroy(e->stream);
     delete e;
@@ -650,9 +679,15 @@ extern "C" int spb_engine_set_linear(spb_engine* e, int layer, int which, const 
         return fail(SPB_E_INVALID, "spb_engine_set_linear: layer %d tensor %d is %dx%d, config wants %dx%d", layer,
                     which, rows, cols, want_rows[which], want_cols[which]);
     Linear& L = e->layers[layer].lin[which];
+    drop_graph(e);
+    if (L.prep) {  // a copy of the tensor this one replaces
+        SPB_ON_ENGINE_DEVICE(e);
+        SPB_CUDA(cudaStreamSynchronize(e->stream));
+        cudaFree(L.prep);
+        L.prep = nullptr;
+    }
     L.meta = d_meta; L.values = d_values; L.gamma = gamma; L.rows = rows; L.cols = cols;
     L.ms = meta_stride; L.vs = values_stride;
-    drop_graph(e);
     return SPB_OK;
 }
 
@@ -744,6 +779,17 @@ extern "C" int spb_engine_set_decode_mode(spb_engine* e, int mode) {
         SPB_CUDA(cudaStreamSynchronize(e->stream));
         drop_graph(e);
         e->decode_mode = mode;
+    }
+    return SPB_OK;
+}
+
+extern "C" int spb_engine_set_prepared_weights(spb_engine* e, int on) {
+    if (!e) return fail(SPB_E_INVALID, "spb_engine_set_prepared_weights: null handle");
+    SPB_ON_ENGINE_DEVICE(e);
+    if ((on != 0) != (e->use_prepared != 0)) {
+        SPB_CUDA(cudaStreamSynchronize(e->stream));
+        drop_graph(e);
+        e->use_prepared = on != 0;
     }
     return SPB_OK;
 }

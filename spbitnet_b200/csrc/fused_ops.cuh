@@ -74,6 +74,9 @@ struct BitLinearGroup {
     float gamma[3];
     int rows[3], ms[3], vs[3];
     int nmat, cols;
+    const void* prep[3];  // optional: spb_prepare_weights copies of the matrices.  With all of them given, the launches
+                          // with a producer (amax, resnorm, relu2) multiply on them when the group fits their one-wave
+                          // form (gemv_prepared.cu: prepared_group_fused), else on the packed format
 };
 bool bitlinear_group_is_fast(const BitLinearGroup& g);
 // activation already quantised (absmax_quantize_gpu output)

@@ -663,6 +663,25 @@ static int run_gemv(const char* name, const MatDesc* mats, int nmat, const XDesc
     return launch(name, gemv_pairs_kernel<IN, OUT>, dim3(blocks), dim3(kThreads), smem, stream, a);
 }
 
+// gemv_prepared.cu
+bool prepared_group_fused_supported(const int* rows, int nmat, int cols);
+int prepared_group_fused(int in, const void* const* prep, void* const* out_half, const float* gamma, const int* rows, int nmat,
+                         const ProducerArgs& p, const RopeScatter* rope, void* stream);
+
+// The group on prepared copies of its matrices, when it has them all and fits; 1 = not applicable.
+static int try_prepared(int in, const BitLinearGroup& g, const XDesc& xd, void* stream) {
+    for (int i = 0; i < g.nmat; ++i)
+        if (!g.prep[i]) return 1;
+    if (g_gemv_variant != 0 || !prepared_group_fused_supported(g.rows, g.nmat, g.cols)) return 1;
+    if (!aligned(xd.x, 16) || (xd.x2 && !aligned(xd.x2, 16)) || (xd.w_norm && !aligned(xd.w_norm, 16)) ||
+        (xd.w_sub && !aligned(xd.w_sub, 16)))
+        return 1;
+    ProducerArgs p{};
+    p.x = xd.x; p.x2 = xd.x2; p.w_sub = xd.w_sub; p.w_norm = xd.w_norm; p.x_out = xd.x_out; p.eps = xd.eps;
+    p.d_absmax = xd.d_absmax; p.cols = g.cols;
+    return prepared_group_fused(in, g.prep, g.out, g.gamma, g.rows, g.nmat, p, xd.rope, stream);
+}
+
 static int fill_mats(MatDesc* d, const BitLinearGroup& g) {
     if (g.nmat < 1 || g.nmat > kMaxMats) return fail(SPB_E_INVALID, "bitlinear group: %d matrices", g.nmat);
     for (int i = 0; i < g.nmat; ++i)
@@ -685,6 +704,7 @@ int bitlinear_amax_group(const BitLinearGroup& g, const void* x_half, void* stre
     if (int rc = fill_mats(d, g)) return rc;
     XDesc xd;
     xd.x = x_half;
+    if (const int rc = try_prepared(IN_F16_AMAX, g, xd, stream); rc != 1) return rc;
     return run_gemv<IN_F16_AMAX, OUT_F16>("bitlinear_amax_group", d, g.nmat, xd, g.cols, stream);
 }
 
@@ -700,6 +720,7 @@ int bitlinear_resnorm_group(const BitLinearGroup& g, const void* x_in, const voi
     xd.x_out = x_out;
     xd.eps = eps;
     xd.rope = rope;
+    if (const int rc = try_prepared(IN_RESNORM, g, xd, stream); rc != 1) return rc;
     return run_gemv<IN_RESNORM, OUT_F16>("bitlinear_resnorm_group", d, g.nmat, xd, g.cols, stream);
 }
 
@@ -712,6 +733,7 @@ int bitlinear_relu2_group(const BitLinearGroup& g, const void* gate, const void*
     xd.x2 = up;
     xd.w_sub = w_sub;
     xd.eps = eps;
+    if (const int rc = try_prepared(IN_RELU2, g, xd, stream); rc != 1) return rc;
     return run_gemv<IN_RELU2, OUT_F16>("bitlinear_relu2_group", d, g.nmat, xd, g.cols, stream);
 }
 

@@ -35,6 +35,7 @@
 // Also measured and dropped: asking L2 for the rest of a warp's run of quads before the dependency wait (one bulk
 // prefetch per warp, or a prefetch per 128 bytes): the 70B-shape decode step got 3 - 4 % slower both ways.
 #include "fused_ops.cuh"
+#include "producers.cuh"
 #include "spb_common.cuh"
 
 namespace spb {
@@ -277,6 +278,173 @@ __global__ void __launch_bounds__(kGpThreads, kGpBlocksPerSm) gemv_prepared_kern
     }
 }
 
+// ---- the same multiplication with the activation producer in front (the decode chain of the single-GPU engine) -------
+// A decode step is a chain of dependent launches, and what a launch can do BEFORE its dependency resolves is free.
+// With prepared weights that is everything except the activation: a block keeps 16 / 32 / 64 rows (8 / 4 / 2 warps
+// per tile) and every warp requests ALL of its quads (at most kGpFusedQuads: the launch is one wave of at most two
+// blocks per SM) into registers before the wait, and the norm weights go to shared memory by cp.async.  After the
+// wait the block forms the int8 activation vector exactly as the SIMT kernels of gemv.cu do (produce_x: same sums,
+// same rounding points), re-orders it for the B registers and multiplies out of registers: nothing of the weight
+// path is left on the critical path.  Epilogue as above (half outputs; RoPE and the KV scatter for q, k, v).
+constexpr int kGpFusedQuads = 6;
+constexpr int kGpFusedBlocksPerSm = 2;
+struct GpFusedArgs {
+    GpMat mat[kGpMaxMats];
+    int nmat;
+    ProducerArgs p;
+    int ntiles, nquads;
+    int ks, ks_log2, qpw;
+    RopeScatter rope;
+};
+
+__device__ __forceinline__ void gp_step(int& c0, int& c1, int& c2, int& c3, int& d0, int& d1, int& d2, int& d3, uint32_t e,
+                                        uint32_t sel, uint32_t x_addr, bool bcol) {
+    const uint32_t a0 = __byte_perm(0xFF00FF00u, 0xFF00FF00u, sel);
+    const uint32_t a1 = __byte_perm(0xFFFF0000u, 0xFFFF0000u, sel);
+    const uint32_t a2 = __byte_perm(0x00000000u, 0xFFFFFFFFu, sel);
+    const uint32_t a3 = __byte_perm(0x00000000u, 0xFFFFFFFFu, sel >> 1);
+    uint32_t b0 = 0, b1 = 0, b2 = 0, b3 = 0;
+    if (bcol) asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(x_addr));
+    asm volatile(
+        "mma.sp::ordered_metadata.sync.aligned.m16n8k64.row.col.s32.s8.s8.s32 "
+        "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9, %10, %11}, {%0, %1, %2, %3}, %12, 0x0;"
+        : "+r"(c0), "+r"(c1), "+r"(c2), "+r"(c3)
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(b2), "r"(b3), "r"(e));
+    asm volatile(
+        "mma.sp::ordered_metadata.sync.aligned.m16n8k64.row.col.s32.s8.s8.s32 "
+        "{%0, %1, %2, %3}, {%4, %4, %4, %4}, {%5, %6, %7, %8}, {%0, %1, %2, %3}, %9, 0x0;"
+        : "+r"(d0), "+r"(d1), "+r"(d2), "+r"(d3)
+        : "r"(0x01010101u), "r"(b0), "r"(b1), "r"(b2), "r"(b3), "r"(e));
+}
+
+template <int IN>
+__global__ void __launch_bounds__(kGpThreads, kGpFusedBlocksPerSm) gemv_prepared_fused_kernel(const GpFusedArgs a) {
+    __shared__ int red[kGpWarps * 16];
+    __shared__ float redf[64];
+    // x in B-register order (cols bytes) | x as the producer writes it, swizzled 16-byte chunks (cols bytes) |
+    // norm weights (cols floats) | sub-norm weights (cols floats)
+    extern __shared__ __align__(16) uint8_t gpf_raw[];
+    const int cols = a.p.cols;
+    const uint32_t xs_s = static_cast<uint32_t>(__cvta_generic_to_shared(gpf_raw));
+    uint4* xs_sw = reinterpret_cast<uint4*>(gpf_raw + cols);
+    float* wbuf = reinterpret_cast<float*>(gpf_raw + 2 * cols);
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xFFFFFFFFu, tid >> 5, 0);
+    const int tiles_blk = kGpWarps >> a.ks_log2;
+    const int tile = blockIdx.x * tiles_blk + (warp >> a.ks_log2), kq = warp & (a.ks - 1);
+    const bool live = tile < a.ntiles;
+    const int q_begin = live ? min(a.nquads, kq * a.qpw) : 0, q_end = live ? min(a.nquads, q_begin + a.qpw) : 0;
+    const int g = lane >> 2, tig = lane & 3;
+    auto mat_of = [&](int t) { return (a.nmat > 2 && t >= a.mat[2].tile0) ? 2 : (a.nmat > 1 && t >= a.mat[1].tile0) ? 1 : 0; };
+    const int wm = mat_of(live ? tile : 0);
+    const uint8_t* wprep = wm == 2 ? a.mat[2].prep : wm == 1 ? a.mat[1].prep : a.mat[0].prep;
+    const int wtile0 = wm == 2 ? a.mat[2].tile0 : wm == 1 ? a.mat[1].tile0 : 0;
+    const uint8_t* tp = wprep + (static_cast<size_t>(live ? tile - wtile0 : 0) * a.nquads) * kGpQuadBytes;
+
+    // ---- before the dependency wait: all weights of the warp, the norm weights ----
+    uint4 m[kGpFusedQuads];
+    uint2 s[kGpFusedQuads];
+#pragma unroll
+    for (int i = 0; i < kGpFusedQuads; ++i) {
+        m[i] = make_uint4(0, 0, 0, 0);
+        s[i] = make_uint2(0, 0);
+        if (q_begin + i < q_end) gp_load_quad(tp, q_begin + i, lane, m[i], s[i]);
+    }
+    ProducerArgs pa = a.p;
+    if (IN >= IN_RESNORM) {
+        auto stage = [&](const float* src, float* dst) {
+            for (int q = tid; q < (cols >> 2); q += kGpThreads)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst + 4 * q))), "l"(src + 4 * q) : "memory");
+        };
+        if (IN == IN_RESNORM) {
+            stage(a.p.w_norm, wbuf);
+            pa.w_norm = wbuf;
+            if (a.p.w_sub) {
+                stage(a.p.w_sub, wbuf + cols);
+                pa.w_sub = wbuf + cols;
+            }
+        } else if (a.p.w_sub) {
+            stage(a.p.w_sub, wbuf);
+            pa.w_sub = wbuf;
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+
+    grid_dep_wait();
+    grid_dep_launch();
+    int rope_pos = 0;
+    if (a.rope.d_pos) asm volatile("ld.global.s32 %0, [%1];" : "=r"(rope_pos) : "l"(a.rope.d_pos));
+    if (IN >= IN_RESNORM) asm volatile("cp.async.wait_group 0;" ::: "memory");  // (each weight is first read after a block-wide reduction)
+    const float absmax = produce_x<IN, OUT_F16>(pa, xs_sw, static_cast<__half*>(nullptr), redf, blockIdx.x == 0);
+    __syncthreads();
+    for (int q = tid; q < (cols >> 4); q += kGpThreads) {
+        const int c = q >> 3, i = q & 7;
+        const uint4 xv = xs_sw[(c << 3) + (i ^ (c & 7))];
+        const uint32_t d = xs_s + (static_cast<uint32_t>(q) >> 2) * 64u + (static_cast<uint32_t>(q) & 3u) * 4u;
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(d), "r"(xv.x) : "memory");
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(d + 16u), "r"(xv.y) : "memory");
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(d + 32u), "r"(xv.z) : "memory");
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(d + 48u), "r"(xv.w) : "memory");
+    }
+    __syncthreads();
+
+    // ---- the multiplication, out of registers ----
+    int r0 = 0, r1 = 0, r2 = 0, r3 = 0, t0 = 0, t1 = 0, t2 = 0, t3 = 0;
+    int u0 = 0, u1 = 0, u2 = 0, u3 = 0, v0 = 0, v1 = 0, v2 = 0, v3 = 0;
+    const bool bcol = g == 0;
+    const uint32_t xq0 = xs_s + static_cast<uint32_t>(tig) * 16u + static_cast<uint32_t>(q_begin) * 256u;
+#pragma unroll
+    for (int i = 0; i < kGpFusedQuads; ++i) {
+        if (q_begin + i < q_end) {  // uniform over the warp
+            const uint32_t xq = xq0 + static_cast<uint32_t>(i) * 256u;
+            gp_step(r0, r1, r2, r3, u0, u1, u2, u3, m[i].x, s[i].x, xq, bcol);
+            gp_step(t0, t1, t2, t3, v0, v1, v2, v3, m[i].y, s[i].x >> 16, xq + 64u, bcol);
+            gp_step(r0, r1, r2, r3, u0, u1, u2, u3, m[i].z, s[i].y, xq + 128u, bcol);
+            gp_step(t0, t1, t2, t3, v0, v1, v2, v3, m[i].w, s[i].y >> 16, xq + 192u, bcol);
+        }
+    }
+    if (tig == 0) {
+        red[warp * 16 + g] = (u0 + v0) + 2 * (r0 + t0);
+        red[warp * 16 + g + 8] = (u2 + v2) + 2 * (r2 + t2);
+    }
+    __syncthreads();
+    if (tid < ((16 * tiles_blk + 31) & ~31)) {
+        const int tl = tid >> 4, r = tid & 15;
+        const int t = blockIdx.x * tiles_blk + tl;
+        const bool in_tile = tl < tiles_blk && t < a.ntiles;
+        const int mi = mat_of(in_tile ? t : 0);
+        const int row = ((in_tile ? t : 0) - (mi == 2 ? a.mat[2].tile0 : mi == 1 ? a.mat[1].tile0 : 0)) * 16 + r;
+        const int mrows = mi == 2 ? a.mat[2].rows : mi == 1 ? a.mat[1].rows : a.mat[0].rows;
+        const bool valid = in_tile && row < mrows;
+        void* y = mi == 2 ? a.mat[2].y : mi == 1 ? a.mat[1].y : a.mat[0].y;
+        const float gamma = mi == 2 ? a.mat[2].gamma : mi == 1 ? a.mat[1].gamma : a.mat[0].gamma;
+        int acc = 0;
+        if (in_tile)
+            for (int k = 0; k < a.ks; ++k) acc += red[((tl << a.ks_log2) + k) * 16 + r];
+        const __half hv = __float2half_rn(__fmul_rn(static_cast<float>(acc), dequant_scale(gamma, absmax)));
+        if (!a.rope.d_pos) {
+            if (valid) static_cast<__half*>(y)[row] = hv;
+        } else {
+            const float v = __half2float(hv);
+            const float pv = __shfl_xor_sync(0xFFFFFFFFu, v, 1);
+            const int hd = a.rope.head_dim;
+            const int head = row / hd, d = row - head * hd;
+            __half out = hv;
+            if (mi != 2) {
+                __half y0, y1;
+                rope_rotate((r & 1) ? pv : v, (r & 1) ? v : pv, rope_pos, d >> 1, hd, a.rope.theta, y0, y1);
+                out = (r & 1) ? y1 : y0;
+            }
+            if (valid) {
+                if (mi == 0)
+                    static_cast<__half*>(y)[row] = out;
+                else
+                    static_cast<__half*>(mi == 1 ? a.rope.kcache : a.rope.vcache)[(static_cast<size_t>(head) * a.rope.max_seq_len + rope_pos) * hd + d] = out;
+            }
+        }
+    }
+}
+
 static bool gp_shape_ok(int rows, int cols) { return rows > 0 && cols > 0 && cols % 256 == 0 && cols <= 65536; }
 static size_t gp_weight_bytes(int rows, int cols) { return static_cast<size_t>((rows + 15) / 16) * (cols / 256) * kGpQuadBytes; }
 
@@ -361,6 +529,84 @@ static int gp_launch(const char* name, const void* prep, const int8_t* x, void* 
     if (!prep || !x || !y) return fail(SPB_E_INVALID, "%s: null pointer", name);
     const GpMatDesc m{prep, y, gamma, rows};
     return gp_launch(name, &m, 1, x, y_acc, d_absmax, out_mode, cols, nullptr, stream);
+}
+
+// Whether a group of BitLinears with prepared copies can run as ONE wave of gemv_prepared_fused_kernel, and how.
+static bool gp_fused_plan(const int* rows, int nmat, int cols, GpFusedArgs& a) {
+    if (nmat < 1 || nmat > kGpMaxMats || cols <= 0 || cols % 256 || cols > 8192) return false;
+    int tiles = 0;
+    for (int i = 0; i < nmat; ++i) {
+        if (rows[i] <= 0) return false;
+        a.mat[i].tile0 = tiles;
+        a.mat[i].rows = rows[i];
+        tiles += (rows[i] + 15) / 16;
+    }
+    a.nmat = nmat;
+    a.ntiles = tiles;
+    a.nquads = cols / 256;
+    const int slots = sm_count() * kGpFusedBlocksPerSm;
+    for (int ks = 8; ks >= 1; ks >>= 1) {  // as many warps per tile as one wave allows: the shortest run of quads per warp
+        const int qpw = (a.nquads + ks - 1) / ks;
+        const int nblocks = (tiles + kGpWarps / ks - 1) / (kGpWarps / ks);
+        if (nblocks <= slots && qpw <= kGpFusedQuads) {
+            a.ks = ks;
+            a.ks_log2 = ks == 8 ? 3 : ks == 4 ? 2 : ks == 2 ? 1 : 0;
+            a.qpw = qpw;
+            return true;
+        }
+    }
+    return false;
+}
+
+bool prepared_group_fused_supported(const int* rows, int nmat, int cols) {
+    GpFusedArgs a{};
+    return gp_fused_plan(rows, nmat, cols, a);
+}
+
+// engine-internal: the BitLinears of a group on prepared weights with the activation producer `in` (IN_F16_AMAX,
+// IN_RESNORM, IN_RELU2) in front, one launch; p as for the SIMT kernels of gemv.cu; half outputs; with `rope` the
+// group is q, k, v.
+int prepared_group_fused(int in, const void* const* prep, void* const* out_half, const float* gamma, const int* rows, int nmat,
+                         const ProducerArgs& p, const RopeScatter* rope, void* stream) {
+    const char* name = "prepared_group_fused";
+    GpFusedArgs a{};
+    if (!gp_fused_plan(rows, nmat, p.cols, a)) return fail(SPB_E_UNSUPPORTED, "%s: shape outside the one-wave form", name);
+    for (int i = 0; i < nmat; ++i) {
+        if (!prep[i] || !out_half[i] || (reinterpret_cast<uintptr_t>(prep[i]) & 15u)) return fail(SPB_E_INVALID, "%s: bad pointer", name);
+        a.mat[i].prep = static_cast<const uint8_t*>(prep[i]);
+        a.mat[i].y = out_half[i];
+        a.mat[i].gamma = gamma[i];
+    }
+    if (!p.x || (reinterpret_cast<uintptr_t>(p.x) & 15u) || (p.x2 && (reinterpret_cast<uintptr_t>(p.x2) & 15u)))
+        return fail(SPB_E_INVALID, "%s: activation vectors must be 16-byte aligned", name);
+    if ((p.w_norm && (reinterpret_cast<uintptr_t>(p.w_norm) & 15u)) || (p.w_sub && (reinterpret_cast<uintptr_t>(p.w_sub) & 15u)))
+        return fail(SPB_E_UNSUPPORTED, "%s: norm weights must be 16-byte aligned", name);
+    if (in == IN_RESNORM && (!p.w_norm || !p.x_out)) return fail(SPB_E_INVALID, "%s: null pointer", name);
+    if (in == IN_RELU2 && !p.x2) return fail(SPB_E_INVALID, "%s: null pointer", name);
+    if (rope) {
+        if (nmat != 3 || rope->head_dim < 2 || rope->head_dim % 2 || rows[0] % rope->head_dim || rows[1] % rope->head_dim ||
+            rows[1] != rows[2] || !rope->d_pos || !rope->kcache || !rope->vcache)
+            return fail(SPB_E_INVALID, "%s: rotation wants q, k, v with whole heads", name);
+        a.rope = *rope;
+    }
+    a.p = p;
+    const int tiles_blk = kGpWarps / a.ks;
+    const unsigned blocks = static_cast<unsigned>((a.ntiles + tiles_blk - 1) / tiles_blk);
+    const size_t smem = static_cast<size_t>(p.cols) * (2 + (in == IN_RESNORM ? 8 : in == IN_RELU2 ? 4 : 0));
+    int rc;
+    switch (in) {
+        case IN_F16_AMAX:
+            if ((rc = ensure_dynamic_smem(name, gemv_prepared_fused_kernel<IN_F16_AMAX>, smem))) return rc;
+            return launch(name, gemv_prepared_fused_kernel<IN_F16_AMAX>, dim3(blocks), dim3(kGpThreads), smem, stream, a);
+        case IN_RESNORM:
+            if ((rc = ensure_dynamic_smem(name, gemv_prepared_fused_kernel<IN_RESNORM>, smem))) return rc;
+            return launch(name, gemv_prepared_fused_kernel<IN_RESNORM>, dim3(blocks), dim3(kGpThreads), smem, stream, a);
+        case IN_RELU2:
+            if ((rc = ensure_dynamic_smem(name, gemv_prepared_fused_kernel<IN_RELU2>, smem))) return rc;
+            return launch(name, gemv_prepared_fused_kernel<IN_RELU2>, dim3(blocks), dim3(kGpThreads), smem, stream, a);
+        default:
+            return fail(SPB_E_INVALID, "%s: producer %d", name, in);
+    }
 }
 
 // engine-internal: BitLinear on prepared weights, quantised activation, scaled half output

@@ -103,6 +103,11 @@ class InferenceEngine:
         All modes give the same tokens and logits."""
         check(self._lib.spb_engine_set_decode_mode(self._h, int(mode)))
 
+    def set_prepared_weights(self, on: bool) -> None:
+        """Whether the default decode chain multiplies on prepared copies of the matrices (built and owned by the
+        engine; default on) or on the packed format.  Same tokens and logits either way."""
+        check(self._lib.spb_engine_set_prepared_weights(self._h, int(bool(on))))
+
     @property
     def decode_is_persistent(self) -> bool:
         return bool(self._lib.spb_engine_decode_is_persistent(self._h))

@@ -88,6 +88,43 @@ def test_every_decode_mode_gives_the_same_tokens_and_logits():
     assert (outs[0][0] == want).all()
 
 
+@pytest.mark.parametrize("cfg", [
+    synth.TINY,
+    dict(synth.TINY, hidden_size=384, intermediate_size=640),  # 384 columns: no prepared form, the packed kernels run
+    dict(synth.BITNET_2B, num_hidden_layers=2, vocab_size=2048, max_position_embeddings=96),
+    dict(synth.BITNET_2B, num_hidden_layers=1, vocab_size=2048, max_position_embeddings=64, num_attention_heads=16,
+         num_key_value_heads=16, head_dim=160, intermediate_size=8192),  # no grouping, a vector of 8192
+], ids=["tiny", "no-prepared-form", "2b4t-width", "wide-ffn"])
+def test_chain_on_prepared_weights_matches_the_packed_format(cfg):
+    """The default decode chain multiplies on the engine's prepared copies of the matrices (all of a warp's weights
+    in registers before the launch's dependency resolves); with the copies switched off it runs the packed-format
+    kernels.  Same tokens, same logits bit for bit at every step, also after switching on a live engine."""
+    dm = synth.DeviceRandomModel(cfg, seed=31)
+    prompt = np.random.default_rng(8).integers(0, cfg["vocab_size"], 7).astype(np.int32)
+    prepared, packed = InferenceEngine(dm), InferenceEngine(dm)
+    packed.set_prepared_weights(False)
+    for t in prompt[:-1]:
+        prepared.forward(int(t))
+        packed.forward(int(t))
+    tok = int(prompt[-1])
+    for step in range(40):
+        prepared.forward(tok)
+        packed.forward(tok)
+        a, b = prepared.logits(), packed.logits()
+        assert (a == b).all(), (step, np.abs(a - b).max())
+        tok = int(np.argmax(a))
+    packed.reset()
+    want = packed.generate(prompt, 24)
+    prepared.reset()
+    assert (prepared.generate(prompt, 24) == want).all()
+    prepared.reset()
+    prepared.set_prepared_weights(False)
+    assert (prepared.generate(prompt, 24) == want).all()
+    prepared.reset()
+    prepared.set_prepared_weights(True)
+    assert (prepared.generate(prompt, 24) == want).all()
+
+
 def test_full_2b4t_shape_against_the_reference_cuda_kernels():
     """The 30-layer 2B-4T-shape model, 16-token prompt + 64 greedy steps, against the reference's
     own kernels on the same GPU: logits within 1e-2 max-abs, identical tokens."""
